@@ -1,0 +1,201 @@
+/*
+ * ibcu.h — C ABI of the sm_100a CUDA backend (libibcu.so) for libinferbit's quantized-weight
+ * product hot path: per-row-scaled INT4/INT8 matvec, the product-quantisation LUT + gather
+ * matvec, the k-means assign/update loop, and the small element-wise kernels a decode step needs.
+ *
+ * Plain C: opaque context, raw device/host pointers, sizes. No CPU fallback anywhere — a call
+ * either runs on the GPU or returns a negative code and records a message (ibcu_last_error).
+ * All launches go to the context's stream and are asynchronous unless stated; ibcu_sync waits.
+ *
+ * Each entry point names the reference interface it stands in for (paths inside the reference
+ * checkout, file:line).
+ */
+#ifndef IBCU_H
+#define IBCU_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes follow include/inferbit.h:43-49 (0 ok, negatives for failure classes). */
+#define IBCU_OK              0
+#define IBCU_ERR_PARAM     (-1)   /* bad argument / unsupported shape */
+#define IBCU_ERR_CUDA      (-2)   /* a CUDA runtime call or launch failed */
+#define IBCU_ERR_NOMEM     (-3)
+#define IBCU_ERR_COMM      (-4)   /* NCCL failure */
+#define IBCU_ERR_STATE     (-5)   /* call not valid in the current state (e.g. no communicator) */
+
+typedef struct ibcu_ctx ibcu_ctx;
+
+/* ── context, memory, stream ─────────────────────────────────────────────────────────── */
+/* The reference has one process-global kernel table (src/kernels/scalar.c:185) and one pool per
+ * model (src/ibf_loader.c:543); here one context = one GPU + one stream + scratch. */
+int  ibcu_ctx_create(int device, ibcu_ctx** out);
+void ibcu_ctx_destroy(ibcu_ctx* ctx);
+/* Sticky status: first failure since the last ibcu_clear_error (0 if none); message is
+ * thread-compatible, owned by the context (src/error.c:7-22 keeps a TLS string instead). */
+int         ibcu_status(const ibcu_ctx* ctx);
+const char* ibcu_last_error(const ibcu_ctx* ctx);
+void        ibcu_clear_error(ibcu_ctx* ctx);
+int  ibcu_device_count(void);
+int  ibcu_device_sm_count(const ibcu_ctx* ctx);
+
+int  ibcu_malloc(ibcu_ctx* ctx, size_t bytes, void** dptr);
+int  ibcu_free(ibcu_ctx* ctx, void* dptr);
+int  ibcu_host_alloc(ibcu_ctx* ctx, size_t bytes, void** hptr);      /* pinned */
+int  ibcu_host_free(ibcu_ctx* ctx, void* hptr);
+int  ibcu_memcpy_h2d(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);   /* async */
+int  ibcu_memcpy_d2h(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);   /* async */
+int  ibcu_memcpy_d2d(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);   /* async */
+int  ibcu_memset(ibcu_ctx* ctx, void* dst, int byte, size_t bytes);              /* async */
+int  ibcu_sync(ibcu_ctx* ctx);
+/* Fill a device buffer with counter-based pseudo-random bytes: byte i = low 8 bits of
+ * mix64(seed, i / 8) >> (8 * (i % 8)) (mix64 = splitmix64 finaliser). Used to build random-weight
+ * models in HBM without a host copy; ibcu_hash_bytes_host computes the same bytes on the CPU. */
+int  ibcu_fill_hash_bytes(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed);
+void ibcu_hash_bytes_host(void* dst, size_t bytes, uint64_t seed, size_t first_byte);
+/* fp16 values lo + (hi-lo)*u, u from the same generator (one 16-bit draw per element). */
+int  ibcu_fill_hash_fp16_uniform(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi);
+void ibcu_hash_fp16_uniform_host(uint16_t* dst, size_t count, uint64_t seed, float lo, float hi, size_t first);
+
+/* Device timing on the context's stream (CUDA events). slot in [0,16). */
+int  ibcu_event_record(ibcu_ctx* ctx, int slot);
+int  ibcu_event_elapsed_ms(ibcu_ctx* ctx, int slot_start, int slot_stop, float* ms);   /* syncs on stop */
+/* Stream capture into a replayable graph (one per context): begin, issue calls, end, replay. */
+int  ibcu_graph_begin(ibcu_ctx* ctx);
+int  ibcu_graph_end(ibcu_ctx* ctx, int* graph_id);
+int  ibcu_graph_launch(ibcu_ctx* ctx, int graph_id);
+int  ibcu_graph_destroy(ibcu_ctx* ctx, int graph_id);
+/* Number of kernels this library has launched through this context since creation. */
+uint64_t ibcu_launch_count(const ibcu_ctx* ctx);
+/* Programmatic dependent launch between consecutive kernels of this library (default on). */
+void ibcu_set_pdl(ibcu_ctx* ctx, int enabled);
+
+/* ── INT4 / INT8 linear layers ───────────────────────────────────────────────────────── */
+/* Stands in for ib_kernels.matmul_int4 / matmul_int8 / matmul_int8_batch
+ * (src/inferbit_internal.h:199-277; scalar definitions src/kernels/scalar.c:9-41,70-84) as driven
+ * by tensor_matmul / tensor_matmul_batch (src/forward.c:144-246) and ib_parallel_matmul*
+ * (src/threading.c:244-258,383-394).
+ *
+ * Weights stay in the reference's own layout in HBM: INT8 row-major [M*N]; INT4 two columns per
+ * byte, low nibble first, bias 8, row stride N/2 (src/kernels/scalar.c:17-22). Scales are the
+ * per-output-row FP16 values as stored in the model file (src/forward.c:31-34), or FP32 when the
+ * caller already widened them as the table contract does. */
+typedef struct {
+    const void* w;            /* device */
+    const void* scales;       /* device, [M] */
+    float*      out;          /* device, out[b*out_stride + row] */
+    int M;                    /* rows of this tensor */
+    int out_stride;           /* >= M; the reference's M_stride */
+    int scales_fp32;          /* 0: fp16 bit patterns, 1: float */
+    int epilogue;             /* IBCU_EPI_* */
+} ibcu_linear_t;
+
+#define IBCU_EPI_STORE     0  /* out  = y                                   */
+#define IBCU_EPI_ADD       1  /* out += y   (residual add, src/forward.c:620-622,644-646) */
+
+/* y_t = W_t x for n_tensors (1..4) tensors that share the activation x[B*N] (device, FP32, x[b*N+j])
+ * and the bit width (4 or 8). B in 1..32 (IB_BATCH_MAX, src/inferbit_internal.h:287).
+ * N must be even for bits == 4. */
+int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
+                const float* x, int N, int B, int bits);
+/* Same, plus silu(gate)*up fused into the epilogue of a gate/up pair (src/forward.c:635-637,
+ * src/kernels/scalar.c:175-181): tensors[0] = gate, tensors[1] = up, equal M; writes only
+ * tensors[0].out[b*out_stride + row] = silu(gate_y) * up_y. */
+int ibcu_linear_gate_up_silu(ibcu_ctx* ctx, const ibcu_linear_t* gate_up,
+                             const float* x, int N, int B, int bits);
+/* Force the portable (non tensor-core) kernel for the next ibcu_linear calls; for tests. */
+void ibcu_linear_force_generic(ibcu_ctx* ctx, int on);
+
+/* W4A8 route (src/threading.c:401-432 activation quantiser, src/kernels/scalar.c:43-124 kernels):
+ * x quantised per 128-column group on the device, exact int32 group dot products. */
+int ibcu_quantize_input_int8_g128(ibcu_ctx* ctx, const float* x, int8_t* q, float* sa, int N, int B);
+int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* tensor, const int8_t* xq, const float* sa,
+                     int N, int B);
+
+/* ── PQ matvec ───────────────────────────────────────────────────────────────────────── */
+/* Stands in for ib_pq_matmul_fp32 / _threaded / _streaming (src/pq_decode.h:189-222; body
+ * src/pq_decode.c:1504-1682) for single-level tensors without outlier columns. Field meanings
+ * follow ib_pq_tensor (src/pq_decode.h:39-87). All pointers are device pointers. */
+typedef struct {
+    int M, N, G, K;                   /* K <= 256, G even, N % G == 0, C = N / G chunks */
+    const uint16_t* codebook_l;       /* fp16 [K * G/2] (shared by all chunks) */
+    const uint16_t* codebook_r;
+    long            cb_chunk_stride;  /* 0 = shared tables (the reference); else fp16 elements between chunk tables */
+    const uint8_t*  idx_l;            /* [M * C] row-major, as in the reference */
+    const uint8_t*  idx_r;
+    const uint16_t* row_scale;        /* fp16 [M] */
+    const uint8_t*  idx_t;            /* subspace-major copy made by ibcu_pq_prepare: [2*C][M_pad] */
+    int             M_pad;
+} ibcu_pq_t;
+
+/* One-off per tensor (like the reference's ib_pq_lut_cache transposed index layout,
+ * src/pq_decode.c:2687-2737): writes the subspace-major code plane into idx_t_out, which must hold
+ * ibcu_pq_idx_t_bytes(M, N, G) bytes, and fills t->idx_t / t->M_pad. */
+size_t ibcu_pq_idx_t_bytes(int M, int N, int G);
+int    ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out);
+/* out[b*M + r] = row_scale[r] * sum_c (TL[c][idx_l[r,c]] + TR[c][idx_r[r,c]]) for B activations
+ * x[b*N + j]; applies the reference's 1 %-of-max chunk skip rule per activation. */
+int    ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
+
+/* ── k-means ─────────────────────────────────────────────────────────────────────────── */
+/* ib_kmeans_assign (src/pq_kmeans.h:70-74, src/pq_kmeans.c:399-413): idx[i] = nearest centroid of
+ * X[i*D..], direct squared distance in the reference binary's rounding order, strict '<'.
+ * dist (may be NULL) receives the winning distance. D <= 32, K <= 1024. */
+int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, const float* C, int K,
+                       int32_t* idx, float* dist);
+/* The accumulate half of pq_assign_task (src/pq_kmeans.c:183-201): sums[K*D] (FP32), counts[K],
+ * inertia (double, sum of dist) over this context's N points, deterministic for a given N. */
+int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int D, int K,
+                           const int32_t* idx, const float* dist,
+                           float* sums, int32_t* counts, double* inertia);
+/* Centroid move of lloyd_one_init (src/pq_kmeans.c:252-283): C[k] = sums[k] * (1/count[k]) for
+ * non-empty clusters; shift (device float, may be NULL) = sum of squared moves. */
+int ibcu_kmeans_update(ibcu_ctx* ctx, float* C, int K, int D, const float* sums,
+                       const int32_t* counts, float* shift);
+/* One Lloyd iteration = assign + accumulate (+ all-reduce of sums/counts/inertia when the context
+ * has a communicator) + update. */
+int ibcu_kmeans_lloyd_iter(ibcu_ctx* ctx, const float* X, long N, int D, float* C, int K,
+                           int32_t* idx, float* dist, float* sums, int32_t* counts, double* inertia);
+
+/* ── decode-step glue (ib_kernels.rmsnorm/rope/softmax/silu_mul, src/kernels/scalar.c:126-181,
+ *    and the helpers of src/forward.c) ─────────────────────────────────────────────────── */
+/* x[b*hidden + i] = embed[token_b*hidden + i] * fp16(scale[token_b])  (src/forward.c:94-106) */
+int ibcu_embed_int8(ibcu_ctx* ctx, const int8_t* embed, const uint16_t* scale, const int32_t* tokens,
+                    float* x, int hidden, int B);
+/* out = x * rsqrt(mean(x^2) + eps) * fp16(w), per row of B (src/forward.c:322-327). */
+int ibcu_rmsnorm_fp16w(ibcu_ctx* ctx, float* out, const float* x, const uint16_t* w, float eps, int N, int B);
+/* RoPE on adjacent pairs for every Q head and every K head of B positions pos0+b, then the FP32
+ * KV-cache write at those positions (src/forward.c:577-593, src/kernels/scalar.c:140-157). */
+int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache,
+                       int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta);
+/* GQA attention of B query positions against cache rows 0..pos0+b (src/forward.c:463-504). */
+int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const float* v_cache, float* out,
+                   int n_heads, int n_kv_heads, int head_dim, int pos0, int B);
+int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n);
+int ibcu_add_inplace(ibcu_ctx* ctx, float* x, const float* y, size_t n);
+int ibcu_softmax(ibcu_ctx* ctx, float* data, int N, int rows);
+
+/* ── multi-GPU (one process per GPU; NCCL over NVLink/NVSwitch) ──────────────────────── */
+/* The reference's only parallelism is a row-slicing thread pool (src/threading.c:220-258); the
+ * same row slices are spread over GPUs here. id is an opaque 128-byte token made on rank 0 and
+ * handed to every rank by the launcher. */
+#define IBCU_COMM_ID_BYTES 128
+int ibcu_comm_get_id(void* id_out);
+int ibcu_comm_init(ibcu_ctx* ctx, const void* id, int rank, int world);
+int ibcu_comm_rank(const ibcu_ctx* ctx, int* rank, int* world);
+/* Rows [row0, row0+rows) of an M-row tensor owned by `rank` (contiguous, remainder to the low ranks,
+ * multiples of `align` rows except for the last owner). */
+void ibcu_shard_rows(int M, int world, int rank, int align, int* row0, int* rows);
+/* In-place all-gather of row-sharded outputs: buf[b*stride + r], every rank owns its ibcu_shard_rows
+ * slice (align as given) and receives the others. */
+int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride, int B, int align);
+int ibcu_allreduce_f32(ibcu_ctx* ctx, float* buf, size_t n);
+int ibcu_allreduce_i32(ibcu_ctx* ctx, int32_t* buf, size_t n);
+int ibcu_allreduce_f64(ibcu_ctx* ctx, double* buf, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,109 @@
+"""ctypes bindings for the two product libraries, libibcu.so (CUDA backend, include/ibcu.h) and
+libib_b200.so (C host layer, include/ib_b200.h).
+
+There is no fallback: if a library is missing or a call fails, an exception is raised.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBIBCU_PATH = os.path.join(_HERE, "libibcu.so")
+LIBHOST_PATH = os.path.join(_HERE, "libib_b200.so")
+
+c_void_pp = C.POINTER(C.c_void_p)
+
+
+class LinearT(C.Structure):
+    """ibcu_linear_t"""
+    _fields_ = [("w", C.c_void_p), ("scales", C.c_void_p), ("out", C.c_void_p),
+                ("M", C.c_int), ("out_stride", C.c_int), ("scales_fp32", C.c_int), ("epilogue", C.c_int)]
+
+
+class PqT(C.Structure):
+    """ibcu_pq_t"""
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K", C.c_int),
+                ("codebook_l", C.c_void_p), ("codebook_r", C.c_void_p), ("cb_chunk_stride", C.c_long),
+                ("idx_l", C.c_void_p), ("idx_r", C.c_void_p), ("row_scale", C.c_void_p),
+                ("idx_t", C.c_void_p), ("M_pad", C.c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/ibcu.h declares
+IBCU_SYMBOLS = {
+    "ibcu_ctx_create": (C.c_int, [C.c_int, c_void_pp]),
+    "ibcu_ctx_destroy": (None, [C.c_void_p]),
+    "ibcu_status": (C.c_int, [C.c_void_p]),
+    "ibcu_last_error": (C.c_char_p, [C.c_void_p]),
+    "ibcu_clear_error": (None, [C.c_void_p]),
+    "ibcu_device_count": (C.c_int, []),
+    "ibcu_device_sm_count": (C.c_int, [C.c_void_p]),
+    "ibcu_malloc": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp]),
+    "ibcu_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ibcu_host_alloc": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp]),
+    "ibcu_host_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ibcu_memcpy_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_memcpy_d2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
+    "ibcu_sync": (C.c_int, [C.c_void_p]),
+    "ibcu_fill_hash_bytes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64]),
+    "ibcu_hash_bytes_host": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_size_t]),
+    "ibcu_fill_hash_fp16_uniform": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float]),
+    "ibcu_hash_fp16_uniform_host": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float, C.c_size_t]),
+    "ibcu_event_record": (C.c_int, [C.c_void_p, C.c_int]),
+    "ibcu_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "ibcu_graph_begin": (C.c_int, [C.c_void_p]),
+    "ibcu_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "ibcu_graph_launch": (C.c_int, [C.c_void_p, C.c_int]),
+    "ibcu_graph_destroy": (C.c_int, [C.c_void_p, C.c_int]),
+    "ibcu_launch_count": (C.c_uint64, [C.c_void_p]),
+    "ibcu_set_pdl": (None, [C.c_void_p, C.c_int]),
+    "ibcu_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "ibcu_linear_gate_up_silu": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "ibcu_linear_force_generic": (None, [C.c_void_p, C.c_int]),
+    "ibcu_quantize_input_int8_g128": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_linear_w4a8": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_pq_idx_t_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "ibcu_pq_prepare": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p]),
+    "ibcu_pq_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
+    "ibcu_kmeans_assign": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ibcu_kmeans_accumulate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ibcu_kmeans_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ibcu_kmeans_lloyd_iter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ibcu_embed_int8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_rmsnorm_fp16w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
+    "ibcu_rope_kv_write": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
+    "ibcu_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "ibcu_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_add_inplace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_comm_get_id": (C.c_int, [C.c_void_p]),
+    "ibcu_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_comm_rank": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ibcu_shard_rows": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ibcu_allgather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "ibcu_allreduce_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_allreduce_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ibcu_allreduce_f64": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+}
+
+_libibcu = None
+
+
+def load_ibcu():
+    """Load libibcu.so and attach prototypes. Raises OSError if the library has not been built."""
+    global _libibcu
+    if _libibcu is None:
+        if not os.path.exists(LIBIBCU_PATH):
+            raise OSError(f"{LIBIBCU_PATH} not found: build it with `make -C libinferbit_b200` "
+                          "(or __graft_entry__.build()); there is no CPU fallback")
+        lib = C.CDLL(LIBIBCU_PATH, mode=C.RTLD_GLOBAL)
+        for name, (res, args) in IBCU_SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _libibcu = lib
+    return _libibcu

@@ -1,0 +1,194 @@
+"""Loads the CPU checkers for the tests: oracle/libib_oracle.so (this repo's restatement, built on
+demand with gcc) and oracle/_ref/libinferbit_ref.so (the unmodified reference, present only where
+oracle/Makefile could build it from a reference checkout)."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_SO = os.path.join(ORACLE_DIR, "libib_oracle.so")
+REF_SO = os.path.join(ORACLE_DIR, "_ref", "libinferbit_ref.so")
+
+f32 = np.ctypeslib.ndpointer(np.float32, flags="C")
+i32 = np.ctypeslib.ndpointer(np.int32, flags="C")
+u8 = np.ctypeslib.ndpointer(np.uint8, flags="C")
+i8 = np.ctypeslib.ndpointer(np.int8, flags="C")
+u16 = np.ctypeslib.ndpointer(np.uint16, flags="C")
+
+
+class IboLinear(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("scale", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("bits", C.c_int)]
+
+
+class IboLayer(C.Structure):
+    _fields_ = [(n, IboLinear) for n in ("q", "k", "v", "o", "gate", "up", "down")] + [
+        ("input_norm", C.c_void_p), ("post_attn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
+class IboModel(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("hidden", "inter", "n_layers", "n_heads", "n_kv_heads", "head_dim", "vocab", "max_ctx")] + [
+        ("eps", C.c_float), ("theta", C.c_float), ("embed", C.c_void_p), ("embed_scale", C.c_void_p),
+        ("final_norm", C.c_void_p), ("head", IboLinear), ("layers", C.POINTER(IboLayer))]
+
+
+class RefKernels(C.Structure):
+    """ib_kernels (src/inferbit_internal.h:199-277), field order as declared there."""
+    _mm = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int)
+    _fields_ = [
+        ("matmul_int4", _mm), ("matmul_int8", _mm), ("matmul_int2", _mm),
+        ("rmsnorm", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int)),
+        ("rope", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float)),
+        ("softmax", C.CFUNCTYPE(None, C.c_void_p, C.c_int)),
+        ("silu_mul", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int)),
+        ("matmul_w4a8", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int)),
+        ("matmul_w4a8_batch", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int)),
+        ("matmul_int8_batch", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int)),
+    ]
+
+
+class RefPqTensor(C.Structure):
+    """ib_pq_tensor (src/pq_decode.h:39-87)."""
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K", C.c_int), ("K_l2", C.c_int),
+                ("n_levels", C.c_int), ("rotate", C.c_int), ("n_outlier", C.c_int), ("format", C.c_int),
+                ("codebook_l1_l", C.c_void_p), ("codebook_l1_r", C.c_void_p),
+                ("codebook_l2_l", C.c_void_p), ("codebook_l2_r", C.c_void_p),
+                ("indices_l1_l", C.c_void_p), ("indices_l1_r", C.c_void_p),
+                ("indices_l2_l", C.c_void_p), ("indices_l2_r", C.c_void_p),
+                ("C", C.c_int), ("l2_idx_bytes", C.c_int), ("l2_packed_bits", C.c_int),
+                ("row_scale", C.c_void_p), ("outlier_cols", C.c_void_p), ("outlier_sidecar", C.c_void_p),
+                ("outlier_scale", C.c_void_p), ("_arena", C.c_void_p), ("_arena_size", C.c_size_t),
+                ("_mmap_base", C.c_void_p), ("_mmap_size", C.c_size_t), ("_owns_mmap", C.c_int)]
+
+
+def build_oracle():
+    subprocess.run(["make", "-s", "-C", ORACLE_DIR, "oracle"], check=True)
+
+
+class Libs:
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(ORACLE_DIR, "ib_oracle.c")):
+            build_oracle()
+        o = C.CDLL(ORACLE_SO)
+        o.ibo_fp16_to_fp32.restype = C.c_float; o.ibo_fp16_to_fp32.argtypes = [C.c_uint16]
+        o.ibo_fp32_to_fp16.restype = C.c_uint16; o.ibo_fp32_to_fp16.argtypes = [C.c_float]
+        o.ibo_fp16_array_to_fp32.argtypes = [u16, f32, C.c_int]
+        o.ibo_matmul_int4.argtypes = [f32, u8, f32, f32, C.c_int, C.c_int]
+        o.ibo_matmul_int8.argtypes = [f32, i8, f32, f32, C.c_int, C.c_int]
+        o.ibo_matmul_int8_batch.argtypes = [f32, i8, f32, f32, C.c_int, C.c_int, C.c_int, C.c_int]
+        o.ibo_matmul_int4_batch.argtypes = [f32, u8, f32, f32, C.c_int, C.c_int, C.c_int, C.c_int]
+        o.ibo_quantize_input_int8_g128.restype = C.c_int
+        o.ibo_quantize_input_int8_g128.argtypes = [f32, i8, f32, C.c_int]
+        o.ibo_matmul_w4a8_batch.argtypes = [f32, u8, f32, i8, f32, C.c_int, C.c_int, C.c_int, C.c_int]
+        o.ibo_pq_matmul_fp32.restype = C.c_int
+        o.ibo_pq_matmul_fp32.argtypes = [C.c_int] * 4 + [u16, u16, C.c_long, u8, u8, u16, f32, f32, C.c_int, C.POINTER(C.c_int)]
+        o.ibo_pq_reconstruct_fp32.restype = C.c_int
+        o.ibo_pq_reconstruct_fp32.argtypes = [C.c_int] * 4 + [u16, u16, u8, u8, u16, f32]
+        o.ibo_kmeans_assign.argtypes = [f32, C.c_long, C.c_int, f32, C.c_int, i32, C.c_void_p, C.c_int]
+        o.ibo_kmeans_lloyd_iter.restype = C.c_float
+        o.ibo_kmeans_lloyd_iter.argtypes = [f32, C.c_long, C.c_int, f32, C.c_int, i32, f32, i32, C.POINTER(C.c_double), C.c_int]
+        o.ibo_kmeans_update.restype = C.c_float
+        o.ibo_kmeans_update.argtypes = [f32, C.c_int, C.c_int, f32, i32]
+        o.ibo_rmsnorm.argtypes = [f32, f32, f32, C.c_float, C.c_int]
+        o.ibo_rope.argtypes = [f32, C.c_void_p, C.c_int, C.c_int, C.c_float]
+        o.ibo_softmax.argtypes = [f32, C.c_int]
+        o.ibo_silu_mul.argtypes = [f32, f32, f32, C.c_int]
+        o.ibo_decode_step.restype = C.c_int
+        o.ibo_decode_step.argtypes = [C.POINTER(IboModel), i32, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        self.oracle = o
+        self.ref = None
+        self.ref_kern = None
+        if os.path.exists(REF_SO):
+            r = C.CDLL(REF_SO)
+            r.ib_init_kernels.argtypes = [C.c_int]
+            r.ib_detect_simd.restype = C.c_int
+            r.ib_fp16_to_fp32.restype = C.c_float; r.ib_fp16_to_fp32.argtypes = [C.c_uint16]
+            r.ib_fp32_to_fp16.restype = C.c_uint16; r.ib_fp32_to_fp16.argtypes = [C.c_float]
+            r.ib_kmeans_assign.restype = C.c_int
+            r.ib_kmeans_assign.argtypes = [f32, C.c_int, C.c_int, f32, C.c_int, i32, C.c_void_p]
+            r.ib_pq_matmul_fp32.restype = C.c_int
+            r.ib_pq_matmul_fp32.argtypes = [C.POINTER(RefPqTensor), f32, f32]
+            r.ib_pq_matmul_fp32_threaded.restype = C.c_int
+            r.ib_pq_matmul_fp32_threaded.argtypes = [C.POINTER(RefPqTensor), f32, f32, C.c_void_p]
+            r.ib_pq_matmul_fp32_streaming.restype = C.c_int
+            r.ib_pq_matmul_fp32_streaming.argtypes = [C.POINTER(RefPqTensor), f32, f32]
+            r.ib_pq_reconstruct_fp32.restype = C.c_int
+            r.ib_pq_reconstruct_fp32.argtypes = [C.POINTER(RefPqTensor), f32]
+            r.ib_quantize_input_int8_g128.restype = C.c_int
+            r.ib_quantize_input_int8_g128.argtypes = [f32, i8, f32, C.c_int]
+            r.ib_pool_create.restype = C.c_void_p; r.ib_pool_create.argtypes = [C.c_int]
+            r.ib_pool_destroy.argtypes = [C.c_void_p]
+            r.ib_parallel_matmul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+            r.ib_parallel_matmul_int8_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+            self.ref = r
+            self.ref_kern = RefKernels.in_dll(r, "ib_kern")
+
+    def ref_scalar(self):
+        """Install the reference's scalar table (IB_SIMD_NONE = 0): the reference of record."""
+        self.ref.ib_init_kernels(0)
+        return self.ref_kern
+
+    def ref_simd(self):
+        self.ref.ib_init_kernels(self.ref.ib_detect_simd())
+        return self.ref_kern
+
+    def ref_pq_tensor(self, M, N, G, K, cb_l, cb_r, idx_l, idx_r, row_scale):
+        t = RefPqTensor()
+        t.M, t.N, t.G, t.K, t.K_l2, t.n_levels, t.rotate, t.n_outlier, t.format = M, N, G, K, 0, 1, 0, 0, 0
+        t.codebook_l1_l = cb_l.ctypes.data; t.codebook_l1_r = cb_r.ctypes.data
+        t.indices_l1_l = idx_l.ctypes.data; t.indices_l1_r = idx_r.ctypes.data
+        t.C = N // G; t.l2_idx_bytes = 1; t.row_scale = row_scale.ctypes.data
+        t._keep = (cb_l, cb_r, idx_l, idx_r, row_scale)
+        return t
+
+
+_libs = None
+
+
+def load():
+    global _libs
+    if _libs is None:
+        _libs = Libs()
+    return _libs
+
+
+def p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# ── seeded synthetic inputs shaped like the benchmark configurations ──
+def fp16_bits(x):
+    return np.asarray(x, np.float32).astype(np.float16).view(np.uint16)
+
+
+def make_int8_case(rng, M, N, B):
+    w = rng.integers(-127, 128, size=(M, N), dtype=np.int8)
+    s16 = fp16_bits(rng.uniform(0.001, 0.01, M))
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    return w, s16, x
+
+
+def make_int4_case(rng, M, N, B):
+    w = rng.integers(0, 256, size=(M, N // 2), dtype=np.uint8)      # nibbles uniform in [-8, 7]
+    s16 = fp16_bits(rng.uniform(0.002, 0.02, M))
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    return w, s16, x
+
+
+def make_pq_case(rng, M, N, G, K, B, scale_one=False):
+    half, Cn = G // 2, N // G
+    cb_l = fp16_bits(rng.standard_normal((K, half)) * 0.02)
+    cb_r = fp16_bits(rng.standard_normal((K, half)) * 0.02)
+    idx_l = rng.integers(0, K, size=(M, Cn), dtype=np.uint8)
+    idx_r = rng.integers(0, K, size=(M, Cn), dtype=np.uint8)
+    rs = fp16_bits(np.ones(M) if scale_one else rng.uniform(0.5, 2.0, M))
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    return cb_l, cb_r, idx_l, idx_r, rs, x
+
+
+def close(a, b, rtol=1e-3, atol=1e-4):
+    """The float parity bar: |a - b| <= atol + rtol * |b| element-wise."""
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return bool(np.all(np.abs(a - b) <= atol + rtol * np.abs(b)))

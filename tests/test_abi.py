@@ -1,0 +1,55 @@
+"""The C ABI loads without a GPU and exports every symbol its header declares."""
+import ctypes as C
+import os
+import re
+
+from libinferbit_b200 import _ffi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared(header):
+    txt = open(os.path.join(ROOT, "include", header)).read()
+    txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:ibcu|ib_b200)_[a-z0-9_]+)\s*\(", txt)))
+
+
+def test_libibcu_exports_every_declared_symbol():
+    lib = _ffi.load_ibcu()
+    names = declared("ibcu.h")
+    assert len(names) > 40
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(_ffi.IBCU_SYMBOLS) == names          # the Python prototypes cover the header exactly
+
+
+def test_no_gpu_means_an_error_not_a_fallback():
+    lib = _ffi.load_ibcu()
+    if lib.ibcu_device_count() > 0:
+        return
+    ctx = C.c_void_p()
+    assert lib.ibcu_ctx_create(0, C.byref(ctx)) != 0 and not ctx.value
+
+
+def test_shard_rows_partitions_exactly():
+    lib = _ffi.load_ibcu()
+    for M in (0, 1, 100, 1024, 4096, 14336, 32000, 32001):
+        for world in (1, 2, 3, 4, 8):
+            for align in (1, 16, 32):
+                nxt = 0
+                for r in range(world):
+                    r0, rn = C.c_int(), C.c_int()
+                    lib.ibcu_shard_rows(M, world, r, align, C.byref(r0), C.byref(rn))
+                    assert r0.value == nxt and rn.value >= 0
+                    if rn.value and r0.value + rn.value < M:
+                        assert rn.value % align == 0
+                    nxt += rn.value
+                assert nxt == M
+
+
+def test_hash_fill_host_side_is_position_addressable():
+    import numpy as np
+    lib = _ffi.load_ibcu()
+    a = np.empty(1000, np.uint8); lib.ibcu_hash_bytes_host(a.ctypes.data, 1000, 42, 0)
+    b = np.empty(100, np.uint8); lib.ibcu_hash_bytes_host(b.ctypes.data, 100, 42, 333)
+    assert np.array_equal(a[333:433], b) and len(set(a.tolist())) > 200

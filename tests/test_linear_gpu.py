@@ -1,0 +1,200 @@
+"""GPU parity of the INT4 / INT8 linear kernels against the CPU restatement of the reference's scalar
+kernels (src/kernels/scalar.c:9-41,70-84), through the C ABI (ibcu_linear)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from libinferbit_b200 import LinearT
+from tests import _cpu
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-3, 1e-4        # the float bar: |gpu - ref| <= 1e-4 + 1e-3 |ref|
+
+
+def oracle_linear(libs, w, s16, x, bits):
+    M = w.shape[0]; B, N = x.shape
+    s = np.empty(M, np.float32); libs.oracle.ibo_fp16_array_to_fp32(s16, s, M)
+    out = np.empty((B, M), np.float32)
+    if bits == 8:
+        libs.oracle.ibo_matmul_int8_batch(out, w, s, x, M, N, B, M)
+    else:
+        libs.oracle.ibo_matmul_int4_batch(out, w, s, x, M, N, B, M)
+    return out
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("M,N,B", [
+    (5632, 2048, 1),      # TinyLlama up_proj
+    (1024, 4096, 1), (1024, 4096, 4), (1024, 4096, 16),     # k/v proj
+    (512, 4096, 2), (512, 4096, 3), (512, 4096, 8), (256, 4096, 32),
+    (4096, 14336, 1),     # down_proj shape
+    (100, 320, 5),        # rows not a multiple of the tile, short rows
+    (33, 96, 1), (1, 64, 1), (17, 4128, 7),
+])
+def test_linear_matches_scalar_reference(backend, cpu_libs, bits, M, N, B):
+    rng = np.random.default_rng(bits * 7919 + M * 31 + N + B)
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    got = backend.linear(w, s16, x, bits)
+    want = oracle_linear(cpu_libs, w, s16, x, bits)
+    assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("M,N,B", [(40, 66, 2), (9, 30, 1), (257, 1000, 3), (64, 4096, 4)])
+def test_portable_kernel(backend, cpu_libs, bits, M, N, B):
+    """Shapes the tensor-core path does not take (row bytes not a multiple of 16) and the forced
+    portable kernel on a shape it does take."""
+    rng = np.random.default_rng(M + N)
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    got = backend.linear(w, s16, x, bits, force_generic=True)
+    want = oracle_linear(cpu_libs, w, s16, x, bits)
+    assert _cpu.close(got, want, RTOL, ATOL)
+    got2 = backend.linear(w, s16, x, bits)
+    assert _cpu.close(got2, want, RTOL, ATOL)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_unpack_is_exact(backend, bits):
+    """One-hot activations read single weights back: out/scale must be the integer itself, for every
+    column position modulo 128 and every nibble / byte value."""
+    rng = np.random.default_rng(11)
+    M, N = 64, 256
+    if bits == 8:
+        w = rng.integers(-128, 128, size=(M, N), dtype=np.int8)
+        w[:, 0] = np.arange(M) - 128; w[:, 1] = np.arange(M) + 64
+        vals = w.astype(np.float32)
+    else:
+        w = rng.integers(0, 256, size=(M, N // 2), dtype=np.uint8)
+        w[:16, 0] = np.arange(16) | (np.arange(16)[::-1] << 4)
+        vals = np.empty((M, N), np.float32)
+        vals[:, 0::2] = (w & 15).astype(np.float32) - 8
+        vals[:, 1::2] = (w >> 4).astype(np.float32) - 8
+    ones = np.full(M, 0x3C00, np.uint16)                       # fp16 1.0
+    for j0 in range(0, N, 32):
+        x = np.zeros((32, N), np.float32)
+        x[np.arange(32), j0 + np.arange(32)] = 1.0
+        got = backend.linear(w, ones, x, bits)                 # [32, M]
+        assert np.array_equal(got, vals[:, j0:j0 + 32].T)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_scales_fp32_and_residual_epilogue(backend, cpu_libs, bits):
+    rng = np.random.default_rng(5)
+    M, N, B = 200, 512, 4
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    want = oracle_linear(cpu_libs, w, s16, x, bits)
+    s32 = np.empty(M, np.float32); cpu_libs.oracle.ibo_fp16_array_to_fp32(s16, s32, M)
+    assert _cpu.close(backend.linear(w, s32, x, bits), want, RTOL, ATOL)
+    base = rng.standard_normal((B, M)).astype(np.float32)
+    got = backend.linear(w, s16, x, bits, epilogue=1, out_init=base)
+    assert _cpu.close(got, base + want, RTOL, ATOL)
+
+
+def test_wide_dynamic_range_activations(backend, cpu_libs):
+    """Activations spanning many orders of magnitude, huge and tiny vectors: the power-of-two
+    pre-scaling keeps the fp16 pieces exact enough."""
+    rng = np.random.default_rng(9)
+    M, N = 128, 1024
+    w, s16, _ = _cpu.make_int8_case(rng, M, N, 1)
+    for scale in (1e-20, 1e-6, 1.0, 3e4, 1e12):
+        x = (rng.standard_normal((2, N)) * scale * 10.0 ** rng.integers(-3, 3, (2, N))).astype(np.float32)
+        got = backend.linear(w, s16, x, 8)
+        want = oracle_linear(cpu_libs, w, s16, x, 8)
+        assert _cpu.close(got, want, RTOL, ATOL * scale), scale
+    x = np.zeros((1, N), np.float32)
+    assert np.array_equal(backend.linear(w, s16, x, 8), np.zeros((1, M), np.float32))
+
+
+def test_three_tensors_one_launch_with_strided_output(backend, cpu_libs):
+    """q, k, v share the activation: one launch, each tensor with its own rows, scales and output
+    stride (the reference's M_stride, src/threading.c:373-380)."""
+    rng = np.random.default_rng(21)
+    N, B = 1024, 4
+    Ms = [256, 64, 80]
+    be = backend
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    dx = be.upload(x)
+    descs = (LinearT * 3)()
+    keep, wants, outs = [], [], []
+    for i, M in enumerate(Ms):
+        w, s16, _ = _cpu.make_int8_case(rng, M, N, 1)
+        wants.append(oracle_linear(cpu_libs, w, s16, x, 8))
+        dw, ds = be.upload(w), be.upload(s16)
+        stride = M + 8
+        do = be.upload(np.full((B, stride), -7.0, np.float32))
+        keep += [dw, ds]; outs.append((do, stride))
+        descs[i] = LinearT(dw.ptr, ds.ptr, do.ptr, M, stride, 0, 0)
+    be._check(be.lib.ibcu_linear(be.ctx, descs, 3, dx.ptr, N, B, 8))
+    be.sync()
+    for (do, stride), want, M in zip(outs, wants, Ms):
+        got = be.download(do, np.float32, B * stride).reshape(B, stride)
+        assert _cpu.close(got[:, :M], want, RTOL, ATOL)
+        assert np.all(got[:, M:] == -7.0)                      # padding untouched
+
+
+def test_gate_up_silu(backend, cpu_libs):
+    rng = np.random.default_rng(22)
+    M, N, B = 300, 512, 2
+    be = backend
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    wg, sg, _ = _cpu.make_int4_case(rng, M, N, 1)
+    wu, su, _ = _cpu.make_int4_case(rng, M, N, 1)
+    g = oracle_linear(cpu_libs, wg, sg, x, 4); u = oracle_linear(cpu_libs, wu, su, x, 4)
+    want = np.empty_like(g)
+    for b in range(B):
+        cpu_libs.oracle.ibo_silu_mul(want[b], g[b], u[b], M)
+    dx = be.upload(x)
+    descs = (LinearT * 2)()
+    og, ou = be.alloc(B * M * 4), be.alloc(B * M * 4)
+    descs[0] = LinearT(be.upload(wg).ptr, be.upload(sg).ptr, og.ptr, M, M, 0, 0)
+    descs[1] = LinearT(be.upload(wu).ptr, be.upload(su).ptr, ou.ptr, M, M, 0, 0)
+    be._check(be.lib.ibcu_linear_gate_up_silu(be.ctx, descs, dx.ptr, N, B, 4))
+    be.sync()
+    got = be.download(og, np.float32, B * M).reshape(B, M)
+    assert _cpu.close(got, want, 2e-3, 2e-4)
+
+
+def test_bad_arguments_are_refused(backend):
+    be = backend
+    d = be.alloc(1024)
+    t = LinearT(d.ptr, d.ptr, d.ptr, 4, 4, 0, 0)
+    assert be.lib.ibcu_linear(be.ctx, C.byref(t), 1, d.ptr, 64, 1, 3) == -1       # bits
+    assert b"bits" in be.lib.ibcu_last_error(be.ctx)
+    assert be.lib.ibcu_status(be.ctx) == -1
+    be.lib.ibcu_clear_error(be.ctx)
+    assert be.lib.ibcu_linear(be.ctx, C.byref(t), 1, d.ptr, 64, 33, 8) == -1      # B > IB_BATCH_MAX
+    be.lib.ibcu_clear_error(be.ctx)
+    assert be.lib.ibcu_linear(be.ctx, C.byref(t), 1, d.ptr, 63, 1, 4) == -1       # odd N for nibbles
+    be.lib.ibcu_clear_error(be.ctx)
+    assert be.lib.ibcu_linear(be.ctx, C.byref(t), 0, d.ptr, 64, 1, 8) == -1
+    be.lib.ibcu_clear_error(be.ctx)
+    assert be.lib.ibcu_status(be.ctx) == 0
+
+
+@pytest.mark.parametrize("N", [128, 4096, 200])
+def test_w4a8_route_bit_exact(backend, cpu_libs, N):
+    """Activation quantiser (src/threading.c:401-432) and INT4 x INT8 kernel (src/kernels/scalar.c:43-124):
+    integer work, so the bar is bit-exact, including the FP32 accumulation order."""
+    rng = np.random.default_rng(N)
+    B, M = 3, 70
+    be = backend
+    x = rng.standard_normal((B, N)).astype(np.float32); x[1, :64] = 0; x[2, :] *= 1e-12
+    groups = (N + 127) // 128
+    q = np.empty((B, N), np.int8); sa = np.empty((B, groups), np.float32)
+    for b in range(B):
+        cpu_libs.oracle.ibo_quantize_input_int8_g128(x[b], q[b], sa[b], N)
+    dx = be.upload(x); dq = be.alloc(B * N); dsa = be.alloc(B * groups * 4)
+    be._check(be.lib.ibcu_quantize_input_int8_g128(be.ctx, dx.ptr, dq.ptr, dsa.ptr, N, B)); be.sync()
+    assert np.array_equal(be.download(dq, np.int8, B * N).reshape(B, N), q)
+    assert np.array_equal(be.download(dsa, np.float32, B * groups).reshape(B, groups), sa)
+    w = rng.integers(0, 256, size=(M, N // 2), dtype=np.uint8)
+    s16 = _cpu.fp16_bits(rng.uniform(0.002, 0.02, M))
+    sw = np.empty(M, np.float32); cpu_libs.oracle.ibo_fp16_array_to_fp32(s16, sw, M)
+    want = np.empty((B, M), np.float32)
+    cpu_libs.oracle.ibo_matmul_w4a8_batch(want, w, sw, q, sa, M, N, B, M)
+    do = be.alloc(B * M * 4)
+    t = LinearT(be.upload(w).ptr, be.upload(s16).ptr, do.ptr, M, M, 0, 0)
+    be._check(be.lib.ibcu_linear_w4a8(be.ctx, C.byref(t), dq.ptr, dsa.ptr, N, B)); be.sync()
+    assert np.array_equal(be.download(do, np.float32, B * M).reshape(B, M), want)

@@ -1,0 +1,116 @@
+"""GPU parity of the PQ LUT + gather matvec against the CPU restatement of matmul_impl
+(src/pq_decode.c:1504-1682), through the C ABI (ibcu_pq_prepare / ibcu_pq_matmul_fp32)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests import _cpu
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-3, 1e-4
+
+
+def oracle_pq(libs, M, N, G, K, cb_l, cb_r, il, ir, rs, x, stride=0):
+    out = np.empty((x.shape[0], M), np.float32)
+    for b in range(x.shape[0]):
+        assert libs.oracle.ibo_pq_matmul_fp32(M, N, G, K, cb_l, cb_r, stride, il, ir, rs, x[b], out[b], 1, None) == 0
+    return out
+
+
+@pytest.mark.parametrize("M,N,G,K,B", [
+    (4096, 14336, 16, 256, 1),      # Mistral-7B down_proj: 1792 subspaces of length 8
+    (4096, 14336, 16, 256, 8),
+    (1000, 2048, 16, 256, 3),       # rows not a multiple of 16
+    (64, 256, 8, 64, 2), (33, 96, 4, 16, 1), (2048, 512, 32, 256, 1), (5, 16, 16, 256, 1),
+])
+def test_pq_matches_reference_restatement(backend, cpu_libs, M, N, G, K, B):
+    rng = np.random.default_rng(M + N + G + K + B)
+    cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, B)
+    t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
+    got = backend.pq_matmul(t, x)
+    want = oracle_pq(cpu_libs, M, N, G, K, cb_l, cb_r, il, ir, rs, x)
+    assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
+
+
+def test_transposed_code_plane_is_a_faithful_copy(backend):
+    rng = np.random.default_rng(3)
+    M, N, G, K = 77, 160, 16, 256
+    cb_l, cb_r, il, ir, rs, _ = _cpu.make_pq_case(rng, M, N, G, K, 1)
+    t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
+    Cn = N // G
+    plane = backend.download(t.idx_t, np.uint8, 2 * Cn * t.M_pad).reshape(2 * Cn, t.M_pad)
+    assert t.M_pad == 80
+    assert np.array_equal(plane[0::2, :M], il.T) and np.array_equal(plane[1::2, :M], ir.T)
+    assert np.all(plane[:, M:] == 0)
+
+
+def test_codes_select_the_right_table_entries(backend):
+    """Codebook entry k of side L holds k in its first element and zeros elsewhere, side R holds 1000*k,
+    and x is one-hot per chunk: the output must be exactly the selected integers."""
+    M, N, G, K = 48, 64, 16, 256
+    half, Cn = 8, 4
+    cb_l = np.zeros((K, half), np.float32); cb_l[:, 0] = np.arange(K)
+    cb_r = np.zeros((K, half), np.float32); cb_r[:, 0] = np.arange(K) * 8.0
+    rng = np.random.default_rng(1)
+    il = rng.integers(0, K, (M, Cn), dtype=np.uint8); ir = rng.integers(0, K, (M, Cn), dtype=np.uint8)
+    rs = np.full(M, 0x3C00, np.uint16)
+    t = backend.make_pq(M, N, G, K, _cpu.fp16_bits(cb_l), _cpu.fp16_bits(cb_r), il, ir, rs)
+    for c in range(Cn):
+        x = np.zeros((1, N), np.float32); x[0, c * G] = 1.0; x[0, c * G + half] = 1.0
+        got = backend.pq_matmul(t, x)[0]
+        assert np.array_equal(got, il[:, c].astype(np.float32) + 8.0 * ir[:, c].astype(np.float32))
+
+
+def test_chunk_skip_rule(backend, cpu_libs):
+    """Chunks whose 16 activations all stay under 1 % of the vector's max contribute nothing
+    (src/pq_decode.c:1582-1616); an all-zero activation gives zeros."""
+    rng = np.random.default_rng(8)
+    M, N, G, K = 256, 1024, 16, 256
+    cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, 3)
+    x[0, 5 * G:9 * G] *= 1e-3
+    x[1, :] = 0.0
+    x[2, ::2] *= 1e-5
+    t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
+    got = backend.pq_matmul(t, x)
+    want = np.empty((3, M), np.float32); skipped = []
+    for b in range(3):
+        n = C.c_int()
+        cpu_libs.oracle.ibo_pq_matmul_fp32(M, N, G, K, cb_l, cb_r, 0, il, ir, rs, x[b], want[b], 1, C.byref(n))
+        skipped.append(n.value)
+    assert skipped[0] >= 4 and skipped[1] == 0
+    assert _cpu.close(got, want, RTOL, ATOL)
+    assert np.all(got[1] == 0.0)
+    # dropping is visible: without the rule row 0 would differ
+    x0 = x[0].copy(); x0[5 * G:9 * G] = 0.0
+    ref0 = np.empty(M, np.float32)
+    cpu_libs.oracle.ibo_pq_matmul_fp32(M, N, G, K, cb_l, cb_r, 0, il, ir, rs, x0, ref0, 1, None)
+    assert _cpu.close(got[0], ref0, RTOL, ATOL)
+
+
+def test_per_subspace_codebooks(backend, cpu_libs):
+    """A codebook per chunk (stride between chunk tables), same arithmetic."""
+    rng = np.random.default_rng(12)
+    M, N, G, K = 128, 512, 16, 256
+    half, Cn = 8, N // G
+    cb_l = _cpu.fp16_bits(rng.standard_normal((Cn, K, half)) * 0.02)
+    cb_r = _cpu.fp16_bits(rng.standard_normal((Cn, K, half)) * 0.02)
+    _, _, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, 2)
+    t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs, cb_chunk_stride=K * half)
+    got = backend.pq_matmul(t, x)
+    want = oracle_pq(cpu_libs, M, N, G, K, cb_l.reshape(-1), cb_r.reshape(-1), il, ir, rs, x, stride=K * half)
+    assert _cpu.close(got, want, RTOL, ATOL)
+
+
+def test_linearity_at_full_size(backend):
+    """Size-independent property at the benchmark shape: with the skip rule inactive the map is linear,
+    f(x + y) = f(x) + f(y) and f(2x) = 2 f(x) exactly."""
+    rng = np.random.default_rng(4)
+    M, N, G, K = 4096, 14336, 16, 256
+    cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, 2)
+    t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
+    fx = backend.pq_matmul(t, x)
+    f2 = backend.pq_matmul(t, 2.0 * x[:1])
+    assert np.array_equal(f2[0], 2.0 * fx[0])
+    fs = backend.pq_matmul(t, (x[0] + x[1])[None, :])
+    assert _cpu.close(fs[0], fx[0] + fx[1], 1e-3, 1e-4)
