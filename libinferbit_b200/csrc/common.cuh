@@ -23,8 +23,9 @@ struct ibcu_ctx {
     int force_generic;
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
-    void*  xpack;      size_t xpack_bytes;      // fp16 split activations + per-vector scales
-    void*  scratch;    size_t scratch_bytes;    // partial sums (PQ slabs, k-means per-block partials)
+    void*  xpack;      size_t xpack_bytes;      // fp16 activation pieces + per-slice scales of the current linear call
+    void*  counters;   size_t counters_bytes;   // arrival counters of split launches; zero whenever no launch is in flight
+    void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, PQ slabs, k-means per-block partials)
     cudaEvent_t events[IBCU_MAX_EVENTS];
     cudaGraphExec_t graphs[IBCU_MAX_GRAPHS];
     int capturing;

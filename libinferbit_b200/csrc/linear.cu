@@ -3,22 +3,31 @@
 // Data in HBM: weights keep the reference layout bit for bit (INT8 row-major; INT4 two columns per
 // byte, low nibble first, bias 8), scales are FP16 (or FP32) per output row.
 //
-// Fast path (linear_mma_kernel): HBM-bound streaming of the weights with 128-bit no-allocate loads.
-// Every lane unpacks its 16 bytes in registers to exact fp16 pairs with the "1024 + n" bit trick
-// (PRMT/LOP3 + one HSUB2/HFMA2 per pair) and feeds them to mma.sync.m16n8k16 (fp16 in, fp32
-// accumulate). The eight MMA columns carry the FP32 activations as exact fp16 pieces
-// (x * 2^-e = hi + mid [+ lo], written once per call by xprep_kernel), so the product is FP32-grade
-// while costing ~1.3 issue slots per weight instead of ~3 for convert + FFMA.
+// Arithmetic of the fast path: integer tensor cores, exactly. xprep_kernel turns every slice of an
+// FP32 activation into a 32-bit fixed-point integer X = rint(x * 2^s) (s per slice, so that the
+// slice maximum sits just under 2^30) and splits X into four signed base-256 digits (int8 "limbs").
+// linear_mma_kernel feeds the weights - INT8 bytes as they are, INT4 nibbles masked in place with
+// one LOP3 per four weights - and the limbs to mma.sync.m16n8k32 (s8/u8 x s8 -> s32): every product
+// and every sum is an exact integer. The four limb sums are recombined in 64-bit, converted to
+// floating point once, scaled back by 2^-s and multiplied by the row scale. The result is the
+// correctly rounded dot product of the weights with x rounded to 2^-32 of its slice maximum: closer
+// to the true value than the reference's own FP32 running sum, and independent of summation order.
 // Because a dot product is invariant under a permutation of k applied to both operands, each lane
-// simply owns 16 contiguous bytes of a row; no shared-memory transpose or ldmatrix is needed.
-// K is split over the warps of a CTA and, for short/wide tensors, over the CTAs of a thread-block
-// cluster; partial sums meet in shared memory / distributed shared memory in a fixed order.
+// simply owns 16 contiguous bytes of a row; no transpose or ldmatrix is needed for the weights.
+//
+// Work split: xprep_kernel runs one block per (activation, column slice). linear_mma_kernel is
+// persistent: a block is bound to one column slice, copies that slice's limbs into shared memory
+// once, and then walks row blocks of RT*16 rows. Weights reach shared memory through a cp.async ring
+// whose stages are RT*16 rows x 512 bytes, written in row-linear order (every warp instruction covers
+// 512 contiguous bytes of one row, which is what HBM wants; lane-owns-a-row-fragment register loads
+// measured 2-3 TB/s, this pattern 6+ TB/s). The W warps of a block take one 64-byte k-block of each
+// stage each and meet in a shared-memory reduction per row block. When the columns are split over
+// several blocks (only when a row's limbs do not fit shared memory), each writes its integer partial
+// sums to scratch and the last block to arrive (a counter per row block) adds them.
 //
 // Portable path (linear_generic_kernel): one warp per output row, plain FP32 FMAs; used for shapes
 // the fast path does not take (row bytes not a multiple of 16, unaligned pointers) and by tests.
 #include "common.cuh"
-#include <cooperative_groups.h>
-namespace cg = cooperative_groups;
 
 namespace {
 
@@ -27,243 +36,368 @@ struct LinTensor {
     const void* scales;
     float* out;
     int M, out_stride, scales_fp32, epilogue;
-    int rg_start;                  // first row-group of this tensor in the launch
+    int rb_start;                  // first row block of this tensor in the launch
 };
 
 struct LinearParams {
     LinTensor t[4];
     int n_tensors;
+    int total_rb;                  // row blocks over all tensors
     int rowbytes;                  // bytes per weight row
     int nkb;                       // 64-byte k-blocks per row
-    int B, P, ncols;               // activations, fp16 pieces per activation, B*P
-    const __half* xpack;           // [ncols][xld] fp16 pieces, fragment order
-    int xld;
-    const float* xscale;           // [B] power-of-two factor removed from x
-    int ks;                        // cluster size = CTAs sharing one row-group
+    int N, B, ncols;               // columns, activations, limb columns (4 per activation)
+    int slice_kb;                  // k-blocks per column slice (a multiple of the stage width)
+    int nks;                       // column slices
+    int xs_ld;                     // bytes per limb row: slice columns + pad
+    const int8_t* xpack;           // [nks][ncols][xs_ld] limbs in fragment order
+    const float* xscale;           // [B][nks] 2^-s of each slice
+    const int* xsum;               // [B][nks][4] sum of each limb over the slice (INT4 bias term)
+    int* partial;                  // [row block][slice][B*4][rows per block] when nks > 1
+    unsigned* counters;            // [row block] arrival counters, zero between launches
 };
 
+constexpr int LIN_LIMBS = 4;
+
 // ── activation split ────────────────────────────────────────────────────────────────────
-// One CTA per activation vector. x is scaled by a power of two so that its largest magnitude
-// lands in [2^14, 2^15) (exact, keeps fp16 away from overflow and from its subnormals), then split
-// into P fp16 pieces whose sum reproduces x to 2^-22 (P = 2) or better (P = 3) relative.
-// perm8 != 0 stores each aligned group of 8 columns as [c0,c4,c1,c5,c2,c6,c3,c7], the order in
-// which the INT4 unpack yields its nibbles.
-__global__ void __launch_bounds__(1024) xprep_kernel(const float* __restrict__ x, int N, int n_pad, int P, int perm8,
-                                                    __half* __restrict__ xpack, float* __restrict__ xscale) {
-    __shared__ float red[32];
+// grid (nks, B), one block per slice of one activation: X = rint(x * 2^s) with 2^s * max|x| in
+// [2^29, 2^30), then X = d0 + 256 d1 + 65536 d2 + 2^24 d3 with every digit in [-128, 127].
+// Eight columns at a time: INT8 consumers get them in natural order, INT4 consumers as
+// c0,c2,c4,c6,c1,c3,c5,c7 (low nibbles of four bytes, then high nibbles).
+__global__ void __launch_bounds__(256) xprep_kernel(const float* __restrict__ x, int N, int slice_cols, int xs_ld, int perm8,
+                                                    int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
+    __shared__ float red[8];
+    __shared__ int sred[8][LIN_LIMBS];
     __shared__ float s_mul;
     pdl_launch_dependents();
     pdl_wait();
-    const int b = blockIdx.x;
-    const float* xb = x + (size_t)b * N;
+    const int ks = blockIdx.x, b = blockIdx.y;
+    const int c0 = ks * slice_cols;
+    const int valid = max(0, min(slice_cols, N - c0));       // N and c0 are multiples of 16
+    const float* xb = x + (size_t)b * N + c0;
     float amax = 0.0f;
-    for (int j = threadIdx.x; j < N; j += blockDim.x) amax = fmaxf(amax, fabsf(xb[j]));
+    for (int j = threadIdx.x * 4; j < valid; j += 1024) {
+        const float4 v = *reinterpret_cast<const float4*>(xb + j);
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
     amax = warp_max(amax);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
-        v = warp_max(v);
-        if (threadIdx.x == 0) {
-            int ex = 0;
-            float mul = 1.0f, back = 1.0f;
-            if (v > 0.0f && v < INFINITY) {
-                frexpf(v, &ex);                       // v = m * 2^ex, m in [0.5, 1)
-                int sh = 15 - ex;
-                sh = sh > 100 ? 100 : (sh < -100 ? -100 : sh);
-                mul = ldexpf(1.0f, sh);
-                back = ldexpf(1.0f, -sh);
-            }
-            s_mul = mul;
-            xscale[b] = back;
-        }
+    if (threadIdx.x == 0) {
+        float v = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) v = fmaxf(v, red[w]);
+        const int e = (int)((__float_as_uint(v) >> 23) & 0xFF);      // v in [2^(e-127), 2^(e-126))
+        int sh = (v > 0.0f && e != 255) ? 156 - e : 0;               // 2^sh * v in [2^29, 2^30)
+        sh = max(-126, min(126, sh));
+        s_mul = __uint_as_float((uint32_t)(127 + sh) << 23);
+        xscale[b * nks + ks] = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
     __syncthreads();
     const float mul = s_mul;
-    for (int j = threadIdx.x; j < n_pad; j += blockDim.x) {
-        float v = j < N ? xb[j] * mul : 0.0f;
-        int jj = perm8 ? ((j & ~7) | (((j & 3) << 1) | ((j >> 2) & 1))) : j;
-#pragma unroll 3
-        for (int p = 0; p < P; p++) {
-            __half h = __float2half_rn(v);
-            xpack[(size_t)(b * P + p) * n_pad + jj] = h;
-            v -= __half2float(h);
+    int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
+    int lsum[LIN_LIMBS] = {0, 0, 0, 0};
+    for (int j = threadIdx.x * 8; j < slice_cols; j += 2048) {
+        int X[8];
+        if (j < valid) {
+            const float4 a = *reinterpret_cast<const float4*>(xb + j), c = *reinterpret_cast<const float4*>(xb + j + 4);
+            X[0] = __float2int_rn(a.x * mul); X[1] = __float2int_rn(a.y * mul); X[2] = __float2int_rn(a.z * mul); X[3] = __float2int_rn(a.w * mul);
+            X[4] = __float2int_rn(c.x * mul); X[5] = __float2int_rn(c.y * mul); X[6] = __float2int_rn(c.z * mul); X[7] = __float2int_rn(c.w * mul);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) X[i] = 0;
         }
+#pragma unroll
+        for (int l = 0; l < LIN_LIMBS; l++) {
+            int d[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                d[i] = l < LIN_LIMBS - 1 ? (int)(int8_t)(X[i] & 0xFF) : X[i];     // balanced digit; the top one is what is left
+                X[i] = (X[i] - d[i]) >> 8;
+                lsum[l] += d[i];
+            }
+            uint2 pk;
+            if (perm8) {
+                pk.x = (d[0] & 0xFF) | ((d[2] & 0xFF) << 8) | ((d[4] & 0xFF) << 16) | ((uint32_t)(d[6] & 0xFF) << 24);
+                pk.y = (d[1] & 0xFF) | ((d[3] & 0xFF) << 8) | ((d[5] & 0xFF) << 16) | ((uint32_t)(d[7] & 0xFF) << 24);
+            } else {
+                pk.x = (d[0] & 0xFF) | ((d[1] & 0xFF) << 8) | ((d[2] & 0xFF) << 16) | ((uint32_t)(d[3] & 0xFF) << 24);
+                pk.y = (d[4] & 0xFF) | ((d[5] & 0xFF) << 8) | ((d[6] & 0xFF) << 16) | ((uint32_t)(d[7] & 0xFF) << 24);
+            }
+            *reinterpret_cast<uint2*>(dst + (size_t)l * xs_ld + j) = pk;
+        }
+    }
+#pragma unroll
+    for (int l = 0; l < LIN_LIMBS; l++) {
+        int v = lsum[l];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5][l] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < LIN_LIMBS) {
+        int v = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) v += sred[w][threadIdx.x];
+        xsum[((size_t)b * nks + ks) * LIN_LIMBS + threadIdx.x] = v;
     }
 }
 
-// ── register unpack ─────────────────────────────────────────────────────────────────────
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-// four int8 -> (w0,w1), (w2,w3) as exact fp16 pairs
-__device__ __forceinline__ void unpack_int8x4(uint32_t raw, uint32_t& h01, uint32_t& h23) {
-    uint32_t u = raw ^ 0x80808080u;                          // w + 128 as unsigned bytes
-    h01 = hsub2_u32(__byte_perm(u, 0x64646464u, 0x4140), 0x64806480u);   // (1024 + u) - 1152
-    h23 = hsub2_u32(__byte_perm(u, 0x64646464u, 0x4342), 0x64806480u);
-}
-// eight nibbles n0..n7 -> (n0,n4), (n1,n5), (n2,n6), (n3,n7), each minus 8, as exact fp16 pairs
-__device__ __forceinline__ void unpack_int4x8(uint32_t raw, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
-    uint32_t hi = raw >> 8;
-    a = hsub2_u32((raw & 0x000F000Fu) | 0x64006400u, 0x64086408u);                 // (1024 + n) - 1032
-    b = hfma2_u32((raw & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);    // (1024 + 16n)/16 - 72
-    c = hsub2_u32((hi & 0x000F000Fu) | 0x64006400u, 0x64086408u);
-    d = hfma2_u32((hi & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);
-}
-__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+__device__ __forceinline__ void imma_s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
+__device__ __forceinline__ void imma_u8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 // ── fast path ───────────────────────────────────────────────────────────────────────────
-// BITS: 4 or 8. NCG: groups of 8 MMA columns (ceil(B*P/8)). RT: 16-row tiles per warp.
-// W: warps per CTA (all on the same RT*16 rows, interleaved over 64-byte k-blocks).
-// U: k-blocks loaded per batch.
-template <int BITS, int NCG, int RT, int W, int U>
+// BITS: 4 or 8. NCG: groups of 8 MMA columns (ceil(4B/8)). RT: 16-row tiles per row block.
+// W: warps per block. STAGES: shared-memory ring depth.
+// MMA operands (m16n8k32, lane = 4g + t): A regs a0/a2 = row g, a1/a3 = row g+8, four bytes of k each;
+// B regs b0/b1 = column g. INT8: a 16-byte lane chunk is four words w0..w3 -> two MMAs (w0,w1), (w2,w3)
+// against 16 consecutive limb bytes. INT4: a raw word holds eight nibbles; raw & 0x0F0F0F0F are
+// columns c0,c2,c4,c6 and raw & 0xF0F0F0F0 are 16 x columns c1,c3,c5,c7, so low and high nibbles go to
+// separate accumulators (the high one is divided by 16 at the end, exactly) and no shift is needed.
+// The nibble bias of 8 is removed once per output as 8 * (sum of the limb over the slice).
+// Dynamic shared memory: stage ring [STAGES][R][LIN_LD] | reduction buffer [W][R][NCG*8] ints (x2 for
+// INT4) | limbs [ncols][xs_ld] | scale-back factors [32] | limb sums [32][4].
+constexpr int LIN_SK = 512;                                   // bytes per row per stage
+constexpr int LIN_LD = LIN_SK + 64;                           // padded row stride: conflict-free fragment reads
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {
+    const int n = valid ? 16 : 0;                             // 0 source bytes -> 16 zero bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(smem_dst), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+template <int BITS, int NCG, int RT, int W, int STAGES>
 __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p) {
-    constexpr int ROWS = RT * 16;
+    constexpr int R = RT * 16;                                // rows per row block
     constexpr int COLS = NCG * 8;
-    constexpr int XK = BITS == 8 ? 64 : 128;                  // activation columns per k-block
-    extern __shared__ __align__(16) float smem[];             // [W][ROWS][COLS] partials, then [ROWS][COLS]
+    constexpr int NACC = BITS == 4 ? 2 : 1;                   // INT4 keeps low- and high-nibble sums apart
+    constexpr int XB = BITS == 8 ? 64 : 128;                  // limb bytes (= columns) per k-block
+    constexpr int KBS = LIN_SK / 64;                          // k-blocks per stage
+    static_assert(KBS == W, "one k-block of every stage per warp");
+    static_assert(W == 8, "copy lanes assume 256 threads");
+    constexpr int STAGE_BYTES = R * LIN_LD;
+    constexpr int NCP = RT * 2;                               // 16-byte chunks per thread per stage
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
 
-    const int ks = p.ks;
-    const int rg = blockIdx.x / ks;
-    const int crank = blockIdx.x - rg * ks;
-    int ti = 0;
-#pragma unroll
-    for (int i = 1; i < 4; i++) if (i < p.n_tensors && rg >= p.t[i].rg_start) ti = i;
-    const LinTensor T = p.t[ti];
-    const int row0 = (rg - T.rg_start) * ROWS;
+    const int ks = blockIdx.x % p.nks;                        // this block's column slice, fixed
+    const int rb_first = blockIdx.x / p.nks, rb_step = gridDim.x / p.nks;
+    const int kb_begin = ks * p.slice_kb;
+    const int nk = min(p.nkb, kb_begin + p.slice_kb) - kb_begin;
+    const int nst = (nk + KBS - 1) / KBS;
 
-    const uint8_t* rowp[RT * 2];
+    unsigned char* ring = smem_raw;
+    int* red = reinterpret_cast<int*>(smem_raw + STAGES * STAGE_BYTES);
+    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw + STAGES * STAGE_BYTES + NACC * W * R * COLS * 4);
+    float* s_back = reinterpret_cast<float*>(xs + (((size_t)p.ncols * p.xs_ld + 15) & ~(size_t)15));
+    int* s_xsum = reinterpret_cast<int*>(s_back + 32);
+
+    // ── producer side: thread owns chunk column cc of rows (tid>>5) + 8i of every stage ──
+    const int cc = threadIdx.x & 31;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + (threadIdx.x >> 5) * LIN_LD + cc * 16;
+    const uint8_t* src[NCP];
+    int pf_rb = rb_first, pf_it = 0, pf_slot = 0;
+    auto pf_setup = [&]() {                                   // row pointers for row block pf_rb
+        int ti = 0;
 #pragma unroll
-    for (int j = 0; j < RT * 2; j++) {
-        int r = row0 + (j >> 1) * 16 + (j & 1) * 8 + g;
-        r = r < T.M ? r : T.M - 1;
-        rowp[j] = T.w + (size_t)r * p.rowbytes + 16 * t;
+        for (int i = 1; i < 4; i++) if (i < p.n_tensors && pf_rb >= p.t[i].rb_start) ti = i;
+        const int r0 = (pf_rb - p.t[ti].rb_start) * R + (threadIdx.x >> 5);
+#pragma unroll
+        for (int i = 0; i < NCP; i++) {
+            int row = r0 + 8 * i;
+            row = row < p.t[ti].M ? row : p.t[ti].M - 1;
+            src[i] = p.t[ti].w + (size_t)row * p.rowbytes + (size_t)kb_begin * 64 + cc * 16;
+        }
+    };
+    auto pf_issue = [&]() {                                   // next stage of the prefetch stream, if any
+        if (pf_rb < p.total_rb) {
+            const bool valid = (kb_begin + pf_it * KBS) * 64 + cc * 16 < p.rowbytes && pf_it * KBS + (cc >> 2) < nk;
+            const uint32_t d = ring_u32 + pf_slot * STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < NCP; i++) cp_async16(d + i * 8 * LIN_LD, valid ? src[i] + pf_it * LIN_SK : src[i], valid);
+            pf_slot = pf_slot + 1 == STAGES ? 0 : pf_slot + 1;
+            if (++pf_it == nst) { pf_it = 0; pf_rb += rb_step; if (pf_rb < p.total_rb) pf_setup(); }
+        }
+        cp_async_commit();
+    };
+    if (pf_rb < p.total_rb) pf_setup();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) pf_issue();          // weights first: they do not depend on x
+
+    pdl_wait();
+
+    // ── this slice's limbs, scale-back factors and limb sums ──
+    {
+        const uint4* gsrc = reinterpret_cast<const uint4*>(p.xpack + (size_t)ks * p.ncols * p.xs_ld);
+        const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(xs);
+        const int nchunk = p.ncols * p.xs_ld / 16;
+        for (int c = threadIdx.x; c < nchunk; c += W * 32) cp_async16(d0 + c * 16, gsrc + c, true);
+        cp_async_commit();
+        if (threadIdx.x < p.B) s_back[threadIdx.x] = p.xscale[threadIdx.x * p.nks + ks];
+        if (threadIdx.x < p.B * LIN_LIMBS)
+            s_xsum[threadIdx.x] = p.xsum[((size_t)(threadIdx.x / LIN_LIMBS) * p.nks + ks) * LIN_LIMBS + (threadIdx.x % LIN_LIMBS)];
     }
-    const __half* xcol[NCG];
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int8_t* xcol[NCG];
 #pragma unroll
     for (int c = 0; c < NCG; c++) {
         int col = c * 8 + g;
         col = col < p.ncols ? col : 0;                        // spare MMA columns reread column 0
-        xcol[c] = p.xpack + (size_t)col * p.xld + (XK / 4) * t;
+        xcol[c] = xs + (size_t)col * p.xs_ld + (XB / 4) * t;
     }
-    float acc[RT][NCG][4];
-#pragma unroll
-    for (int i = 0; i < RT; i++)
-#pragma unroll
-        for (int c = 0; c < NCG; c++) { acc[i][c][0] = acc[i][c][1] = acc[i][c][2] = acc[i][c][3] = 0.0f; }
 
-    const int S = ks * W;
-    const uint32_t fill = BITS == 8 ? 0u : 0x88888888u;      // encodes weight 0
-    bool waited = false;
-    for (int kb0 = crank * W + warp; kb0 < p.nkb; kb0 += S * U) {
-        uint4 wreg[U][RT * 2];
+    int slot = 0;
+    for (int rb = rb_first; rb < p.total_rb; rb += rb_step) {
+        int acc[NACC][RT][NCG][4];
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int kb = kb0 + u * S;
-            const bool in = kb < p.nkb && kb * 64 + 16 * t < p.rowbytes;
+        for (int a = 0; a < NACC; a++)
 #pragma unroll
-            for (int j = 0; j < RT * 2; j++)
-                wreg[u][j] = in ? ld_stream_u4(rowp[j] + (size_t)kb * 64) : make_uint4(fill, fill, fill, fill);
-        }
-        if (!waited) { pdl_wait(); waited = true; }          // weights are in flight; now x may be read
+            for (int i = 0; i < RT; i++)
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int kb = kb0 + u * S;
-            if (kb >= p.nkb) break;
-            if (BITS == 8) {
+                for (int c = 0; c < NCG; c++) { acc[a][i][c][0] = acc[a][i][c][1] = acc[a][i][c][2] = acc[a][i][c][3] = 0; }
+
+        for (int it = 0; it < nst; it++) {
+            cp_async_wait<STAGES - 2>();
+            __syncthreads();                                  // this stage has landed for everyone; the previous one is free
+            pf_issue();
+            const int k = it * KBS + warp;                    // this warp's k-block within the slice
+            if (k < nk) {
+                const unsigned char* sw = ring + slot * STAGE_BYTES + warp * 64 + 16 * t;
+                uint4 cur[RT * 2];
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
+                for (int j = 0; j < RT * 2; j++)
+                    cur[j] = *reinterpret_cast<const uint4*>(sw + ((j >> 1) * 16 + (j & 1) * 8 + g) * LIN_LD);
+                if (BITS == 8) {
                     uint4 xf[NCG];
 #pragma unroll
-                    for (int c = 0; c < NCG; c++) xf[c] = *reinterpret_cast<const uint4*>(xcol[c] + (size_t)kb * XK + 8 * h);
-#pragma unroll
-                    for (int s = 0; s < 2; s++) {
-                        uint32_t lo[RT * 2], hi[RT * 2];
-#pragma unroll
-                        for (int j = 0; j < RT * 2; j++) unpack_int8x4(u4_get(wreg[u][j], 2 * h + s), lo[j], hi[j]);
-#pragma unroll
-                        for (int i = 0; i < RT; i++)
-#pragma unroll
-                            for (int c = 0; c < NCG; c++)
-                                mma16816(acc[i][c], lo[2 * i], lo[2 * i + 1], hi[2 * i], hi[2 * i + 1],
-                                         s ? xf[c].z : xf[c].x, s ? xf[c].w : xf[c].y);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int wd = 0; wd < 4; wd++) {
-                    uint4 xf[NCG];
-#pragma unroll
-                    for (int c = 0; c < NCG; c++) xf[c] = *reinterpret_cast<const uint4*>(xcol[c] + (size_t)kb * XK + 8 * wd);
-                    uint32_t qa[RT * 2], qb[RT * 2], qc[RT * 2], qd[RT * 2];
-#pragma unroll
-                    for (int j = 0; j < RT * 2; j++) unpack_int4x8(u4_get(wreg[u][j], wd), qa[j], qb[j], qc[j], qd[j]);
+                    for (int c = 0; c < NCG; c++) xf[c] = *reinterpret_cast<const uint4*>(xcol[c] + (size_t)k * XB);
 #pragma unroll
                     for (int i = 0; i < RT; i++)
 #pragma unroll
                         for (int c = 0; c < NCG; c++) {
-                            mma16816(acc[i][c], qa[2 * i], qa[2 * i + 1], qb[2 * i], qb[2 * i + 1], xf[c].x, xf[c].y);
-                            mma16816(acc[i][c], qc[2 * i], qc[2 * i + 1], qd[2 * i], qd[2 * i + 1], xf[c].z, xf[c].w);
+                            imma_s8(acc[0][i][c], cur[2 * i].x, cur[2 * i + 1].x, cur[2 * i].y, cur[2 * i + 1].y, xf[c].x, xf[c].y);
+                            imma_s8(acc[0][i][c], cur[2 * i].z, cur[2 * i + 1].z, cur[2 * i].w, cur[2 * i + 1].w, xf[c].z, xf[c].w);
                         }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {             // two raw words (16 columns... 8 each) per half
+                        uint4 xf[NCG];
+#pragma unroll
+                        for (int c = 0; c < NCG; c++) xf[c] = *reinterpret_cast<const uint4*>(xcol[c] + (size_t)k * XB + 16 * h);
+#pragma unroll
+                        for (int i = 0; i < RT; i++) {
+                            const uint32_t r0a = u4_get(cur[2 * i], 2 * h), r0b = u4_get(cur[2 * i], 2 * h + 1);
+                            const uint32_t r1a = u4_get(cur[2 * i + 1], 2 * h), r1b = u4_get(cur[2 * i + 1], 2 * h + 1);
+#pragma unroll
+                            for (int c = 0; c < NCG; c++) {
+                                // low nibbles of words a, b against columns c0,c2,c4,c6 of each word
+                                imma_u8(acc[0][i][c], r0a & 0x0F0F0F0Fu, r1a & 0x0F0F0F0Fu, r0b & 0x0F0F0F0Fu, r1b & 0x0F0F0F0Fu, xf[c].x, xf[c].z);
+                                // high nibbles (x16) against columns c1,c3,c5,c7
+                                imma_u8(acc[1][i][c], r0a & 0xF0F0F0F0u, r1a & 0xF0F0F0F0u, r0b & 0xF0F0F0F0u, r1b & 0xF0F0F0F0u, xf[c].y, xf[c].w);
+                            }
+                        }
+                    }
+                }
+            }
+            slot = slot + 1 == STAGES ? 0 : slot + 1;
+        }
+
+        // ── row block done: every warp holds integer partial sums of all R rows over its k-blocks ──
+#pragma unroll
+        for (int a = 0; a < NACC; a++) {
+            int* mine = red + ((size_t)a * W + warp) * R * COLS;
+#pragma unroll
+            for (int i = 0; i < RT; i++)
+#pragma unroll
+                for (int c = 0; c < NCG; c++) {
+                    *reinterpret_cast<int2*>(mine + (i * 16 + g) * COLS + c * 8 + 2 * t) = make_int2(acc[a][i][c][0], acc[a][i][c][1]);
+                    *reinterpret_cast<int2*>(mine + (i * 16 + g + 8) * COLS + c * 8 + 2 * t) = make_int2(acc[a][i][c][2], acc[a][i][c][3]);
+                }
+        }
+        __syncthreads();
+        int ti = 0;
+#pragma unroll
+        for (int i = 1; i < 4; i++) if (i < p.n_tensors && rb >= p.t[i].rb_start) ti = i;
+        const LinTensor& T = p.t[ti];
+        const int row0 = (rb - T.rb_start) * R;
+        const int B = p.B;
+        // one thread per (row, activation): limb sums over the warps, bias, recombination
+        for (int e = threadIdx.x; e < R * B; e += W * 32) {
+            const int r = e % R, b = e / R;
+            const int row = row0 + r;
+            int limb[LIN_LIMBS];
+#pragma unroll
+            for (int l = 0; l < LIN_LIMBS; l++) {
+                int v = 0;
+#pragma unroll
+                for (int w = 0; w < W; w++) v += red[((size_t)w * R + r) * COLS + b * LIN_LIMBS + l];
+                if (BITS == 4) {
+                    int hi = 0;
+#pragma unroll
+                    for (int w = 0; w < W; w++) hi += red[((size_t)(W + w) * R + r) * COLS + b * LIN_LIMBS + l];
+                    v += (hi >> 4) - 8 * s_xsum[b * LIN_LIMBS + l];
+                }
+                limb[l] = v;
+            }
+            if (p.nks == 1) {
+                if (row < T.M) {
+                    const long long V = (((long long)limb[3] * 256 + limb[2]) * 256 + limb[1]) * 256 + limb[0];
+                    const float y = (float)((double)V * (double)s_back[b]);
+                    const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
+                                                   : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
+                    float* o = T.out + (size_t)b * T.out_stride + row;
+                    *o = T.epilogue == IBCU_EPI_ADD ? *o + y * sc : y * sc;
+                }
+            } else {
+#pragma unroll
+                for (int l = 0; l < LIN_LIMBS; l++)
+                    p.partial[(((size_t)rb * p.nks + ks) * (B * LIN_LIMBS) + b * LIN_LIMBS + l) * R + r] = limb[l];
+            }
+        }
+        if (p.nks > 1) {
+            // the last slice to arrive recombines all slices (each with its own scale) in slice order
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned prev = atomicAdd(p.counters + rb, 1u);
+                s_last = prev == (unsigned)p.nks - 1;
+                if (s_last) p.counters[rb] = 0;               // ready for the next launch
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                for (int e = threadIdx.x; e < R * B; e += W * 32) {
+                    const int r = e % R, b = e / R;
+                    const int row = row0 + r;
+                    if (row >= T.M) continue;
+                    double y = 0.0;
+                    for (int k = 0; k < p.nks; k++) {
+                        const int* src_p = p.partial + (((size_t)rb * p.nks + k) * (B * LIN_LIMBS) + b * LIN_LIMBS) * R + r;
+                        const long long V = (((long long)__ldcg(src_p + 3 * R) * 256 + __ldcg(src_p + 2 * R)) * 256 + __ldcg(src_p + R)) * 256 + __ldcg(src_p);
+                        y += (double)V * (double)__ldcg(p.xscale + b * p.nks + k);
+                    }
+                    const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
+                                                   : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
+                    float* o = T.out + (size_t)b * T.out_stride + row;
+                    *o = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
                 }
             }
         }
     }
-    if (!waited) pdl_wait();
-
-    // per-warp partials -> shared memory
-    float* part = smem + (size_t)warp * ROWS * COLS;
-#pragma unroll
-    for (int i = 0; i < RT; i++)
-#pragma unroll
-        for (int c = 0; c < NCG; c++) {
-            *reinterpret_cast<float2*>(part + (i * 16 + g) * COLS + c * 8 + 2 * t) = make_float2(acc[i][c][0], acc[i][c][1]);
-            *reinterpret_cast<float2*>(part + (i * 16 + g + 8) * COLS + c * 8 + 2 * t) = make_float2(acc[i][c][2], acc[i][c][3]);
-        }
-    __syncthreads();
-    // sum over the warps in warp order; result lands in warp 0's slab
-    for (int e = threadIdx.x; e < ROWS * COLS; e += W * 32) {
-        float s = smem[e];
-#pragma unroll
-        for (int w = 1; w < W; w++) s += smem[(size_t)w * ROWS * COLS + e];
-        smem[e] = s;
-    }
-    if (ks > 1) cg::this_cluster().sync(); else __syncthreads();
-
-    if (crank == 0) {
-        const int B = p.B, P = p.P;
-        for (int e = threadIdx.x; e < ROWS * B; e += W * 32) {
-            const int b = e / ROWS, r = e - b * ROWS;
-            const int row = row0 + r;
-            if (row >= T.M) continue;
-            float y = 0.0f;
-            for (int k = 0; k < ks; k++) {
-                const float* src = k == 0 ? smem : cg::this_cluster().map_shared_rank(smem, k);
-                for (int q = 0; q < P; q++) y += src[r * COLS + b * P + q];
-            }
-            const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
-                                           : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
-            y = y * p.xscale[b] * sc;
-            float* o = T.out + (size_t)b * T.out_stride + row;
-            *o = T.epilogue == IBCU_EPI_ADD ? *o + y : y;
-        }
-    }
-    if (ks > 1) cg::this_cluster().sync();                    // keep remote shared memory alive until read
+    cp_async_wait<0>();
 }
 
 // ── portable path ───────────────────────────────────────────────────────────────────────
@@ -300,21 +434,27 @@ __global__ void __launch_bounds__(256) linear_generic_kernel(LinTensor T, const 
     }
 }
 
-template <int BITS, int NCG, int RT, int W, int U>
-int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int total_rg) {
-    auto kern = linear_mma_kernel<BITS, NCG, RT, W, U>;
-    size_t smem = (size_t)W * RT * 16 * NCG * 8 * sizeof(float);
+template <int BITS, int NCG, int RT, int W, int STAGES>
+int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail) {
+    auto kern = linear_mma_kernel<BITS, NCG, RT, W, STAGES>;
+    const size_t smem = (size_t)STAGES * RT * 16 * LIN_LD + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * NCG * 8 * 4 + smem_tail;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
     }
-    return ibcu_launch(ctx, kern, dim3(total_rg * p.ks), dim3(W * 32), smem, p.ks, true, p);
+    return ibcu_launch(ctx, kern, dim3(grid), dim3(W * 32), smem, 1, true, p);
 }
 
+constexpr int LIN_W = 8;
+
 template <int BITS, int NCG>
-int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int total_rg, int rt) {
-    if (rt == 2) return launch_mma<BITS, NCG, 2, 8, 2>(ctx, p, total_rg);
-    return launch_mma<BITS, NCG, 1, 8, 2>(ctx, p, total_rg);
+int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int stages, size_t smem_tail) {
+    if (rt == 2) {
+        if (stages >= 6) return launch_mma<BITS, NCG, 2, LIN_W, 6>(ctx, p, grid, smem_tail);
+        return launch_mma<BITS, NCG, 2, LIN_W, 4>(ctx, p, grid, smem_tail);
+    }
+    if (stages >= 8) return launch_mma<BITS, NCG, 1, LIN_W, 8>(ctx, p, grid, smem_tail);
+    return launch_mma<BITS, NCG, 1, LIN_W, 4>(ctx, p, grid, smem_tail);
 }
 
 }  // namespace
@@ -340,7 +480,7 @@ extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_te
         IBCU_REQUIRE(ctx, tensors[i].M >= 0 && tensors[i].out_stride >= tensors[i].M, "ibcu_linear: tensor %d M=%d stride=%d", i, tensors[i].M, tensors[i].out_stride);
     }
     const int rowbytes = bits == 8 ? N : N / 2;
-    bool fast = !ctx->force_generic && (rowbytes % 16 == 0);
+    bool fast = !ctx->force_generic && (rowbytes % 16 == 0) && ((uintptr_t)x & 15) == 0;
     for (int i = 0; i < n_tensors; i++) if (((uintptr_t)tensors[i].w & 15) != 0) fast = false;
 
     if (!fast) {
@@ -356,52 +496,99 @@ extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_te
         return IBCU_OK;
     }
 
-    // fast path: split activations, then stream the weights
-    const int P = B <= 2 ? 3 : 2;
-    const int ncols = B * P;
-    const int ncg = ncols <= 8 ? 1 : (ncols <= 16 ? 2 : (ncols <= 32 ? 4 : 8));
+    if (B > 16) {
+        // sixteen activations fill the eight column groups of one pass; more go in a second pass
+        ibcu_linear_t part[4];
+        for (int b0 = 0; b0 < B; b0 += 16) {
+            for (int i = 0; i < n_tensors; i++) { part[i] = tensors[i]; part[i].out = tensors[i].out + (size_t)b0 * tensors[i].out_stride; }
+            int rc2 = ibcu_linear(ctx, part, n_tensors, x + (size_t)b0 * N, N, B - b0 < 16 ? B - b0 : 16, bits);
+            if (rc2) return rc2;
+        }
+        return IBCU_OK;
+    }
+    const int ncols = B * LIN_LIMBS;
+    const int ncg = (ncols + 7) / 8 <= 1 ? 1 : ((ncols + 7) / 8 <= 2 ? 2 : ((ncols + 7) / 8 <= 4 ? 4 : 8));
     const int nkb = (rowbytes + 63) / 64;
     const int xk = bits == 8 ? 64 : 128;
-    const int xld = nkb * xk;
-    size_t xbytes = (size_t)ncols * xld * sizeof(__half);
-    xbytes = (xbytes + 255) & ~(size_t)255;
-    int rc = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, xbytes + 32 * sizeof(float));
-    if (rc) return rc;
-    __half* xpack = (__half*)ctx->xpack;
-    float* xscale = (float*)((char*)ctx->xpack + xbytes);
-    int threads = N >= 4096 ? 1024 : (N >= 1024 ? 512 : 128);
-    rc = ibcu_launch(ctx, xprep_kernel, dim3(B), dim3(threads), 0, 1, true, x, N, xld, P, bits == 4 ? 1 : 0, xpack, xscale);
-    if (rc) return rc;
-
+    const int xpad = bits == 8 ? 64 : 16;                     // keeps limb rows of neighbouring columns on different banks
     static const int rt_env = env_int("IBCU_LINEAR_RT", 0);
-    static const int ks_env = env_int("IBCU_LINEAR_KS", 0);
+    static const int nks_env = env_int("IBCU_LINEAR_NKS", 0);
+    static const int stages_env = env_int("IBCU_LINEAR_STAGES", 0);
     long total_rows = 0;
     for (int i = 0; i < n_tensors; i++) total_rows += tensors[i].M;
-    int rt = rt_env ? rt_env : ((ncg >= 8 || total_rows < 32L * ctx->sm_count) ? 1 : 2);
-    const int rows_per_rg = rt * 16;
+    // 32-row blocks when that still gives every SM a couple of blocks, else 16-row blocks
+    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows < 64L * ctx->sm_count) ? 1 : 2);
+    const int R = 16 * rt;
     LinearParams p;
     memset(&p, 0, sizeof p);
-    int total_rg = 0;
+    int total_rb = 0;
     for (int i = 0; i < n_tensors; i++) {
         p.t[i] = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
-                   tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, total_rg };
-        total_rg += (tensors[i].M + rows_per_rg - 1) / rows_per_rg;
+                   tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, total_rb };
+        total_rb += (tensors[i].M + R - 1) / R;
     }
-    if (total_rg == 0) return IBCU_OK;
-    p.n_tensors = n_tensors; p.rowbytes = rowbytes; p.nkb = nkb; p.B = B; p.P = P; p.ncols = ncols;
-    p.xpack = xpack; p.xld = xld; p.xscale = xscale;
-    // cluster split of K: enough CTAs to fill the machine a few times over, at least 2 k-blocks per warp
-    int ks = 1;
-    while (ks < 8 && total_rg * ks < 4 * ctx->sm_count && nkb / (ks * 2 * 8) >= 2) ks *= 2;
-    if (ks_env) ks = ks_env;
-    p.ks = ks;
+    if (total_rb == 0) return IBCU_OK;
+    // Shared memory per block: stage ring + reduction buffer + the slice's fp16 pieces. Columns are
+    // split over several blocks only when the pieces of a whole row do not fit.
+    const int kbs = LIN_SK / 64;
+    int stages = stages_env ? stages_env : (rt == 2 ? 4 : 8);
+    stages = rt == 2 ? (stages >= 6 ? 6 : 4) : (stages >= 8 ? 8 : 4);
+    const size_t fixed_smem = (size_t)stages * R * LIN_LD + (size_t)(bits == 4 ? 2 : 1) * LIN_W * R * ncg * 8 * 4 + 1024;
+    const size_t smem_cap = 200 * 1024;
+    long piece_budget = (long)smem_cap - (long)fixed_smem;
+    int max_slice_kb = (int)((piece_budget / ncols - xpad) / xk) / kbs * kbs;
+    if (max_slice_kb < kbs) max_slice_kb = kbs;
+    int nks = 1;
+    if (nks_env) nks = nks_env;
+    int slice_kb = ((nkb + nks - 1) / nks + kbs - 1) / kbs * kbs;      // whole stages per slice
+    if (slice_kb > max_slice_kb) slice_kb = max_slice_kb;
+    nks = (nkb + slice_kb - 1) / slice_kb;
+    const int xs_ld = slice_kb * xk + xpad;
+    const size_t piece_smem = (((size_t)ncols * xs_ld) + 15) & ~(size_t)15;
+    // persistent grid: as many blocks as fit on the machine at once, a multiple of nks, at most one per item
+    int fit = (int)((227 * 1024) / (fixed_smem + piece_smem + 1024));
+    if (fit < 1) fit = 1;
+    if (fit > 4) fit = 4;
+    const int slots = fit * ctx->sm_count;
+    int per_slice = slots / nks;
+    if (per_slice < 1) per_slice = 1;
+    if (per_slice > total_rb) per_slice = total_rb;
+    const int grid = per_slice * nks;
 
+    const size_t xpack_bytes = (((size_t)nks * ncols * xs_ld) + 255) & ~(size_t)255;
+    const size_t xscale_bytes = (((size_t)B * nks * sizeof(float)) + 255) & ~(size_t)255;
+    int rc = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, xpack_bytes + xscale_bytes + (size_t)B * nks * LIN_LIMBS * sizeof(int));
+    if (rc) return rc;
+    int8_t* xpack = (int8_t*)ctx->xpack;
+    float* xscale = (float*)((char*)ctx->xpack + xpack_bytes);
+    int* xsum = (int*)((char*)ctx->xpack + xpack_bytes + xscale_bytes);
+    p.n_tensors = n_tensors; p.total_rb = total_rb; p.rowbytes = rowbytes; p.nkb = nkb; p.N = N; p.B = B; p.ncols = ncols;
+    p.slice_kb = slice_kb; p.nks = nks; p.xs_ld = xs_ld;
+    p.xpack = xpack; p.xscale = xscale; p.xsum = xsum;
+    if (nks > 1) {
+        const size_t part_bytes = (size_t)total_rb * nks * R * B * LIN_LIMBS * sizeof(int);
+        const size_t cnt_bytes = (size_t)total_rb * sizeof(unsigned);
+        rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, part_bytes);
+        if (rc) return rc;
+        if (cnt_bytes > ctx->counters_bytes) {
+            // kernels leave their counters at zero, so clearing is needed only when the array grows
+            rc = ibcu_reserve(ctx, &ctx->counters, &ctx->counters_bytes, cnt_bytes < 4096 ? 4096 : cnt_bytes);
+            if (rc) return rc;
+            IBCU_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, ctx->counters_bytes, ctx->stream));
+        }
+        p.counters = (unsigned*)ctx->counters;
+        p.partial = (int*)ctx->scratch;
+    }
+    rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(256), 0, 1, true, x, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
+                     xpack, xscale, xsum);
+    if (rc) return rc;
+    const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
     switch (ncg) { \
-        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, total_rg, rt); break; \
-        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, total_rg, rt); break; \
-        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, total_rg, rt); break; \
-        default: rc = dispatch_shape<BITS, 8>(ctx, p, total_rg, rt); break; \
+        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, grid, rt, stages, smem); break; \
+        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, grid, rt, stages, smem); break; \
+        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, grid, rt, stages, smem); break; \
+        default: rc = dispatch_shape<BITS, 8>(ctx, p, grid, rt, stages, smem); break; \
     }
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH

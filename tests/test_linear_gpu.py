@@ -93,8 +93,9 @@ def test_scales_fp32_and_residual_epilogue(backend, cpu_libs, bits):
 
 
 def test_wide_dynamic_range_activations(backend, cpu_libs):
-    """Activations spanning many orders of magnitude, huge and tiny vectors: the power-of-two
-    pre-scaling keeps the fp16 pieces exact enough."""
+    """Activations spanning six orders of magnitude inside one vector, and huge and tiny vectors: the
+    per-slice power-of-two scaling keeps the fixed-point limbs exact enough. The absolute term of the
+    bar is scaled by the largest activation, which is what sets the reference's own rounding noise."""
     rng = np.random.default_rng(9)
     M, N = 128, 1024
     w, s16, _ = _cpu.make_int8_case(rng, M, N, 1)
@@ -102,7 +103,7 @@ def test_wide_dynamic_range_activations(backend, cpu_libs):
         x = (rng.standard_normal((2, N)) * scale * 10.0 ** rng.integers(-3, 3, (2, N))).astype(np.float32)
         got = backend.linear(w, s16, x, 8)
         want = oracle_linear(cpu_libs, w, s16, x, 8)
-        assert _cpu.close(got, want, RTOL, ATOL * scale), scale
+        assert _cpu.close(got, want, RTOL, ATOL * float(np.abs(x).max())), scale
     x = np.zeros((1, N), np.float32)
     assert np.array_equal(backend.linear(w, s16, x, 8), np.zeros((1, M), np.float32))
 
