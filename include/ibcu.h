@@ -166,8 +166,11 @@ int ibcu_embed_int8(ibcu_ctx* ctx, const int8_t* embed, const uint16_t* scale, c
                     float* x, int hidden, int B);
 /* out = x * rsqrt(mean(x^2) + eps) * fp16(w), per row of B (src/forward.c:322-327). */
 int ibcu_rmsnorm_fp16w(ibcu_ctx* ctx, float* out, const float* x, const uint16_t* w, float eps, int N, int B);
+/* Same with FP32 weights, the form ib_kernels.rmsnorm receives (src/kernels/scalar.c:126-138). */
+int ibcu_rmsnorm_f32w(ibcu_ctx* ctx, float* out, const float* x, const float* w, float eps, int N, int B);
 /* RoPE on adjacent pairs for every Q head and every K head of B positions pos0+b, then the FP32
- * KV-cache write at those positions (src/forward.c:577-593, src/kernels/scalar.c:140-157). */
+ * KV-cache write at those positions (src/forward.c:577-593, src/kernels/scalar.c:140-157).
+ * k_cache / v_cache / v may be NULL: rotation only (the plain ib_kernels.rope call). */
 int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache,
                        int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta);
 /* GQA attention of B query positions against cache rows 0..pos0+b (src/forward.c:463-504). */

@@ -73,6 +73,7 @@ IBCU_SYMBOLS = {
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_embed_int8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "ibcu_rmsnorm_fp16w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
+    "ibcu_rmsnorm_f32w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
     "ibcu_rope_kv_write": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
     "ibcu_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -107,3 +108,101 @@ def load_ibcu():
             fn.argtypes = args
         _libibcu = lib
     return _libibcu
+
+
+class ModelCfg(C.Structure):
+    """ib_b200_model_cfg"""
+    _fields_ = [(n, C.c_int) for n in ("hidden", "inter", "n_layers", "n_heads", "n_kv_heads", "head_dim", "vocab", "max_ctx")] + [
+        ("eps", C.c_float), ("theta", C.c_float), ("attn_bits", C.c_int), ("mlp_bits", C.c_int), ("head_bits", C.c_int)]
+
+
+class HostPqTensor(C.Structure):
+    """ib_b200_pq_tensor == ib_pq_tensor (src/pq_decode.h:39-87)"""
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K", C.c_int), ("K_l2", C.c_int),
+                ("n_levels", C.c_int), ("rotate", C.c_int), ("n_outlier", C.c_int), ("format", C.c_int),
+                ("codebook_l1_l", C.c_void_p), ("codebook_l1_r", C.c_void_p),
+                ("codebook_l2_l", C.c_void_p), ("codebook_l2_r", C.c_void_p),
+                ("indices_l1_l", C.c_void_p), ("indices_l1_r", C.c_void_p),
+                ("indices_l2_l", C.c_void_p), ("indices_l2_r", C.c_void_p),
+                ("C", C.c_int), ("l2_idx_bytes", C.c_int), ("l2_packed_bits", C.c_int),
+                ("row_scale", C.c_void_p), ("outlier_cols", C.c_void_p), ("outlier_sidecar", C.c_void_p),
+                ("outlier_scale", C.c_void_p), ("_arena", C.c_void_p), ("_arena_size", C.c_size_t),
+                ("_mmap_base", C.c_void_p), ("_mmap_size", C.c_size_t), ("_owns_mmap", C.c_int)]
+
+
+_MM = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int)
+
+
+class HostKernels(C.Structure):
+    """ib_b200_kernels == ib_kernels (src/inferbit_internal.h:199-277)"""
+    _fields_ = [
+        ("matmul_int4", _MM), ("matmul_int8", _MM), ("matmul_int2", _MM),
+        ("rmsnorm", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int)),
+        ("rope", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float)),
+        ("softmax", C.CFUNCTYPE(None, C.c_void_p, C.c_int)),
+        ("silu_mul", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int)),
+        ("matmul_w4a8", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int)),
+        ("matmul_w4a8_batch", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int)),
+        ("matmul_int8_batch", C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int)),
+    ]
+
+
+_vp, _i, _f = C.c_void_p, C.c_int, C.c_float
+HOST_SYMBOLS = {
+    "ib_b200_init": (_i, [_i]),
+    "ib_b200_shutdown": (None, []),
+    "ib_b200_ctx": (_vp, []),
+    "ib_b200_status": (_i, []),
+    "ib_b200_last_error": (C.c_char_p, []),
+    "ib_b200_register": (_i, [_vp, C.c_size_t]),
+    "ib_b200_unregister": (_i, [_vp]),
+    "ib_b200_install_kernels": (None, [_vp]),
+    "ib_b200_matmul_int4": (None, [_vp, _vp, _vp, _vp, _i, _i]),
+    "ib_b200_matmul_int8": (None, [_vp, _vp, _vp, _vp, _i, _i]),
+    "ib_b200_matmul_int8_batch": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "ib_b200_matmul_w4a8": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "ib_b200_matmul_w4a8_batch": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "ib_b200_rmsnorm": (None, [_vp, _vp, _vp, _f, _i]),
+    "ib_b200_rope": (None, [_vp, _vp, _i, _i, _f]),
+    "ib_b200_softmax": (None, [_vp, _i]),
+    "ib_b200_silu_mul": (None, [_vp, _vp, _vp, _i]),
+    "ib_b200_quantize_input_int8_g128": (_i, [_vp, _vp, _vp, _i]),
+    "ib_b200_pq_matmul_fp32": (_i, [C.POINTER(HostPqTensor), _vp, _vp]),
+    "ib_b200_pq_matmul_fp32_threaded": (_i, [C.POINTER(HostPqTensor), _vp, _vp, _vp]),
+    "ib_b200_pq_matmul_fp32_streaming": (_i, [C.POINTER(HostPqTensor), _vp, _vp]),
+    "ib_b200_pq_matmul_fp32_batch": (_i, [C.POINTER(HostPqTensor), _vp, _vp, _i]),
+    "ib_b200_pq_release": (None, [C.POINTER(HostPqTensor)]),
+    "ib_b200_kmeans_assign": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
+    "ib_b200_kmeans_lloyd": (_i, [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
+    "ib_b200_model_create": (_vp, [_vp, C.POINTER(ModelCfg)]),
+    "ib_b200_model_free": (None, [_vp]),
+    "ib_b200_model_fill_random": (_i, [_vp, C.c_uint64, _i]),
+    "ib_b200_model_set_linear": (_i, [_vp, _i, _i, _vp, _vp]),
+    "ib_b200_model_set_norms": (_i, [_vp, _i, _vp, _vp]),
+    "ib_b200_model_set_embedding": (_i, [_vp, _vp, _vp, _vp]),
+    "ib_b200_model_set_kv": (_i, [_vp, _i, _vp, _vp, _i]),
+    "ib_b200_model_get_kv": (_i, [_vp, _i, _vp, _vp, _i]),
+    "ib_b200_forward_step": (_i, [_vp, _vp, _i, _i, _vp]),
+    "ib_b200_forward_step_device": (_i, [_vp, _i, _i]),
+    "ib_b200_model_tokens": (_vp, [_vp]),
+    "ib_b200_model_logits": (_vp, [_vp]),
+    "ib_b200_model_weight_bytes": (C.c_size_t, [_vp]),
+}
+
+_libhost = None
+
+
+def load_host():
+    """Load libib_b200.so (and libibcu.so before it). Raises OSError if it has not been built."""
+    global _libhost
+    if _libhost is None:
+        load_ibcu()
+        if not os.path.exists(LIBHOST_PATH):
+            raise OSError(f"{LIBHOST_PATH} not found: build it with `make -C libinferbit_b200`")
+        lib = C.CDLL(LIBHOST_PATH, mode=C.RTLD_GLOBAL)
+        for name, (res, args) in HOST_SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _libhost = lib
+    return _libhost

@@ -42,8 +42,9 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return t;
 }
 
-__global__ void __launch_bounds__(1024) rmsnorm_fp16w_kernel(float* __restrict__ out, const float* __restrict__ x,
-                                                             const __half* __restrict__ w, float eps, int N) {
+template <typename WT>
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                                       const WT* __restrict__ w, float eps, int N) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_fp16w_kernel(float* __restrict__
     for (int i = threadIdx.x; i < N; i += blockDim.x) ss = fmaf(xb[i], xb[i], ss);
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)N + eps);
-    for (int i = threadIdx.x; i < N; i += blockDim.x) ob[i] = xb[i] * r * __half2float(w[i]);
+    for (int i = threadIdx.x; i < N; i += blockDim.x) ob[i] = xb[i] * r * (float)w[i];
 }
 
 // One block per position b. Rotates every Q head and every K head (each K head once, as the
@@ -78,12 +79,12 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(float* __restrict__ 
         const float a0 = p[0], a1 = p[1];
         const float r0 = a0 * c - a1 * s, r1 = a0 * s + a1 * c;
         p[0] = r0; p[1] = r1;
-        if (h >= n_heads) {
+        if (h >= n_heads && k_cache) {
             float* dst = k_cache + (size_t)pos * kv_dim + (size_t)(h - n_heads) * hd + 2 * m;
             dst[0] = r0; dst[1] = r1;
         }
     }
-    for (int e = threadIdx.x; e < kv_dim; e += blockDim.x) v_cache[(size_t)pos * kv_dim + e] = vb[e];
+    if (v_cache && v) for (int e = threadIdx.x; e < kv_dim; e += blockDim.x) v_cache[(size_t)pos * kv_dim + e] = vb[e];
 }
 
 // One block per (query head, position b). Scores against cache rows 0..pos, max-subtracted softmax,
@@ -183,13 +184,20 @@ extern "C" int ibcu_rmsnorm_fp16w(ibcu_ctx* ctx, float* out, const float* x, con
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, out && x && w && N > 0 && B > 0, "ibcu_rmsnorm_fp16w: bad arguments");
     int threads = N >= 4096 ? 1024 : (N >= 1024 ? 512 : 128);
-    return ibcu_launch(ctx, rmsnorm_fp16w_kernel, dim3(B), dim3(threads), 0, 1, true, out, x, (const __half*)w, eps, N);
+    return ibcu_launch(ctx, rmsnorm_kernel<__half>, dim3(B), dim3(threads), 0, 1, true, out, x, (const __half*)w, eps, N);
+}
+
+extern "C" int ibcu_rmsnorm_f32w(ibcu_ctx* ctx, float* out, const float* x, const float* w, float eps, int N, int B) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, out && x && w && N > 0 && B > 0, "ibcu_rmsnorm_f32w: bad arguments");
+    int threads = N >= 4096 ? 1024 : (N >= 1024 ? 512 : 128);
+    return ibcu_launch(ctx, rmsnorm_kernel<float>, dim3(B), dim3(threads), 0, 1, true, out, x, w, eps, N);
 }
 
 extern "C" int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache,
                                   int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta) {
     IBCU_CHECK_CTX(ctx);
-    IBCU_REQUIRE(ctx, q && k && v && k_cache && v_cache, "ibcu_rope_kv_write: null pointer");
+    IBCU_REQUIRE(ctx, q && k, "ibcu_rope_kv_write: null pointer");
     IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && (head_dim & 1) == 0 && pos0 >= 0 && B > 0,
                  "ibcu_rope_kv_write: bad shape heads=%d kv=%d hd=%d pos0=%d B=%d", n_heads, n_kv_heads, head_dim, pos0, B);
     return ibcu_launch(ctx, rope_kv_write_kernel, dim3(B), dim3(256), 0, 1, true, q, k, v, k_cache, v_cache,

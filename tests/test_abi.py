@@ -23,6 +23,29 @@ def test_libibcu_exports_every_declared_symbol():
     assert sorted(_ffi.IBCU_SYMBOLS) == names          # the Python prototypes cover the header exactly
 
 
+def test_libib_b200_exports_every_declared_symbol():
+    lib = _ffi.load_host()
+    names = [n for n in declared("ib_b200.h") if n.startswith("ib_b200_")]
+    assert len(names) > 30
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(_ffi.HOST_SYMBOLS) == names
+
+
+def test_host_layer_without_gpu_reports_errors():
+    import numpy as np
+    lib = _ffi.load_host()
+    if _ffi.load_ibcu().ibcu_device_count() > 0:
+        return
+    assert lib.ib_b200_init(0) != 0
+    assert b"no usable" in lib.ib_b200_last_error()
+    out = np.full(4, 7.0, np.float32); w = np.zeros(64, np.int8); s = np.ones(4, np.float32); x = np.ones(16, np.float32)
+    lib.ib_b200_matmul_int8(out.ctypes.data, w.ctypes.data, s.ctypes.data, x.ctypes.data, 4, 16)
+    assert lib.ib_b200_status() != 0 and np.all(out == 7.0)          # error recorded, output untouched
+    assert b"before ib_b200_init" in lib.ib_b200_last_error()
+    assert lib.ib_b200_status() == 0                                  # read-once
+
+
 def test_no_gpu_means_an_error_not_a_fallback():
     lib = _ffi.load_ibcu()
     if lib.ibcu_device_count() > 0:
