@@ -1,0 +1,265 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight product hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload ("int8_attn_proj_b1"): the INT8 attention projections of a Mistral-7B layer,
+q and o 4096x4096, k and v 1024x4096, per-row FP16 scales, one FP32 activation (batch 1). One step =
+one pass over one layer's four projections (q, k, v in one launch sharing the activation, then o);
+consecutive steps walk a ring of distinct weight sets larger than L2, so every byte comes from HBM.
+metric = weight GB/s = algorithmic bytes of a step / device time of a step.
+With N > 1 the output rows of every projection are split over the ranks and all-gathered with NCCL
+(total work fixed: strong scaling).
+
+The JSON line also carries, under "other", quick measurements of the other configurations (INT4,
+PQ, k-means, 7B-shape decode step); they are context, not the headline.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HID, KV = 4096, 1024
+PROJ = [("q", HID, HID), ("k", KV, HID), ("v", KV, HID), ("o", HID, HID)]
+RING = 16                                # weight sets in the ring: 16 x 42 MB = 671 MB >> 126 MB of L2
+
+
+def algo_bytes_int8(M, N, B):
+    """weights + fp16 scales + FP32 activations in + FP32 outputs"""
+    return M * N + 2 * M + 4 * B * N + 4 * B * M
+
+
+STEP_BYTES = sum(algo_bytes_int8(M, N, 1) for _, M, N in PROJ)
+
+
+# ── clocks ──────────────────────────────────────────────────────────────────────────────
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.stop, self.th = index, [], False, None
+
+    def _run(self):
+        while not self.stop:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def __enter__(self):
+        self.th = threading.Thread(target=self._run, daemon=True)
+        self.th.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop = True
+        self.th.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows if len(r) >= 6)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+# ── CPU baseline: the reference's own kernels when its library was built, else this repo's port ──
+class CpuBaseline:
+    def __init__(self):
+        ref = os.path.join(ROOT, "oracle", "_ref", "libinferbit_ref.so")
+        self.threads = os.cpu_count() or 1
+        if os.path.exists(ref):
+            self.kind, self.lib = "reference", C.CDLL(ref)
+            self.lib.ib_detect_simd.restype = C.c_int
+            self.lib.ib_init_kernels(self.lib.ib_detect_simd())          # AVX2 table on x86-64
+            self.lib.ib_pool_create.restype = C.c_void_p
+            self.lib.ib_pool_create.argtypes = [C.c_int]
+            self.pool = self.lib.ib_pool_create(self.threads)
+            self.lib.ib_parallel_matmul.argtypes = [C.c_void_p] * 5 + [C.c_int] * 3
+        else:
+            port = os.path.join(ROOT, "oracle", "libib_oracle.so")
+            if not os.path.exists(port):
+                subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "oracle"], check=True)
+            self.kind, self.lib, self.threads = "port", C.CDLL(port), 1
+
+    def matvec_int8(self, out, w, s32, x, M, N):
+        if self.kind == "reference":
+            self.lib.ib_parallel_matmul(self.pool, out.ctypes.data, w.ctypes.data, s32.ctypes.data, x.ctypes.data, M, N, 8)
+        else:
+            self.lib.ibo_matmul_int8(out.ctypes.data, w.ctypes.data, s32.ctypes.data, x.ctypes.data, M, N)
+
+    def time_steps(self, steps, warmup, seed=1234):
+        """One step = q, k, v, o of one layer on host memory; a ring of 4 sets (168 MB) keeps the weights out of cache."""
+        rng = np.random.default_rng(seed)
+        sets = []
+        for _ in range(4):
+            sets.append([(rng.integers(-127, 128, (M, N), dtype=np.int8), rng.uniform(0.001, 0.01, M).astype(np.float32),
+                          np.empty(M, np.float32), M, N) for _, M, N in PROJ])
+        x = rng.standard_normal(HID).astype(np.float32)
+        def step(i):
+            for w, s, o, M, N in sets[i % len(sets)]:
+                self.matvec_int8(o, w, s, x, M, N)
+        for i in range(warmup):
+            step(i)
+        t0 = time.perf_counter()
+        for i in range(steps):
+            step(i)
+        dt = (time.perf_counter() - t0) / steps
+        return dt, STEP_BYTES / dt / 1e9
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    cpu = CpuBaseline()
+    steps = max(1, min(args.steps, 200))
+    dt, gbs = cpu.time_steps(steps, max(3, min(args.warmup, 10)))
+    line = {"impl": "reference", "metric": "int8_matvec_weight_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": max(3, min(args.warmup, 10)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 weights x f32 activations, f32 accumulate",
+            "data": "synthetic", "config": {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind,
+                             "sample": f"{steps} steps of q,k,v,o over a ring of 4 host-resident weight sets"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ── GPU arm ─────────────────────────────────────────────────────────────────────────────
+def dist_setup(n):
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        return rank, world, local, dist
+    return rank, world, local, None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-other", action="store_true", help="skip the secondary configurations")
+    args = ap.parse_args()
+    rank, world, local, dist = dist_setup(args.gpus)
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    from libinferbit_b200 import _ffi, LinearT
+    from libinferbit_b200 import bench_support as bs
+    lib = _ffi.load_ibcu()
+    host = _ffi.load_host()
+    if lib.ibcu_device_count() < 1:
+        raise SystemExit("bench.py needs a B200: no CUDA device is visible and there is no CPU path")
+    assert host.ib_b200_init(local) == 0, host.ib_b200_last_error()
+    ctx = host.ib_b200_ctx()
+    if world > 1:
+        import torch
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (C.c_ubyte * 128)(); assert lib.ibcu_comm_get_id(raw) == 0
+            idbuf = torch.tensor(list(raw), dtype=torch.uint8)
+        dist.broadcast(idbuf, 0)
+        raw = (C.c_ubyte * 128)(*idbuf.tolist())
+        assert lib.ibcu_comm_init(ctx, raw, rank, world) == 0, lib.ibcu_last_error(ctx)
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    def barrier():
+        bs.check(lib, ctx, lib.ibcu_sync(ctx))
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    wl = bs.AttnProjWorkload(lib, ctx, rank, world, RING, PROJ, B=1)
+    # device-resident timing: graphs of 100 steps each, replayed
+    per_graph = 100 if K >= 100 else K
+    n_replay = (K + per_graph - 1) // per_graph
+    K = per_graph * n_replay
+    gid = wl.capture(per_graph)
+    launches_per_graph = wl.graph_launches               # kernels of this library recorded into the graph
+    for _ in range((W + per_graph - 1) // per_graph):
+        wl.replay(gid)
+    barrier()
+    with ClockSampler(local) as clk:
+        lib.ibcu_event_record(ctx, 0)
+        for _ in range(n_replay):
+            wl.replay(gid)
+        lib.ibcu_event_record(ctx, 1)
+        ms = C.c_float()
+        bs.check(lib, ctx, lib.ibcu_event_elapsed_ms(ctx, 0, 1, C.byref(ms)))
+        barrier()
+        # keep sampling long enough for a few readings on short runs
+        if ms.value < 400:
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                wl.replay(gid)
+            bs.check(lib, ctx, lib.ibcu_sync(ctx))
+    t_step = max_over_ranks(ms.value / K) * 1e-3
+    value = STEP_BYTES / t_step / 1e9
+    mma_launches_per_step = 2
+    # end to end through the reference-shaped table: host buffers, copies inside the timed region
+    e2e = wl.time_table_calls(host, min(K, 300), W)
+    e2e_t = max_over_ranks(e2e["t_step"])
+    peaks = bs.load_peaks(ROOT)
+    line = {
+        "metric": "int8_matvec_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 weights x int8 limbs of 32-bit fixed-point activations, s32 accumulate (exact); f32 in/out",
+        "data": "synthetic",
+        "config": {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1,
+                   "bytes_per_step": STEP_BYTES, "l2": f"ring of {RING} distinct weight sets ({RING * STEP_BYTES >> 20} MiB) > L2",
+                   "parallelism": f"rows/{world} + NCCL all-gather" if world > 1 else "1 GPU"},
+        "clocks": clk.summary(),
+        "gpu_launches": int(launches_per_graph * n_replay),
+        "e2e": {"value": STEP_BYTES / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "ms_per_step": e2e_t * 1e3, "api": "ib_kernels table: matmul_int8 x4 with host buffers"},
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / world / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "linear_mma_kernel<8,...>", "launches_per_step": mma_launches_per_step,
+                     "note": "achieved = algorithmic bytes of a step / device time of a step (xprep launches included)"},
+    }
+    if rank == 0 and world == 1:
+        cpu = CpuBaseline()
+        dt, gbs = cpu.time_steps(60, 5)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind,
+                                "sample": "60 steps of q,k,v,o over a ring of 4 host-resident weight sets"}
+    if not args.no_other:
+        line["other"] = bs.other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier)
+    wl.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    host.ib_b200_shutdown()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,300 @@
+"""Workload builders and timers shared by bench.py (device buffers through the C ABI, timing with
+CUDA events on the context's stream). Nothing here computes results on the host."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+
+from ._ffi import LinearT, ModelCfg, PqT
+
+
+def check(lib, ctx, rc):
+    if rc != 0:
+        msg = lib.ibcu_last_error(ctx).decode()
+        raise RuntimeError(f"ibcu error {rc}: {msg}")
+
+
+def load_peaks(root):
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 0)), "source": "of measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "of fallback (6.65 TB/s, 1.59 PFLOP/s)"}
+
+
+class Dev:
+    """Small helper around ibcu_malloc / copies."""
+
+    def __init__(self, lib, ctx):
+        self.lib, self.ctx, self.bufs = lib, ctx, []
+
+    def alloc(self, nbytes):
+        p = C.c_void_p()
+        check(self.lib, self.ctx, self.lib.ibcu_malloc(self.ctx, max(int(nbytes), 16), C.byref(p)))
+        self.bufs.append(p.value)
+        return p.value
+
+    def upload(self, arr):
+        arr = np.ascontiguousarray(arr)
+        d = self.alloc(arr.nbytes)
+        check(self.lib, self.ctx, self.lib.ibcu_memcpy_h2d(self.ctx, d, arr.ctypes.data, arr.nbytes))
+        check(self.lib, self.ctx, self.lib.ibcu_sync(self.ctx))
+        return d
+
+    def free_all(self):
+        for b in self.bufs:
+            self.lib.ibcu_free(self.ctx, b)
+        self.bufs = []
+
+    def timed(self, fn, reps=1):
+        """device milliseconds of fn() (issued `reps` times) between two events on the stream"""
+        self.lib.ibcu_event_record(self.ctx, 2)
+        for _ in range(reps):
+            fn()
+        self.lib.ibcu_event_record(self.ctx, 3)
+        ms = C.c_float()
+        check(self.lib, self.ctx, self.lib.ibcu_event_elapsed_ms(self.ctx, 2, 3, C.byref(ms)))
+        return ms.value / reps
+
+    def graph(self, fn):
+        """run fn once eagerly (sizes scratch), then capture it; returns the graph id"""
+        fn()
+        check(self.lib, self.ctx, self.lib.ibcu_sync(self.ctx))
+        check(self.lib, self.ctx, self.lib.ibcu_graph_begin(self.ctx))
+        fn()
+        gid = C.c_int()
+        check(self.lib, self.ctx, self.lib.ibcu_graph_end(self.ctx, C.byref(gid)))
+        return gid.value
+
+
+def shard(lib, M, world, rank, align=32):
+    r0, rn = C.c_int(), C.c_int()
+    lib.ibcu_shard_rows(M, world, rank, align, C.byref(r0), C.byref(rn))
+    return r0.value, rn.value
+
+
+class AttnProjWorkload:
+    """RING sets of (q, k, v, o) INT8 projections in HBM; with world > 1 each rank holds its row slices."""
+
+    def __init__(self, lib, ctx, rank, world, ring, proj, B=1, seed=1234):
+        self.lib, self.ctx, self.rank, self.world, self.ring, self.proj, self.B = lib, ctx, rank, world, ring, proj, B
+        self.dev = Dev(lib, ctx)
+        self.N = proj[0][2]
+        rng = np.random.default_rng(seed)
+        self.x = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
+        self.x2 = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
+        self.out = {name: self.dev.alloc(B * M * 4) for name, M, _ in proj}
+        self.sets = []
+        s = seed * 977 + rank
+        for r in range(ring):
+            ent = {}
+            for name, M, N in proj:
+                r0, rn = shard(lib, M, world, rank)
+                w = self.dev.alloc(rn * N)
+                sc = self.dev.alloc(rn * 2)
+                s += 1; check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, w, rn * N, s))
+                s += 1; check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, sc, rn, s, 0.001, 0.01))
+                ent[name] = (w, sc, M, r0, rn)
+            self.sets.append(ent)
+        check(lib, ctx, lib.ibcu_sync(ctx))
+
+    def _desc(self, ent, name):
+        w, sc, M, r0, rn = ent[name]
+        return LinearT(w, sc, self.out[name] + 4 * r0, rn, M, 0, 0)
+
+    def step(self, i):
+        lib, ctx, ent = self.lib, self.ctx, self.sets[i % self.ring]
+        qkv = (LinearT * 3)(self._desc(ent, "q"), self._desc(ent, "k"), self._desc(ent, "v"))
+        check(lib, ctx, lib.ibcu_linear(ctx, qkv, 3, self.x, self.N, self.B, 8))
+        if self.world > 1:
+            for name in ("q", "k", "v"):
+                check(lib, ctx, lib.ibcu_allgather_rows(ctx, self.out[name], ent[name][2], ent[name][2], self.B, 32))
+        o = self._desc(ent, "o")
+        check(lib, ctx, lib.ibcu_linear(ctx, C.byref(o), 1, self.x2, self.N, self.B, 8))
+        if self.world > 1:
+            check(lib, ctx, lib.ibcu_allgather_rows(ctx, self.out["o"], ent["o"][2], ent["o"][2], self.B, 32))
+
+    def capture(self, n):
+        self.step(0)
+        check(self.lib, self.ctx, self.lib.ibcu_sync(self.ctx))
+        before = self.lib.ibcu_launch_count(self.ctx)
+        check(self.lib, self.ctx, self.lib.ibcu_graph_begin(self.ctx))
+        for i in range(n):
+            self.step(i)
+        gid = C.c_int()
+        check(self.lib, self.ctx, self.lib.ibcu_graph_end(self.ctx, C.byref(gid)))
+        self.graph_launches = self.lib.ibcu_launch_count(self.ctx) - before
+        return gid.value
+
+    def replay(self, gid):
+        check(self.lib, self.ctx, self.lib.ibcu_graph_launch(self.ctx, gid))
+
+    def time_table_calls(self, host, steps, warmup, nsets=4, seed=99):
+        """End to end through the ib_kernels-shaped table: host weights registered once (the model
+        mapping), then per step four matmul_int8 calls with host activations, host FP32 scales and host
+        outputs; every call moves its operands host->device and its result device->host."""
+        import time
+        rng = np.random.default_rng(seed)
+        sets, blobs = [], []
+        for _ in range(nsets):
+            ent = []
+            for name, M, N in self.proj:
+                w = rng.integers(-127, 128, (M, N), dtype=np.int8)
+                assert host.ib_b200_register(w.ctypes.data, w.nbytes) == 0, host.ib_b200_last_error()
+                blobs.append(w)
+                ent.append((w, rng.uniform(0.001, 0.01, M).astype(np.float32), np.empty(M, np.float32), M, N))
+            sets.append(ent)
+        x = rng.standard_normal(self.N).astype(np.float32)
+        h2d = d2h = 0
+        calls = []
+        for ent in sets:
+            cs = []
+            for w, s, o, M, N in ent:
+                r0, rn = shard(self.lib, M, self.world, self.rank)
+                cs.append((o.ctypes.data + 4 * r0, w.ctypes.data + r0 * N, s.ctypes.data + 4 * r0, x.ctypes.data, rn, N))
+            calls.append(cs)
+        for o_, w_, s_, x_, rn, N in calls[0]:
+            h2d += 4 * N + 4 * rn; d2h += 4 * rn
+
+        def step(i):
+            for a in calls[i % nsets]:
+                host.ib_b200_matmul_int8(*a)
+        for i in range(warmup):
+            step(i)
+        t0 = time.perf_counter()
+        for i in range(steps):
+            step(i)
+        dt = (time.perf_counter() - t0) / steps
+        assert host.ib_b200_status() == 0, host.ib_b200_last_error()
+        for w in blobs:
+            host.ib_b200_unregister(w.ctypes.data)
+        return {"t_step": dt, "h2d": h2d, "d2h": d2h}
+
+    def close(self):
+        self.dev.free_all()
+
+
+# ── secondary configurations ────────────────────────────────────────────────────────────
+def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
+    """us per call and weight GB/s of one linear over a ring of distinct weight buffers (graph replay)."""
+    dev = Dev(lib, ctx)
+    rowbytes = N if bits == 8 else N // 2
+    wbytes = M * rowbytes
+    R = max(2, int(reps_target_bytes // wbytes))
+    dW = dev.alloc(R * wbytes); check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, dW, R * wbytes, 7))
+    dS = dev.alloc(M * 2); check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, dS, M, 8, 0.002, 0.02))
+    dx = dev.upload(np.random.default_rng(0).standard_normal((B, N)).astype(np.float32))
+    do = dev.alloc(B * M * 4)
+    descs = [LinearT(dW + r * wbytes, dS, do, M, M, 0, 0) for r in range(R)]
+
+    def run():
+        for d in descs:
+            check(lib, ctx, lib.ibcu_linear(ctx, C.byref(d), 1, dx, N, B, bits))
+    gid = dev.graph(run)
+    for _ in range(3):
+        lib.ibcu_graph_launch(ctx, gid)
+    ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid)) for _ in range(5)) / R
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    algo = wbytes + 2 * M + 4 * B * N + 4 * B * M
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6}
+
+
+def _pq(lib, ctx, M, N, G, K, B):
+    dev = Dev(lib, ctx)
+    rng = np.random.default_rng(3)
+    half, Cn = G // 2, N // G
+    R = 24                                                 # 24 x 7.3 MB of codes > L2
+    cb = [dev.upload((rng.standard_normal((K, half)) * 0.02).astype(np.float16)) for _ in range(2)]
+    rs = dev.upload(np.ones(M, np.float16))
+    x = dev.upload(rng.standard_normal((B, N)).astype(np.float32))
+    out = dev.alloc(B * M * 4)
+    ts = []
+    for r in range(R):
+        t = PqT()
+        t.M, t.N, t.G, t.K = M, N, G, K
+        t.codebook_l, t.codebook_r, t.row_scale, t.cb_chunk_stride = cb[0], cb[1], rs, 0
+        il = dev.alloc(M * Cn); ir = dev.alloc(M * Cn)
+        check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, il, M * Cn, 100 + 2 * r))
+        check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, ir, M * Cn, 101 + 2 * r))
+        t.idx_l, t.idx_r = il, ir
+        it = dev.alloc(lib.ibcu_pq_idx_t_bytes(M, N, G))
+        check(lib, ctx, lib.ibcu_pq_prepare(ctx, C.byref(t), it))
+        ts.append(t)
+
+    def run():
+        for t in ts:
+            check(lib, ctx, lib.ibcu_pq_matmul_fp32(ctx, C.byref(t), x, out, B))
+    gid = dev.graph(run)
+    for _ in range(3):
+        lib.ibcu_graph_launch(ctx, gid)
+    ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid)) for _ in range(5)) / R
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    algo = 2 * M * Cn + 2 * K * half * 2 + 2 * M + 4 * B * N + 4 * B * M
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6}
+
+
+def _kmeans(lib, ctx, rank, world, max_over_ranks, barrier, N_total=1 << 22, D=8, K=256, iters=10):
+    dev = Dev(lib, ctx)
+    n0 = N_total * rank // world; n1 = N_total * (rank + 1) // world
+    rng = np.random.default_rng(1234)
+    C0 = (rng.standard_normal((K, D)) * 0.02).astype(np.float32)        # stands for X[:K]; same on every rank
+    X = (np.random.default_rng(5000 + rank).standard_normal((n1 - n0, D)) * 0.02).astype(np.float32)
+    if rank == 0:
+        X[:K] = C0
+    dX = dev.upload(X); dC = dev.upload(C0)
+    n = n1 - n0
+    di, dd = dev.alloc(n * 4), dev.alloc(n * 4)
+    ds, dc, dn = dev.alloc(K * D * 4), dev.alloc(K * 4), dev.alloc(16)
+
+    def it():
+        check(lib, ctx, lib.ibcu_kmeans_lloyd_iter(ctx, dX, n, D, dC, K, di, dd, ds, dc, dn))
+    it(); barrier()
+    check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, dC, C0.ctypes.data, C0.nbytes))
+    barrier()
+    ms = dev.timed(lambda: [it() for _ in range(iters)])
+    ms = max_over_ranks(ms)
+    dev.free_all()
+    return {"ms_per_iter": ms / iters, "Mpoints_per_s": N_total / (ms / iters) / 1e3, "points": N_total, "K": K, "D": D, "iters": iters}
+
+
+def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20):
+    cfg = ModelCfg(4096, 14336, 32, 32, 8, 128, 32000, 1024, 1e-5, 10000.0, 8, 4, 8)
+    m = host.ib_b200_model_create(ctx, C.byref(cfg))
+    if not m:
+        return {"error": "model allocation failed"}
+    assert host.ib_b200_model_fill_random(m, 4321, 512) == 0
+    toks = np.arange(B, dtype=np.int32) * 7 + 11
+    check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, host.ib_b200_model_tokens(m), toks.ctypes.data, toks.nbytes))
+    for _ in range(3):
+        check(lib, ctx, host.ib_b200_forward_step_device(m, 512, B))
+    barrier()
+    dev = Dev(lib, ctx)
+    ms = dev.timed(lambda: check(lib, ctx, host.ib_b200_forward_step_device(m, 512, B)), reps=steps)
+    ms = max_over_ranks(ms)
+    logits = np.empty(8, np.float32)
+    check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, logits.ctypes.data, host.ib_b200_model_logits(m), 32))
+    check(lib, ctx, lib.ibcu_sync(ctx))
+    wb = host.ib_b200_model_weight_bytes(m)
+    host.ib_b200_model_free(m)
+    return {"ms_per_step": ms, "tok_per_s": B / ms * 1e3, "batch": B, "pos": 512, "weight_GBps_per_gpu": wb / ms / 1e6,
+            "logits_finite": bool(np.isfinite(logits).all())}
+
+
+def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier):
+    out = {}
+    if world == 1:
+        out["int4_tinyllama_up_5632x2048_b1"] = _linear_ring(lib, ctx, 4, 5632, 2048, 1)
+        out["int4_gate_14336x4096_b1"] = _linear_ring(lib, ctx, 4, 14336, 4096, 1)
+        out["int4_down_4096x14336_b1"] = _linear_ring(lib, ctx, 4, 4096, 14336, 1)
+        out["int8_q_4096x4096_b4"] = _linear_ring(lib, ctx, 8, 4096, 4096, 4)
+        out["int8_q_4096x4096_b16"] = _linear_ring(lib, ctx, 8, 4096, 4096, 16)
+        out["int8_head_32000x4096_b1"] = _linear_ring(lib, ctx, 8, 32000, 4096, 1)
+        out["pq_down_4096x14336_b1"] = _pq(lib, ctx, 4096, 14336, 16, 256, 1)
+        out["pq_down_4096x14336_b8"] = _pq(lib, ctx, 4096, 14336, 16, 256, 8)
+    out["kmeans_4Mx8_k256"] = _kmeans(lib, ctx, rank, world, max_over_ranks, barrier)
+    out["decode_7b_b1"] = _decode(lib, host, ctx, 1, max_over_ranks, barrier)
+    out["decode_7b_b8"] = _decode(lib, host, ctx, 8, max_over_ranks, barrier)
+    return out
