@@ -138,6 +138,21 @@ int    ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out);
 /* out[b*M + r] = row_scale[r] * sum_c (TL[c][idx_l[r,c]] + TR[c][idx_r[r,c]]) for B activations
  * x[b*N + j]; applies the reference's 1 %-of-max chunk skip rule per activation. */
 int    ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
+/* Same result as ibcu_pq_matmul_fp32 for callers that must not allocate device memory: serving
+ * loops that cannot take cudaMalloc's device-wide synchronisation, plugins living inside a fixed
+ * memory budget, processes whose allocator belongs to another runtime. This entry point has no
+ * counterpart in the reference (its matmul_impl mallocs its tables on every call,
+ * src/pq_decode.c:1519-1680). It calls no cudaMalloc / cudaFree or any allocating routine: the slab
+ * partial sums live in an array built into the library, ibcu_pq_noalloc_max_floats() floats (4 MiB)
+ * held by every GPU that loads the library from load to exit. A tensor that needs more (slabs x
+ * padded rows + 32 floats) is refused with IBCU_ERR_PARAM and a message giving both numbers.
+ * The first call on a device looks up the array's device address; make that call before any stream
+ * capture. All calls on a device share the one array and it keeps the previous call's contents
+ * (nothing in it needs clearing: every value read is written first by the same call), so two calls
+ * whose kernels may overlap on the GPU - different contexts or streams on the same device - race and
+ * must be serialised by the caller. */
+int    ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
+size_t ibcu_pq_noalloc_max_floats(void);
 
 /* ── k-means ─────────────────────────────────────────────────────────────────────────── */
 /* ib_kmeans_assign (src/pq_kmeans.h:70-74, src/pq_kmeans.c:399-413): idx[i] = nearest centroid of

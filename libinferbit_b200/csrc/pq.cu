@@ -219,3 +219,73 @@ extern "C" int ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const floa
     }
     return IBCU_OK;
 }
+
+// ── PQ matvec without any allocation ────────────────────────────────────────────────────
+// Some callers must not (or cannot) allocate device memory at call time: code that runs inside a
+// latency-critical serving loop where cudaMalloc's implicit device synchronisation is unacceptable,
+// plugins that are handed a fixed memory budget by their host application, and processes whose
+// allocator is owned by another runtime. For them the slab partial sums and the per-activation
+// maxima live in a fixed array that is part of the library image: every GPU that loads the library
+// holds PQ_STATIC_FLOATS floats (4 MiB) from load until exit, whether or not this entry point is used.
+constexpr size_t PQ_STATIC_FLOATS = (size_t)1 << 20;
+static __device__ __align__(256) float pq_static_scratch[PQ_STATIC_FLOATS];
+
+// In host code `pq_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use is looked up once per device, with that device current.
+static float* pq_static_address(ibcu_ctx* ctx) {
+    static float* per_device[64];
+    if (ctx->device < 0 || ctx->device >= 64) return nullptr;
+    if (!per_device[ctx->device]) {
+        if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, pq_static_scratch);
+        if (e != cudaSuccess) { ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaGetSymbolAddress(pq_static_scratch) failed: %s", cudaGetErrorString(e)); return nullptr; }
+        per_device[ctx->device] = p;
+    }
+    return per_device[ctx->device];
+}
+
+extern "C" size_t ibcu_pq_noalloc_max_floats(void) { return PQ_STATIC_FLOATS; }
+
+extern "C" int ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, t && x && out, "ibcu_pq_matmul_fp32_noalloc: null pointer");
+    IBCU_REQUIRE(ctx, t->codebook_l && t->codebook_r && t->row_scale, "ibcu_pq_matmul_fp32_noalloc: tensor has a null pointer");
+    IBCU_REQUIRE(ctx, t->idx_t && t->M_pad >= t->M, "ibcu_pq_matmul_fp32_noalloc: call ibcu_pq_prepare on the tensor first");
+    IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->G <= 32 && t->N % t->G == 0 && t->K >= 1 && t->K <= 256,
+                 "ibcu_pq_matmul_fp32_noalloc: bad shape M=%d N=%d G=%d K=%d", t->M, t->N, t->G, t->K);
+    IBCU_REQUIRE(ctx, B >= 1 && B <= 32, "ibcu_pq_matmul_fp32_noalloc: B=%d not in 1..32", B);
+    const int C = t->N / t->G, nsub = 2 * C;
+    const int row_blocks = (t->M_pad + PQ_ROWS_PER_BLOCK - 1) / PQ_ROWS_PER_BLOCK;
+    int S = (int)(((long)nsub * row_blocks + 2L * ctx->sm_count - 1) / (2L * ctx->sm_count));
+    if (S < 4) S = 4;
+    if (S > 32) S = 32;
+    S = (S + 3) & ~3;
+    const int nslabs = (nsub + S - 1) / S;
+    const size_t need = (size_t)nslabs * t->M_pad + 32;
+    if (need > PQ_STATIC_FLOATS)
+        return ibcu_fail(ctx, IBCU_ERR_PARAM, "ibcu_pq_matmul_fp32_noalloc: this tensor needs %zu floats of scratch (%d slabs x %d padded rows + 32), "
+                         "the built-in array holds %zu; use ibcu_pq_matmul_fp32", need, nslabs, t->M_pad, PQ_STATIC_FLOATS);
+    float* base = pq_static_address(ctx);
+    if (!base) return ctx->status ? ctx->status : ibcu_fail(ctx, IBCU_ERR_CUDA, "ibcu_pq_matmul_fp32_noalloc: no address for the built-in scratch on device %d", ctx->device);
+    // Nothing in the array has to start at zero: the maxima kernel writes amax[0..B) and the gather
+    // kernel writes every partial sum the reduce kernel reads, before it reads them.
+    float* amax = base;
+    float* partial = base + 32;
+    int threads = t->N >= 4096 ? 1024 : 256;
+    int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(threads), 0, 1, true, x, t->N, amax);
+    if (rc) return rc;
+    const size_t smem = ((size_t)S * t->K + 256) * sizeof(float);
+    for (int b = 0; b < B; b++) {
+        PqParams p;
+        p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = C; p.S = S;
+        p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
+        p.idx_t = t->idx_t; p.x = x + (size_t)b * t->N; p.amax = amax + b; p.partial = partial;
+        rc = ibcu_launch(ctx, pq_gather_kernel, dim3(nslabs, row_blocks), dim3(PQ_THREADS), smem, 1, true, p);
+        if (rc) return rc;
+        rc = ibcu_launch(ctx, pq_reduce_kernel, dim3((t->M + 255) / 256), dim3(256), 0, 1, true,
+                         (const float*)partial, nslabs, t->M, t->M_pad, (const __half*)t->row_scale, out + (size_t)b * t->M);
+        if (rc) return rc;
+    }
+    return IBCU_OK;
+}
