@@ -3,6 +3,48 @@
 // centroid sums / counts. Everything else is replicated.
 #include "common.cuh"
 #include <nccl.h>
+#include <dlfcn.h>
+
+// NCCL is bound at run time, on the first communicator call, not at link time: a process that also
+// loads PyTorch must end up with exactly one libnccl.so.2 (PyTorch ships its own, newer one), and
+// single-GPU users need no NCCL at all. dlopen by soname returns the copy already in the process.
+namespace {
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    const char* (*GetErrorString)(ncclResult_t);
+    ncclResult_t (*GroupStart)();
+    ncclResult_t (*GroupEnd)();
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    bool ok;
+};
+NcclApi g_nccl;
+bool nccl_load() {
+    if (g_nccl.ok) return true;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return false;
+#define IBCU_SYM(field, name) *(void**)&g_nccl.field = dlsym(h, name); if (!g_nccl.field) return false;
+    IBCU_SYM(GetUniqueId, "ncclGetUniqueId") IBCU_SYM(CommInitRank, "ncclCommInitRank") IBCU_SYM(CommDestroy, "ncclCommDestroy")
+    IBCU_SYM(GetErrorString, "ncclGetErrorString") IBCU_SYM(GroupStart, "ncclGroupStart") IBCU_SYM(GroupEnd, "ncclGroupEnd")
+    IBCU_SYM(AllGather, "ncclAllGather") IBCU_SYM(Broadcast, "ncclBroadcast") IBCU_SYM(AllReduce, "ncclAllReduce")
+#undef IBCU_SYM
+    g_nccl.ok = true;
+    return true;
+}
+}  // namespace
+#define ncclGetUniqueId g_nccl.GetUniqueId
+#define ncclCommInitRank g_nccl.CommInitRank
+#define ncclCommDestroy g_nccl.CommDestroy
+#define ncclGetErrorString g_nccl.GetErrorString
+#define ncclGroupStart g_nccl.GroupStart
+#define ncclGroupEnd g_nccl.GroupEnd
+#define ncclAllGather g_nccl.AllGather
+#define ncclBroadcast g_nccl.Broadcast
+#define ncclAllReduce g_nccl.AllReduce
 
 #define IBCU_NCCL(ctx, expr) do { ncclResult_t r_ = (expr); if (r_ != ncclSuccess) \
     return ibcu_fail((ctx), IBCU_ERR_COMM, "%s failed: %s", #expr, ncclGetErrorString(r_)); } while (0)
@@ -10,11 +52,12 @@
 static_assert(sizeof(ncclUniqueId) <= IBCU_COMM_ID_BYTES, "communicator id does not fit the ABI token");
 
 void ibcu_comm_destroy_internal(ibcu_ctx* ctx) {
-    if (ctx->comm) { ncclCommDestroy((ncclComm_t)ctx->comm); ctx->comm = nullptr; }
+    if (ctx->comm && g_nccl.ok) { ncclCommDestroy((ncclComm_t)ctx->comm); ctx->comm = nullptr; }
 }
 
 extern "C" int ibcu_comm_get_id(void* id_out) {
     if (!id_out) return IBCU_ERR_PARAM;
+    if (!nccl_load()) return IBCU_ERR_COMM;
     ncclUniqueId id;
     if (ncclGetUniqueId(&id) != ncclSuccess) return IBCU_ERR_COMM;
     memset(id_out, 0, IBCU_COMM_ID_BYTES);
@@ -28,6 +71,7 @@ extern "C" int ibcu_comm_init(ibcu_ctx* ctx, const void* id, int rank, int world
     if (ctx->comm) return ibcu_fail(ctx, IBCU_ERR_STATE, "communicator already initialised");
     ctx->rank = rank; ctx->world = world;
     if (world == 1) return IBCU_OK;
+    if (!nccl_load()) return ibcu_fail(ctx, IBCU_ERR_COMM, "libnccl.so.2 could not be loaded: %s", dlerror());
     ncclUniqueId uid;
     memcpy(&uid, id, sizeof uid);
     IBCU_CUDA(ctx, cudaSetDevice(ctx->device));
