@@ -216,12 +216,14 @@ def main():
         ms = C.c_float()
         bs.check(lib, ctx, lib.ibcu_event_elapsed_ms(ctx, 0, 1, C.byref(ms)))
         barrier()
-        # keep sampling long enough for a few readings on short runs
-        if ms.value < 400:
-            t_end = time.time() + 0.5
-            while time.time() < t_end:
-                wl.replay(gid)
-            bs.check(lib, ctx, lib.ibcu_sync(ctx))
+        # keep the GPU under the same load a little longer so that the clock sampler gets a few
+        # readings on short runs; the number of extra replays is agreed between the ranks (a time-based
+        # loop would issue different numbers of collectives per rank and deadlock)
+        t_graph = max_over_ranks(ms.value / n_replay)
+        extra = 0 if ms.value >= 400 else min(20000, int(500.0 / max(t_graph, 1e-3)))
+        for _ in range(extra):
+            wl.replay(gid)
+        barrier()
     t_step = max_over_ranks(ms.value / K) * 1e-3
     value = STEP_BYTES / t_step / 1e9
     mma_launches_per_step = 2

@@ -100,6 +100,20 @@ typedef struct {
  * N must be even for bits == 4. */
 int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
                 const float* x, int N, int B, int bits);
+/* Same with a transformation of the activation folded into the call (no separate launch, no
+ * intermediate vector): RMSNorm with fp16 weights ahead of the q/k/v and gate/up projections
+ * (src/forward.c:566-572,625-636), or silu(x)*x2 ahead of down_proj (src/forward.c:637-640). */
+#define IBCU_PRO_NONE      0
+#define IBCU_PRO_RMSNORM   1  /* x <- x * rsqrt(mean(x^2) + eps) * fp16(norm_w) */
+#define IBCU_PRO_SILU_MUL  2  /* x <- x / (1 + exp(-x)) * x2 */
+typedef struct {
+    int op;
+    const float*    x2;       /* device [B*N], IBCU_PRO_SILU_MUL */
+    const uint16_t* norm_w;   /* device fp16 [N], IBCU_PRO_RMSNORM */
+    float eps;
+} ibcu_prologue_t;
+int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
+                   const float* x, int N, int B, int bits, const ibcu_prologue_t* prologue);
 /* Same, plus silu(gate)*up fused into the epilogue of a gate/up pair (src/forward.c:635-637,
  * src/kernels/scalar.c:175-181): tensors[0] = gate, tensors[1] = up, equal M; writes only
  * tensors[0].out[b*out_stride + row] = silu(gate_y) * up_y. */

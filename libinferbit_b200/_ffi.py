@@ -19,6 +19,11 @@ class LinearT(C.Structure):
                 ("M", C.c_int), ("out_stride", C.c_int), ("scales_fp32", C.c_int), ("epilogue", C.c_int)]
 
 
+class PrologueT(C.Structure):
+    """ibcu_prologue_t"""
+    _fields_ = [("op", C.c_int), ("x2", C.c_void_p), ("norm_w", C.c_void_p), ("eps", C.c_float)]
+
+
 class PqT(C.Structure):
     """ibcu_pq_t"""
     _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K", C.c_int),
@@ -58,6 +63,7 @@ IBCU_SYMBOLS = {
     "ibcu_launch_count": (C.c_uint64, [C.c_void_p]),
     "ibcu_set_pdl": (None, [C.c_void_p, C.c_int]),
     "ibcu_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "ibcu_linear_ex": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(PrologueT)]),
     "ibcu_linear_gate_up_silu": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "ibcu_linear_force_generic": (None, [C.c_void_p, C.c_int]),
     "ibcu_quantize_input_int8_g128": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),

@@ -57,34 +57,35 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ out, 
     for (int i = threadIdx.x; i < N; i += blockDim.x) ob[i] = xb[i] * r * (float)w[i];
 }
 
-// One block per position b. Rotates every Q head and every K head (each K head once, as the
-// reference does through the first Q head of its group), then stores K and V at cache row pos0+b.
-__global__ void __launch_bounds__(256) rope_kv_write_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
+// grid (Q heads + K heads, B): one block per head and position, one thread per rotated pair. Each K
+// head is rotated once (the reference does it through the first Q head of its group) and stored,
+// with its V row, at cache row pos0 + b.
+__global__ void __launch_bounds__(128) rope_kv_write_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
                                                             float* __restrict__ k_cache, float* __restrict__ v_cache,
                                                             int n_heads, int n_kv, int hd, int pos0, float theta) {
     pdl_launch_dependents();
     pdl_wait();
-    const int b = blockIdx.x, pos = pos0 + b, half = hd / 2;
+    const int h = blockIdx.x, b = blockIdx.y, pos = pos0 + b, half = hd / 2;
     const int kv_dim = n_kv * hd;
-    float* qb = q + (size_t)b * n_heads * hd;
-    float* kb = k + (size_t)b * kv_dim;
-    const float* vb = v + (size_t)b * kv_dim;
-    const int total = (n_heads + n_kv) * half;
-    for (int e = threadIdx.x; e < total; e += blockDim.x) {
-        const int h = e / half, m = e - h * half;
+    const bool is_k = h >= n_heads;
+    float* p = is_k ? k + (size_t)b * kv_dim + (size_t)(h - n_heads) * hd : q + (size_t)b * n_heads * hd + (size_t)h * hd;
+    for (int m = threadIdx.x; m < half; m += blockDim.x) {
         const float freq = 1.0f / powf(theta, (float)(2 * m) / (float)hd);
         const float ang = (float)pos * freq;
         const float c = cosf(ang), s = sinf(ang);
-        float* p = h < n_heads ? qb + (size_t)h * hd + 2 * m : kb + (size_t)(h - n_heads) * hd + 2 * m;
-        const float a0 = p[0], a1 = p[1];
+        const float a0 = p[2 * m], a1 = p[2 * m + 1];
         const float r0 = a0 * c - a1 * s, r1 = a0 * s + a1 * c;
-        p[0] = r0; p[1] = r1;
-        if (h >= n_heads && k_cache) {
+        p[2 * m] = r0; p[2 * m + 1] = r1;
+        if (is_k && k_cache) {
             float* dst = k_cache + (size_t)pos * kv_dim + (size_t)(h - n_heads) * hd + 2 * m;
             dst[0] = r0; dst[1] = r1;
         }
     }
-    if (v_cache && v) for (int e = threadIdx.x; e < kv_dim; e += blockDim.x) v_cache[(size_t)pos * kv_dim + e] = vb[e];
+    if (is_k && v_cache && v) {
+        const float* vb = v + (size_t)b * kv_dim + (size_t)(h - n_heads) * hd;
+        float* dst = v_cache + (size_t)pos * kv_dim + (size_t)(h - n_heads) * hd;
+        for (int e = threadIdx.x; e < hd; e += blockDim.x) dst[e] = vb[e];
+    }
 }
 
 // One block per (query head, position b). Scores against cache rows 0..pos, max-subtracted softmax,
@@ -130,6 +131,141 @@ __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict_
         float a = 0.0f;
         for (int w = 0; w < nwarp; w++) a += part[w * hd + d];
         out[((size_t)b * n_heads + h) * hd + d] = a;
+    }
+}
+
+// ── split attention for decode ──────────────────────────────────────────────────────────
+// attn_partial_kernel: grid (kv heads, position chunks, B). A block owns one KV head, so the K and V
+// rows it reads serve all query heads of the group, and one chunk of cache positions. Thread t of the
+// block scores position t of the chunk for every query head of the group (K row read as float4s, the
+// query heads broadcast from shared memory), the block forms the chunk-local softmax weights, then
+// thread d accumulates dimension d of the weighted V sum. Chunk results (max, sum, weighted sum) go to
+// scratch; attn_combine_kernel merges the chunks of a head with the usual max/sum rescaling.
+constexpr int ATT_GMAX = 8;          // query heads per KV head handled by the split path
+constexpr int ATT_T = 128;           // threads = positions per chunk
+
+__global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                             const float* __restrict__ v_cache, float* __restrict__ part,
+                                                             int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit) {
+    extern __shared__ __align__(16) float asm_[];
+    const int group = n_heads / n_kv;
+    const int ld = hd + 4;                          // padded tile rows: conflict-free float4 reads down a column of rows
+    float* qs = asm_;                               // [group][hd]
+    float* ps = qs + group * hd;                    // [group][ATT_T] scores, then weights
+    float* red = ps + group * ATT_T;                // [group][4]
+    float* kt = red + group * 4;                    // [chunk][ld]
+    float* vt = kt + (size_t)chunk * ld;            // [chunk][ld]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kvh = blockIdx.x, sp = blockIdx.y, b = blockIdx.z, pos = pos0 + b;
+    const int kv_dim = n_kv * hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = sp * chunk, t1 = min(pos + 1, t0 + chunk), n = max(0, t1 - t0);
+    // the whole K and V tile of this chunk goes in flight at once (one memory round trip)
+    {
+        const int per_row = hd / 4;
+        const uint32_t kd = (uint32_t)__cvta_generic_to_shared(kt), vd = (uint32_t)__cvta_generic_to_shared(vt);
+        for (int e = tid; e < n * per_row; e += ATT_T) {
+            const int r = e / per_row, c = e - r * per_row;
+            const size_t g = (size_t)(t0 + r) * kv_dim + (size_t)kvh * hd + 4 * c;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(kd + (r * ld + 4 * c) * 4), "l"(k_cache + g) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(vd + (r * ld + 4 * c) * 4), "l"(v_cache + g) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int e = tid; e < group * hd; e += ATT_T) qs[e] = q[((size_t)b * n_heads + (size_t)kvh * group) * hd + e];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const float scale = 1.0f / sqrtf((float)hd);
+    float sc[ATT_GMAX];
+#pragma unroll
+    for (int g = 0; g < ATT_GMAX; g++) sc[g] = 0.0f;
+    if (tid < n) {
+        const float4* kr = reinterpret_cast<const float4*>(kt + (size_t)tid * ld);
+        for (int d4 = 0; d4 < hd / 4; d4++) {
+            const float4 kk = kr[d4];
+#pragma unroll
+            for (int g = 0; g < ATT_GMAX; g++) {
+                if (g >= group) break;
+                const float4 qq = *reinterpret_cast<const float4*>(qs + g * hd + 4 * d4);
+                sc[g] = fmaf(qq.x, kk.x, fmaf(qq.y, kk.y, fmaf(qq.z, kk.z, fmaf(qq.w, kk.w, sc[g]))));
+            }
+        }
+    }
+    // chunk-local max and sum per query head
+    float mloc[ATT_GMAX], lloc[ATT_GMAX];
+#pragma unroll
+    for (int g = 0; g < ATT_GMAX; g++) {
+        if (g >= group) break;
+        float v = tid < n ? sc[g] * scale : -INFINITY;
+        sc[g] = v;
+        v = warp_max(v);
+        if (lane == 0) red[g * 4 + warp] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < ATT_GMAX; g++) {
+        if (g >= group) break;
+        mloc[g] = fmaxf(fmaxf(red[g * 4], red[g * 4 + 1]), fmaxf(red[g * 4 + 2], red[g * 4 + 3]));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < ATT_GMAX; g++) {
+        if (g >= group) break;
+        const float pw = tid < n ? expf(sc[g] - mloc[g]) : 0.0f;
+        ps[g * ATT_T + tid] = pw;
+        const float v = warp_sum(pw);
+        if (lane == 0) red[g * 4 + warp] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < ATT_GMAX; g++) {
+        if (g >= group) break;
+        lloc[g] = red[g * 4] + red[g * 4 + 1] + red[g * 4 + 2] + red[g * 4 + 3];
+    }
+    // weighted V sum: thread d owns dimension d (and d + 128, ...)
+    const size_t pstride = (size_t)hd + 2;          // per (b, head, split): m, l, acc[hd]
+    for (int d = tid; d < hd; d += ATT_T) {
+        float acc[ATT_GMAX];
+#pragma unroll
+        for (int g = 0; g < ATT_GMAX; g++) acc[g] = 0.0f;
+#pragma unroll 4
+        for (int t = 0; t < n; t++) {
+            const float vv = vt[(size_t)t * ld + d];
+#pragma unroll
+            for (int g = 0; g < ATT_GMAX; g++) { if (g >= group) break; acc[g] = fmaf(ps[g * ATT_T + t], vv, acc[g]); }
+        }
+#pragma unroll
+        for (int g = 0; g < ATT_GMAX; g++) {
+            if (g >= group) break;
+            part[(((size_t)b * n_heads + (size_t)kvh * group + g) * nsplit + sp) * pstride + 2 + d] = acc[g];
+        }
+    }
+    if (tid < group) {
+        float* dst = part + (((size_t)b * n_heads + (size_t)kvh * group + tid) * nsplit + sp) * pstride;
+        dst[0] = n > 0 ? mloc[tid] : -INFINITY;
+        dst[1] = n > 0 ? lloc[tid] : 0.0f;
+    }
+}
+
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                           int n_heads, int hd, int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const size_t pstride = (size_t)hd + 2;
+    const float* src = part + ((size_t)b * n_heads + h) * nsplit * pstride;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; s++) M = fmaxf(M, src[s * pstride]);
+    float L = 0.0f;
+    for (int s = 0; s < nsplit; s++) L += src[s * pstride + 1] * expf(src[s * pstride] - M);
+    const float inv = 1.0f / L;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float a = 0.0f;
+        for (int s = 0; s < nsplit; s++) {
+            const float w = src[s * pstride + 1] > 0.0f ? expf(src[s * pstride] - M) : 0.0f;
+            a = fmaf(w, src[s * pstride + 2 + d], a);
+        }
+        out[((size_t)b * n_heads + h) * hd + d] = a * inv;
     }
 }
 
@@ -200,7 +336,8 @@ extern "C" int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float
     IBCU_REQUIRE(ctx, q && k, "ibcu_rope_kv_write: null pointer");
     IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && (head_dim & 1) == 0 && pos0 >= 0 && B > 0,
                  "ibcu_rope_kv_write: bad shape heads=%d kv=%d hd=%d pos0=%d B=%d", n_heads, n_kv_heads, head_dim, pos0, B);
-    return ibcu_launch(ctx, rope_kv_write_kernel, dim3(B), dim3(256), 0, 1, true, q, k, v, k_cache, v_cache,
+    const int threads = head_dim / 2 >= 128 ? 128 : (head_dim / 2 >= 64 ? 64 : 32);
+    return ibcu_launch(ctx, rope_kv_write_kernel, dim3(n_heads + n_kv_heads, B), dim3(threads), 0, 1, true, q, k, v, k_cache, v_cache,
                        n_heads, n_kv_heads, head_dim, pos0, theta);
 }
 
@@ -210,6 +347,25 @@ extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cach
     IBCU_REQUIRE(ctx, q && k_cache && v_cache && out, "ibcu_attention: null pointer");
     IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && pos0 >= 0 && B > 0,
                  "ibcu_attention: bad shape");
+    const int group = n_heads / n_kv_heads;
+    if (group <= ATT_GMAX && head_dim % 4 == 0 && head_dim <= 256 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0) {
+        // split path: chunks of up to 128 cache positions per block, merged by a second small kernel
+        const int cap = pos0 + B;
+        int nsplit = (cap + ATT_T - 1) / ATT_T;
+        const int want = (2 * ctx->sm_count) / (n_kv_heads * B);      // enough blocks to cover the machine
+        int chunk = ATT_T;
+        if (nsplit < want) { chunk = (cap + want - 1) / want; if (chunk < 32) chunk = 32; chunk = (chunk + 3) & ~3; nsplit = (cap + chunk - 1) / chunk; }
+        const size_t pbytes = (size_t)B * n_heads * nsplit * (head_dim + 2) * sizeof(float);
+        int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, pbytes);
+        if (rc) return rc;
+        const size_t smem = ((size_t)group * head_dim + (size_t)group * ATT_T + group * 4 + 2 * (size_t)chunk * (head_dim + 4)) * sizeof(float);
+        if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, nsplit, B), dim3(ATT_T), smem, 1, true,
+                         q, k_cache, v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit);
+        if (rc) return rc;
+        return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), 0, 1, true,
+                           (const float*)ctx->scratch, out, n_heads, head_dim, nsplit);
+    }
     int cap = pos0 + B;
     size_t smem = ((size_t)cap + 8 * (size_t)head_dim) * sizeof(float);
     IBCU_REQUIRE(ctx, smem <= 200 * 1024, "ibcu_attention: context %d too long for one block's shared memory", cap);

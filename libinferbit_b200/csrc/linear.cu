@@ -63,29 +63,74 @@ constexpr int LIN_LIMBS = 4;
 // [2^29, 2^30), then X = d0 + 256 d1 + 65536 d2 + 2^24 d3 with every digit in [-128, 127].
 // Eight columns at a time: INT8 consumers get them in natural order, INT4 consumers as
 // c0,c2,c4,c6,c1,c3,c5,c7 (low nibbles of four bytes, then high nibbles).
-__global__ void __launch_bounds__(256) xprep_kernel(const float* __restrict__ x, int N, int slice_cols, int xs_ld, int perm8,
-                                                    int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
-    __shared__ float red[8];
-    __shared__ int sred[8][LIN_LIMBS];
-    __shared__ float s_mul;
+struct XSource {                   // where an activation value comes from
+    const float* x;                // [B][N]
+    const float* x2;               // second operand of silu(x)*x2, or NULL
+    const __half* norm_w;          // RMSNorm weights, or NULL
+    float eps;
+    int op;                        // IBCU_PRO_*
+};
+
+// four consecutive transformed activation values starting at column j of activation row xb
+__device__ __forceinline__ float4 xsrc_load4(const XSource& s, const float* xb, const float* x2b, int col, float r) {
+    float4 v = *reinterpret_cast<const float4*>(xb + col);
+    if (s.op == IBCU_PRO_RMSNORM) {
+        const __half2 w01 = *reinterpret_cast<const __half2*>(s.norm_w + col), w23 = *reinterpret_cast<const __half2*>(s.norm_w + col + 2);
+        v.x = v.x * r * __low2float(w01); v.y = v.y * r * __high2float(w01);
+        v.z = v.z * r * __low2float(w23); v.w = v.w * r * __high2float(w23);
+    } else if (s.op == IBCU_PRO_SILU_MUL) {
+        const float4 u = *reinterpret_cast<const float4*>(x2b + col);
+        v.x = v.x / (1.0f + expf(-v.x)) * u.x; v.y = v.y / (1.0f + expf(-v.y)) * u.y;
+        v.z = v.z / (1.0f + expf(-v.z)) * u.z; v.w = v.w / (1.0f + expf(-v.w)) * u.w;
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
+                                                     int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
+    __shared__ float red[32];
+    __shared__ int sred[32][LIN_LIMBS];
+    __shared__ float s_mul, s_r;
     pdl_launch_dependents();
     pdl_wait();
-    const int ks = blockIdx.x, b = blockIdx.y;
+    const int ks = blockIdx.x, b = blockIdx.y, nth = blockDim.x, nwarp = nth >> 5;
     const int c0 = ks * slice_cols;
     const int valid = max(0, min(slice_cols, N - c0));       // N and c0 are multiples of 16
-    const float* xb = x + (size_t)b * N + c0;
+    const float* xrow = src.x + (size_t)b * N;
+    const float* xb = xrow + c0;
+    const float* x2b = src.x2 ? src.x2 + (size_t)b * N + c0 : nullptr;
+    float r = 1.0f;
+    if (src.op == IBCU_PRO_RMSNORM) {                         // 1/sqrt(mean(x^2) + eps) over the whole row (src/kernels/scalar.c:126-138)
+        float ss = 0.0f;
+        for (int j = threadIdx.x * 4; j < N; j += nth * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xrow + j);
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < nwarp; w++) t += red[w];
+            s_r = 1.0f / sqrtf(t / (float)N + src.eps);
+        }
+        __syncthreads();
+        r = s_r;
+    }
+    XSource sl = src;
+    sl.norm_w = src.norm_w ? src.norm_w + c0 : nullptr;
     float amax = 0.0f;
-    for (int j = threadIdx.x * 4; j < valid; j += 1024) {
-        const float4 v = *reinterpret_cast<const float4*>(xb + j);
+    for (int j = threadIdx.x * 4; j < valid; j += nth * 4) {
+        const float4 v = xsrc_load4(sl, xb, x2b, j, r);
         amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
     }
     amax = warp_max(amax);
+    __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
     if (threadIdx.x == 0) {
         float v = red[0];
-#pragma unroll
-        for (int w = 1; w < 8; w++) v = fmaxf(v, red[w]);
+        for (int w = 1; w < nwarp; w++) v = fmaxf(v, red[w]);
         const int e = (int)((__float_as_uint(v) >> 23) & 0xFF);      // v in [2^(e-127), 2^(e-126))
         int sh = (v > 0.0f && e != 255) ? 156 - e : 0;               // 2^sh * v in [2^29, 2^30)
         sh = max(-126, min(126, sh));
@@ -96,10 +141,10 @@ __global__ void __launch_bounds__(256) xprep_kernel(const float* __restrict__ x,
     const float mul = s_mul;
     int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
     int lsum[LIN_LIMBS] = {0, 0, 0, 0};
-    for (int j = threadIdx.x * 8; j < slice_cols; j += 2048) {
+    for (int j = threadIdx.x * 8; j < slice_cols; j += nth * 8) {
         int X[8];
         if (j < valid) {
-            const float4 a = *reinterpret_cast<const float4*>(xb + j), c = *reinterpret_cast<const float4*>(xb + j + 4);
+            const float4 a = xsrc_load4(sl, xb, x2b, j, r), c = xsrc_load4(sl, xb, x2b, j + 4, r);
             X[0] = __float2int_rn(a.x * mul); X[1] = __float2int_rn(a.y * mul); X[2] = __float2int_rn(a.z * mul); X[3] = __float2int_rn(a.w * mul);
             X[4] = __float2int_rn(c.x * mul); X[5] = __float2int_rn(c.y * mul); X[6] = __float2int_rn(c.z * mul); X[7] = __float2int_rn(c.w * mul);
         } else {
@@ -136,8 +181,7 @@ __global__ void __launch_bounds__(256) xprep_kernel(const float* __restrict__ x,
     __syncthreads();
     if (threadIdx.x < LIN_LIMBS) {
         int v = 0;
-#pragma unroll
-        for (int w = 0; w < 8; w++) v += sred[w][threadIdx.x];
+        for (int w = 0; w < nwarp; w++) v += sred[w][threadIdx.x];
         xsum[((size_t)b * nks + ks) * LIN_LIMBS + threadIdx.x] = v;
     }
 }
@@ -469,7 +513,15 @@ extern "C" void ibcu_linear_force_generic(ibcu_ctx* ctx, int on) { if (ctx) ctx-
 
 extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
                            const float* x, int N, int B, int bits) {
+    return ibcu_linear_ex(ctx, tensors, n_tensors, x, N, B, bits, nullptr);
+}
+
+extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
+                              const float* x, int N, int B, int bits, const ibcu_prologue_t* pro) {
     IBCU_CHECK_CTX(ctx);
+    const int op = pro ? pro->op : IBCU_PRO_NONE;
+    IBCU_REQUIRE(ctx, op == IBCU_PRO_NONE || (op == IBCU_PRO_RMSNORM && pro->norm_w) || (op == IBCU_PRO_SILU_MUL && pro->x2),
+                 "ibcu_linear_ex: prologue %d lacks its operand", op);
     IBCU_REQUIRE(ctx, tensors && x, "ibcu_linear: null pointer");
     IBCU_REQUIRE(ctx, n_tensors >= 1 && n_tensors <= 4, "ibcu_linear: n_tensors=%d not in 1..4", n_tensors);
     IBCU_REQUIRE(ctx, bits == 4 || bits == 8, "ibcu_linear: bits=%d (4 or 8 supported)", bits);
@@ -480,10 +532,21 @@ extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_te
         IBCU_REQUIRE(ctx, tensors[i].M >= 0 && tensors[i].out_stride >= tensors[i].M, "ibcu_linear: tensor %d M=%d stride=%d", i, tensors[i].M, tensors[i].out_stride);
     }
     const int rowbytes = bits == 8 ? N : N / 2;
-    bool fast = !ctx->force_generic && (rowbytes % 16 == 0) && ((uintptr_t)x & 15) == 0;
+    bool fast = !ctx->force_generic && (rowbytes % 16 == 0) && ((uintptr_t)x & 15) == 0 &&
+                (!pro || ((((uintptr_t)pro->x2) & 15) == 0 && (((uintptr_t)pro->norm_w) & 3) == 0));
     for (int i = 0; i < n_tensors; i++) if (((uintptr_t)tensors[i].w & 15) != 0) fast = false;
 
     if (!fast) {
+        if (op != IBCU_PRO_NONE) {
+            // portable path: apply the prologue with the element-wise kernels into the context's activation buffer
+            int rc0 = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, (size_t)B * N * sizeof(float));
+            if (rc0) return rc0;
+            float* tmp = (float*)ctx->xpack;
+            rc0 = op == IBCU_PRO_RMSNORM ? ibcu_rmsnorm_fp16w(ctx, tmp, x, pro->norm_w, pro->eps, N, B)
+                                         : ibcu_silu_mul(ctx, tmp, x, pro->x2, (size_t)B * N);
+            if (rc0) return rc0;
+            x = tmp;
+        }
         for (int i = 0; i < n_tensors; i++) {
             if (tensors[i].M == 0) continue;
             LinTensor T = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
@@ -501,7 +564,8 @@ extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_te
         ibcu_linear_t part[4];
         for (int b0 = 0; b0 < B; b0 += 16) {
             for (int i = 0; i < n_tensors; i++) { part[i] = tensors[i]; part[i].out = tensors[i].out + (size_t)b0 * tensors[i].out_stride; }
-            int rc2 = ibcu_linear(ctx, part, n_tensors, x + (size_t)b0 * N, N, B - b0 < 16 ? B - b0 : 16, bits);
+            ibcu_prologue_t pp; if (pro) { pp = *pro; if (pp.x2) pp.x2 += (size_t)b0 * N; }
+            int rc2 = ibcu_linear_ex(ctx, part, n_tensors, x + (size_t)b0 * N, N, B - b0 < 16 ? B - b0 : 16, bits, pro ? &pp : nullptr);
             if (rc2) return rc2;
         }
         return IBCU_OK;
@@ -579,7 +643,9 @@ extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_te
         p.counters = (unsigned*)ctx->counters;
         p.partial = (int*)ctx->scratch;
     }
-    rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(256), 0, 1, true, x, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
+    XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op };
+    const int xthreads = slice_kb * xk >= 8192 ? 1024 : (slice_kb * xk >= 2048 ? 512 : 256);
+    rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(xthreads), 0, 1, true, xsrc, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
                      xpack, xscale, xsum);
     if (rc) return rc;
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);

@@ -215,9 +215,10 @@ static int issue(ib_b200_model* m, int pos0, int B) {
     int rc = ibcu_embed_int8(ctx, (const int8_t*)m->embed, (const uint16_t*)m->embed_scale, m->tokens, m->x, H, B);
     for (int l = 0; l < c->n_layers && !rc; l++) {
         layer* y = &m->L[l];
-        rc = ibcu_rmsnorm_fp16w(ctx, m->xb, m->x, (const uint16_t*)y->in_norm, c->eps, H, B);
+        /* RMSNorm is folded into the activation preparation of the projections that consume it */
+        ibcu_prologue_t n1 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->in_norm, c->eps };
         ibcu_linear_t qkv[3] = { desc(&y->t[IB_B200_Q], m->q, 0), desc(&y->t[IB_B200_K], m->k, 0), desc(&y->t[IB_B200_V], m->v, 0) };
-        if (!rc) rc = ibcu_linear(ctx, qkv, 3, m->xb, H, B, c->attn_bits);
+        rc = ibcu_linear_ex(ctx, qkv, 3, m->x, H, B, c->attn_bits, &n1);
         if (!rc) rc = gather(m, &y->t[IB_B200_Q], m->q, B);
         if (!rc) rc = gather(m, &y->t[IB_B200_K], m->k, B);
         if (!rc) rc = gather(m, &y->t[IB_B200_V], m->v, B);
@@ -229,17 +230,20 @@ static int issue(ib_b200_model* m, int pos0, int B) {
         ibcu_linear_t o = desc(&y->t[IB_B200_O], m->x, IBCU_EPI_ADD);
         if (!rc) rc = ibcu_linear(ctx, &o, 1, m->att, H, B, c->attn_bits);
         if (!rc) rc = gather(m, &y->t[IB_B200_O], m->x, B);
-        if (!rc) rc = ibcu_rmsnorm_fp16w(ctx, m->xb, m->x, (const uint16_t*)y->post_norm, c->eps, H, B);
+        ibcu_prologue_t n2 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->post_norm, c->eps };
         ibcu_linear_t gu[2] = { desc(&y->t[IB_B200_GATE], m->hg, 0), desc(&y->t[IB_B200_UP], m->hu, 0) };
-        if (!rc) rc = ibcu_linear_gate_up_silu(ctx, gu, m->xb, H, B, c->mlp_bits);
+        if (!rc) rc = ibcu_linear_ex(ctx, gu, 2, m->x, H, B, c->mlp_bits, &n2);
         if (!rc) rc = gather(m, &y->t[IB_B200_GATE], m->hg, B);
+        if (!rc) rc = gather(m, &y->t[IB_B200_UP], m->hu, B);
+        /* silu(gate) * up is formed while down_proj's activation is prepared (src/forward.c:637-640) */
+        ibcu_prologue_t sm = { IBCU_PRO_SILU_MUL, m->hu, NULL, 0.0f };
         ibcu_linear_t dn = desc(&y->t[IB_B200_DOWN], m->x, IBCU_EPI_ADD);
-        if (!rc) rc = ibcu_linear(ctx, &dn, 1, m->hg, c->inter, B, c->mlp_bits);
+        if (!rc) rc = ibcu_linear_ex(ctx, &dn, 1, m->hg, c->inter, B, c->mlp_bits, &sm);
         if (!rc) rc = gather(m, &y->t[IB_B200_DOWN], m->x, B);
     }
-    if (!rc) rc = ibcu_rmsnorm_fp16w(ctx, m->xb, m->x, (const uint16_t*)m->final_norm, c->eps, H, B);
+    ibcu_prologue_t nf = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)m->final_norm, c->eps };
     ibcu_linear_t hd = desc(&m->head, m->logits, 0);
-    if (!rc) rc = ibcu_linear(ctx, &hd, 1, m->xb, H, B, c->head_bits);
+    if (!rc) rc = ibcu_linear_ex(ctx, &hd, 1, m->x, H, B, c->head_bits, &nf);
     if (!rc) rc = gather(m, &m->head, m->logits, B);
     return rc;
 }

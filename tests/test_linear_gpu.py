@@ -199,3 +199,32 @@ def test_w4a8_route_bit_exact(backend, cpu_libs, N):
     t = LinearT(be.upload(w).ptr, be.upload(s16).ptr, do.ptr, M, M, 0, 0)
     be._check(be.lib.ibcu_linear_w4a8(be.ctx, C.byref(t), dq.ptr, dsa.ptr, N, B)); be.sync()
     assert np.array_equal(be.download(do, np.float32, B * M).reshape(B, M), want)
+
+
+@pytest.mark.parametrize("bits,N", [(8, 1024), (4, 2048), (8, 200)])
+def test_prologues_rmsnorm_and_silu_mul(backend, cpu_libs, bits, N):
+    """RMSNorm (fp16 weights) and silu(x)*x2 folded into the call equal the separate scalar kernels
+    (src/kernels/scalar.c:126-138,175-181) followed by the matvec; N = 200 takes the portable path."""
+    from libinferbit_b200 import _ffi
+    rng = np.random.default_rng(bits + N)
+    be, o = backend, cpu_libs.oracle
+    M, B = 96, 3
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    x *= 3.0
+    x2 = rng.standard_normal((B, N)).astype(np.float32)
+    nw16 = _cpu.fp16_bits(rng.uniform(0.9, 1.1, N)); nw = np.empty(N, np.float32); o.ibo_fp16_array_to_fp32(nw16, nw, N)
+    dw, ds, dx, dx2, dn, do = be.upload(w), be.upload(s16), be.upload(x), be.upload(x2), be.upload(nw16), be.alloc(B * M * 4)
+    t = LinearT(dw.ptr, ds.ptr, do.ptr, M, M, 0, 0)
+    for op in (1, 2):
+        xin = np.empty_like(x)
+        for b in range(B):
+            if op == 1:
+                o.ibo_rmsnorm(xin[b], x[b], nw, 1e-5, N)
+            else:
+                o.ibo_silu_mul(xin[b], x[b], x2[b], N)
+        want = oracle_linear(cpu_libs, w, s16, xin, bits)
+        pro = _ffi.PrologueT(op, dx2.ptr, dn.ptr, 1e-5)
+        be._check(be.lib.ibcu_linear_ex(be.ctx, C.byref(t), 1, dx.ptr, N, B, bits, C.byref(pro)))
+        be.sync()
+        got = be.download(do, np.float32, B * M).reshape(B, M)
+        assert _cpu.close(got, want, 2e-3, 2e-4), op
