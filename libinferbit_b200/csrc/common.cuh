@@ -24,7 +24,6 @@ struct ibcu_ctx {
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
     void*  xpack;      size_t xpack_bytes;      // fp16 activation pieces + per-slice scales of the current linear call
-    void*  counters;   size_t counters_bytes;   // arrival counters of split launches; zero whenever no launch is in flight
     void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, PQ slabs, k-means per-block partials)
     cudaEvent_t events[IBCU_MAX_EVENTS];
     cudaGraphExec_t graphs[IBCU_MAX_GRAPHS];

@@ -67,7 +67,6 @@ extern "C" void ibcu_ctx_destroy(ibcu_ctx* ctx) {
     ibcu_comm_destroy_internal(ctx);
     for (int i = 0; i < IBCU_MAX_GRAPHS; i++) if (ctx->graphs[i]) cudaGraphExecDestroy(ctx->graphs[i]);
     for (int i = 0; i < IBCU_MAX_EVENTS; i++) cudaEventDestroy(ctx->events[i]);
-    if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->xpack) cudaFree(ctx->xpack);
     if (ctx->scratch) cudaFree(ctx->scratch);
     cudaStreamDestroy(ctx->stream);

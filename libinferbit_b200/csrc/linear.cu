@@ -23,7 +23,8 @@
 // measured 2-3 TB/s, this pattern 6+ TB/s). The W warps of a block take one 64-byte k-block of each
 // stage each and meet in a shared-memory reduction per row block. When the columns are split over
 // several blocks (only when a row's limbs do not fit shared memory), each writes its integer partial
-// sums to scratch and the last block to arrive (a counter per row block) adds them.
+// sums to scratch and linear_finalize_kernel recombines them (a fence + arrival-counter epilogue
+// inside the main kernel cost ~3 us per row block and slice, a second small launch costs ~2 us once).
 //
 // Portable path (linear_generic_kernel): one warp per output row, plain FP32 FMAs; used for shapes
 // the fast path does not take (row bytes not a multiple of 16, unaligned pointers) and by tests.
@@ -37,6 +38,14 @@ struct LinTensor {
     float* out;
     int M, out_stride, scales_fp32, epilogue;
     int rb_start;                  // first row block of this tensor in the launch
+};
+
+struct XSource {                   // where an activation value comes from
+    const float* x;                // [B][N]
+    const float* x2;               // second operand of silu(x)*x2, or NULL
+    const __half* norm_w;          // RMSNorm weights, or NULL
+    float eps;
+    int op;                        // IBCU_PRO_*
 };
 
 struct LinearParams {
@@ -53,7 +62,8 @@ struct LinearParams {
     const float* xscale;           // [B][nks] 2^-s of each slice
     const int* xsum;               // [B][nks][4] sum of each limb over the slice (INT4 bias term)
     int* partial;                  // [row block][slice][B*4][rows per block] when nks > 1
-    unsigned* counters;            // [row block] arrival counters, zero between launches
+    XSource xsrc;                  // FP32 source of the activations when the block converts them itself
+    int fused_x;                   // 1: convert in the block, 0: limbs were prepared by xprep_kernel
 };
 
 constexpr int LIN_LIMBS = 4;
@@ -63,13 +73,6 @@ constexpr int LIN_LIMBS = 4;
 // [2^29, 2^30), then X = d0 + 256 d1 + 65536 d2 + 2^24 d3 with every digit in [-128, 127].
 // Eight columns at a time: INT8 consumers get them in natural order, INT4 consumers as
 // c0,c2,c4,c6,c1,c3,c5,c7 (low nibbles of four bytes, then high nibbles).
-struct XSource {                   // where an activation value comes from
-    const float* x;                // [B][N]
-    const float* x2;               // second operand of silu(x)*x2, or NULL
-    const __half* norm_w;          // RMSNorm weights, or NULL
-    float eps;
-    int op;                        // IBCU_PRO_*
-};
 
 // four consecutive transformed activation values starting at column j of activation row xb
 __device__ __forceinline__ float4 xsrc_load4(const XSource& s, const float* xb, const float* x2b, int col, float r) {
@@ -86,15 +89,14 @@ __device__ __forceinline__ float4 xsrc_load4(const XSource& s, const float* xb, 
     return v;
 }
 
-__global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
-                                                     int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
-    __shared__ float red[32];
-    __shared__ int sred[32][LIN_LIMBS];
-    __shared__ float s_mul, s_r;
-    pdl_launch_dependents();
-    pdl_wait();
-    const int ks = blockIdx.x, b = blockIdx.y, nth = blockDim.x, nwarp = nth >> 5;
-    const int c0 = ks * slice_cols;
+// Converts columns [c0, c0 + slice_cols) of activation b to limbs. Called by every thread of a block
+// (it synchronises); dst_b is the [LIN_LIMBS][xs_ld] limb block of this activation and slice, in
+// global or shared memory. Thread 0 stores 2^-s to *back_out, threads 0..3 the limb sums to sum_out.
+struct XScratch { float red[32]; int sred[32][LIN_LIMBS]; float mul, r; };
+
+__device__ __forceinline__ void xconvert(const XSource& src, int N, int b, int c0, int slice_cols, int8_t* dst_b, int xs_ld,
+                                         int perm8, XScratch& sc, float* back_out, int* sum_out) {
+    const int nth = blockDim.x, nwarp = nth >> 5;
     const int valid = max(0, min(slice_cols, N - c0));       // N and c0 are multiples of 16
     const float* xrow = src.x + (size_t)b * N;
     const float* xb = xrow + c0;
@@ -107,15 +109,16 @@ __global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, i
             ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
         }
         ss = warp_sum(ss);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) sc.red[threadIdx.x >> 5] = ss;
         __syncthreads();
         if (threadIdx.x == 0) {
             float t = 0.0f;
-            for (int w = 0; w < nwarp; w++) t += red[w];
-            s_r = 1.0f / sqrtf(t / (float)N + src.eps);
+            for (int w = 0; w < nwarp; w++) t += sc.red[w];
+            sc.r = 1.0f / sqrtf(t / (float)N + src.eps);
         }
         __syncthreads();
-        r = s_r;
+        r = sc.r;
     }
     XSource sl = src;
     sl.norm_w = src.norm_w ? src.norm_w + c0 : nullptr;
@@ -126,20 +129,19 @@ __global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, i
     }
     amax = warp_max(amax);
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    if ((threadIdx.x & 31) == 0) sc.red[threadIdx.x >> 5] = amax;
     __syncthreads();
     if (threadIdx.x == 0) {
-        float v = red[0];
-        for (int w = 1; w < nwarp; w++) v = fmaxf(v, red[w]);
+        float v = sc.red[0];
+        for (int w = 1; w < nwarp; w++) v = fmaxf(v, sc.red[w]);
         const int e = (int)((__float_as_uint(v) >> 23) & 0xFF);      // v in [2^(e-127), 2^(e-126))
         int sh = (v > 0.0f && e != 255) ? 156 - e : 0;               // 2^sh * v in [2^29, 2^30)
         sh = max(-126, min(126, sh));
-        s_mul = __uint_as_float((uint32_t)(127 + sh) << 23);
-        xscale[b * nks + ks] = __uint_as_float((uint32_t)(127 - sh) << 23);
+        sc.mul = __uint_as_float((uint32_t)(127 + sh) << 23);
+        *back_out = __uint_as_float((uint32_t)(127 - sh) << 23);
     }
     __syncthreads();
-    const float mul = s_mul;
-    int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
+    const float mul = sc.mul;
     int lsum[LIN_LIMBS] = {0, 0, 0, 0};
     for (int j = threadIdx.x * 8; j < slice_cols; j += nth * 8) {
         int X[8];
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, i
                 pk.x = (d[0] & 0xFF) | ((d[1] & 0xFF) << 8) | ((d[2] & 0xFF) << 16) | ((uint32_t)(d[3] & 0xFF) << 24);
                 pk.y = (d[4] & 0xFF) | ((d[5] & 0xFF) << 8) | ((d[6] & 0xFF) << 16) | ((uint32_t)(d[7] & 0xFF) << 24);
             }
-            *reinterpret_cast<uint2*>(dst + (size_t)l * xs_ld + j) = pk;
+            *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk;
         }
     }
 #pragma unroll
@@ -176,14 +178,26 @@ __global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, i
         int v = lsum[l];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5][l] = v;
+        if ((threadIdx.x & 31) == 0) sc.sred[threadIdx.x >> 5][l] = v;
     }
     __syncthreads();
     if (threadIdx.x < LIN_LIMBS) {
         int v = 0;
-        for (int w = 0; w < nwarp; w++) v += sred[w][threadIdx.x];
-        xsum[((size_t)b * nks + ks) * LIN_LIMBS + threadIdx.x] = v;
+        for (int w = 0; w < nwarp; w++) v += sc.sred[w][threadIdx.x];
+        sum_out[threadIdx.x] = v;
     }
+}
+
+// grid (nks, B): the conversion as a kernel of its own, used when doing it inside every block of the
+// main kernel would cost more than a launch (several activations, long rows, the SiLU prologue).
+__global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
+                                                     int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
+    __shared__ XScratch sc;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int ks = blockIdx.x, b = blockIdx.y;
+    int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
+    xconvert(src, N, b, ks * slice_cols, slice_cols, dst, xs_ld, perm8, sc, xscale + b * nks + ks, xsum + ((size_t)b * nks + ks) * LIN_LIMBS);
 }
 
 __device__ __forceinline__ void imma_s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -231,7 +245,6 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     constexpr int STAGE_BYTES = R * LIN_LD;
     constexpr int NCP = RT * 2;                               // 16-byte chunks per thread per stage
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
 
@@ -282,7 +295,12 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     pdl_wait();
 
     // ── this slice's limbs, scale-back factors and limb sums ──
-    {
+    if (p.fused_x) {
+        __shared__ XScratch xsc;
+        for (int b = 0; b < p.B; b++)
+            xconvert(p.xsrc, p.N, b, kb_begin * XB, p.slice_kb * XB, xs + (size_t)b * LIN_LIMBS * p.xs_ld, p.xs_ld, BITS == 4 ? 1 : 0,
+                     xsc, s_back + b, s_xsum + b * LIN_LIMBS);
+    } else {
         const uint4* gsrc = reinterpret_cast<const uint4*>(p.xpack + (size_t)ks * p.ncols * p.xs_ld);
         const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(xs);
         const int nchunk = p.ncols * p.xs_ld / 16;
@@ -411,37 +429,38 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
                     p.partial[(((size_t)rb * p.nks + ks) * (B * LIN_LIMBS) + b * LIN_LIMBS + l) * R + r] = limb[l];
             }
         }
-        if (p.nks > 1) {
-            // the last slice to arrive recombines all slices (each with its own scale) in slice order
-            __threadfence();
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const unsigned prev = atomicAdd(p.counters + rb, 1u);
-                s_last = prev == (unsigned)p.nks - 1;
-                if (s_last) p.counters[rb] = 0;               // ready for the next launch
-            }
-            __syncthreads();
-            if (s_last) {
-                __threadfence();
-                for (int e = threadIdx.x; e < R * B; e += W * 32) {
-                    const int r = e % R, b = e / R;
-                    const int row = row0 + r;
-                    if (row >= T.M) continue;
-                    double y = 0.0;
-                    for (int k = 0; k < p.nks; k++) {
-                        const int* src_p = p.partial + (((size_t)rb * p.nks + k) * (B * LIN_LIMBS) + b * LIN_LIMBS) * R + r;
-                        const long long V = (((long long)__ldcg(src_p + 3 * R) * 256 + __ldcg(src_p + 2 * R)) * 256 + __ldcg(src_p + R)) * 256 + __ldcg(src_p);
-                        y += (double)V * (double)__ldcg(p.xscale + b * p.nks + k);
-                    }
-                    const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
-                                                   : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
-                    float* o = T.out + (size_t)b * T.out_stride + row;
-                    *o = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
-                }
-            }
-        }
     }
     cp_async_wait<0>();
+}
+
+// When the columns are split over several blocks: one thread per (row, activation) recombines the
+// integer partial sums of all slices, each with its own 2^-s, in slice order.
+__global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams p, int R) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int B = p.B;
+    const long total = (long)p.total_rb * R * B;
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(e % R);
+        const int b = (int)((e / R) % B);
+        const int rb = (int)(e / ((long)R * B));
+        int ti = 0;
+#pragma unroll
+        for (int i = 1; i < 4; i++) if (i < p.n_tensors && rb >= p.t[i].rb_start) ti = i;
+        const LinTensor& T = p.t[ti];
+        const int row = (rb - T.rb_start) * R + r;
+        if (row >= T.M) continue;
+        double y = 0.0;
+        for (int k = 0; k < p.nks; k++) {
+            const int* src_p = p.partial + (((size_t)rb * p.nks + k) * (B * LIN_LIMBS) + b * LIN_LIMBS) * R + r;
+            const long long V = (((long long)src_p[3 * R] * 256 + src_p[2 * R]) * 256 + src_p[R]) * 256 + src_p[0];
+            y += (double)V * (double)p.xscale[b * p.nks + k];
+        }
+        const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
+                                       : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
+        float* o = T.out + (size_t)b * T.out_stride + row;
+        *o = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
+    }
 }
 
 // ── portable path ───────────────────────────────────────────────────────────────────────
@@ -595,9 +614,13 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     // Shared memory per block: stage ring + reduction buffer + the slice's fp16 pieces. Columns are
     // split over several blocks only when the pieces of a whole row do not fit.
     const int kbs = LIN_SK / 64;
-    int stages = stages_env ? stages_env : (rt == 2 ? 4 : 8);
-    stages = rt == 2 ? (stages >= 6 ? 6 : 4) : (stages >= 8 ? 8 : 4);
-    const size_t fixed_smem = (size_t)stages * R * LIN_LD + (size_t)(bits == 4 ? 2 : 1) * LIN_W * R * ncg * 8 * 4 + 1024;
+    // ring depth: the deeper ring when two blocks per SM still fit with it, else the shallower one
+    const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * LIN_W * R * ncg * 8 * 4;
+    const size_t whole_row_pieces = (size_t)ncols * ((size_t)nkb * xk + xpad);
+    int stages = rt == 2 ? 6 : 8;
+    if (2 * ((size_t)stages * R * LIN_LD + red_bytes + whole_row_pieces + 2048) > 227 * 1024) stages = 4;
+    if (stages_env) stages = rt == 2 ? (stages_env >= 6 ? 6 : 4) : (stages_env >= 8 ? 8 : 4);
+    const size_t fixed_smem = (size_t)stages * R * LIN_LD + red_bytes + 1024;
     const size_t smem_cap = 200 * 1024;
     long piece_budget = (long)smem_cap - (long)fixed_smem;
     int max_slice_kb = (int)((piece_budget / ncols - xpad) / xk) / kbs * kbs;
@@ -631,22 +654,22 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     p.xpack = xpack; p.xscale = xscale; p.xsum = xsum;
     if (nks > 1) {
         const size_t part_bytes = (size_t)total_rb * nks * R * B * LIN_LIMBS * sizeof(int);
-        const size_t cnt_bytes = (size_t)total_rb * sizeof(unsigned);
         rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, part_bytes);
         if (rc) return rc;
-        if (cnt_bytes > ctx->counters_bytes) {
-            // kernels leave their counters at zero, so clearing is needed only when the array grows
-            rc = ibcu_reserve(ctx, &ctx->counters, &ctx->counters_bytes, cnt_bytes < 4096 ? 4096 : cnt_bytes);
-            if (rc) return rc;
-            IBCU_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, ctx->counters_bytes, ctx->stream));
-        }
-        p.counters = (unsigned*)ctx->counters;
         p.partial = (int*)ctx->scratch;
     }
     XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op };
+    // Cheap conversions are done by every block of the main kernel for itself (no extra launch, no
+    // dependency chain); expensive ones (SiLU, several activations, long rows) once, by xprep_kernel.
+    static const int fuse_env = env_int("IBCU_LINEAR_FUSE_X", -1);
+    int fused = (op != IBCU_PRO_SILU_MUL && (long)B * slice_kb * xk <= 8192 && nks == 1) ? 1 : 0;
+    if (fuse_env >= 0) fused = fuse_env && nks == 1;
+    p.xsrc = xsrc; p.fused_x = fused;
+    static const int skip_xprep = env_int("IBCU_LINEAR_SKIP_XPREP", 0);   // timing experiments only: results are then stale
     const int xthreads = slice_kb * xk >= 8192 ? 1024 : (slice_kb * xk >= 2048 ? 512 : 256);
-    rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(xthreads), 0, 1, true, xsrc, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
-                     xpack, xscale, xsum);
+    if (!fused && !skip_xprep)
+        rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(xthreads), 0, 1, true, xsrc, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
+                         xpack, xscale, xsum);
     if (rc) return rc;
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
@@ -658,7 +681,11 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     }
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH
-    return rc;
+    if (rc || nks == 1) return rc;
+    long outs = (long)total_rb * R * B;
+    int fgrid = (int)((outs + 255) / 256);
+    if (fgrid > 4 * ctx->sm_count) fgrid = 4 * ctx->sm_count;
+    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p, R);
 }
 
 // v1: the two projections in one launch, then the element-wise kernel over gate.out.
