@@ -175,6 +175,7 @@ def main():
     ctx = host.ib_b200_ctx()
     if world > 1:
         import torch
+        os.environ["NCCL_DEBUG"] = os.environ.get("IB_NCCL_DEBUG", "WARN")     # keep stdout to the one JSON line
         idbuf = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
             raw = (C.c_ubyte * 128)(); assert lib.ibcu_comm_get_id(raw) == 0

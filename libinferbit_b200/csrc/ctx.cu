@@ -64,8 +64,10 @@ extern "C" void ibcu_ctx_destroy(ibcu_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    // graphs first: a captured collective keeps a reference to the communicator, and destroying the
+    // communicator while such a graph is alive blocks
+    for (int i = 0; i < IBCU_MAX_GRAPHS; i++) if (ctx->graphs[i]) { cudaGraphExecDestroy(ctx->graphs[i]); ctx->graphs[i] = nullptr; }
     ibcu_comm_destroy_internal(ctx);
-    for (int i = 0; i < IBCU_MAX_GRAPHS; i++) if (ctx->graphs[i]) cudaGraphExecDestroy(ctx->graphs[i]);
     for (int i = 0; i < IBCU_MAX_EVENTS; i++) cudaEventDestroy(ctx->events[i]);
     if (ctx->xpack) cudaFree(ctx->xpack);
     if (ctx->scratch) cudaFree(ctx->scratch);
