@@ -5,15 +5,16 @@
 // separately for dimensions below 4*floor(D/4), fused for the remaining D%4), strict '<' so the
 // lowest index wins ties. Codes are therefore bit-identical to the reference, not "close".
 //   assign_exact_kernel   every distance in that exact form (CUDA cores).
-//   assign_filter_kernel  (D == 8) bf16 tensor-core scores x.c - |c|^2/2 for all K centroids per
-//                         16-point tile, best / second-best tracked in registers; a point whose
-//                         margin exceeds a rigorous error bound takes the tensor-core winner, every
-//                         other point is re-evaluated in the exact form. Same codes, ~4x fewer
-//                         issue slots.
+//   assign_filter_kernel  (D == 8, K % 8 == 0) TF32 tensor-core scores x.c - |c|^2/2 for all K
+//                         centroids per 16-point tile, best / second-best tracked in registers; a
+//                         point whose margin exceeds a rigorous error bound takes the tensor-core
+//                         winner, every other point is re-evaluated in the exact form. Same codes,
+//                         several times fewer issue slots.
 // accumulate: per-cluster sums / counts / inertia with a fixed order of additions (no atomics):
 // each warp adds its points in index order into a private shared-memory table, warps and blocks are
 // then combined in index order.
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -80,6 +81,161 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
         }
         idx[i] = arg;
         if (dist) dist[i] = best;
+    }
+}
+
+// ── tensor-core filter (D == 8, K a multiple of 8) ──────────────────────────────────────
+// Scores s_k = x.c_k - |c_k|^2/2 (the nearest centroid maximises s_k) come from TF32 tensor-core MMAs,
+// m16n8k8: one MMA covers 16 points x 8 centroids with the whole D = 8 contraction. Both operands are
+// split into two TF32 terms (x = xh + xl, c = ch + cl) and three MMAs (xh.ch + xh.cl + xl.ch) give the
+// dot product to about 2^-21 |x||c|; -|c|^2/2 is the accumulator's initial value. Each lane keeps the
+// best and second-best score of its rows; after a 4-lane merge a row whose margin exceeds
+//   2^-16 (|x|^2 + max|c|^2)   (> twice the score error plus the FP32 rounding of the reference's own
+//                                distances, see below)
+// takes the tensor-core winner: then the exact distances of the reference also order that way, so the
+// code is the reference's. Every other row (near ties, NaN/Inf) is evaluated in the exact form by the
+// whole warp, lowest index winning ties. The reported distance is always the exact-form one.
+// Bound: |s_k - true| <= 2^-18 |x||c_k| <= 2^-19 (|x|^2+|c|^2) (dropped xl.cl term, TF32 rounding of the low
+// terms, FP32 accumulation of 24 products); true squared distances differ by twice
+// the score gap; the reference's FP32 distance errs by < 12 * 2^-24 * d <= 2^-19.4 (|x|^2+|c|^2).
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void top2_push(float s, int k, float& m1, float& m2, int& i1) {
+    m2 = fmaxf(m2, fminf(m1, s));
+    i1 = s > m1 ? k : i1;
+    m1 = fmaxf(m1, s);
+}
+
+// Shared memory: B fragments [K/8][32] float4 (ch_t, ch_t+4, cl_t, cl_t+4 of centroid 8j+g) |
+// -|c|^2/2 [K] | exact centroids [K][8] | max |c|^2 [1].
+__global__ void __launch_bounds__(256) assign_filter_kernel(const float* __restrict__ X, long N, const float* __restrict__ C, int K,
+                                                            int32_t* __restrict__ idx, float* __restrict__ dist) {
+    extern __shared__ __align__(16) float fs[];
+    float4* bfrag = reinterpret_cast<float4*>(fs);  // (K/8) * 32 float4 = K * 16 floats
+    float* nh = fs + (size_t)K * 16;
+    pdl_launch_dependents();
+    pdl_wait();
+    float* cex = nh + K;
+    float* cmax2 = cex + (size_t)K * 8;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    for (int e = tid; e < K * 8; e += blockDim.x) cex[e] = C[e];
+    __syncthreads();
+    for (int e = tid; e < (K / 8) * 32; e += blockDim.x) {
+        const int j = e >> 5, l = e & 31, gg = l >> 2, tt = l & 3;
+        const float c0 = cex[(8 * j + gg) * 8 + tt], c1 = cex[(8 * j + gg) * 8 + tt + 4];
+        const uint32_t h0 = to_tf32(c0), h1 = to_tf32(c1);
+        const uint32_t l0 = to_tf32(c0 - __uint_as_float(h0)), l1 = to_tf32(c1 - __uint_as_float(h1));
+        bfrag[e] = make_float4(__uint_as_float(h0), __uint_as_float(h1), __uint_as_float(l0), __uint_as_float(l1));
+    }
+    float mx = 0.0f;
+    for (int k = tid; k < K; k += blockDim.x) {
+        float n = 0.0f;
+#pragma unroll
+        for (int d = 0; d < 8; d++) n = fmaf(cex[k * 8 + d], cex[k * 8 + d], n);
+        nh[k] = -0.5f * n;
+        mx = fmaxf(mx, n);
+    }
+    mx = warp_max(mx);
+    if (tid == 0) *cmax2 = 0.0f;
+    __syncthreads();
+    if (lane == 0) atomicMax(reinterpret_cast<int*>(cmax2), __float_as_int(mx));    // non-negative floats order like ints
+    __syncthreads();
+    const float cm2 = *cmax2;
+
+    const long ntile = (N + 15) / 16;
+    const long wglobal = (long)blockIdx.x * (blockDim.x >> 5) + (tid >> 5), wstride = (long)gridDim.x * (blockDim.x >> 5);
+    for (long tile = wglobal; tile < ntile; tile += wstride) {
+        const long p0 = tile * 16;
+        const long r0 = min(p0 + g, N - 1), r1 = min(p0 + g + 8, N - 1);     // rows past the end repeat the last point
+        const float x00 = X[r0 * 8 + t], x01 = X[r0 * 8 + t + 4], x10 = X[r1 * 8 + t], x11 = X[r1 * 8 + t + 4];
+        const uint32_t ah0 = to_tf32(x00), ah1 = to_tf32(x10), ah2 = to_tf32(x01), ah3 = to_tf32(x11);
+        const uint32_t al0 = to_tf32(x00 - __uint_as_float(ah0)), al1 = to_tf32(x10 - __uint_as_float(ah1));
+        const uint32_t al2 = to_tf32(x01 - __uint_as_float(ah2)), al3 = to_tf32(x11 - __uint_as_float(ah3));
+        float xn0 = fmaf(x00, x00, x01 * x01), xn1 = fmaf(x10, x10, x11 * x11);
+        xn0 += __shfl_xor_sync(0xffffffffu, xn0, 1); xn0 += __shfl_xor_sync(0xffffffffu, xn0, 2);
+        xn1 += __shfl_xor_sync(0xffffffffu, xn1, 1); xn1 += __shfl_xor_sync(0xffffffffu, xn1, 2);
+        float m1a = -INFINITY, m2a = -INFINITY, m1b = -INFINITY, m2b = -INFINITY;
+        int ia = 0, ib = 0;
+        for (int j = 0; j < K / 8; j++) {
+            const float4 bf = bfrag[j * 32 + lane];
+            const float2 ni = *reinterpret_cast<const float2*>(nh + 8 * j + 2 * t);
+            float c[4] = { ni.x, ni.y, ni.x, ni.y };
+            const uint32_t bh0 = __float_as_uint(bf.x), bh1 = __float_as_uint(bf.y), bl0 = __float_as_uint(bf.z), bl1 = __float_as_uint(bf.w);
+            mma_tf32(c, al0, al1, al2, al3, bh0, bh1);
+            mma_tf32(c, ah0, ah1, ah2, ah3, bl0, bl1);
+            mma_tf32(c, ah0, ah1, ah2, ah3, bh0, bh1);
+            const int k0 = 8 * j + 2 * t;
+            top2_push(c[0], k0, m1a, m2a, ia); top2_push(c[1], k0 + 1, m1a, m2a, ia);
+            top2_push(c[2], k0, m1b, m2b, ib); top2_push(c[3], k0 + 1, m1b, m2b, ib);
+        }
+        // merge the four lanes of a row
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+            float om1 = __shfl_xor_sync(0xffffffffu, m1a, o), om2 = __shfl_xor_sync(0xffffffffu, m2a, o);
+            int oi = __shfl_xor_sync(0xffffffffu, ia, o);
+            m2a = fmaxf(fmaxf(m2a, om2), fminf(m1a, om1));
+            if (om1 > m1a || (om1 == m1a && oi < ia)) ia = oi;
+            m1a = fmaxf(m1a, om1);
+            om1 = __shfl_xor_sync(0xffffffffu, m1b, o); om2 = __shfl_xor_sync(0xffffffffu, m2b, o);
+            oi = __shfl_xor_sync(0xffffffffu, ib, o);
+            m2b = fmaxf(fmaxf(m2b, om2), fminf(m1b, om1));
+            if (om1 > m1b || (om1 == m1b && oi < ib)) ib = oi;
+            m1b = fmaxf(m1b, om1);
+        }
+        const float marg0 = 1.52587890625e-5f * (xn0 + cm2), marg1 = 1.52587890625e-5f * (xn1 + cm2);
+        const bool sure0 = (m1a - m2a) > marg0, sure1 = (m1b - m2b) > marg1;   // false for NaN / Inf as well
+        // lanes 0..15 finish one row each: row l's result lives in the quad of g = l & 7 (second half: rows 8..15)
+        const int srcl = (lane & 7) * 4;
+        const int wi_a = __shfl_sync(0xffffffffu, ia, srcl), wi_b = __shfl_sync(0xffffffffu, ib, srcl);
+        const bool s_a = __shfl_sync(0xffffffffu, (int)sure0, srcl), s_b = __shfl_sync(0xffffffffu, (int)sure1, srcl);
+        const bool second = (lane & 8) != 0;
+        int win = second ? wi_b : wi_a;
+        bool sure = second ? s_b : s_a;
+        const long myp = p0 + (lane & 15);
+        const bool have = lane < 16 && myp < N;
+        float xr[8];
+        if (have) {
+            const float4 u = *reinterpret_cast<const float4*>(X + myp * 8), v = *reinterpret_cast<const float4*>(X + myp * 8 + 4);
+            xr[0] = u.x; xr[1] = u.y; xr[2] = u.z; xr[3] = u.w; xr[4] = v.x; xr[5] = v.y; xr[6] = v.z; xr[7] = v.w;
+        } else {
+#pragma unroll
+            for (int d = 0; d < 8; d++) xr[d] = 0.0f;
+        }
+        float best = have ? ref_sqdist<8>(xr, cex + win * 8, 8) : 0.0f;
+        // rows the filter could not decide: the whole warp evaluates all centroids exactly
+        unsigned todo = __ballot_sync(0xffffffffu, have && !sure);
+        while (todo) {
+            const int rl = __ffs(todo) - 1;
+            todo &= todo - 1;
+            float xq[8];
+#pragma unroll
+            for (int d = 0; d < 8; d++) xq[d] = __shfl_sync(0xffffffffu, xr[d], rl);
+            float bd = INFINITY; int bk = 0x7fffffff;
+            for (int k = lane; k < K; k += 32) {
+                const float dk = ref_sqdist<8>(xq, cex + k * 8, 8);
+                if (dk < bd) { bd = dk; bk = k; }
+            }
+            // lexicographic (distance, index) minimum: the reference's strict '<' scan keeps the lowest index
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+                if (od < bd || (od == bd && ok < bk)) { bd = od; bk = ok; }
+            }
+            if (lane == rl) {
+                if (bk == 0x7fffffff) { bk = 0; bd = ref_sqdist<8>(xr, cex, 8); }   // every distance NaN: centroid 0 (the reference's seed)
+                win = bk; best = bd;
+            }
+        }
+        if (have) { idx[myp] = win; if (dist) dist[myp] = best; }
     }
 }
 
@@ -230,6 +386,16 @@ extern "C" int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, 
     IBCU_REQUIRE(ctx, X && C && idx, "ibcu_kmeans_assign: null pointer");
     IBCU_REQUIRE(ctx, N > 0 && D >= 1 && D <= KM_MAX_D && K >= 1 && K <= 1024, "ibcu_kmeans_assign: N=%ld D=%d K=%d out of range", N, D, K);
     IBCU_REQUIRE(ctx, (size_t)K * D * sizeof(float) <= 128 * 1024, "ibcu_kmeans_assign: K*D=%d too large", K * D);
+    static const int no_filter = getenv("IBCU_KMEANS_EXACT_ONLY") != nullptr;
+    if (D == 8 && K % 8 == 0 && K >= 8 && !no_filter && ((uintptr_t)X & 15) == 0) {
+        const size_t smem = ((size_t)K * 16 + K + (size_t)K * 8 + 4) * sizeof(float);
+        if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_filter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        long tiles = (N + 15) / 16;
+        long blocks = (tiles + 7) / 8;
+        const long cap = (long)ctx->sm_count * 6;
+        if (blocks > cap) blocks = cap;
+        return ibcu_launch(ctx, assign_filter_kernel, dim3((unsigned)blocks), dim3(256), smem, 1, true, X, N, C, K, idx, dist);
+    }
     return assign_exact_launch(ctx, X, N, D, C, K, idx, dist, nullptr, nullptr, N);
 }
 
