@@ -277,11 +277,29 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const float* __restrict
         if (dist && mine < p1) inert += (double)dist[mine];
         for (int e = lane; e < n * D; e += 32) stage[e] = X[(size_t)p * D + e];
         __syncwarp();
-        for (int j = 0; j < n; j++) {
-            const int k = __shfl_sync(0xffffffffu, code, j);
-            if (lane < D) ms[(size_t)k * D + lane] += stage[j * D + lane];
-            if (lane == 31) mc[k] += 1;
-            __syncwarp();
+        // 32/D points per step, one lane group per point. Points of a step that share a cluster are
+        // applied one after another, so every table entry still sees its points in index order.
+        const int gpw = 32 / D, q = lane / D, d = lane - q * D;
+        for (int j = 0; j < n; j += gpw) {
+            const int mine_j = j + q;
+            const bool act = q < gpw && mine_j < n;
+            const int k = __shfl_sync(0xffffffffu, code, act ? mine_j : j);
+            bool clash = false;
+            // compare my cluster with those of the lower groups
+            for (int o = 0; o < gpw - 1; o++) {
+                const int ko = __shfl_sync(0xffffffffu, code, min(j + o, n - 1));
+                if (act && o < q && ko == k) clash = true;
+            }
+            const bool any = __any_sync(0xffffffffu, clash);
+            if (!any) {
+                if (act) { ms[(size_t)k * D + d] += stage[mine_j * D + d]; if (d == 0) mc[k] += 1; }
+                __syncwarp();
+            } else {
+                for (int o = 0; o < gpw; o++) {
+                    if (act && q == o) { ms[(size_t)k * D + d] += stage[mine_j * D + d]; if (d == 0) mc[k] += 1; }
+                    __syncwarp();
+                }
+            }
         }
     }
     __syncthreads();
