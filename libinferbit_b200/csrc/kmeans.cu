@@ -331,9 +331,15 @@ __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __r
     pdl_wait();
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e < KD) {
-        double s = 0.0;
-        for (int b = 0; b < nblocks; b++) s += (double)part_sums[(size_t)b * KD + e];
-        sums[e] = (float)s;
+        // eight interleaved running sums (independent loads in flight), combined in a fixed order
+        double s8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int b = 0;
+        for (; b + 8 <= nblocks; b += 8) {
+#pragma unroll
+            for (int u = 0; u < 8; u++) s8[u] += (double)part_sums[(size_t)(b + u) * KD + e];
+        }
+        for (; b < nblocks; b++) s8[0] += (double)part_sums[(size_t)b * KD + e];
+        sums[e] = (float)(((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7])));
     }
     if (e < K) {
         int c = 0;
