@@ -161,7 +161,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-other", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--case", default=None, help="run one small secondary case alone (for profiler captures): "
-                    "int8_4096x4096_b1, int8_32000x4096_b1, int4_14336x4096_b1, pq_4096x14336_b1, kmeans_4Mx8_k256, decode_7b_b1")
+                    "int8_4096x4096_b1, int8_32000x4096_b1, int4_14336x4096_b1, pq_4096x14336_b1, pq_4096x14336_b8, kmeans_4Mx8_k256, decode_7b_b1")
     args = ap.parse_args()
     rank, world, local, dist = dist_setup(args.gpus)
     if args.impl == "reference":
@@ -192,6 +192,7 @@ def main():
             "int8_32000x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 1, reps_target_bytes=400e6),
             "int4_14336x4096_b1": lambda: bs._linear_ring(lib, ctx, 4, 14336, 4096, 1, reps_target_bytes=300e6),
             "pq_4096x14336_b1": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 1),
+            "pq_4096x14336_b8": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 8),
             "kmeans_4Mx8_k256": lambda: bs._kmeans(lib, ctx, 0, 1, lambda v: v, sync, iters=2),
             "decode_7b_b1": lambda: bs._decode(lib, host, ctx, 1, lambda v: v, sync, steps=3),
         }

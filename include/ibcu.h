@@ -158,8 +158,8 @@ int    ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, fl
  * counterpart in the reference (its matmul_impl mallocs its tables on every call,
  * src/pq_decode.c:1519-1680). It calls no cudaMalloc / cudaFree or any allocating routine: the slab
  * partial sums live in an array built into the library, ibcu_pq_noalloc_max_floats() floats (4 MiB)
- * held by every GPU that loads the library from load to exit. A tensor that needs more (slabs x
- * padded rows + 32 floats) is refused with IBCU_ERR_PARAM and a message giving both numbers.
+ * held by every GPU that loads the library from load to exit. A call that needs more (activations x
+ * slabs x padded rows floats) is refused with IBCU_ERR_PARAM and a message giving both numbers.
  * The first call on a device looks up the array's device address; make that call before any stream
  * capture. All calls on a device share the one array and it keeps the previous call's contents
  * (nothing in it needs clearing: every value read is written first by the same call), so two calls

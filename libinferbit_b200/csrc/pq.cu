@@ -7,19 +7,22 @@
 // slab of subspaces reads long contiguous runs of codes (128-bit loads, every byte used) instead of a
 // few bytes out of every row.
 //
-// pq_gather_kernel: grid = (slabs of S subspaces) x (blocks of rows). A block first puts its code
-// loads in flight, then builds the slab's lookup table in shared memory straight from the fp16
-// codebooks and the activation slice (dropping chunks under the reference's 1 %-of-max rule), then
-// each thread walks 16 rows x S subspaces: one byte extract, one shared-memory read and one add per
-// code. Partial row sums go to scratch [slab][row]; pq_reduce_kernel adds the slabs in slab order,
-// applies the row scale and stores. No atomics, so results are run-to-run identical.
+// pq_gather_kernel: grid = (slabs of S <= 24 subspaces) x (blocks of 2048 rows). A block first puts
+// the codes of its slab in flight (4 rows per thread, all S subspaces, kept in registers), then, for
+// every activation in turn: finds the activation's max |x| (the reference's 1 %-of-max rule drops
+// whole chunks), builds the slab's lookup table in shared memory straight from the fp16 codebooks
+// (128-bit codebook loads), and walks its rows: one byte extract, one shared-memory read and one add
+// per code. The codes are read from HBM once however many activations there are. Partial row sums go
+// to scratch [activation][slab][row]; pq_reduce_kernel adds the slabs in slab order, applies the row
+// scale and stores. No atomics, so results are run-to-run identical.
 #include "common.cuh"
 
 namespace {
 
-constexpr int PQ_THREADS = 128;
-constexpr int PQ_ROWS_PER_THREAD = 16;
+constexpr int PQ_THREADS = 512;
+constexpr int PQ_ROWS_PER_THREAD = 4;
 constexpr int PQ_ROWS_PER_BLOCK = PQ_THREADS * PQ_ROWS_PER_THREAD;
+constexpr int PQ_SMAX = 24;                 // subspaces per slab (even): their codes live in PQ_SMAX registers
 
 // rows x C bytes  ->  2C x M_pad bytes (tile transpose through shared memory)
 __global__ void __launch_bounds__(256) pq_transpose_kernel(const uint8_t* __restrict__ idx_l, const uint8_t* __restrict__ idx_r,
@@ -40,122 +43,246 @@ __global__ void __launch_bounds__(256) pq_transpose_kernel(const uint8_t* __rest
     }
 }
 
-// amax[b] = max |x[b]|
-__global__ void __launch_bounds__(1024) pq_amax_kernel(const float* __restrict__ x, int N, float* __restrict__ amax) {
-    __shared__ float red[32];
-    pdl_launch_dependents();
-    pdl_wait();
-    const float* xb = x + (size_t)blockIdx.x * N;
-    float m = 0.0f;
-    for (int j = threadIdx.x; j < N; j += blockDim.x) m = fmaxf(m, fabsf(xb[j]));
-    m = warp_max(m);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
-        v = warp_max(v);
-        if (threadIdx.x == 0) amax[blockIdx.x] = v;
-    }
-}
-
 struct PqParams {
-    int M, M_pad, N, G, K, C, S;          // S = subspaces per slab
+    int M, M_pad, N, G, K, C, S, B, nslabs;   // S = subspaces per slab
     const __half* cb_l; const __half* cb_r; long cb_stride;
     const uint8_t* idx_t;
-    const float* x;                        // this activation
-    const float* amax;                     // its max |x|
-    float* partial;                        // [nslabs][M_pad]
+    const float* x;                            // [B][N]
+    float* partial;                            // [B][nslabs][M_pad]
 };
 
-__global__ void __launch_bounds__(PQ_THREADS) pq_gather_kernel(const PqParams p) {
-    extern __shared__ __align__(16) float lut[];          // [S][K]
-    __shared__ float xs[32 * 16];                          // activation slice of the slab, S * G/2 <= 512
-    __shared__ unsigned char live[32];
+__device__ __forceinline__ uint32_t ld_stream_u1(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// Every global read of this kernel is issued in batches of independent loads: with one block per SM
+// there are too few warps to hide one L2 round trip per loop iteration.
+template <int SMAX, int BT>   // BT activations share one pass over the table: entries are BT floats wide
+__global__ void __launch_bounds__(PQ_THREADS, SMAX <= 12 ? 2 : 1) pq_gather_kernel(const PqParams p) {
+    extern __shared__ __align__(16) float lut[];          // [S][K][BT] (+ slack)
+    __shared__ __align__(16) float xs[BT][PQ_SMAX * 16];   // activation slices of the slab
+    __shared__ unsigned char live[BT][PQ_SMAX];
+    __shared__ float red[BT][PQ_THREADS / 32];
     pdl_launch_dependents();
-    const int half = p.G >> 1;
-    const int s0 = blockIdx.x * p.S;
+    const int half = p.G >> 1, tid = threadIdx.x;
+    const int s0 = blockIdx.x * p.S;                       // even: a chunk's two subspaces share a slab
     const int ns = min(p.S, 2 * p.C - s0);
-    const int row = blockIdx.y * PQ_ROWS_PER_BLOCK + threadIdx.x * PQ_ROWS_PER_THREAD;
+    const int row = blockIdx.y * PQ_ROWS_PER_BLOCK + tid * PQ_ROWS_PER_THREAD;
     const bool has_rows = row < p.M_pad;
 
-    // codes of the first subspaces go in flight before anything else (they do not depend on x)
-    constexpr int PF = 4;
-    uint4 pre[PF];
+    // the slab's codes for this thread's 4 rows: loaded once, before anything that depends on x
+    uint32_t cd[SMAX];
 #pragma unroll
-    for (int i = 0; i < PF; i++)
-        pre[i] = (has_rows && i < ns) ? ld_stream_u4(p.idx_t + (size_t)(s0 + i) * p.M_pad + row) : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < SMAX; i++)
+        cd[i] = (has_rows && i < ns) ? ld_stream_u1(p.idx_t + (size_t)(s0 + i) * p.M_pad + row) : 0u;
 
     pdl_wait();
-    // activation slice + live flags
-    for (int e = threadIdx.x; e < ns * half; e += PQ_THREADS) {
-        const int sl = e / half, i = e - sl * half, s = s0 + sl;
-        xs[e] = p.x[(size_t)(s >> 1) * p.G + (s & 1) * half + i];
-    }
-    if (threadIdx.x < ns) {
-        const int c = (s0 + threadIdx.x) >> 1;
-        const float am = *p.amax;
-        bool keep = true;
-        if (am > 0.0f) {
-            const float thr = am * 0.01f;
-            float cm = 0.0f;
-            for (int i = 0; i < p.G; i++) cm = fmaxf(cm, fabsf(p.x[(size_t)c * p.G + i]));
-            keep = cm >= thr;
-        }
-        live[threadIdx.x] = keep;
-    }
-    __syncthreads();
-    // lookup table of the slab
-    for (int e = threadIdx.x; e < ns * p.K; e += PQ_THREADS) {
-        const int sl = e / p.K, k = e - sl * p.K, s = s0 + sl;
-        const __half* ent = ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride + (size_t)k * half;
-        float acc = 0.0f;
-        if (live[sl]) for (int i = 0; i < half; i++) acc = fmaf(__half2float(ent[i]), xs[sl * half + i], acc);
-        lut[sl * p.K + k] = acc;
-    }
-    __syncthreads();
-    if (!has_rows) return;
-
-    float acc[PQ_ROWS_PER_THREAD];
+    const bool vec_cb = half == 8 && (p.cb_stride & 7) == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
+    const bool vec_x = (p.N & 3) == 0 && ((uintptr_t)p.x & 15) == 0;
+    const int kshift = (p.K & (p.K - 1)) == 0 ? __ffs(p.K) - 1 : -1;
+    const int per = ns * p.K;
+    for (int b0 = 0; b0 < p.B; b0 += BT) {
+        const int nb = min(BT, p.B - b0);
+        // max |x| of each activation
+        float am[BT];
 #pragma unroll
-    for (int r = 0; r < PQ_ROWS_PER_THREAD; r++) acc[r] = 0.0f;
-    for (int sl = 0; sl < ns; sl += PF) {
-        uint4 cur[PF];
-#pragma unroll
-        for (int i = 0; i < PF; i++) cur[i] = pre[i];
-#pragma unroll
-        for (int i = 0; i < PF; i++) {
-            const int nx = sl + PF + i;
-            pre[i] = nx < ns ? ld_stream_u4(p.idx_t + (size_t)(s0 + nx) * p.M_pad + row) : make_uint4(0, 0, 0, 0);
+        for (int t = 0; t < BT; t++) {
+            am[t] = 0.0f;
+            if (t >= nb) continue;
+            const float* xb = p.x + (size_t)(b0 + t) * p.N;
+            if (vec_x) {
+                const float4* x4 = reinterpret_cast<const float4*>(xb);
+                const int n4 = p.N >> 2;
+#pragma unroll 8
+                for (int j = tid; j < n4; j += PQ_THREADS) {
+                    const float4 v = x4[j];
+                    am[t] = fmaxf(am[t], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            } else {
+#pragma unroll 8
+                for (int j = tid; j < p.N; j += PQ_THREADS) am[t] = fmaxf(am[t], fabsf(xb[j]));
+            }
         }
 #pragma unroll
-        for (int i = 0; i < PF; i++) {
-            if (sl + i >= ns) break;
-            const float* T = lut + (size_t)(sl + i) * p.K;
-            const uint32_t w[4] = { cur[i].x, cur[i].y, cur[i].z, cur[i].w };
+        for (int t = 0; t < BT; t++) am[t] = warp_max(am[t]);
+        __syncthreads();                                   // the previous pass's table reads are done
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                acc[4 * q + 0] += T[w[q] & 0xFF];
-                acc[4 * q + 1] += T[(w[q] >> 8) & 0xFF];
-                acc[4 * q + 2] += T[(w[q] >> 16) & 0xFF];
-                acc[4 * q + 3] += T[w[q] >> 24];
+        for (int t = 0; t < BT; t++) {
+            if ((tid & 31) == 0) red[t][tid >> 5] = am[t];
+            // subspace s covers x[s * half, (s + 1) * half)
+            if (tid < ns * half) xs[t][tid] = t < nb ? p.x[(size_t)(b0 + t) * p.N + (size_t)s0 * half + tid] : 0.0f;
+        }
+        __syncthreads();
+        if (tid < ns * BT) {
+            const int t = tid / ns, sl = tid - t * ns;
+            float amax = red[t][0];
+#pragma unroll
+            for (int w = 1; w < PQ_THREADS / 32; w++) amax = fmaxf(amax, red[t][w]);
+            bool keep = t < nb;
+            if (keep && amax > 0.0f) {
+                const float* xc = xs[t] + (sl & ~1) * half;  // the chunk of this subspace
+                float cm = 0.0f;
+                for (int i = 0; i < p.G; i++) cm = fmaxf(cm, fabsf(xc[i]));
+                keep = cm >= amax * 0.01f;
+            }
+            live[t][sl] = keep;
+        }
+        __syncthreads();
+        // lookup table of the slab for these activations
+        if (vec_cb) {
+            for (int e0 = 0; e0 < per; e0 += 4 * PQ_THREADS) {
+                uint4 raw[4];
+                int sls[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int e = e0 + u * PQ_THREADS + tid;
+                    const int sl = kshift >= 0 ? e >> kshift : e / p.K;
+                    const int k = e - sl * p.K, s = s0 + sl;
+                    sls[u] = e < per ? sl : -1;
+                    raw[u] = make_uint4(0, 0, 0, 0);
+                    if (e < per)
+                        raw[u] = *reinterpret_cast<const uint4*>(((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride + (size_t)k * 8);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (sls[u] < 0) continue;
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw[u]);
+                    const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+                    float v[BT];
+#pragma unroll
+                    for (int t = 0; t < BT; t++) {
+                        const float4 xa = *reinterpret_cast<const float4*>(xs[t] + sls[u] * 8);
+                        const float4 xc = *reinterpret_cast<const float4*>(xs[t] + sls[u] * 8 + 4);
+                        float acc = 0.0f;
+                        acc = fmaf(f0.x, xa.x, acc); acc = fmaf(f0.y, xa.y, acc); acc = fmaf(f1.x, xa.z, acc); acc = fmaf(f1.y, xa.w, acc);
+                        acc = fmaf(f2.x, xc.x, acc); acc = fmaf(f2.y, xc.y, acc); acc = fmaf(f3.x, xc.z, acc); acc = fmaf(f3.y, xc.w, acc);
+                        v[t] = live[t][sls[u]] ? acc : 0.0f;
+                    }
+                    float* dst = lut + (size_t)(e0 + u * PQ_THREADS + tid) * BT;
+                    if constexpr (BT == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                    else {
+#pragma unroll
+                        for (int t = 0; t < BT; t++) dst[t] = v[t];
+                    }
+                }
+            }
+        } else {
+            for (int e = tid; e < per; e += PQ_THREADS) {
+                const int sl = e / p.K, k = e - sl * p.K, s = s0 + sl;
+                const __half* ent = ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride + (size_t)k * half;
+#pragma unroll
+                for (int t = 0; t < BT; t++) {
+                    float acc = 0.0f;
+                    if (live[t][sl])
+                        for (int i = 0; i < half; i++) acc = fmaf(__half2float(ent[i]), xs[t][sl * half + i], acc);
+                    lut[(size_t)e * BT + t] = acc;
+                }
+            }
+        }
+        __syncthreads();
+        if (has_rows) {
+            float acc[PQ_ROWS_PER_THREAD][BT];
+#pragma unroll
+            for (int r = 0; r < PQ_ROWS_PER_THREAD; r++)
+#pragma unroll
+                for (int t = 0; t < BT; t++) acc[r][t] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < SMAX; i++) {
+                if (i < ns) {
+                    const float* T = lut + (size_t)i * p.K * BT;
+                    const uint32_t w = cd[i];
+#pragma unroll
+                    for (int r = 0; r < PQ_ROWS_PER_THREAD; r++) {
+                        const uint32_t code = (w >> (8 * r)) & 0xFF;
+                        if constexpr (BT == 4) {
+                            const float4 q = *reinterpret_cast<const float4*>(T + code * 4);
+                            acc[r][0] += q.x; acc[r][1] += q.y; acc[r][2] += q.z; acc[r][3] += q.w;
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < BT; t++) acc[r][t] += T[code * BT + t];
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < BT; t++) {
+                if (t >= nb) continue;
+                float* dst = p.partial + ((size_t)(b0 + t) * p.nslabs + blockIdx.x) * p.M_pad + row;
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[0][t], acc[1][t], acc[2][t], acc[3][t]);
             }
         }
     }
-    float* dst = p.partial + (size_t)blockIdx.x * p.M_pad + row;
-#pragma unroll
-    for (int q = 0; q < 4; q++)
-        *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
 }
 
+// block = 32 rows x 8 slab groups: group g adds slabs g, g + 8, ... in ascending order with all its loads in
+// flight at once, then the 8 group sums are combined in a fixed tree.
 __global__ void __launch_bounds__(256) pq_reduce_kernel(const float* __restrict__ partial, int nslabs, int M, int M_pad,
                                                         const __half* __restrict__ row_scale, float* __restrict__ out) {
+    __shared__ float part[8][32];
     pdl_launch_dependents();
     pdl_wait();
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= M) return;
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int r = blockIdx.x * 32 + lane, b = blockIdx.y;
     float s = 0.0f;
-    for (int b = 0; b < nslabs; b++) s += partial[(size_t)b * M_pad + r];
-    out[r] = s * __half2float(row_scale[r]);
+    if (r < M) {
+        const float* src = partial + (size_t)b * nslabs * M_pad + r;
+#pragma unroll 10
+        for (int k = g; k < nslabs; k += 8) s += src[(size_t)k * M_pad];
+    }
+    part[g][lane] = s;
+    __syncthreads();
+    if (g == 0 && r < M) {
+        const float t = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
+                        ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
+        out[(size_t)b * M + r] = t * __half2float(row_scale[r]);
+    }
+}
+
+// Shared launch logic of the two entry points: `scratch` must hold pq_scratch_floats() floats.
+struct PqPlan { int C, S, nslabs, row_blocks; size_t floats; };
+
+PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
+    PqPlan pl;
+    pl.C = t->N / t->G;
+    const int nsub = 2 * pl.C;
+    pl.row_blocks = (t->M_pad + PQ_ROWS_PER_BLOCK - 1) / PQ_ROWS_PER_BLOCK;
+    int S = (int)(((long)nsub * pl.row_blocks + ctx->sm_count - 1) / ctx->sm_count);   // about one block per SM
+    S = (S + 1) & ~1;                                      // even: both halves of a chunk in one slab
+    if (S < 4) S = 4;
+    if (S > PQ_SMAX) S = PQ_SMAX;
+    pl.S = S;
+    pl.nslabs = (nsub + S - 1) / S;
+    pl.floats = (size_t)B * pl.nslabs * t->M_pad;
+    return pl;
+}
+
+int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B, const PqPlan& pl, float* scratch) {
+    PqParams p;
+    p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = pl.C; p.S = pl.S; p.B = B; p.nslabs = pl.nslabs;
+    p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
+    p.idx_t = t->idx_t; p.x = x; p.partial = scratch;
+    const int bt = B >= 2 ? 4 : 1;
+    const size_t smem = ((size_t)pl.S * t->K + 256) * bt * sizeof(float);   // + slack: a code >= K must not leave the allocation
+    const dim3 grid(pl.nslabs, pl.row_blocks), block(PQ_THREADS);
+    int rc;
+    if (bt == 4) {
+        static bool attr_done[64];                                          // per device: the wide table needs the opt-in shared-memory size
+        if (!attr_done[ctx->device & 63]) {
+            IBCU_CUDA(ctx, cudaFuncSetAttribute(pq_gather_kernel<12, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (12 * 256 + 256) * 4 * 4));
+            IBCU_CUDA(ctx, cudaFuncSetAttribute(pq_gather_kernel<PQ_SMAX, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (PQ_SMAX * 256 + 256) * 4 * 4));
+            attr_done[ctx->device & 63] = true;
+        }
+        rc = pl.S <= 12 ? ibcu_launch(ctx, pq_gather_kernel<12, 4>, grid, block, smem, 1, true, p)
+                        : ibcu_launch(ctx, pq_gather_kernel<PQ_SMAX, 4>, grid, block, smem, 1, true, p);
+    } else {
+        rc = pl.S <= 12 ? ibcu_launch(ctx, pq_gather_kernel<12, 1>, grid, block, smem, 1, true, p)
+                        : ibcu_launch(ctx, pq_gather_kernel<PQ_SMAX, 1>, grid, block, smem, 1, true, p);
+    }
+    if (rc) return rc;
+    return ibcu_launch(ctx, pq_reduce_kernel, dim3((t->M + 31) / 32, B), dim3(256), 0, 1, true,
+                       (const float*)scratch, pl.nslabs, t->M, t->M_pad, (const __half*)t->row_scale, out);
 }
 
 }  // namespace
@@ -189,35 +316,10 @@ extern "C" int ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const floa
     IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->G <= 32 && t->N % t->G == 0 && t->K >= 1 && t->K <= 256,
                  "ibcu_pq_matmul_fp32: bad shape M=%d N=%d G=%d K=%d", t->M, t->N, t->G, t->K);
     IBCU_REQUIRE(ctx, B >= 1 && B <= 32, "ibcu_pq_matmul_fp32: B=%d not in 1..32", B);
-    const int C = t->N / t->G, nsub = 2 * C;
-    const int row_blocks = (t->M_pad + PQ_ROWS_PER_BLOCK - 1) / PQ_ROWS_PER_BLOCK;
-    // slab size: about two blocks per SM, at most 32 subspaces (32 KB of table at K = 256)
-    int S = (int)(((long)nsub * row_blocks + 2L * ctx->sm_count - 1) / (2L * ctx->sm_count));
-    if (S < 4) S = 4;
-    if (S > 32) S = 32;
-    S = (S + 3) & ~3;
-    const int nslabs = (nsub + S - 1) / S;
-    size_t need = (size_t)nslabs * t->M_pad * sizeof(float) + 32 * sizeof(float);
-    int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+    const PqPlan pl = pq_plan(ctx, t, B);
+    int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, pl.floats * sizeof(float));
     if (rc) return rc;
-    float* amax = (float*)ctx->scratch;
-    float* partial = amax + 32;
-    int threads = t->N >= 4096 ? 1024 : 256;
-    rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(threads), 0, 1, true, x, t->N, amax);
-    if (rc) return rc;
-    const size_t smem = ((size_t)S * t->K + 256) * sizeof(float);   // + slack: a code >= K must not leave the allocation
-    for (int b = 0; b < B; b++) {
-        PqParams p;
-        p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = C; p.S = S;
-        p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
-        p.idx_t = t->idx_t; p.x = x + (size_t)b * t->N; p.amax = amax + b; p.partial = partial;
-        rc = ibcu_launch(ctx, pq_gather_kernel, dim3(nslabs, row_blocks), dim3(PQ_THREADS), smem, 1, true, p);
-        if (rc) return rc;
-        rc = ibcu_launch(ctx, pq_reduce_kernel, dim3((t->M + 255) / 256), dim3(256), 0, 1, true,
-                         (const float*)partial, nslabs, t->M, t->M_pad, (const __half*)t->row_scale, out + (size_t)b * t->M);
-        if (rc) return rc;
-    }
-    return IBCU_OK;
+    return pq_launch(ctx, t, x, out, B, pl, (float*)ctx->scratch);
 }
 
 // ── PQ matvec without any allocation ────────────────────────────────────────────────────
@@ -255,37 +357,13 @@ extern "C" int ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, co
     IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->G <= 32 && t->N % t->G == 0 && t->K >= 1 && t->K <= 256,
                  "ibcu_pq_matmul_fp32_noalloc: bad shape M=%d N=%d G=%d K=%d", t->M, t->N, t->G, t->K);
     IBCU_REQUIRE(ctx, B >= 1 && B <= 32, "ibcu_pq_matmul_fp32_noalloc: B=%d not in 1..32", B);
-    const int C = t->N / t->G, nsub = 2 * C;
-    const int row_blocks = (t->M_pad + PQ_ROWS_PER_BLOCK - 1) / PQ_ROWS_PER_BLOCK;
-    int S = (int)(((long)nsub * row_blocks + 2L * ctx->sm_count - 1) / (2L * ctx->sm_count));
-    if (S < 4) S = 4;
-    if (S > 32) S = 32;
-    S = (S + 3) & ~3;
-    const int nslabs = (nsub + S - 1) / S;
-    const size_t need = (size_t)nslabs * t->M_pad + 32;
-    if (need > PQ_STATIC_FLOATS)
-        return ibcu_fail(ctx, IBCU_ERR_PARAM, "ibcu_pq_matmul_fp32_noalloc: this tensor needs %zu floats of scratch (%d slabs x %d padded rows + 32), "
-                         "the built-in array holds %zu; use ibcu_pq_matmul_fp32", need, nslabs, t->M_pad, PQ_STATIC_FLOATS);
+    const PqPlan pl = pq_plan(ctx, t, B);
+    if (pl.floats > PQ_STATIC_FLOATS)
+        return ibcu_fail(ctx, IBCU_ERR_PARAM, "ibcu_pq_matmul_fp32_noalloc: this call needs %zu floats of scratch (%d activations x %d slabs x %d padded rows), "
+                         "the built-in array holds %zu; use ibcu_pq_matmul_fp32", pl.floats, B, pl.nslabs, t->M_pad, PQ_STATIC_FLOATS);
     float* base = pq_static_address(ctx);
     if (!base) return ctx->status ? ctx->status : ibcu_fail(ctx, IBCU_ERR_CUDA, "ibcu_pq_matmul_fp32_noalloc: no address for the built-in scratch on device %d", ctx->device);
-    // Nothing in the array has to start at zero: the maxima kernel writes amax[0..B) and the gather
-    // kernel writes every partial sum the reduce kernel reads, before it reads them.
-    float* amax = base;
-    float* partial = base + 32;
-    int threads = t->N >= 4096 ? 1024 : 256;
-    int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(threads), 0, 1, true, x, t->N, amax);
-    if (rc) return rc;
-    const size_t smem = ((size_t)S * t->K + 256) * sizeof(float);
-    for (int b = 0; b < B; b++) {
-        PqParams p;
-        p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = C; p.S = S;
-        p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
-        p.idx_t = t->idx_t; p.x = x + (size_t)b * t->N; p.amax = amax + b; p.partial = partial;
-        rc = ibcu_launch(ctx, pq_gather_kernel, dim3(nslabs, row_blocks), dim3(PQ_THREADS), smem, 1, true, p);
-        if (rc) return rc;
-        rc = ibcu_launch(ctx, pq_reduce_kernel, dim3((t->M + 255) / 256), dim3(256), 0, 1, true,
-                         (const float*)partial, nslabs, t->M, t->M_pad, (const __half*)t->row_scale, out + (size_t)b * t->M);
-        if (rc) return rc;
-    }
-    return IBCU_OK;
+    // Nothing in the array has to start at zero: the gather kernel writes every partial sum that the
+    // reduce kernel reads, before it reads them.
+    return pq_launch(ctx, t, x, out, B, pl, base);
 }
