@@ -270,7 +270,7 @@ def _kmeans(lib, ctx, rank, world, max_over_ranks, barrier, N_total=1 << 22, D=8
     return {"ms_per_iter": ms / iters, "Mpoints_per_s": N_total / (ms / iters) / 1e3, "points": N_total, "K": K, "D": D, "iters": iters}
 
 
-def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20):
+def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20, warm=60):
     cfg = ModelCfg(4096, 14336, 32, 32, 8, 128, 32000, 1024, 1e-5, 10000.0, 8, 4, 8)
     m = host.ib_b200_model_create(ctx, C.byref(cfg))
     if not m:
@@ -278,7 +278,7 @@ def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20):
     assert host.ib_b200_model_fill_random(m, 4321, 512) == 0
     toks = np.arange(B, dtype=np.int32) * 7 + 11
     check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, host.ib_b200_model_tokens(m), toks.ctypes.data, toks.nbytes))
-    for _ in range(60):                                    # a fixed count, the same on every rank: clocks up
+    for _ in range(warm):                                  # a fixed count, the same on every rank: clocks up
         check(lib, ctx, host.ib_b200_forward_step_device(m, 512, B))
     barrier()
     dev = Dev(lib, ctx)

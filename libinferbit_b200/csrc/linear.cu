@@ -37,7 +37,8 @@ struct LinTensor {
     const void* scales;
     float* out;
     int M, out_stride, scales_fp32, epilogue;
-    int rb_start;                  // first row block of this tensor in the launch
+    int row_start;                 // first row of this tensor in the launch's concatenated row space
+    int blk_start, rows_per;       // its blocks (per column slice) start at blk_start; each owns rows_per contiguous rows
 };
 
 struct XSource {                   // where an activation value comes from
@@ -51,7 +52,7 @@ struct XSource {                   // where an activation value comes from
 struct LinearParams {
     LinTensor t[4];
     int n_tensors;
-    int total_rb;                  // row blocks over all tensors
+    int total_rows;                // rows over all tensors
     int rowbytes;                  // bytes per weight row
     int nkb;                       // 64-byte k-blocks per row
     int N, B, ncols;               // columns, activations, limb columns (4 per activation)
@@ -61,7 +62,9 @@ struct LinearParams {
     const int8_t* xpack;           // [nks][ncols][xs_ld] limbs in fragment order
     const float* xscale;           // [B][nks] 2^-s of each slice
     const int* xsum;               // [B][nks][4] sum of each limb over the slice (INT4 bias term)
-    int* partial;                  // [row block][slice][B*4][rows per block] when nks > 1
+    int* partial;                  // [slice][B*4][total_rows] when nks > 1
+    int trace_slot;
+    int xregs;
     XSource xsrc;                  // FP32 source of the activations when the block converts them itself
     int fused_x;                   // 1: convert in the block, 0: limbs were prepared by xprep_kernel
 };
@@ -87,6 +90,29 @@ __device__ __forceinline__ float4 xsrc_load4(const XSource& s, const float* xb, 
         v.z = v.z / (1.0f + expf(-v.z)) * u.z; v.w = v.w / (1.0f + expf(-v.w)) * u.w;
     }
     return v;
+}
+
+// Balanced base-256 digits of eight fixed-point values, as limb words. With Y = X + 0x00808080 the
+// unsigned bytes u_l of Y satisfy X = sum (u_l - 128) 256^l (l < 3) + (Y >> 24) 2^24, and u_l - 128 as
+// a signed byte is u_l ^ 0x80: so the four digits of X are the four bytes of Y ^ 0x00808080. Two 4x4
+// byte transposes turn eight such words into limb-major words; perm8 picks the INT4 column order.
+__device__ __forceinline__ void transpose4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t* o) {
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
+    const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
+    o[0] = __byte_perm(t0, t2, 0x5410); o[1] = __byte_perm(t0, t2, 0x7632);
+    o[2] = __byte_perm(t1, t3, 0x5410); o[3] = __byte_perm(t1, t3, 0x7632);
+}
+__device__ __forceinline__ void limbs8(const int* X, int perm8, uint2* pk, int* lsum) {
+    uint32_t D[8], lo[4], hi[4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) D[i] = ((uint32_t)X[i] + 0x00808080u) ^ 0x00808080u;
+    if (perm8) { transpose4x4_bytes(D[0], D[2], D[4], D[6], lo); transpose4x4_bytes(D[1], D[3], D[5], D[7], hi); }
+    else       { transpose4x4_bytes(D[0], D[1], D[2], D[3], lo); transpose4x4_bytes(D[4], D[5], D[6], D[7], hi); }
+#pragma unroll
+    for (int l = 0; l < LIN_LIMBS; l++) {
+        pk[l] = make_uint2(lo[l], hi[l]);
+        lsum[l] = __dp4a((int)lo[l], 0x01010101, __dp4a((int)hi[l], 0x01010101, lsum[l]));
+    }
 }
 
 // Converts columns [c0, c0 + slice_cols) of activation b to limbs. Called by every thread of a block
@@ -153,25 +179,10 @@ __device__ __forceinline__ void xconvert(const XSource& src, int N, int b, int c
 #pragma unroll
             for (int i = 0; i < 8; i++) X[i] = 0;
         }
+        uint2 pk[LIN_LIMBS];
+        limbs8(X, perm8, pk, lsum);
 #pragma unroll
-        for (int l = 0; l < LIN_LIMBS; l++) {
-            int d[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                d[i] = l < LIN_LIMBS - 1 ? (int)(int8_t)(X[i] & 0xFF) : X[i];     // balanced digit; the top one is what is left
-                X[i] = (X[i] - d[i]) >> 8;
-                lsum[l] += d[i];
-            }
-            uint2 pk;
-            if (perm8) {
-                pk.x = (d[0] & 0xFF) | ((d[2] & 0xFF) << 8) | ((d[4] & 0xFF) << 16) | ((uint32_t)(d[6] & 0xFF) << 24);
-                pk.y = (d[1] & 0xFF) | ((d[3] & 0xFF) << 8) | ((d[5] & 0xFF) << 16) | ((uint32_t)(d[7] & 0xFF) << 24);
-            } else {
-                pk.x = (d[0] & 0xFF) | ((d[1] & 0xFF) << 8) | ((d[2] & 0xFF) << 16) | ((uint32_t)(d[3] & 0xFF) << 24);
-                pk.y = (d[4] & 0xFF) | ((d[5] & 0xFF) << 8) | ((d[6] & 0xFF) << 16) | ((uint32_t)(d[7] & 0xFF) << 24);
-            }
-            *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk;
-        }
+        for (int l = 0; l < LIN_LIMBS; l++) *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk[l];
     }
 #pragma unroll
     for (int l = 0; l < LIN_LIMBS; l++) {
@@ -188,16 +199,141 @@ __device__ __forceinline__ void xconvert(const XSource& src, int N, int b, int c
     }
 }
 
+// The same conversion with the whole slice held in registers (up to V float4 per thread): every global
+// load of the block is issued before the first one is used, so the block pays one memory round trip
+// instead of one per loop iteration. Values, digits and sums are those of xconvert.
+template <int V>
+__device__ __forceinline__ void xconvert_regs(const XSource& src, int N, int b, int c0, int slice_cols, int8_t* dst_b, int xs_ld,
+                                              int perm8, XScratch& sc, float* back_out, int* sum_out) {
+    constexpr int P = V / 2;                                  // groups of 8 columns per thread
+    const int nth = blockDim.x, nwarp = nth >> 5;
+    const int valid = max(0, min(slice_cols, N - c0));       // N and c0 are multiples of 16
+    const float* xrow = src.x + (size_t)b * N;
+    const float* xb = xrow + c0;
+    float4 va[P], vc[P];
+#pragma unroll
+    for (int i = 0; i < P; i++) {
+        const int j = (threadIdx.x + i * nth) * 8;
+        va[i] = vc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (j < valid) { va[i] = *reinterpret_cast<const float4*>(xb + j); vc[i] = *reinterpret_cast<const float4*>(xb + j + 4); }
+    }
+    if (src.op == IBCU_PRO_SILU_MUL) {
+        const float* x2b = src.x2 + (size_t)b * N + c0;
+        float4 ua[P], uc[P];
+#pragma unroll
+        for (int i = 0; i < P; i++) {
+            const int j = (threadIdx.x + i * nth) * 8;
+            ua[i] = uc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < valid) { ua[i] = *reinterpret_cast<const float4*>(x2b + j); uc[i] = *reinterpret_cast<const float4*>(x2b + j + 4); }
+        }
+#pragma unroll
+        for (int i = 0; i < P; i++) {
+            float4& a = va[i]; float4& c = vc[i];
+            a.x = a.x / (1.0f + expf(-a.x)) * ua[i].x; a.y = a.y / (1.0f + expf(-a.y)) * ua[i].y;
+            a.z = a.z / (1.0f + expf(-a.z)) * ua[i].z; a.w = a.w / (1.0f + expf(-a.w)) * ua[i].w;
+            c.x = c.x / (1.0f + expf(-c.x)) * uc[i].x; c.y = c.y / (1.0f + expf(-c.y)) * uc[i].y;
+            c.z = c.z / (1.0f + expf(-c.z)) * uc[i].z; c.w = c.w / (1.0f + expf(-c.w)) * uc[i].w;
+        }
+    } else if (src.op == IBCU_PRO_RMSNORM) {                  // 1/sqrt(mean(x^2) + eps) over the whole row (src/kernels/scalar.c:126-138)
+        __half2 w[P][4];
+#pragma unroll
+        for (int i = 0; i < P; i++) {
+            const int j = (threadIdx.x + i * nth) * 8;
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                w[i][q] = j < valid ? *reinterpret_cast<const __half2*>(src.norm_w + c0 + j + 2 * q) : __floats2half2_rn(0.0f, 0.0f);
+        }
+        float ss = 0.0f;
+        if (c0 == 0 && valid == N) {
+#pragma unroll
+            for (int i = 0; i < P; i++) {
+                ss = fmaf(va[i].x, va[i].x, fmaf(va[i].y, va[i].y, fmaf(va[i].z, va[i].z, fmaf(va[i].w, va[i].w, ss))));
+                ss = fmaf(vc[i].x, vc[i].x, fmaf(vc[i].y, vc[i].y, fmaf(vc[i].z, vc[i].z, fmaf(vc[i].w, vc[i].w, ss))));
+            }
+        } else {
+            for (int j = threadIdx.x * 4; j < N; j += nth * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(xrow + j);
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+        }
+        ss = warp_sum(ss);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) sc.red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float t = 0.0f;
+        for (int q = 0; q < nwarp; q++) t += sc.red[q];       // every thread adds in the same order: no broadcast step
+        const float r = 1.0f / sqrtf(t / (float)N + src.eps);
+#pragma unroll
+        for (int i = 0; i < P; i++) {
+            va[i].x = va[i].x * r * __low2float(w[i][0]); va[i].y = va[i].y * r * __high2float(w[i][0]);
+            va[i].z = va[i].z * r * __low2float(w[i][1]); va[i].w = va[i].w * r * __high2float(w[i][1]);
+            vc[i].x = vc[i].x * r * __low2float(w[i][2]); vc[i].y = vc[i].y * r * __high2float(w[i][2]);
+            vc[i].z = vc[i].z * r * __low2float(w[i][3]); vc[i].w = vc[i].w * r * __high2float(w[i][3]);
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < P; i++) {
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(va[i].x), fabsf(va[i].y))), fmaxf(fabsf(va[i].z), fabsf(va[i].w)));
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(vc[i].x), fabsf(vc[i].y))), fmaxf(fabsf(vc[i].z), fabsf(vc[i].w)));
+    }
+    amax = warp_max(amax);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sc.red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    float vmax = sc.red[0];
+    for (int q = 1; q < nwarp; q++) vmax = fmaxf(vmax, sc.red[q]);
+    const int e = (int)((__float_as_uint(vmax) >> 23) & 0xFF);       // vmax in [2^(e-127), 2^(e-126))
+    int sh = (vmax > 0.0f && e != 255) ? 156 - e : 0;                // 2^sh * vmax in [2^29, 2^30)
+    sh = max(-126, min(126, sh));
+    const float mul = __uint_as_float((uint32_t)(127 + sh) << 23);
+    if (threadIdx.x == 0) *back_out = __uint_as_float((uint32_t)(127 - sh) << 23);
+    int lsum[LIN_LIMBS] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < P; i++) {
+        const int j = (threadIdx.x + i * nth) * 8;
+        if (j >= slice_cols) continue;
+        int X[8];
+        X[0] = __float2int_rn(va[i].x * mul); X[1] = __float2int_rn(va[i].y * mul); X[2] = __float2int_rn(va[i].z * mul); X[3] = __float2int_rn(va[i].w * mul);
+        X[4] = __float2int_rn(vc[i].x * mul); X[5] = __float2int_rn(vc[i].y * mul); X[6] = __float2int_rn(vc[i].z * mul); X[7] = __float2int_rn(vc[i].w * mul);
+        uint2 pk[LIN_LIMBS];
+        limbs8(X, perm8, pk, lsum);
+#pragma unroll
+        for (int l = 0; l < LIN_LIMBS; l++) *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk[l];
+    }
+#pragma unroll
+    for (int l = 0; l < LIN_LIMBS; l++) {
+        int v = lsum[l];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) sc.sred[threadIdx.x >> 5][l] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < LIN_LIMBS) {
+        int v = 0;
+        for (int q = 0; q < nwarp; q++) v += sc.sred[q][threadIdx.x];
+        sum_out[threadIdx.x] = v;
+    }
+}
+
+constexpr int XREG_V = 8;                                     // 32 columns per thread in registers
+__device__ __forceinline__ void xconvert_any(const XSource& src, int N, int b, int c0, int slice_cols, int8_t* dst_b, int xs_ld,
+                                             int perm8, XScratch& sc, float* back_out, int* sum_out, int xregs = 1) {
+    if (xregs && slice_cols <= XREG_V * 4 * (int)blockDim.x) xconvert_regs<XREG_V>(src, N, b, c0, slice_cols, dst_b, xs_ld, perm8, sc, back_out, sum_out);
+    else xconvert(src, N, b, c0, slice_cols, dst_b, xs_ld, perm8, sc, back_out, sum_out);
+}
+
 // grid (nks, B): the conversion as a kernel of its own, used when doing it inside every block of the
 // main kernel would cost more than a launch (several activations, long rows, the SiLU prologue).
-__global__ void __launch_bounds__(1024) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
-                                                     int nks, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
+template <int T>
+__global__ void __launch_bounds__(T) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
+                                                     int nks, int xregs, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
     __shared__ XScratch sc;
     pdl_launch_dependents();
     pdl_wait();
     const int ks = blockIdx.x, b = blockIdx.y;
     int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
-    xconvert(src, N, b, ks * slice_cols, slice_cols, dst, xs_ld, perm8, sc, xscale + b * nks + ks, xsum + ((size_t)b * nks + ks) * LIN_LIMBS);
+    xconvert_any(src, N, b, ks * slice_cols, slice_cols, dst, xs_ld, perm8, sc, xscale + b * nks + ks, xsum + ((size_t)b * nks + ks) * LIN_LIMBS, xregs);
 }
 
 __device__ __forceinline__ void imma_s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -223,6 +359,13 @@ __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 
 // The nibble bias of 8 is removed once per output as 8 * (sum of the limb over the slice).
 // Dynamic shared memory: stage ring [STAGES][R][LIN_LD] | reduction buffer [W][R][NCG*8] ints (x2 for
 // INT4) | limbs [ncols][xs_ld] | scale-back factors [32] | limb sums [32][4].
+#ifdef IBCU_TRACE
+__device__ unsigned long long ibcu_trace_buf[16][512][8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TRACE(i) do { if (threadIdx.x == 0 && blockIdx.x < 512) ibcu_trace_buf[p.trace_slot & 15][blockIdx.x][i] = gtime(); } while (0)
+#else
+#define TRACE(i) do { } while (0)
+#endif
 constexpr int LIN_SK = 512;                                   // bytes per row per stage
 constexpr int LIN_LD = LIN_SK + 64;                           // padded row stride: conflict-free fragment reads
 
@@ -246,10 +389,17 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     constexpr int NCP = RT * 2;                               // 16-byte chunks per thread per stage
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    TRACE(0);
     pdl_launch_dependents();
 
     const int ks = blockIdx.x % p.nks;                        // this block's column slice, fixed
-    const int rb_first = blockIdx.x / p.nks, rb_step = gridDim.x / p.nks;
+    const int cb = blockIdx.x / p.nks;                        // a block works on one tensor: a contiguous run of its rows, in tiles of up to R
+    int ti = 0;
+#pragma unroll
+    for (int i = 1; i < 4; i++) if (i < p.n_tensors && cb >= p.t[i].blk_start) ti = i;
+    const LinTensor& T = p.t[ti];
+    const int row_begin = (cb - T.blk_start) * T.rows_per;
+    const int row_end = min(T.M, row_begin + T.rows_per);
     const int kb_begin = ks * p.slice_kb;
     const int nk = min(p.nkb, kb_begin + p.slice_kb) - kb_begin;
     const int nst = (nk + KBS - 1) / KBS;
@@ -264,42 +414,48 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     const int cc = threadIdx.x & 31;
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + (threadIdx.x >> 5) * LIN_LD + cc * 16;
     const uint8_t* src[NCP];
-    int pf_rb = rb_first, pf_it = 0, pf_slot = 0;
-    auto pf_setup = [&]() {                                   // row pointers for row block pf_rb
-        int ti = 0;
-#pragma unroll
-        for (int i = 1; i < 4; i++) if (i < p.n_tensors && pf_rb >= p.t[i].rb_start) ti = i;
-        const int r0 = (pf_rb - p.t[ti].rb_start) * R + (threadIdx.x >> 5);
+    // A tile is up to R consecutive rows; rows of the tile that do not exist are zero-filled.
+    int pf_row = row_begin, pf_rows = 0, pf_it = 0, pf_slot = 0;
+    unsigned pf_mask = 0;                                     // bit i: row (tid>>5) + 8i exists in the tile
+    auto pf_setup = [&]() {                                   // row pointers for the tile at pf_row
+        pf_rows = min(R, row_end - pf_row);
+        const int r0 = threadIdx.x >> 5;
+        pf_mask = 0;
 #pragma unroll
         for (int i = 0; i < NCP; i++) {
-            int row = r0 + 8 * i;
-            row = row < p.t[ti].M ? row : p.t[ti].M - 1;
-            src[i] = p.t[ti].w + (size_t)row * p.rowbytes + (size_t)kb_begin * 64 + cc * 16;
+            const bool has = r0 + 8 * i < pf_rows;
+            pf_mask |= has ? 1u << i : 0u;
+            src[i] = T.w + (size_t)(pf_row + (has ? r0 + 8 * i : 0)) * p.rowbytes + (size_t)kb_begin * 64 + cc * 16;
         }
     };
     auto pf_issue = [&]() {                                   // next stage of the prefetch stream, if any
-        if (pf_rb < p.total_rb) {
+        if (pf_row < row_end) {
             const bool valid = (kb_begin + pf_it * KBS) * 64 + cc * 16 < p.rowbytes && pf_it * KBS + (cc >> 2) < nk;
             const uint32_t d = ring_u32 + pf_slot * STAGE_BYTES;
 #pragma unroll
-            for (int i = 0; i < NCP; i++) cp_async16(d + i * 8 * LIN_LD, valid ? src[i] + pf_it * LIN_SK : src[i], valid);
+            for (int i = 0; i < NCP; i++) {
+                const bool v = valid && ((pf_mask >> i) & 1u);
+                cp_async16(d + i * 8 * LIN_LD, v ? src[i] + pf_it * LIN_SK : src[i], v);
+            }
             pf_slot = pf_slot + 1 == STAGES ? 0 : pf_slot + 1;
-            if (++pf_it == nst) { pf_it = 0; pf_rb += rb_step; if (pf_rb < p.total_rb) pf_setup(); }
+            if (++pf_it == nst) { pf_it = 0; pf_row += pf_rows; if (pf_row < row_end) pf_setup(); }
         }
         cp_async_commit();
     };
-    if (pf_rb < p.total_rb) pf_setup();
+    if (pf_row < row_end) pf_setup();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) pf_issue();          // weights first: they do not depend on x
 
+    TRACE(1);
     pdl_wait();
+    TRACE(2);
 
     // ── this slice's limbs, scale-back factors and limb sums ──
     if (p.fused_x) {
         __shared__ XScratch xsc;
         for (int b = 0; b < p.B; b++)
-            xconvert(p.xsrc, p.N, b, kb_begin * XB, p.slice_kb * XB, xs + (size_t)b * LIN_LIMBS * p.xs_ld, p.xs_ld, BITS == 4 ? 1 : 0,
-                     xsc, s_back + b, s_xsum + b * LIN_LIMBS);
+            xconvert_any(p.xsrc, p.N, b, kb_begin * XB, p.slice_kb * XB, xs + (size_t)b * LIN_LIMBS * p.xs_ld, p.xs_ld, BITS == 4 ? 1 : 0,
+                         xsc, s_back + b, s_xsum + b * LIN_LIMBS);
     } else {
         const uint4* gsrc = reinterpret_cast<const uint4*>(p.xpack + (size_t)ks * p.ncols * p.xs_ld);
         const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(xs);
@@ -312,6 +468,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     }
     cp_async_wait<0>();
     __syncthreads();
+    TRACE(3);
 
     const int8_t* xcol[NCG];
 #pragma unroll
@@ -322,7 +479,9 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     }
 
     int slot = 0;
-    for (int rb = rb_first; rb < p.total_rb; rb += rb_step) {
+    int tile_rows = 0;
+    for (int row0 = row_begin; row0 < row_end; row0 += tile_rows) {
+        tile_rows = min(R, row_end - row0);
         int acc[NACC][RT][NCG][4];
 #pragma unroll
         for (int a = 0; a < NACC; a++)
@@ -377,6 +536,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
             slot = slot + 1 == STAGES ? 0 : slot + 1;
         }
 
+        TRACE(4);
         // ── row block done: every warp holds integer partial sums of all R rows over its k-blocks ──
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
@@ -390,15 +550,11 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
                 }
         }
         __syncthreads();
-        int ti = 0;
-#pragma unroll
-        for (int i = 1; i < 4; i++) if (i < p.n_tensors && rb >= p.t[i].rb_start) ti = i;
-        const LinTensor& T = p.t[ti];
-        const int row0 = (rb - T.rb_start) * R;
         const int B = p.B;
         // one thread per (row, activation): limb sums over the warps, bias, recombination
         for (int e = threadIdx.x; e < R * B; e += W * 32) {
             const int r = e % R, b = e / R;
+            if (r >= tile_rows) continue;
             const int row = row0 + r;
             int limb[LIN_LIMBS];
 #pragma unroll
@@ -415,7 +571,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
                 limb[l] = v;
             }
             if (p.nks == 1) {
-                if (row < T.M) {
+                {
                     const long long V = (((long long)limb[3] * 256 + limb[2]) * 256 + limb[1]) * 256 + limb[0];
                     const float y = (float)((double)V * (double)s_back[b]);
                     const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
@@ -426,34 +582,34 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
             } else {
 #pragma unroll
                 for (int l = 0; l < LIN_LIMBS; l++)
-                    p.partial[(((size_t)rb * p.nks + ks) * (B * LIN_LIMBS) + b * LIN_LIMBS + l) * R + r] = limb[l];
+                    p.partial[((size_t)ks * (B * LIN_LIMBS) + b * LIN_LIMBS + l) * p.total_rows + T.row_start + row] = limb[l];
             }
         }
     }
     cp_async_wait<0>();
+    TRACE(5);
 }
 
 // When the columns are split over several blocks: one thread per (row, activation) recombines the
 // integer partial sums of all slices, each with its own 2^-s, in slice order.
-__global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams p, int R) {
+__global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int B = p.B;
-    const long total = (long)p.total_rb * R * B;
+    const long total = (long)p.total_rows * B;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
-        const int r = (int)(e % R);
-        const int b = (int)((e / R) % B);
-        const int rb = (int)(e / ((long)R * B));
+        const int vrow = (int)(e % p.total_rows);
+        const int b = (int)(e / p.total_rows);
         int ti = 0;
 #pragma unroll
-        for (int i = 1; i < 4; i++) if (i < p.n_tensors && rb >= p.t[i].rb_start) ti = i;
+        for (int i = 1; i < 4; i++) if (i < p.n_tensors && vrow >= p.t[i].row_start) ti = i;
         const LinTensor& T = p.t[ti];
-        const int row = (rb - T.rb_start) * R + r;
-        if (row >= T.M) continue;
+        const int row = vrow - T.row_start;
         double y = 0.0;
         for (int k = 0; k < p.nks; k++) {
-            const int* src_p = p.partial + (((size_t)rb * p.nks + k) * (B * LIN_LIMBS) + b * LIN_LIMBS) * R + r;
-            const long long V = (((long long)src_p[3 * R] * 256 + src_p[2 * R]) * 256 + src_p[R]) * 256 + src_p[0];
+            const int* src_p = p.partial + ((size_t)k * (B * LIN_LIMBS) + b * LIN_LIMBS) * p.total_rows + vrow;
+            const size_t st = p.total_rows;
+            const long long V = (((long long)src_p[3 * st] * 256 + src_p[2 * st]) * 256 + src_p[st]) * 256 + src_p[0];
             y += (double)V * (double)p.xscale[b * p.nks + k];
         }
         const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
@@ -516,6 +672,7 @@ int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int s
         if (stages >= 6) return launch_mma<BITS, NCG, 2, LIN_W, 6>(ctx, p, grid, smem_tail);
         return launch_mma<BITS, NCG, 2, LIN_W, 4>(ctx, p, grid, smem_tail);
     }
+    if (stages >= 9) return launch_mma<BITS, NCG, 1, LIN_W, 9>(ctx, p, grid, smem_tail);
     if (stages >= 8) return launch_mma<BITS, NCG, 1, LIN_W, 8>(ctx, p, grid, smem_tail);
     return launch_mma<BITS, NCG, 1, LIN_W, 4>(ctx, p, grid, smem_tail);
 }
@@ -599,18 +756,21 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     static const int stages_env = env_int("IBCU_LINEAR_STAGES", 0);
     long total_rows = 0;
     for (int i = 0; i < n_tensors; i++) total_rows += tensors[i].M;
-    // 32-row blocks when that still gives every SM a couple of blocks, else 16-row blocks
-    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows < 64L * ctx->sm_count) ? 1 : 2);
+    if (total_rows == 0) return IBCU_OK;
+    // Rows are dealt out evenly: every block of the persistent grid owns one contiguous run of rows and
+    // walks it in tiles of up to R = 16 or 32 rows. 32-row tiles once a block's run is longer than 16.
+    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows <= 16L * 2 * ctx->sm_count) ? 1 : 2);
     const int R = 16 * rt;
     LinearParams p;
     memset(&p, 0, sizeof p);
-    int total_rb = 0;
-    for (int i = 0; i < n_tensors; i++) {
-        p.t[i] = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
-                   tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, total_rb };
-        total_rb += (tensors[i].M + R - 1) / R;
+    {
+        int row_start = 0;
+        for (int i = 0; i < n_tensors; i++) {
+            p.t[i] = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
+                       tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, row_start, 0, 0 };
+            row_start += tensors[i].M;
+        }
     }
-    if (total_rb == 0) return IBCU_OK;
     // Shared memory per block: stage ring + reduction buffer + the slice's fp16 pieces. Columns are
     // split over several blocks only when the pieces of a whole row do not fit.
     const int kbs = LIN_SK / 64;
@@ -619,7 +779,7 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     const size_t whole_row_pieces = (size_t)ncols * ((size_t)nkb * xk + xpad);
     int stages = rt == 2 ? 6 : 8;
     if (2 * ((size_t)stages * R * LIN_LD + red_bytes + whole_row_pieces + 2048) > 227 * 1024) stages = 4;
-    if (stages_env) stages = rt == 2 ? (stages_env >= 6 ? 6 : 4) : (stages_env >= 8 ? 8 : 4);
+    if (stages_env) stages = rt == 2 ? (stages_env >= 6 ? 6 : 4) : (stages_env >= 9 ? 9 : (stages_env >= 8 ? 8 : 4));
     const size_t fixed_smem = (size_t)stages * R * LIN_LD + red_bytes + 1024;
     const size_t smem_cap = 200 * 1024;
     long piece_budget = (long)smem_cap - (long)fixed_smem;
@@ -636,11 +796,29 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     int fit = (int)((227 * 1024) / (fixed_smem + piece_smem + 1024));
     if (fit < 1) fit = 1;
     if (fit > 4) fit = 4;
+    static const int fit_env = env_int("IBCU_LINEAR_FIT", 0);
+    if (fit_env && fit > fit_env) fit = fit_env;
     const int slots = fit * ctx->sm_count;
     int per_slice = slots / nks;
     if (per_slice < 1) per_slice = 1;
-    if (per_slice > total_rb) per_slice = total_rb;
-    const int grid = per_slice * nks;
+    // every tensor gets blocks in proportion to its rows, and its rows are dealt out evenly among them;
+    // the run length grows until all blocks are resident at once
+    int rows_per_block = (int)((total_rows + per_slice - 1) / per_slice);
+    if (rows_per_block < 4) rows_per_block = 4;
+    int nblk;
+    for (;; rows_per_block++) {
+        nblk = 0;
+        for (int i = 0; i < n_tensors; i++) nblk += (tensors[i].M + rows_per_block - 1) / rows_per_block;
+        if (nblk <= per_slice || rows_per_block >= total_rows) break;
+    }
+    nblk = 0;
+    for (int i = 0; i < n_tensors; i++) {
+        const int n = (tensors[i].M + rows_per_block - 1) / rows_per_block;
+        p.t[i].blk_start = nblk;
+        p.t[i].rows_per = n ? (tensors[i].M + n - 1) / n : 0;
+        nblk += n;
+    }
+    const int grid = nblk * nks;
 
     const size_t xpack_bytes = (((size_t)nks * ncols * xs_ld) + 255) & ~(size_t)255;
     const size_t xscale_bytes = (((size_t)B * nks * sizeof(float)) + 255) & ~(size_t)255;
@@ -649,15 +827,18 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     int8_t* xpack = (int8_t*)ctx->xpack;
     float* xscale = (float*)((char*)ctx->xpack + xpack_bytes);
     int* xsum = (int*)((char*)ctx->xpack + xpack_bytes + xscale_bytes);
-    p.n_tensors = n_tensors; p.total_rb = total_rb; p.rowbytes = rowbytes; p.nkb = nkb; p.N = N; p.B = B; p.ncols = ncols;
+    p.n_tensors = n_tensors; p.total_rows = (int)total_rows; p.rowbytes = rowbytes; p.nkb = nkb; p.N = N; p.B = B; p.ncols = ncols;
     p.slice_kb = slice_kb; p.nks = nks; p.xs_ld = xs_ld;
     p.xpack = xpack; p.xscale = xscale; p.xsum = xsum;
     if (nks > 1) {
-        const size_t part_bytes = (size_t)total_rb * nks * R * B * LIN_LIMBS * sizeof(int);
+        const size_t part_bytes = (size_t)total_rows * nks * B * LIN_LIMBS * sizeof(int);
         rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, part_bytes);
         if (rc) return rc;
         p.partial = (int*)ctx->scratch;
     }
+#ifdef IBCU_TRACE
+    { static int seq = 0; p.trace_slot = seq++; }
+#endif
     XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op };
     // Cheap conversions are done by every block of the main kernel for itself (no extra launch, no
     // dependency chain); expensive ones (SiLU, several activations, long rows) once, by xprep_kernel.
@@ -666,10 +847,16 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     if (fuse_env >= 0) fused = fuse_env && nks == 1;
     p.xsrc = xsrc; p.fused_x = fused;
     static const int skip_xprep = env_int("IBCU_LINEAR_SKIP_XPREP", 0);   // timing experiments only: results are then stale
-    const int xthreads = slice_kb * xk >= 8192 ? 1024 : (slice_kb * xk >= 2048 ? 512 : 256);
-    if (!fused && !skip_xprep)
-        rc = ibcu_launch(ctx, xprep_kernel, dim3(nks, B), dim3(xthreads), 0, 1, true, xsrc, N, slice_kb * xk, xs_ld, bits == 4 ? 1 : 0, nks,
-                         xpack, xscale, xsum);
+    // 512 threads hold up to 16384 columns in registers; longer slices take 1024 threads and the looping conversion
+    const int xthreads = slice_kb * xk > XREG_V * 4 * 512 ? 1024 : (slice_kb * xk >= 2048 ? 512 : 256);
+    static const int xregs_env = env_int("IBCU_LINEAR_XREGS", 1);
+    if (!fused && !skip_xprep) {
+        const dim3 xg(nks, B);
+        const int perm8 = bits == 4 ? 1 : 0, cols = slice_kb * xk;
+        rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum)
+           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, xregs_env, xpack, xscale, xsum)
+                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, xregs_env, xpack, xscale, xsum);
+    }
     if (rc) return rc;
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
@@ -682,10 +869,10 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH
     if (rc || nks == 1) return rc;
-    long outs = (long)total_rb * R * B;
+    long outs = total_rows * B;
     int fgrid = (int)((outs + 255) / 256);
     if (fgrid > 4 * ctx->sm_count) fgrid = 4 * ctx->sm_count;
-    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p, R);
+    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p);
 }
 
 // v1: the two projections in one launch, then the element-wise kernel over gate.out.
@@ -699,3 +886,7 @@ extern "C" int ibcu_linear_gate_up_silu(ibcu_ctx* ctx, const ibcu_linear_t* gate
     return ibcu_silu_mul(ctx, gate_up[0].out, gate_up[0].out, gate_up[1].out,
                          (size_t)(B - 1) * gate_up[0].out_stride + gate_up[0].M);
 }
+
+#ifdef IBCU_TRACE
+extern "C" int ibcu_trace_read(void* dst) { return (int)cudaMemcpyFromSymbol(dst, ibcu_trace_buf, sizeof(ibcu_trace_buf)); }
+#endif
