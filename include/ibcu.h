@@ -205,6 +205,12 @@ int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float* v, float*
 /* GQA attention of B query positions against cache rows 0..pos0+b (src/forward.c:463-504). */
 int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const float* v_cache, float* out,
                    int n_heads, int n_kv_heads, int head_dim, int pos0, int B);
+/* The attention step of a decode layer in one call: what ibcu_rope_kv_write followed by ibcu_attention
+ * computes for out and for the cache rows pos0..pos0+B-1 (src/forward.c:577-593 and 463-504). q and k
+ * hold the raw projections and are left as they are (the reference rotates its scratch copies in
+ * place; nothing reads them afterwards). */
+int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
+                          int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta);
 int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n);
 int ibcu_add_inplace(ibcu_ctx* ctx, float* x, const float* y, size_t n);
 int ibcu_softmax(ibcu_ctx* ctx, float* data, int N, int rows);

@@ -57,6 +57,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ out, 
     for (int i = threadIdx.x; i < N; i += blockDim.x) ob[i] = xb[i] * r * (float)w[i];
 }
 
+// Rotation of pair m of a head at position pos (src/kernels/scalar.c:140-157).
+__device__ __forceinline__ void rope_pair(float a0, float a1, int m, int hd, int pos, float theta, float& r0, float& r1) {
+    const float freq = 1.0f / powf(theta, (float)(2 * m) / (float)hd);
+    const float ang = (float)pos * freq;
+    const float c = cosf(ang), s = sinf(ang);
+    r0 = a0 * c - a1 * s; r1 = a0 * s + a1 * c;
+}
+
 // grid (Q heads + K heads, B): one block per head and position, one thread per rotated pair. Each K
 // head is rotated once (the reference does it through the first Q head of its group) and stored,
 // with its V row, at cache row pos0 + b.
@@ -70,11 +78,8 @@ __global__ void __launch_bounds__(128) rope_kv_write_kernel(float* __restrict__ 
     const bool is_k = h >= n_heads;
     float* p = is_k ? k + (size_t)b * kv_dim + (size_t)(h - n_heads) * hd : q + (size_t)b * n_heads * hd + (size_t)h * hd;
     for (int m = threadIdx.x; m < half; m += blockDim.x) {
-        const float freq = 1.0f / powf(theta, (float)(2 * m) / (float)hd);
-        const float ang = (float)pos * freq;
-        const float c = cosf(ang), s = sinf(ang);
-        const float a0 = p[2 * m], a1 = p[2 * m + 1];
-        const float r0 = a0 * c - a1 * s, r1 = a0 * s + a1 * c;
+        float r0, r1;
+        rope_pair(p[2 * m], p[2 * m + 1], m, hd, pos, theta, r0, r1);
         p[2 * m] = r0; p[2 * m + 1] = r1;
         if (is_k && k_cache) {
             float* dst = k_cache + (size_t)pos * kv_dim + (size_t)(h - n_heads) * hd + 2 * m;
@@ -141,12 +146,19 @@ __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict_
 // query heads broadcast from shared memory), the block forms the chunk-local softmax weights, then
 // thread d accumulates dimension d of the weighted V sum. Chunk results (max, sum, weighted sum) go to
 // scratch; attn_combine_kernel merges the chunks of a head with the usual max/sum rescaling.
+// With k_new set the kernel is the whole attention step of a decode layer: q and k_new / v_new are
+// the raw projections of positions pos0..pos0+B-1; the queries are rotated as they are loaded, tile
+// rows of those positions are built from k_new / v_new (rotated) instead of being read from the cache,
+// and the block whose own position is such a row also stores it in the cache. No block reads a cache
+// row that another block of the same launch writes.
 constexpr int ATT_GMAX = 8;          // query heads per KV head handled by the split path
 constexpr int ATT_T = 128;           // threads = positions per chunk
 
 __global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                              const float* __restrict__ v_cache, float* __restrict__ part,
-                                                             int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit) {
+                                                             int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit,
+                                                             const float* __restrict__ k_new, const float* __restrict__ v_new,
+                                                             float* __restrict__ k_cache_w, float* __restrict__ v_cache_w, float theta) {
     extern __shared__ __align__(16) float asm_[];
     const int group = n_heads / n_kv;
     const int ld = hd + 4;                          // padded tile rows: conflict-free float4 reads down a column of rows
@@ -164,7 +176,8 @@ __global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __rest
     {
         const int per_row = hd / 4;
         const uint32_t kd = (uint32_t)__cvta_generic_to_shared(kt), vd = (uint32_t)__cvta_generic_to_shared(vt);
-        for (int e = tid; e < n * per_row; e += ATT_T) {
+        const int n_old = k_new ? max(0, min(n, pos0 - t0)) : n;      // rows that are in the cache already
+        for (int e = tid; e < n_old * per_row; e += ATT_T) {
             const int r = e / per_row, c = e - r * per_row;
             const size_t g = (size_t)(t0 + r) * kv_dim + (size_t)kvh * hd + 4 * c;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(kd + (r * ld + 4 * c) * 4), "l"(k_cache + g) : "memory");
@@ -172,7 +185,30 @@ __global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __rest
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    for (int e = tid; e < group * hd; e += ATT_T) qs[e] = q[((size_t)b * n_heads + (size_t)kvh * group) * hd + e];
+    if (k_new) {
+        const int half = hd / 2, r_first = max(t0, pos0);
+        for (int e = tid; e < group * half; e += ATT_T) {
+            const int g = e / half, m = e - g * half;
+            const float* src = q + ((size_t)b * n_heads + (size_t)kvh * group + g) * hd;
+            rope_pair(src[2 * m], src[2 * m + 1], m, hd, pos, theta, qs[g * hd + 2 * m], qs[g * hd + 2 * m + 1]);
+        }
+        for (int e = tid; e < (t1 - r_first) * half; e += ATT_T) {     // this step's K rows: rotate, use, and store the block's own
+            const int rr = e / half, m = e - rr * half, t = r_first + rr;
+            const float* src = k_new + (size_t)(t - pos0) * kv_dim + (size_t)kvh * hd;
+            float r0, r1;
+            rope_pair(src[2 * m], src[2 * m + 1], m, hd, t, theta, r0, r1);
+            kt[(size_t)(t - t0) * ld + 2 * m] = r0; kt[(size_t)(t - t0) * ld + 2 * m + 1] = r1;
+            if (t == pos) { float* dst = k_cache_w + (size_t)t * kv_dim + (size_t)kvh * hd + 2 * m; dst[0] = r0; dst[1] = r1; }
+        }
+        for (int e = tid; e < (t1 - r_first) * hd; e += ATT_T) {
+            const int rr = e / hd, d = e - rr * hd, t = r_first + rr;
+            const float vv = v_new[(size_t)(t - pos0) * kv_dim + (size_t)kvh * hd + d];
+            vt[(size_t)(t - t0) * ld + d] = vv;
+            if (t == pos) v_cache_w[(size_t)t * kv_dim + (size_t)kvh * hd + d] = vv;
+        }
+    } else {
+        for (int e = tid; e < group * hd; e += ATT_T) qs[e] = q[((size_t)b * n_heads + (size_t)kvh * group) * hd + e];
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)hd);
@@ -341,14 +377,16 @@ extern "C" int ibcu_rope_kv_write(ibcu_ctx* ctx, float* q, float* k, const float
                        n_heads, n_kv_heads, head_dim, pos0, theta);
 }
 
-extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const float* v_cache, float* out,
-                              int n_heads, int n_kv_heads, int head_dim, int pos0, int B) {
-    IBCU_CHECK_CTX(ctx);
-    IBCU_REQUIRE(ctx, q && k_cache && v_cache && out, "ibcu_attention: null pointer");
-    IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && pos0 >= 0 && B > 0,
-                 "ibcu_attention: bad shape");
+static bool attn_split_ok(const float* q, const float* k_cache, const float* v_cache, int n_heads, int n_kv_heads, int head_dim) {
+    return n_heads / n_kv_heads <= ATT_GMAX && head_dim % 4 == 0 && head_dim <= 256 &&
+           ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0;
+}
+
+// k_new / v_new NULL: q is rotated already and the cache holds rows 0..pos0+B-1. Otherwise the fused decode step.
+static int attention_split(ibcu_ctx* ctx, const float* q, float* k_cache, float* v_cache, float* out,
+                           int n_heads, int n_kv_heads, int head_dim, int pos0, int B, const float* k_new, const float* v_new, float theta) {
     const int group = n_heads / n_kv_heads;
-    if (group <= ATT_GMAX && head_dim % 4 == 0 && head_dim <= 256 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0) {
+    {
         // split path: chunks of up to 128 cache positions per block, merged by a second small kernel
         const int cap = pos0 + B;
         int nsplit = (cap + ATT_T - 1) / ATT_T;
@@ -361,17 +399,42 @@ extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cach
         const size_t smem = ((size_t)group * head_dim + (size_t)group * ATT_T + group * 4 + 2 * (size_t)chunk * (head_dim + 4)) * sizeof(float);
         if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, nsplit, B), dim3(ATT_T), smem, 1, true,
-                         q, k_cache, v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit);
+                         q, (const float*)k_cache, (const float*)v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit,
+                         k_new, v_new, k_cache, v_cache, theta);
         if (rc) return rc;
         return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), 0, 1, true,
                            (const float*)ctx->scratch, out, n_heads, head_dim, nsplit);
     }
+}
+
+extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const float* v_cache, float* out,
+                              int n_heads, int n_kv_heads, int head_dim, int pos0, int B) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, q && k_cache && v_cache && out, "ibcu_attention: null pointer");
+    IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && pos0 >= 0 && B > 0,
+                 "ibcu_attention: bad shape");
+    if (attn_split_ok(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim))
+        return attention_split(ctx, q, (float*)k_cache, (float*)v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, nullptr, nullptr, 0.0f);
     int cap = pos0 + B;
     size_t smem = ((size_t)cap + 8 * (size_t)head_dim) * sizeof(float);
     IBCU_REQUIRE(ctx, smem <= 200 * 1024, "ibcu_attention: context %d too long for one block's shared memory", cap);
     if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     return ibcu_launch(ctx, attention_kernel, dim3(n_heads, B), dim3(256), smem, 1, true, q, k_cache, v_cache, out,
                        n_heads, n_kv_heads, head_dim, pos0, cap);
+}
+
+extern "C" int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
+                                     int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, q && k && v && k_cache && v_cache && out, "ibcu_attention_decode: null pointer");
+    IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && (head_dim & 1) == 0 && pos0 >= 0 && B > 0,
+                 "ibcu_attention_decode: bad shape heads=%d kv=%d hd=%d pos0=%d B=%d", n_heads, n_kv_heads, head_dim, pos0, B);
+    if (attn_split_ok(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim))
+        return attention_split(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, k, v, theta);
+    // shapes the split kernel does not take: the two steps one after the other
+    int rc = ibcu_rope_kv_write(ctx, q, k, v, k_cache, v_cache, n_heads, n_kv_heads, head_dim, pos0, B, theta);
+    if (rc) return rc;
+    return ibcu_attention(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B);
 }
 
 extern "C" int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n) {

@@ -366,8 +366,8 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #else
 #define TRACE(i) do { } while (0)
 #endif
-constexpr int LIN_SK = 512;                                   // bytes per row per stage
-constexpr int LIN_LD = LIN_SK + 64;                           // padded row stride: conflict-free fragment reads
+__host__ __device__ constexpr int lin_sk(int W) { return W * 64; }                // bytes per row per stage: one 64-byte k-block per warp
+__host__ __device__ constexpr int lin_ld(int W) { return W * 64 + 64; }           // padded row stride: conflict-free fragment reads
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {
     const int n = valid ? 16 : 0;                             // 0 source bytes -> 16 zero bytes
@@ -382,9 +382,10 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     constexpr int COLS = NCG * 8;
     constexpr int NACC = BITS == 4 ? 2 : 1;                   // INT4 keeps low- and high-nibble sums apart
     constexpr int XB = BITS == 8 ? 64 : 128;                  // limb bytes (= columns) per k-block
-    constexpr int KBS = LIN_SK / 64;                          // k-blocks per stage
-    static_assert(KBS == W, "one k-block of every stage per warp");
-    static_assert(W == 8, "copy lanes assume 256 threads");
+    constexpr int KBS = W;                                    // k-blocks per stage: one per warp
+    constexpr int LIN_SK = lin_sk(W), LIN_LD = lin_ld(W);
+    constexpr int CPR = LIN_SK / 16;                          // 16-byte chunks per row per stage; the block copies 8 rows per pass
+    static_assert(W == 4 || W == 8, "4 or 8 warps");
     constexpr int STAGE_BYTES = R * LIN_LD;
     constexpr int NCP = RT * 2;                               // 16-byte chunks per thread per stage
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -410,16 +411,16 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     float* s_back = reinterpret_cast<float*>(xs + (((size_t)p.ncols * p.xs_ld + 15) & ~(size_t)15));
     int* s_xsum = reinterpret_cast<int*>(s_back + 32);
 
-    // ── producer side: thread owns chunk column cc of rows (tid>>5) + 8i of every stage ──
-    const int cc = threadIdx.x & 31;
-    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + (threadIdx.x >> 5) * LIN_LD + cc * 16;
+    // ── producer side: thread owns chunk column cc of rows pr + 8i of every stage ──
+    const int cc = threadIdx.x % CPR, pr = threadIdx.x / CPR;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + pr * LIN_LD + cc * 16;
     const uint8_t* src[NCP];
     // A tile is up to R consecutive rows; rows of the tile that do not exist are zero-filled.
     int pf_row = row_begin, pf_rows = 0, pf_it = 0, pf_slot = 0;
-    unsigned pf_mask = 0;                                     // bit i: row (tid>>5) + 8i exists in the tile
+    unsigned pf_mask = 0;                                     // bit i: row pr + 8i exists in the tile
     auto pf_setup = [&]() {                                   // row pointers for the tile at pf_row
         pf_rows = min(R, row_end - pf_row);
-        const int r0 = threadIdx.x >> 5;
+        const int r0 = pr;
         pf_mask = 0;
 #pragma unroll
         for (int i = 0; i < NCP; i++) {
@@ -656,7 +657,7 @@ __global__ void __launch_bounds__(256) linear_generic_kernel(LinTensor T, const 
 template <int BITS, int NCG, int RT, int W, int STAGES>
 int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail) {
     auto kern = linear_mma_kernel<BITS, NCG, RT, W, STAGES>;
-    const size_t smem = (size_t)STAGES * RT * 16 * LIN_LD + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * NCG * 8 * 4 + smem_tail;
+    const size_t smem = (size_t)STAGES * RT * 16 * lin_ld(W) + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * NCG * 8 * 4 + smem_tail;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
@@ -664,17 +665,22 @@ int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail)
     return ibcu_launch(ctx, kern, dim3(grid), dim3(W * 32), smem, 1, true, p);
 }
 
-constexpr int LIN_W = 8;
-
+// Ring depths: 8 warps x 512-byte stages for long streams; 4 warps x 256-byte stages (four blocks per SM) when
+// the launch is short, so that the blocks of the next launch fit beside this one's and fetch their
+// weights while this one still computes.
 template <int BITS, int NCG>
-int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int stages, size_t smem_tail) {
-    if (rt == 2) {
-        if (stages >= 6) return launch_mma<BITS, NCG, 2, LIN_W, 6>(ctx, p, grid, smem_tail);
-        return launch_mma<BITS, NCG, 2, LIN_W, 4>(ctx, p, grid, smem_tail);
+int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int w, int stages, size_t smem_tail) {
+    if (w == 4) {
+        if (rt == 2) return launch_mma<BITS, NCG, 2, 4, 4>(ctx, p, grid, smem_tail);
+        return launch_mma<BITS, NCG, 1, 4, 6>(ctx, p, grid, smem_tail);
     }
-    if (stages >= 9) return launch_mma<BITS, NCG, 1, LIN_W, 9>(ctx, p, grid, smem_tail);
-    if (stages >= 8) return launch_mma<BITS, NCG, 1, LIN_W, 8>(ctx, p, grid, smem_tail);
-    return launch_mma<BITS, NCG, 1, LIN_W, 4>(ctx, p, grid, smem_tail);
+    if (rt == 2) {
+        if (stages >= 6) return launch_mma<BITS, NCG, 2, 8, 6>(ctx, p, grid, smem_tail);
+        return launch_mma<BITS, NCG, 2, 8, 4>(ctx, p, grid, smem_tail);
+    }
+    if (stages >= 9) return launch_mma<BITS, NCG, 1, 8, 9>(ctx, p, grid, smem_tail);
+    if (stages >= 8) return launch_mma<BITS, NCG, 1, 8, 8>(ctx, p, grid, smem_tail);
+    return launch_mma<BITS, NCG, 1, 8, 4>(ctx, p, grid, smem_tail);
 }
 
 }  // namespace
@@ -754,12 +760,14 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     static const int rt_env = env_int("IBCU_LINEAR_RT", 0);
     static const int nks_env = env_int("IBCU_LINEAR_NKS", 0);
     static const int stages_env = env_int("IBCU_LINEAR_STAGES", 0);
+    static const int w_env = env_int("IBCU_LINEAR_W", 0);
     long total_rows = 0;
     for (int i = 0; i < n_tensors; i++) total_rows += tensors[i].M;
     if (total_rows == 0) return IBCU_OK;
     // Rows are dealt out evenly: every block of the persistent grid owns one contiguous run of rows and
     // walks it in tiles of up to R = 16 or 32 rows. 32-row tiles once a block's run is longer than 16.
-    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows <= 16L * 2 * ctx->sm_count) ? 1 : 2);
+    const int w = w_env == 4 ? 4 : 8;                        // warps per block; four blocks of 4 warps or two of 8 share an SM
+    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows <= 16L * (w == 4 ? 4 : 2) * ctx->sm_count) ? 1 : 2);
     const int R = 16 * rt;
     LinearParams p;
     memset(&p, 0, sizeof p);
@@ -773,13 +781,17 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     }
     // Shared memory per block: stage ring + reduction buffer + the slice's fp16 pieces. Columns are
     // split over several blocks only when the pieces of a whole row do not fit.
-    const int kbs = LIN_SK / 64;
+    const int kbs = w;
+    const int LIN_LD = lin_ld(w);
     // ring depth: the deeper ring when two blocks per SM still fit with it, else the shallower one
-    const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * LIN_W * R * ncg * 8 * 4;
+    const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * w * R * ncg * 8 * 4;
     const size_t whole_row_pieces = (size_t)ncols * ((size_t)nkb * xk + xpad);
     int stages = rt == 2 ? 6 : 8;
+    if (w == 4) stages = rt == 2 ? 4 : 6;
+    else {
     if (2 * ((size_t)stages * R * LIN_LD + red_bytes + whole_row_pieces + 2048) > 227 * 1024) stages = 4;
     if (stages_env) stages = rt == 2 ? (stages_env >= 6 ? 6 : 4) : (stages_env >= 9 ? 9 : (stages_env >= 8 ? 8 : 4));
+    }
     const size_t fixed_smem = (size_t)stages * R * LIN_LD + red_bytes + 1024;
     const size_t smem_cap = 200 * 1024;
     long piece_budget = (long)smem_cap - (long)fixed_smem;
@@ -861,10 +873,10 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
     switch (ncg) { \
-        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, grid, rt, stages, smem); break; \
-        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, grid, rt, stages, smem); break; \
-        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, grid, rt, stages, smem); break; \
-        default: rc = dispatch_shape<BITS, 8>(ctx, p, grid, rt, stages, smem); break; \
+        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, grid, rt, w, stages, smem); break; \
+        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, grid, rt, w, stages, smem); break; \
+        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, grid, rt, w, stages, smem); break; \
+        default: rc = dispatch_shape<BITS, 8>(ctx, p, grid, rt, w, stages, smem); break; \
     }
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH

@@ -222,10 +222,9 @@ static int issue(ib_b200_model* m, int pos0, int B) {
         if (!rc) rc = gather(m, &y->t[IB_B200_Q], m->q, B);
         if (!rc) rc = gather(m, &y->t[IB_B200_K], m->k, B);
         if (!rc) rc = gather(m, &y->t[IB_B200_V], m->v, B);
-        if (!rc) rc = ibcu_rope_kv_write(ctx, m->q, m->k, m->v, (float*)y->k_cache, (float*)y->v_cache,
-                                         c->n_heads, c->n_kv_heads, c->head_dim, pos0, B, c->theta);
-        if (!rc) rc = ibcu_attention(ctx, m->q, (const float*)y->k_cache, (const float*)y->v_cache, m->att,
-                                     c->n_heads, c->n_kv_heads, c->head_dim, pos0, B);
+        /* RoPE, the KV-cache write and the attention itself are one step on the device */
+        if (!rc) rc = ibcu_attention_decode(ctx, m->q, m->k, m->v, (float*)y->k_cache, (float*)y->v_cache, m->att,
+                                            c->n_heads, c->n_kv_heads, c->head_dim, pos0, B, c->theta);
         /* o_proj and down_proj add straight into the residual stream (src/forward.c:620-622, 644-646) */
         ibcu_linear_t o = desc(&y->t[IB_B200_O], m->x, IBCU_EPI_ADD);
         if (!rc) rc = ibcu_linear(ctx, &o, 1, m->att, H, B, c->attn_bits);

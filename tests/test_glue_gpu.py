@@ -51,8 +51,12 @@ def test_rmsnorm_silu_softmax_add_embed(backend, cpu_libs):
     assert np.array_equal(be.download(dxo, np.float32, 3 * H).reshape(3, H), emb[toks].astype(np.float32) * esf[toks][:, None])
 
 
-@pytest.mark.parametrize("n_heads,n_kv,hd,pos0,B", [(32, 8, 128, 512, 1), (32, 8, 128, 512, 8), (4, 4, 64, 0, 3), (8, 2, 32, 5, 2)])
-def test_rope_kv_write_and_attention(backend, cpu_libs, n_heads, n_kv, hd, pos0, B):
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("n_heads,n_kv,hd,pos0,B", [(32, 8, 128, 512, 1), (32, 8, 128, 512, 8), (4, 4, 64, 0, 3), (8, 2, 32, 5, 2),
+                                                     (32, 8, 128, 0, 1), (32, 8, 128, 127, 3), (16, 1, 64, 300, 2), (12, 12, 20, 40, 2)])
+def test_rope_kv_write_and_attention(backend, cpu_libs, n_heads, n_kv, hd, pos0, B, fused):
+    """fused=False: ibcu_rope_kv_write then ibcu_attention; fused=True: ibcu_attention_decode, which must
+    give the same output and cache rows and leave q and k as they were."""
     rng = np.random.default_rng(n_heads + hd + pos0 + B)
     be, o = backend, cpu_libs.oracle
     kv_dim, H, ctx_len = n_kv * hd, n_heads * hd, pos0 + B
@@ -61,8 +65,11 @@ def test_rope_kv_write_and_attention(backend, cpu_libs, n_heads, n_kv, hd, pos0,
     kc = rng.standard_normal((ctx_len, kv_dim)).astype(np.float32); vc = rng.standard_normal((ctx_len, kv_dim)).astype(np.float32)
     dq, dk, dv, dkc, dvc = be.upload(q), be.upload(k), be.upload(v), be.upload(kc), be.upload(vc)
     dout = be.alloc(B * H * 4)
-    be._check(be.lib.ibcu_rope_kv_write(be.ctx, dq.ptr, dk.ptr, dv.ptr, dkc.ptr, dvc.ptr, n_heads, n_kv, hd, pos0, B, 10000.0))
-    be._check(be.lib.ibcu_attention(be.ctx, dq.ptr, dkc.ptr, dvc.ptr, dout.ptr, n_heads, n_kv, hd, pos0, B))
+    if fused:
+        be._check(be.lib.ibcu_attention_decode(be.ctx, dq.ptr, dk.ptr, dv.ptr, dkc.ptr, dvc.ptr, dout.ptr, n_heads, n_kv, hd, pos0, B, 10000.0))
+    else:
+        be._check(be.lib.ibcu_rope_kv_write(be.ctx, dq.ptr, dk.ptr, dv.ptr, dkc.ptr, dvc.ptr, n_heads, n_kv, hd, pos0, B, 10000.0))
+        be._check(be.lib.ibcu_attention(be.ctx, dq.ptr, dkc.ptr, dvc.ptr, dout.ptr, n_heads, n_kv, hd, pos0, B))
     be.sync()
     # CPU: same sequence as src/forward.c:745-784
     group = n_heads // n_kv
@@ -82,8 +89,12 @@ def test_rope_kv_write_and_attention(backend, cpu_libs, n_heads, n_kv, hd, pos0,
             sc = (kcr[:pos + 1, kvh * hd:(kvh + 1) * hd] @ qr[b, h * hd:(h + 1) * hd]).astype(np.float32) * np.float32(1.0 / np.sqrt(np.float32(hd)))
             sc = np.ascontiguousarray(sc, np.float32); o.ibo_softmax(sc, pos + 1)
             want[b, h * hd:(h + 1) * hd] = sc @ vcr[:pos + 1, kvh * hd:(kvh + 1) * hd]
-    assert _cpu.close(be.download(dq, np.float32, B * H).reshape(B, H), qr, RTOL, ATOL)
-    assert _cpu.close(be.download(dk, np.float32, B * kv_dim).reshape(B, kv_dim), kr, RTOL, ATOL)
+    if fused and n_heads // n_kv <= 8 and hd % 4 == 0:
+        assert np.array_equal(be.download(dq, np.float32, B * H).reshape(B, H), q)
+        assert np.array_equal(be.download(dk, np.float32, B * kv_dim).reshape(B, kv_dim), k)
+    else:
+        assert _cpu.close(be.download(dq, np.float32, B * H).reshape(B, H), qr, RTOL, ATOL)
+        assert _cpu.close(be.download(dk, np.float32, B * kv_dim).reshape(B, kv_dim), kr, RTOL, ATOL)
     assert _cpu.close(be.download(dkc, np.float32, ctx_len * kv_dim).reshape(ctx_len, kv_dim), kcr, RTOL, ATOL)
     assert np.array_equal(be.download(dvc, np.float32, ctx_len * kv_dim).reshape(ctx_len, kv_dim), vcr)
     assert _cpu.close(be.download(dout, np.float32, B * H).reshape(B, H), want, RTOL, ATOL)
