@@ -5,6 +5,13 @@
 #include "common.cuh"
 
 namespace {
+#ifdef IBCU_TRACE
+__device__ unsigned long long att_trace_buf[2][512][8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define ATRACE(k, i) do { if (threadIdx.x == 0) { int bid = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); if (bid < 512) att_trace_buf[k][bid][i] = gtime(); } } while (0)
+#else
+#define ATRACE(k, i) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(256) embed_int8_kernel(const int8_t* __restrict__ embed, const __half* __restrict__ scale,
                                                          const int32_t* __restrict__ tokens, float* __restrict__ x, int hidden) {
@@ -140,59 +147,59 @@ __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict_
 }
 
 // ── split attention for decode ──────────────────────────────────────────────────────────
-// attn_partial_kernel: grid (kv heads, position chunks, B). A block owns one KV head, so the K and V
-// rows it reads serve all query heads of the group, and one chunk of cache positions. Thread t of the
-// block scores position t of the chunk for every query head of the group (K row read as float4s, the
-// query heads broadcast from shared memory), the block forms the chunk-local softmax weights, then
-// thread d accumulates dimension d of the weighted V sum. Chunk results (max, sum, weighted sum) go to
-// scratch; attn_combine_kernel merges the chunks of a head with the usual max/sum rescaling.
+// attn_partial_kernel: grid (kv heads, position chunks, B), one warp per query head of the group. A
+// block owns one KV head, so the K and V rows it stages in shared memory serve all query heads of the
+// group, and one chunk of cache positions. After the tile has landed the warps do not synchronise
+// again: a warp walks the chunk 32 rows at a time (lane = row for the scores, lane = dimension for the
+// weighted V sum) keeping a running max / sum / accumulator. Chunk results (max, sum, weighted sum) go to
+// scratch rows of hd + 4 floats; attn_combine_kernel merges the chunks of a head with the usual
+// max/sum rescaling.
 // With k_new set the kernel is the whole attention step of a decode layer: q and k_new / v_new are
 // the raw projections of positions pos0..pos0+B-1; the queries are rotated as they are loaded, tile
 // rows of those positions are built from k_new / v_new (rotated) instead of being read from the cache,
 // and the block whose own position is such a row also stores it in the cache. No block reads a cache
 // row that another block of the same launch writes.
-constexpr int ATT_GMAX = 8;          // query heads per KV head handled by the split path
-constexpr int ATT_T = 128;           // threads = positions per chunk
+constexpr int ATT_GMAX = 8;          // query heads per KV head handled by the split path (warps per block)
+constexpr int ATT_CHUNK = 128;       // most cache positions per block
 
-__global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+__global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                              const float* __restrict__ v_cache, float* __restrict__ part,
                                                              int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit,
                                                              const float* __restrict__ k_new, const float* __restrict__ v_new,
                                                              float* __restrict__ k_cache_w, float* __restrict__ v_cache_w, float theta) {
     extern __shared__ __align__(16) float asm_[];
-    const int group = n_heads / n_kv;
+    const int group = n_heads / n_kv;               // = warps in the block
     const int ld = hd + 4;                          // padded tile rows: conflict-free float4 reads down a column of rows
     float* qs = asm_;                               // [group][hd]
-    float* ps = qs + group * hd;                    // [group][ATT_T] scores, then weights
-    float* red = ps + group * ATT_T;                // [group][4]
-    float* kt = red + group * 4;                    // [chunk][ld]
+    float* ps = qs + group * hd;                    // [group][32]
+    float* kt = ps + group * 32;                    // [chunk][ld]
     float* vt = kt + (size_t)chunk * ld;            // [chunk][ld]
+    ATRACE(0, 0);
     pdl_launch_dependents();
     pdl_wait();
+    ATRACE(0, 1);
     const int kvh = blockIdx.x, sp = blockIdx.y, b = blockIdx.z, pos = pos0 + b;
-    const int kv_dim = n_kv * hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kv_dim = n_kv * hd, tid = threadIdx.x, lane = tid & 31, g = tid >> 5, nth = blockDim.x;
     const int t0 = sp * chunk, t1 = min(pos + 1, t0 + chunk), n = max(0, t1 - t0);
-    // the whole K and V tile of this chunk goes in flight at once (one memory round trip)
+    // the K and V rows of this chunk that the cache holds go in flight at once (one memory round trip)
     {
         const int per_row = hd / 4;
         const uint32_t kd = (uint32_t)__cvta_generic_to_shared(kt), vd = (uint32_t)__cvta_generic_to_shared(vt);
-        const int n_old = k_new ? max(0, min(n, pos0 - t0)) : n;      // rows that are in the cache already
-        for (int e = tid; e < n_old * per_row; e += ATT_T) {
+        const int n_old = k_new ? max(0, min(n, pos0 - t0)) : n;
+        for (int e = tid; e < n_old * per_row; e += nth) {
             const int r = e / per_row, c = e - r * per_row;
-            const size_t g = (size_t)(t0 + r) * kv_dim + (size_t)kvh * hd + 4 * c;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(kd + (r * ld + 4 * c) * 4), "l"(k_cache + g) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(vd + (r * ld + 4 * c) * 4), "l"(v_cache + g) : "memory");
+            const size_t go = (size_t)(t0 + r) * kv_dim + (size_t)kvh * hd + 4 * c;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(kd + (r * ld + 4 * c) * 4), "l"(k_cache + go) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(vd + (r * ld + 4 * c) * 4), "l"(v_cache + go) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    const float* qh = q + ((size_t)b * n_heads + (size_t)kvh * group + g) * hd;
     if (k_new) {
         const int half = hd / 2, r_first = max(t0, pos0);
-        for (int e = tid; e < group * half; e += ATT_T) {
-            const int g = e / half, m = e - g * half;
-            const float* src = q + ((size_t)b * n_heads + (size_t)kvh * group + g) * hd;
-            rope_pair(src[2 * m], src[2 * m + 1], m, hd, pos, theta, qs[g * hd + 2 * m], qs[g * hd + 2 * m + 1]);
-        }
-        for (int e = tid; e < (t1 - r_first) * half; e += ATT_T) {     // this step's K rows: rotate, use, and store the block's own
+        for (int m = lane; m < half; m += 32)
+            rope_pair(qh[2 * m], qh[2 * m + 1], m, hd, pos, theta, qs[g * hd + 2 * m], qs[g * hd + 2 * m + 1]);
+        for (int e = tid; e < (t1 - r_first) * half; e += nth) {       // this step's K rows: rotate, use, and store the block's own
             const int rr = e / half, m = e - rr * half, t = r_first + rr;
             const float* src = k_new + (size_t)(t - pos0) * kv_dim + (size_t)kvh * hd;
             float r0, r1;
@@ -200,109 +207,103 @@ __global__ void __launch_bounds__(ATT_T) attn_partial_kernel(const float* __rest
             kt[(size_t)(t - t0) * ld + 2 * m] = r0; kt[(size_t)(t - t0) * ld + 2 * m + 1] = r1;
             if (t == pos) { float* dst = k_cache_w + (size_t)t * kv_dim + (size_t)kvh * hd + 2 * m; dst[0] = r0; dst[1] = r1; }
         }
-        for (int e = tid; e < (t1 - r_first) * hd; e += ATT_T) {
+        for (int e = tid; e < (t1 - r_first) * hd; e += nth) {
             const int rr = e / hd, d = e - rr * hd, t = r_first + rr;
             const float vv = v_new[(size_t)(t - pos0) * kv_dim + (size_t)kvh * hd + d];
             vt[(size_t)(t - t0) * ld + d] = vv;
             if (t == pos) v_cache_w[(size_t)t * kv_dim + (size_t)kvh * hd + d] = vv;
         }
     } else {
-        for (int e = tid; e < group * hd; e += ATT_T) qs[e] = q[((size_t)b * n_heads + (size_t)kvh * group) * hd + e];
+        for (int d = lane; d < hd; d += 32) qs[g * hd + d] = qh[d];
     }
+    ATRACE(0, 2);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    ATRACE(0, 3);
     const float scale = 1.0f / sqrtf((float)hd);
-    float sc[ATT_GMAX];
-#pragma unroll
-    for (int g = 0; g < ATT_GMAX; g++) sc[g] = 0.0f;
-    if (tid < n) {
-        const float4* kr = reinterpret_cast<const float4*>(kt + (size_t)tid * ld);
-        for (int d4 = 0; d4 < hd / 4; d4++) {
-            const float4 kk = kr[d4];
-#pragma unroll
-            for (int g = 0; g < ATT_GMAX; g++) {
-                if (g >= group) break;
-                const float4 qq = *reinterpret_cast<const float4*>(qs + g * hd + 4 * d4);
-                sc[g] = fmaf(qq.x, kk.x, fmaf(qq.y, kk.y, fmaf(qq.z, kk.z, fmaf(qq.w, kk.w, sc[g]))));
+    const float4* q4 = reinterpret_cast<const float4*>(qs + g * hd);
+    const int hd4 = hd / 4, ld4 = ld / 4;
+    const float4* vt4 = reinterpret_cast<const float4*>(vt);
+    float* pwarp = ps + g * 32;                      // this warp's weights of the current 32 rows
+    float m_run = -INFINITY, l_run = 0.0f;
+    float4 acc[2];                                   // lane owns dimensions 4*lane..4*lane+3 (and 128 + those when hd > 128)
+    acc[0] = acc[1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const bool own0 = lane < hd4, own1 = lane + 32 < hd4;
+    for (int r0 = 0; r0 < n; r0 += 32) {
+        const int row = r0 + lane;
+        float sc = -INFINITY;
+        if (row < n) {
+            const float4* kr = reinterpret_cast<const float4*>(kt + (size_t)row * ld);
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;           // four chains: the sum order is fixed, the latency a quarter
+#pragma unroll 8
+            for (int d4 = 0; d4 < hd4; d4++) {
+                const float4 kk = kr[d4], qq = q4[d4];
+                s0 = fmaf(qq.x, kk.x, s0); s1 = fmaf(qq.y, kk.y, s1); s2 = fmaf(qq.z, kk.z, s2); s3 = fmaf(qq.w, kk.w, s3);
             }
+            sc = ((s0 + s1) + (s2 + s3)) * scale;
+        }
+        const float m_new = fmaxf(m_run, warp_max(sc));
+        const float pw = row < n ? expf(sc - m_new) : 0.0f;
+        const float corr = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
+        l_run = l_run * corr + warp_sum(pw);
+        m_run = m_new;
+        __syncwarp();
+        pwarp[lane] = pw;
+        __syncwarp();
+        acc[0].x *= corr; acc[0].y *= corr; acc[0].z *= corr; acc[0].w *= corr;
+        acc[1].x *= corr; acc[1].y *= corr; acc[1].z *= corr; acc[1].w *= corr;
+        const int cnt = min(32, n - r0);
+        const float4* vrow = vt4 + (size_t)r0 * ld4 + lane;
+#pragma unroll 8
+        for (int t = 0; t < cnt; t++) {
+            const float pt = pwarp[t];
+            if (own0) { const float4 v = vrow[(size_t)t * ld4]; acc[0].x = fmaf(pt, v.x, acc[0].x); acc[0].y = fmaf(pt, v.y, acc[0].y); acc[0].z = fmaf(pt, v.z, acc[0].z); acc[0].w = fmaf(pt, v.w, acc[0].w); }
+            if (own1) { const float4 v = vrow[(size_t)t * ld4 + 32]; acc[1].x = fmaf(pt, v.x, acc[1].x); acc[1].y = fmaf(pt, v.y, acc[1].y); acc[1].z = fmaf(pt, v.z, acc[1].z); acc[1].w = fmaf(pt, v.w, acc[1].w); }
         }
     }
-    // chunk-local max and sum per query head
-    float mloc[ATT_GMAX], lloc[ATT_GMAX];
-#pragma unroll
-    for (int g = 0; g < ATT_GMAX; g++) {
-        if (g >= group) break;
-        float v = tid < n ? sc[g] * scale : -INFINITY;
-        sc[g] = v;
-        v = warp_max(v);
-        if (lane == 0) red[g * 4 + warp] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < ATT_GMAX; g++) {
-        if (g >= group) break;
-        mloc[g] = fmaxf(fmaxf(red[g * 4], red[g * 4 + 1]), fmaxf(red[g * 4 + 2], red[g * 4 + 3]));
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < ATT_GMAX; g++) {
-        if (g >= group) break;
-        const float pw = tid < n ? expf(sc[g] - mloc[g]) : 0.0f;
-        ps[g * ATT_T + tid] = pw;
-        const float v = warp_sum(pw);
-        if (lane == 0) red[g * 4 + warp] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < ATT_GMAX; g++) {
-        if (g >= group) break;
-        lloc[g] = red[g * 4] + red[g * 4 + 1] + red[g * 4 + 2] + red[g * 4 + 3];
-    }
-    // weighted V sum: thread d owns dimension d (and d + 128, ...)
-    const size_t pstride = (size_t)hd + 2;          // per (b, head, split): m, l, acc[hd]
-    for (int d = tid; d < hd; d += ATT_T) {
-        float acc[ATT_GMAX];
-#pragma unroll
-        for (int g = 0; g < ATT_GMAX; g++) acc[g] = 0.0f;
-#pragma unroll 4
-        for (int t = 0; t < n; t++) {
-            const float vv = vt[(size_t)t * ld + d];
-#pragma unroll
-            for (int g = 0; g < ATT_GMAX; g++) { if (g >= group) break; acc[g] = fmaf(ps[g * ATT_T + t], vv, acc[g]); }
-        }
-#pragma unroll
-        for (int g = 0; g < ATT_GMAX; g++) {
-            if (g >= group) break;
-            part[(((size_t)b * n_heads + (size_t)kvh * group + g) * nsplit + sp) * pstride + 2 + d] = acc[g];
-        }
-    }
-    if (tid < group) {
-        float* dst = part + (((size_t)b * n_heads + (size_t)kvh * group + tid) * nsplit + sp) * pstride;
-        dst[0] = n > 0 ? mloc[tid] : -INFINITY;
-        dst[1] = n > 0 ? lloc[tid] : 0.0f;
-    }
+    ATRACE(0, 5);
+    float* dst = part + (((size_t)b * n_heads + (size_t)kvh * group + g) * nsplit + sp) * (size_t)(hd + 4);
+    if (own0) *reinterpret_cast<float4*>(dst + 4 + 4 * lane) = acc[0];
+    if (own1) *reinterpret_cast<float4*>(dst + 4 + 4 * (lane + 32)) = acc[1];
+    if (lane == 0) { dst[0] = m_run; dst[1] = l_run; }
+    ATRACE(0, 6);
 }
 
+// grid (query heads, B): merges the chunk results of one head. All of them are loaded at once, as float4s.
+constexpr int ATT_CMB_V = 8;
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
                                                            int n_heads, int hd, int nsplit) {
+    extern __shared__ __align__(16) float cs[];      // the head's chunk results: [nsplit][hd + 4], then weights [nsplit]
+    ATRACE(1, 0);
     pdl_launch_dependents();
     pdl_wait();
+    ATRACE(1, 1);
     const int h = blockIdx.x, b = blockIdx.y;
-    const size_t pstride = (size_t)hd + 2;
-    const float* src = part + ((size_t)b * n_heads + h) * nsplit * pstride;
+    const int pstride = hd + 4, total = nsplit * pstride, total4 = total / 4;
+    const float4* src = reinterpret_cast<const float4*>(part + ((size_t)b * n_heads + h) * (size_t)total);
+    float4* cs4 = reinterpret_cast<float4*>(cs);
+    float* wgt = cs + total;
+    for (int e0 = 0; e0 < total4; e0 += ATT_CMB_V * 128) {
+        float4 tmp[ATT_CMB_V];
+#pragma unroll
+        for (int u = 0; u < ATT_CMB_V; u++) { const int e = e0 + u * 128 + threadIdx.x; if (e < total4) tmp[u] = src[e]; }
+#pragma unroll
+        for (int u = 0; u < ATT_CMB_V; u++) { const int e = e0 + u * 128 + threadIdx.x; if (e < total4) cs4[e] = tmp[u]; }
+    }
+    __syncthreads();
     float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++) M = fmaxf(M, src[s * pstride]);
+    for (int s = 0; s < nsplit; s++) M = fmaxf(M, cs[s * pstride]);
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) wgt[s] = cs[s * pstride + 1] > 0.0f ? expf(cs[s * pstride] - M) : 0.0f;
+    __syncthreads();
     float L = 0.0f;
-    for (int s = 0; s < nsplit; s++) L += src[s * pstride + 1] * expf(src[s * pstride] - M);
+    for (int s = 0; s < nsplit; s++) L = fmaf(cs[s * pstride + 1], wgt[s], L);
     const float inv = 1.0f / L;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.0f;
-        for (int s = 0; s < nsplit; s++) {
-            const float w = src[s * pstride + 1] > 0.0f ? expf(src[s * pstride] - M) : 0.0f;
-            a = fmaf(w, src[s * pstride + 2 + d], a);
-        }
+        for (int s = 0; s < nsplit; s++) a = fmaf(wgt[s], cs[s * pstride + 4 + d], a);
         out[((size_t)b * n_heads + h) * hd + d] = a * inv;
     }
+    ATRACE(1, 2);
 }
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(float* __restrict__ out, const float* __restrict__ gate,
@@ -389,20 +390,23 @@ static int attention_split(ibcu_ctx* ctx, const float* q, float* k_cache, float*
     {
         // split path: chunks of up to 128 cache positions per block, merged by a second small kernel
         const int cap = pos0 + B;
-        int nsplit = (cap + ATT_T - 1) / ATT_T;
+        int nsplit = (cap + ATT_CHUNK - 1) / ATT_CHUNK;
         const int want = (2 * ctx->sm_count) / (n_kv_heads * B);      // enough blocks to cover the machine
-        int chunk = ATT_T;
+        int chunk = ATT_CHUNK;
         if (nsplit < want) { chunk = (cap + want - 1) / want; if (chunk < 32) chunk = 32; chunk = (chunk + 3) & ~3; nsplit = (cap + chunk - 1) / chunk; }
-        const size_t pbytes = (size_t)B * n_heads * nsplit * (head_dim + 2) * sizeof(float);
+        const size_t pbytes = (size_t)B * n_heads * nsplit * (head_dim + 4) * sizeof(float);
         int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, pbytes);
         if (rc) return rc;
-        const size_t smem = ((size_t)group * head_dim + (size_t)group * ATT_T + group * 4 + 2 * (size_t)chunk * (head_dim + 4)) * sizeof(float);
+        const size_t smem = ((size_t)group * head_dim + group * 32 + 2 * (size_t)chunk * (head_dim + 4)) * sizeof(float);
         if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, nsplit, B), dim3(ATT_T), smem, 1, true,
+        rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, nsplit, B), dim3(32 * group), smem, 1, true,
                          q, (const float*)k_cache, (const float*)v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit,
                          k_new, v_new, k_cache, v_cache, theta);
         if (rc) return rc;
-        return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), 0, 1, true,
+        const size_t csmem = ((size_t)nsplit * (head_dim + 4) + nsplit) * sizeof(float);
+        IBCU_REQUIRE(ctx, csmem <= 200 * 1024, "ibcu_attention: %d chunks of cache positions are more than the merge step holds", nsplit);
+        if (csmem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+        return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), csmem, 1, true,
                            (const float*)ctx->scratch, out, n_heads, head_dim, nsplit);
     }
 }
@@ -456,3 +460,7 @@ extern "C" int ibcu_softmax(ibcu_ctx* ctx, float* data, int N, int rows) {
     IBCU_REQUIRE(ctx, data && N > 0 && rows > 0, "ibcu_softmax: bad arguments");
     return ibcu_launch(ctx, softmax_rows_kernel, dim3(rows), dim3(256), 0, 1, true, data, N);
 }
+
+#ifdef IBCU_TRACE
+extern "C" int ibcu_att_trace_read(void* dst) { return (int)cudaMemcpyFromSymbol(dst, att_trace_buf, sizeof(att_trace_buf)); }
+#endif
