@@ -106,11 +106,15 @@ int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
 #define IBCU_PRO_NONE      0
 #define IBCU_PRO_RMSNORM   1  /* x <- x * rsqrt(mean(x^2) + eps) * fp16(norm_w) */
 #define IBCU_PRO_SILU_MUL  2  /* x <- x / (1 + exp(-x)) * x2 */
+#define IBCU_PRO_KNOWN_MAX 3  /* x as it is; the caller supplies max|x[b]| in pieces (ibcu_silu_mul_amax makes them), which
+                               * spares every block of the kernel its own reduction over the activation */
 typedef struct {
     int op;
     const float*    x2;       /* device [B*N], IBCU_PRO_SILU_MUL */
     const uint16_t* norm_w;   /* device fp16 [N], IBCU_PRO_RMSNORM */
     float eps;
+    const float*    amax;     /* device [B*n_amax], IBCU_PRO_KNOWN_MAX: max over amax[b*n_amax .. +n_amax) == max|x[b]| */
+    int n_amax;
 } ibcu_prologue_t;
 int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
                    const float* x, int N, int B, int bits, const ibcu_prologue_t* prologue);
@@ -211,6 +215,9 @@ int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const fl
  * place; nothing reads them afterwards). */
 int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
                           int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta);
+/* out[b] = silu(gate[b]) * up[b] over rows of N, and amax[b*parts + p] = max|out[b]| over the p-th of `parts`
+ * equal column ranges: the element-wise step of the MLP (src/forward.c:637-640) shaped for IBCU_PRO_KNOWN_MAX. */
+int ibcu_silu_mul_amax(ibcu_ctx* ctx, float* out, const float* gate, const float* up, int N, int B, float* amax, int parts);
 int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n);
 int ibcu_add_inplace(ibcu_ctx* ctx, float* x, const float* y, size_t n);
 int ibcu_softmax(ibcu_ctx* ctx, float* data, int N, int rows);

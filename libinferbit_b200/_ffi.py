@@ -21,7 +21,8 @@ class LinearT(C.Structure):
 
 class PrologueT(C.Structure):
     """ibcu_prologue_t"""
-    _fields_ = [("op", C.c_int), ("x2", C.c_void_p), ("norm_w", C.c_void_p), ("eps", C.c_float)]
+    _fields_ = [("op", C.c_int), ("x2", C.c_void_p), ("norm_w", C.c_void_p), ("eps", C.c_float),
+                ("amax", C.c_void_p), ("n_amax", C.c_int)]
 
 
 class PqT(C.Structure):
@@ -84,6 +85,7 @@ IBCU_SYMBOLS = {
     "ibcu_rmsnorm_f32w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
     "ibcu_rope_kv_write": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
+    "ibcu_silu_mul_amax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "ibcu_attention_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
     "ibcu_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -316,6 +316,27 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(float* __restrict__ out, 
     }
 }
 
+// grid (parts, B): silu(gate) * up over one column range of one row, and the largest magnitude written
+__global__ void __launch_bounds__(256) silu_mul_amax_kernel(float* __restrict__ out, const float* __restrict__ gate, const float* __restrict__ up,
+                                                            int N, int chunk, float* __restrict__ amax) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x, b = blockIdx.y;
+    const size_t base = (size_t)b * N;
+    const int c1 = min(N, (p + 1) * chunk);
+    float mx = 0.0f;
+#pragma unroll 4
+    for (int i = p * chunk + threadIdx.x; i < c1; i += blockDim.x) {
+        const float g = gate[base + i];
+        const float h = g / (1.0f + expf(-g)) * up[base + i];
+        out[base + i] = h;
+        mx = fmaxf(mx, fabsf(h));
+    }
+    mx = block_max(mx, red);
+    if (threadIdx.x == 0) amax[(size_t)b * gridDim.x + p] = mx;
+}
+
 __global__ void __launch_bounds__(256) add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
     pdl_launch_dependents();
     pdl_wait();
@@ -439,6 +460,13 @@ extern "C" int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const fl
     int rc = ibcu_rope_kv_write(ctx, q, k, v, k_cache, v_cache, n_heads, n_kv_heads, head_dim, pos0, B, theta);
     if (rc) return rc;
     return ibcu_attention(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B);
+}
+
+extern "C" int ibcu_silu_mul_amax(ibcu_ctx* ctx, float* out, const float* gate, const float* up, int N, int B, float* amax, int parts) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, out && gate && up && amax && N > 0 && B > 0 && parts > 0, "ibcu_silu_mul_amax: bad arguments");
+    const int chunk = (N + parts - 1) / parts;
+    return ibcu_launch(ctx, silu_mul_amax_kernel, dim3(parts, B), dim3(256), 0, 1, true, out, gate, up, N, chunk, amax);
 }
 
 extern "C" int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n) {

@@ -47,6 +47,8 @@ struct XSource {                   // where an activation value comes from
     const __half* norm_w;          // RMSNorm weights, or NULL
     float eps;
     int op;                        // IBCU_PRO_*
+    const float* amax;             // IBCU_PRO_KNOWN_MAX: [B][n_amax] pieces of max|x[b]|
+    int n_amax;
 };
 
 struct LinearParams {
@@ -316,9 +318,62 @@ __device__ __forceinline__ void xconvert_regs(const XSource& src, int N, int b, 
     }
 }
 
+// The conversion when the caller knows max|x[b]| (IBCU_PRO_KNOWN_MAX): no reduction before the digits, so
+// rows of any length stream through in one pass, four groups of 8 columns in flight per thread.
+__device__ __forceinline__ void xconvert_known(const XSource& src, int N, int b, int c0, int slice_cols, int8_t* dst_b, int xs_ld,
+                                               int perm8, XScratch& sc, float* back_out, int* sum_out) {
+    const int nth = blockDim.x, nwarp = nth >> 5;
+    const int valid = max(0, min(slice_cols, N - c0));
+    const float* xb = src.x + (size_t)b * N + c0;
+    float vmax = 0.0f;
+    for (int q = 0; q < src.n_amax; q++) vmax = fmaxf(vmax, src.amax[(size_t)b * src.n_amax + q]);
+    const int e = (int)((__float_as_uint(vmax) >> 23) & 0xFF);
+    int sh = (vmax > 0.0f && e != 255) ? 156 - e : 0;
+    sh = max(-126, min(126, sh));
+    const float mul = __uint_as_float((uint32_t)(127 + sh) << 23);
+    if (threadIdx.x == 0) *back_out = __uint_as_float((uint32_t)(127 - sh) << 23);
+    int lsum[LIN_LIMBS] = {0, 0, 0, 0};
+    constexpr int U = 4;
+    for (int j0 = threadIdx.x * 8; j0 < slice_cols; j0 += nth * 8 * U) {
+        float4 va[U], vc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int j = j0 + u * nth * 8;
+            va[u] = vc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < valid) { va[u] = *reinterpret_cast<const float4*>(xb + j); vc[u] = *reinterpret_cast<const float4*>(xb + j + 4); }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int j = j0 + u * nth * 8;
+            if (j >= slice_cols) continue;
+            int X[8];
+            X[0] = __float2int_rn(va[u].x * mul); X[1] = __float2int_rn(va[u].y * mul); X[2] = __float2int_rn(va[u].z * mul); X[3] = __float2int_rn(va[u].w * mul);
+            X[4] = __float2int_rn(vc[u].x * mul); X[5] = __float2int_rn(vc[u].y * mul); X[6] = __float2int_rn(vc[u].z * mul); X[7] = __float2int_rn(vc[u].w * mul);
+            uint2 pk[LIN_LIMBS];
+            limbs8(X, perm8, pk, lsum);
+#pragma unroll
+            for (int l = 0; l < LIN_LIMBS; l++) *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk[l];
+        }
+    }
+#pragma unroll
+    for (int l = 0; l < LIN_LIMBS; l++) {
+        int v = lsum[l];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) sc.sred[threadIdx.x >> 5][l] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < LIN_LIMBS) {
+        int v = 0;
+        for (int q = 0; q < nwarp; q++) v += sc.sred[q][threadIdx.x];
+        sum_out[threadIdx.x] = v;
+    }
+}
+
 constexpr int XREG_V = 8;                                     // 32 columns per thread in registers
 __device__ __forceinline__ void xconvert_any(const XSource& src, int N, int b, int c0, int slice_cols, int8_t* dst_b, int xs_ld,
                                              int perm8, XScratch& sc, float* back_out, int* sum_out, int xregs = 1) {
+    if (src.op == IBCU_PRO_KNOWN_MAX) { xconvert_known(src, N, b, c0, slice_cols, dst_b, xs_ld, perm8, sc, back_out, sum_out); return; }
     if (xregs && slice_cols <= XREG_V * 4 * (int)blockDim.x) xconvert_regs<XREG_V>(src, N, b, c0, slice_cols, dst_b, xs_ld, perm8, sc, back_out, sum_out);
     else xconvert(src, N, b, c0, slice_cols, dst_b, xs_ld, perm8, sc, back_out, sum_out);
 }
@@ -702,7 +757,8 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
                               const float* x, int N, int B, int bits, const ibcu_prologue_t* pro) {
     IBCU_CHECK_CTX(ctx);
     const int op = pro ? pro->op : IBCU_PRO_NONE;
-    IBCU_REQUIRE(ctx, op == IBCU_PRO_NONE || (op == IBCU_PRO_RMSNORM && pro->norm_w) || (op == IBCU_PRO_SILU_MUL && pro->x2),
+    IBCU_REQUIRE(ctx, op == IBCU_PRO_NONE || (op == IBCU_PRO_RMSNORM && pro->norm_w) || (op == IBCU_PRO_SILU_MUL && pro->x2) ||
+                      (op == IBCU_PRO_KNOWN_MAX && pro->amax && pro->n_amax >= 1),
                  "ibcu_linear_ex: prologue %d lacks its operand", op);
     IBCU_REQUIRE(ctx, tensors && x, "ibcu_linear: null pointer");
     IBCU_REQUIRE(ctx, n_tensors >= 1 && n_tensors <= 4, "ibcu_linear: n_tensors=%d not in 1..4", n_tensors);
@@ -719,7 +775,7 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     for (int i = 0; i < n_tensors; i++) if (((uintptr_t)tensors[i].w & 15) != 0) fast = false;
 
     if (!fast) {
-        if (op != IBCU_PRO_NONE) {
+        if (op == IBCU_PRO_RMSNORM || op == IBCU_PRO_SILU_MUL) {
             // portable path: apply the prologue with the element-wise kernels into the context's activation buffer
             int rc0 = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, (size_t)B * N * sizeof(float));
             if (rc0) return rc0;
@@ -746,7 +802,7 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
         ibcu_linear_t part[4];
         for (int b0 = 0; b0 < B; b0 += 16) {
             for (int i = 0; i < n_tensors; i++) { part[i] = tensors[i]; part[i].out = tensors[i].out + (size_t)b0 * tensors[i].out_stride; }
-            ibcu_prologue_t pp; if (pro) { pp = *pro; if (pp.x2) pp.x2 += (size_t)b0 * N; }
+            ibcu_prologue_t pp; if (pro) { pp = *pro; if (pp.x2) pp.x2 += (size_t)b0 * N; if (pp.amax) pp.amax += (size_t)b0 * pp.n_amax; }
             int rc2 = ibcu_linear_ex(ctx, part, n_tensors, x + (size_t)b0 * N, N, B - b0 < 16 ? B - b0 : 16, bits, pro ? &pp : nullptr);
             if (rc2) return rc2;
         }
@@ -851,11 +907,13 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
 #ifdef IBCU_TRACE
     { static int seq = 0; p.trace_slot = seq++; }
 #endif
-    XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op };
+    XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op,
+                     op == IBCU_PRO_KNOWN_MAX ? pro->amax : nullptr, op == IBCU_PRO_KNOWN_MAX ? pro->n_amax : 0 };
     // Cheap conversions are done by every block of the main kernel for itself (no extra launch, no
     // dependency chain); expensive ones (SiLU, several activations, long rows) once, by xprep_kernel.
     static const int fuse_env = env_int("IBCU_LINEAR_FUSE_X", -1);
     int fused = (op != IBCU_PRO_SILU_MUL && (long)B * slice_kb * xk <= 8192 && nks == 1) ? 1 : 0;
+    if (op == IBCU_PRO_KNOWN_MAX && nks == 1 && B <= 2) fused = 1;          // no reduction: cheap at any row length
     if (fuse_env >= 0) fused = fuse_env && nks == 1;
     p.xsrc = xsrc; p.fused_x = fused;
     static const int skip_xprep = env_int("IBCU_LINEAR_SKIP_XPREP", 0);   // timing experiments only: results are then stale

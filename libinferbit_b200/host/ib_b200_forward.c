@@ -32,6 +32,7 @@ struct ib_b200_model {
     void *embed, *embed_scale, *final_norm;
     /* activations, all [IB max batch][...] */
     float *x, *xb, *q, *k, *v, *att, *hg, *hu, *logits;
+    float* amax;              /* [BMAX][AMAX_PARTS] pieces of max|silu(gate)*up| per position */
     int32_t* tokens;
     void* pin;                /* pinned staging for tokens / logits */
     size_t pin_bytes;
@@ -41,6 +42,7 @@ struct ib_b200_model {
 };
 
 #define BMAX 32
+#define AMAX_PARTS 28
 
 static int dmalloc(ib_b200_model* m, void** p, size_t bytes) { return ibcu_malloc(m->ctx, bytes ? bytes : 16, p); }
 
@@ -86,6 +88,7 @@ ib_b200_model* ib_b200_model_create(ibcu_ctx* ctx, const ib_b200_model_cfg* cfg)
     const size_t asz[] = { (size_t)H, (size_t)H, (size_t)H, (size_t)kv, (size_t)kv, (size_t)H, (size_t)I, (size_t)I, (size_t)c.vocab };
     for (int i = 0; i < 9 && !rc; i++) rc = dmalloc(m, act[i], asz[i] * BMAX * sizeof(float));
     if (!rc) rc = dmalloc(m, (void**)&m->tokens, BMAX * sizeof(int32_t));
+    if (!rc) rc = dmalloc(m, (void**)&m->amax, (size_t)BMAX * AMAX_PARTS * sizeof(float));
     m->pin_bytes = (size_t)BMAX * c.vocab * sizeof(float) + 256;
     if (!rc) rc = ibcu_host_alloc(ctx, m->pin_bytes, &m->pin);
     if (rc) { ib_b200_model_free(m); return NULL; }
@@ -102,7 +105,7 @@ void ib_b200_model_free(ib_b200_model* m) {
         ibcu_free(m->ctx, y->in_norm); ibcu_free(m->ctx, y->post_norm); ibcu_free(m->ctx, y->k_cache); ibcu_free(m->ctx, y->v_cache);
     }
     ibcu_free(m->ctx, m->head.w); ibcu_free(m->ctx, m->head.scale);
-    void* v[] = { m->embed, m->embed_scale, m->final_norm, m->x, m->xb, m->q, m->k, m->v, m->att, m->hg, m->hu, m->logits, m->tokens };
+    void* v[] = { m->embed, m->embed_scale, m->final_norm, m->x, m->xb, m->q, m->k, m->v, m->att, m->hg, m->hu, m->logits, m->tokens, m->amax };
     for (unsigned i = 0; i < sizeof v / sizeof *v; i++) ibcu_free(m->ctx, v[i]);
     if (m->pin) ibcu_host_free(m->ctx, m->pin);
     free(m->L);
@@ -216,7 +219,7 @@ static int issue(ib_b200_model* m, int pos0, int B) {
     for (int l = 0; l < c->n_layers && !rc; l++) {
         layer* y = &m->L[l];
         /* RMSNorm is folded into the activation preparation of the projections that consume it */
-        ibcu_prologue_t n1 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->in_norm, c->eps };
+        ibcu_prologue_t n1 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->in_norm, c->eps, NULL, 0 };
         ibcu_linear_t qkv[3] = { desc(&y->t[IB_B200_Q], m->q, 0), desc(&y->t[IB_B200_K], m->k, 0), desc(&y->t[IB_B200_V], m->v, 0) };
         rc = ibcu_linear_ex(ctx, qkv, 3, m->x, H, B, c->attn_bits, &n1);
         if (!rc) rc = gather(m, &y->t[IB_B200_Q], m->q, B);
@@ -229,18 +232,20 @@ static int issue(ib_b200_model* m, int pos0, int B) {
         ibcu_linear_t o = desc(&y->t[IB_B200_O], m->x, IBCU_EPI_ADD);
         if (!rc) rc = ibcu_linear(ctx, &o, 1, m->att, H, B, c->attn_bits);
         if (!rc) rc = gather(m, &y->t[IB_B200_O], m->x, B);
-        ibcu_prologue_t n2 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->post_norm, c->eps };
+        ibcu_prologue_t n2 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->post_norm, c->eps, NULL, 0 };
         ibcu_linear_t gu[2] = { desc(&y->t[IB_B200_GATE], m->hg, 0), desc(&y->t[IB_B200_UP], m->hu, 0) };
         if (!rc) rc = ibcu_linear_ex(ctx, gu, 2, m->x, H, B, c->mlp_bits, &n2);
         if (!rc) rc = gather(m, &y->t[IB_B200_GATE], m->hg, B);
         if (!rc) rc = gather(m, &y->t[IB_B200_UP], m->hu, B);
-        /* silu(gate) * up is formed while down_proj's activation is prepared (src/forward.c:637-640) */
-        ibcu_prologue_t sm = { IBCU_PRO_SILU_MUL, m->hu, NULL, 0.0f };
+        /* silu(gate) * up (src/forward.c:637-640) in one small launch that also leaves max|h| for down_proj,
+         * whose blocks then turn h into their integer operand without a reduction of their own */
+        if (!rc) rc = ibcu_silu_mul_amax(ctx, m->hg, m->hg, m->hu, c->inter, B, m->amax, AMAX_PARTS);
+        ibcu_prologue_t km = { IBCU_PRO_KNOWN_MAX, NULL, NULL, 0.0f, m->amax, AMAX_PARTS };
         ibcu_linear_t dn = desc(&y->t[IB_B200_DOWN], m->x, IBCU_EPI_ADD);
-        if (!rc) rc = ibcu_linear_ex(ctx, &dn, 1, m->hg, c->inter, B, c->mlp_bits, &sm);
+        if (!rc) rc = ibcu_linear_ex(ctx, &dn, 1, m->hg, c->inter, B, c->mlp_bits, &km);
         if (!rc) rc = gather(m, &y->t[IB_B200_DOWN], m->x, B);
     }
-    ibcu_prologue_t nf = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)m->final_norm, c->eps };
+    ibcu_prologue_t nf = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)m->final_norm, c->eps, NULL, 0 };
     ibcu_linear_t hd = desc(&m->head, m->logits, 0);
     if (!rc) rc = ibcu_linear_ex(ctx, &hd, 1, m->x, H, B, c->head_bits, &nf);
     if (!rc) rc = gather(m, &m->head, m->logits, B);

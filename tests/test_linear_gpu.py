@@ -228,3 +228,41 @@ def test_prologues_rmsnorm_and_silu_mul(backend, cpu_libs, bits, N):
         be.sync()
         got = be.download(do, np.float32, B * M).reshape(B, M)
         assert _cpu.close(got, want, 2e-3, 2e-4), op
+
+
+@pytest.mark.parametrize("bits,M,N,B,parts", [(4, 96, 14336, 1, 28), (8, 80, 4096, 2, 7), (4, 64, 2048, 3, 5), (8, 48, 200, 2, 3), (8, 40, 40960, 1, 16)])
+def test_silu_mul_amax_then_known_max_prologue(backend, cpu_libs, bits, M, N, B, parts):
+    """ibcu_silu_mul_amax followed by a linear call told max|x| (IBCU_PRO_KNOWN_MAX) gives bit for bit what the
+    silu(x)*x2 prologue gives: same activation values, same maximum, hence the same fixed-point operand.
+    The pieces written by the element-wise step are checked against numpy."""
+    from libinferbit_b200 import _ffi
+    rng = np.random.default_rng(bits * 1000 + N + B)
+    be, o = backend, cpu_libs.oracle
+    w, s16, g = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    g *= 2.0
+    u = rng.standard_normal((B, N)).astype(np.float32)
+    dw, ds, dg, du = be.upload(w), be.upload(s16), be.upload(g), be.upload(u)
+    dh, da, do1, do2 = be.alloc(B * N * 4), be.alloc(B * parts * 4), be.alloc(B * M * 4), be.alloc(B * M * 4)
+    t1, t2 = LinearT(dw.ptr, ds.ptr, do1.ptr, M, M, 0, 0), LinearT(dw.ptr, ds.ptr, do2.ptr, M, M, 0, 0)
+    p_silu = _ffi.PrologueT(2, du.ptr, None, 0.0, None, 0)
+    be._check(be.lib.ibcu_linear_ex(be.ctx, C.byref(t1), 1, dg.ptr, N, B, bits, C.byref(p_silu)))
+    be._check(be.lib.ibcu_silu_mul_amax(be.ctx, dh.ptr, dg.ptr, du.ptr, N, B, da.ptr, parts))
+    p_known = _ffi.PrologueT(3, None, None, 0.0, da.ptr, parts)
+    be._check(be.lib.ibcu_linear_ex(be.ctx, C.byref(t2), 1, dh.ptr, N, B, bits, C.byref(p_known)))
+    be.sync()
+    h = be.download(dh, np.float32, B * N).reshape(B, N)
+    want_h = np.empty_like(h)
+    for b in range(B):
+        o.ibo_silu_mul(want_h[b], g[b], u[b], N)
+    assert _cpu.close(h, want_h, 1e-5, 1e-6)
+    am = be.download(da, np.float32, B * parts).reshape(B, parts)
+    chunk = (N + parts - 1) // parts
+    for b in range(B):
+        for p in range(parts):
+            seg = np.abs(h[b, p * chunk:(p + 1) * chunk])
+            assert am[b, p] == (seg.max() if seg.size else 0.0)
+    got1 = be.download(do1, np.float32, B * M).reshape(B, M)
+    got2 = be.download(do2, np.float32, B * M).reshape(B, M)
+    if N % 16 == 0:                       # the tensor-core path: identical fixed-point operands
+        assert np.array_equal(got1, got2)
+    assert _cpu.close(got2, oracle_linear(cpu_libs, w, s16, want_h, bits), 2e-3, 2e-4)
