@@ -324,32 +324,51 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const float* __restrict
     }
 }
 
+// Adds the per-block partial tables. A block of 256 threads owns 32 columns (table entries): thread
+// (g, c) adds partials g, g + 8, ... of column c with its loads in flight eight at a time, then the
+// eight group sums are combined in a fixed order. Blocks [0, nS) do the sums (in double), [nS, nS + nC)
+// the counts, the last one the inertia.
 __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __restrict__ part_sums, const int32_t* __restrict__ part_counts,
                                                                 const double* __restrict__ part_inertia, int nblocks, int KD, int K,
                                                                 float* __restrict__ sums, int32_t* __restrict__ counts, double* __restrict__ inertia) {
+    __shared__ double dsh[8][32];
+    __shared__ int ish[8][32];
     pdl_launch_dependents();
     pdl_wait();
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if (e < KD) {
-        // eight interleaved running sums (independent loads in flight), combined in a fixed order
-        double s8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        int b = 0;
-        for (; b + 8 <= nblocks; b += 8) {
-#pragma unroll
-            for (int u = 0; u < 8; u++) s8[u] += (double)part_sums[(size_t)(b + u) * KD + e];
+    const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int nS = (KD + 31) / 32, nC = (K + 31) / 32;
+    if ((int)blockIdx.x < nS) {
+        const int e = blockIdx.x * 32 + c;
+        double s = 0.0;
+        if (e < KD) {
+#pragma unroll 8
+            for (int b = g; b < nblocks; b += 8) s += (double)part_sums[(size_t)b * KD + e];
         }
-        for (; b < nblocks; b++) s8[0] += (double)part_sums[(size_t)b * KD + e];
-        sums[e] = (float)(((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7])));
-    }
-    if (e < K) {
-        int c = 0;
-        for (int b = 0; b < nblocks; b++) c += part_counts[(size_t)b * K + e];
-        counts[e] = c;
-    }
-    if (e == 0 && inertia) {
-        double t = 0.0;
-        for (int b = 0; b < nblocks; b++) t += part_inertia[b];
-        *inertia = t;
+        dsh[g][c] = s;
+        __syncthreads();
+        if (g == 0 && e < KD)
+            sums[e] = (float)(((dsh[0][c] + dsh[1][c]) + (dsh[2][c] + dsh[3][c])) + ((dsh[4][c] + dsh[5][c]) + (dsh[6][c] + dsh[7][c])));
+    } else if ((int)blockIdx.x < nS + nC) {
+        const int e = (blockIdx.x - nS) * 32 + c;
+        int s = 0;
+        if (e < K) {
+#pragma unroll 8
+            for (int b = g; b < nblocks; b += 8) s += part_counts[(size_t)b * K + e];
+        }
+        ish[g][c] = s;
+        __syncthreads();
+        if (g == 0 && e < K) counts[e] = ish[0][c] + ish[1][c] + ish[2][c] + ish[3][c] + ish[4][c] + ish[5][c] + ish[6][c] + ish[7][c];
+    } else if (inertia) {
+        double s = 0.0;
+#pragma unroll 4
+        for (int b = threadIdx.x; b < nblocks; b += 256) s += part_inertia[b];
+        // fixed-order tree over the 256 threads
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (c == 0) dsh[0][g] = s;
+        __syncthreads();
+        if (threadIdx.x == 0)
+            *inertia = ((dsh[0][0] + dsh[0][1]) + (dsh[0][2] + dsh[0][3])) + ((dsh[0][4] + dsh[0][5]) + (dsh[0][6] + dsh[0][7]));
     }
 }
 
@@ -450,7 +469,7 @@ extern "C" int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int
     rc = ibcu_launch(ctx, accumulate_kernel, dim3((unsigned)nblocks), dim3(nwarp * 32), smem, 1, true,
                      X, N, D, K, idx, dist, chunk, part_sums, part_counts, part_inertia);
     if (rc) return rc;
-    int fin_blocks = (int)((KD + 255) / 256);
+    int fin_blocks = (int)((KD + 31) / 32) + (K + 31) / 32 + 1;
     return ibcu_launch(ctx, accumulate_finish_kernel, dim3(fin_blocks), dim3(256), 0, 1, true,
                        (const float*)part_sums, (const int32_t*)part_counts, (const double*)part_inertia, (int)nblocks, (int)KD, K,
                        sums, counts, inertia);

@@ -228,8 +228,13 @@ __global__ void __launch_bounds__(256) pq_reduce_kernel(const float* __restrict_
     float s = 0.0f;
     if (r < M) {
         const float* src = partial + (size_t)b * nslabs * M_pad + r;
-#pragma unroll 10
-        for (int k = g; k < nslabs; k += 8) s += src[(size_t)k * M_pad];
+        for (int k0 = g; k0 < nslabs; k0 += 64) {                   // eight loads in flight, added in slab order
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = k0 + 8 * u < nslabs ? src[(size_t)(k0 + 8 * u) * M_pad] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) s += v[u];
+        }
     }
     part[g][lane] = s;
     __syncthreads();
