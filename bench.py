@@ -153,6 +153,11 @@ def dist_setup(n):
     return rank, world, local, None
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one captured INT8 4096x4096 launch over its weight bytes
+# (the ncu summary of this kernel kept under profiles/); traffic grows with the rows streamed, so a step scales by bytes
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 16.873472e6 / 16.777216e6
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,7 +166,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-other", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--case", default=None, help="run one small secondary case alone (for profiler captures): "
-                    "int8_4096x4096_b1, int8_32000x4096_b1, int4_14336x4096_b1, pq_4096x14336_b1, pq_4096x14336_b8, kmeans_4Mx8_k256, decode_7b_b1")
+                    "int8_4096x4096_b1, int8_32000x4096_b1, int4_14336x4096_b1, pq_4096x14336_b1, pq_4096x14336_b8, timeline_int8_4096x4096_b1 (trace build only), kmeans_4Mx8_k256, decode_7b_b1")
     args = ap.parse_args()
     rank, world, local, dist = dist_setup(args.gpus)
     if args.impl == "reference":
@@ -191,6 +196,7 @@ def main():
             "int8_4096x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 1, reps_target_bytes=300e6),
             "int8_32000x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 1, reps_target_bytes=400e6),
             "int4_14336x4096_b1": lambda: bs._linear_ring(lib, ctx, 4, 14336, 4096, 1, reps_target_bytes=300e6),
+            "timeline_int8_4096x4096_b1": lambda: bs._timeline_linear(lib, ctx, 8, 4096, 4096, 1),
             "pq_4096x14336_b1": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 1),
             "pq_4096x14336_b8": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 8),
             "kmeans_4Mx8_k256": lambda: bs._kmeans(lib, ctx, 0, 1, lambda v: v, sync, iters=2),
@@ -261,9 +267,12 @@ def main():
         "e2e": {"value": STEP_BYTES / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                 "ms_per_step": e2e_t * 1e3, "api": "ib_kernels table: matmul_int8 x4 with host buffers"},
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": value / world / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": value / world / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * STEP_BYTES / world,
+                     "peak_source": peaks["source"],
                      "kernel": "linear_mma_kernel<8,...>", "launches_per_step": mma_launches_per_step,
-                     "note": "achieved = algorithmic bytes of a step / device time of a step (xprep launches included)"},
+                     "note": "achieved = algorithmic bytes of a step / device time of a step, both launches of the step together; "
+                             "traffic = DRAM bytes of a step, scaled from the ncu capture of one 4096x4096 launch "
+                             "(16.873 MB read + 0 written for 16.777 MB of weights; the 32000x4096 launch gives the same ratio)"},
     }
     if rank == 0 and world == 1:
         cpu = CpuBaseline()

@@ -210,6 +210,43 @@ def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
     return {"us": ms * 1e3, "GBps": algo / ms / 1e6}
 
 
+def _timeline_linear(lib, ctx, bits, M, N, B):
+    """Phase times of back-to-back linear launches from the kernels' own %globaltimer stamps. Needs the
+    library built with `make -C libinferbit_b200 clean all TRACE=1`; a number from that build is a timeline,
+    not a benchmark."""
+    if not hasattr(lib, "ibcu_trace_read"):
+        raise SystemExit("timeline cases need the trace build: make -C libinferbit_b200 clean all TRACE=1")
+    dev = Dev(lib, ctx)
+    rowbytes = N if bits == 8 else N // 2
+    wbytes, R = M * rowbytes, 16
+    dW = dev.alloc(R * wbytes); check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, dW, R * wbytes, 7))
+    dS = dev.alloc(M * 2); check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, dS, M, 8, 0.002, 0.02))
+    dx = dev.upload(np.random.default_rng(0).standard_normal((B, N)).astype(np.float32))
+    do = dev.alloc(B * M * 4)
+    descs = [LinearT(dW + r * wbytes, dS, do, M, M, 0, 0) for r in range(R)]
+
+    def run():
+        for d in descs:
+            check(lib, ctx, lib.ibcu_linear(ctx, C.byref(d), 1, dx, N, B, bits))
+    gid = dev.graph(run)
+    dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
+    buf = np.zeros((16, 512, 8), np.uint64)
+    lib.ibcu_trace_read.argtypes = [C.c_void_p]
+    assert lib.ibcu_trace_read(buf.ctypes.data) == 0
+    t = buf.astype(np.int64)
+    nb = int((t[0, :, 0] > 0).sum())
+    order = np.argsort(t[:, :nb, 0].min(axis=1))
+    base = t[order[0], :nb, 0].min()
+    names = ["start", "prefetch_issued", "wait_done", "x_ready", "loop_done", "end"]
+    out = {"blocks": nb, "unit": "us since the first block of the first launch; min..max over blocks", "launches": []}
+    for j in order:
+        out["launches"].append({names[i]: [round(float((t[j, :nb, i] - base).min()) / 1e3, 2), round(float((t[j, :nb, i] - base).max()) / 1e3, 2)]
+                                for i in range(6)})
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    return out
+
+
 def _pq(lib, ctx, M, N, G, K, B):
     dev = Dev(lib, ctx)
     rng = np.random.default_rng(3)
