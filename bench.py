@@ -190,6 +190,16 @@ def main():
         dist.broadcast(idbuf, 0)
         raw = (C.c_ubyte * 128)(*idbuf.tolist())
         assert lib.ibcu_comm_init(ctx, raw, rank, world) == 0, lib.ibcu_last_error(ctx)
+        if not os.environ.get("IB_BENCH_NCCL_ONLY"):
+            # peer window: every rank maps the others' slab, gathers become pushes over NVLink
+            mine = (C.c_ubyte * 64)()
+            assert lib.ibcu_window_create(ctx, 96 << 20, mine) == 0, lib.ibcu_last_error(ctx)
+            allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+            dist.all_gather(allh, torch.tensor(list(mine), dtype=torch.uint8))
+            for r in range(world):
+                if r != rank:
+                    assert lib.ibcu_window_open(ctx, r, (C.c_ubyte * 64)(*allh[r].tolist())) == 0, lib.ibcu_last_error(ctx)
+            dist.barrier()
     if args.case:
         sync = lambda: bs.check(lib, ctx, lib.ibcu_sync(ctx))
         cases = {
@@ -261,7 +271,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1,
                    "bytes_per_step": STEP_BYTES, "l2": f"ring of {RING} distinct weight sets ({RING * STEP_BYTES >> 20} MiB) > L2",
-                   "parallelism": f"rows/{world} + NCCL all-gather" if world > 1 else "1 GPU"},
+                   "parallelism": (f"rows/{world} + " + ("NCCL all-gather" if os.environ.get("IB_BENCH_NCCL_ONLY") else "push all-gather over peer memory (NVLink)")) if world > 1 else "1 GPU"},
         "clocks": clk.summary(),
         "gpu_launches": int(launches_per_graph * n_replay),
         "e2e": {"value": STEP_BYTES / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],

@@ -236,6 +236,24 @@ void ibcu_shard_rows(int M, int world, int rank, int align, int* row0, int* rows
 /* In-place all-gather of row-sharded outputs: buf[b*stride + r], every rank owns its ibcu_shard_rows
  * slice (align as given) and receives the others. */
 int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride, int B, int align);
+/* Peer window: a slab of this GPU's memory that the other ranks of the node map (CUDA IPC) so that an
+ * all-gather becomes one kernel per rank storing its row slice straight into the peers' buffers over
+ * NVLink, with an epoch flag and a bounded wait, instead of an NCCL launch. Every rank calls
+ * ibcu_window_create (after ibcu_comm_init) with the same size, the launcher hands the 64-byte handles
+ * round, every rank calls ibcu_window_open for every peer, and buffers to be gathered are taken from
+ * the window with ibcu_window_alloc in the same order on every rank (same offsets). ibcu_window_alloc
+ * returns IBCU_ERR_STATE without touching the context's error when there is no window.
+ * ibcu_allgather_rows_n gathers up to four such buffers in one kernel; it falls back to NCCL for
+ * buffers outside the window, when not every peer is mapped, after ibcu_window_enable(ctx, 0), and for
+ * a buffer that was part of the previous push (peers may still be reading it). A rank whose peers do
+ * not arrive within about a second stops waiting and the next ibcu_sync returns IBCU_ERR_COMM.
+ * No counterpart in the reference (its workers share one address space). */
+#define IBCU_WINDOW_HANDLE_BYTES 64
+int ibcu_window_create(ibcu_ctx* ctx, size_t bytes, void* handle_out);
+int ibcu_window_open(ibcu_ctx* ctx, int peer_rank, const void* handle);
+int ibcu_window_alloc(ibcu_ctx* ctx, size_t bytes, void** dptr);
+void ibcu_window_enable(ibcu_ctx* ctx, int on);
+int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const int* M, const int* stride, int n, int B, int align);
 int ibcu_allreduce_f32(ibcu_ctx* ctx, float* buf, size_t n);
 int ibcu_allreduce_i32(ibcu_ctx* ctx, int32_t* buf, size_t n);
 int ibcu_allreduce_f64(ibcu_ctx* ctx, double* buf, size_t n);

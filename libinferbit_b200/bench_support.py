@@ -47,6 +47,13 @@ class Dev:
             self.lib.ibcu_free(self.ctx, b)
         self.bufs = []
 
+    def alloc_gathered(self, nbytes):
+        """a buffer that will be all-gathered: from the peer window when the context has one"""
+        p = C.c_void_p()
+        if self.lib.ibcu_window_alloc(self.ctx, nbytes, C.byref(p)) == 0:
+            return p.value
+        return self.alloc(nbytes)
+
     def timed(self, fn, reps=1):
         """device milliseconds of fn() (issued `reps` times) between two events on the stream"""
         self.lib.ibcu_event_record(self.ctx, 2)
@@ -94,7 +101,7 @@ class AttnProjWorkload:
         rng = np.random.default_rng(seed)
         self.x = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
         self.x2 = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
-        self.out = {name: self.dev.alloc(B * M * 4) for name, M, _ in proj}
+        self.out = {name: self.dev.alloc_gathered(B * M * 4) for name, M, _ in proj}
         self.sets = []
         s = seed * 977 + rank
         for r in range(ring):
@@ -118,12 +125,14 @@ class AttnProjWorkload:
         qkv = (LinearT * 3)(self._desc(ent, "q"), self._desc(ent, "k"), self._desc(ent, "v"))
         check(lib, ctx, lib.ibcu_linear(ctx, qkv, 3, self.x, self.N, self.B, 8))
         if self.world > 1:
-            for name in ("q", "k", "v"):
-                check(lib, ctx, lib.ibcu_allgather_rows(ctx, self.out[name], ent[name][2], ent[name][2], self.B, 32))
+            bufs = (C.c_void_p * 3)(*[self.out[n] for n in ("q", "k", "v")])
+            Ms = (C.c_int * 3)(*[ent[n][2] for n in ("q", "k", "v")])
+            check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 3, self.B, 32))
         o = self._desc(ent, "o")
         check(lib, ctx, lib.ibcu_linear(ctx, C.byref(o), 1, self.x2, self.N, self.B, 8))
         if self.world > 1:
-            check(lib, ctx, lib.ibcu_allgather_rows(ctx, self.out["o"], ent["o"][2], ent["o"][2], self.B, 32))
+            bufs = (C.c_void_p * 1)(self.out["o"]); Ms = (C.c_int * 1)(ent["o"][2])
+            check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 1, self.B, 32))
 
     def capture(self, n):
         self.step(0)
@@ -327,7 +336,7 @@ def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20, warm=60):
     wb = host.ib_b200_model_weight_bytes(m)
     host.ib_b200_model_free(m)
     return {"ms_per_step": ms, "tok_per_s": B / ms * 1e3, "batch": B, "pos": 512, "weight_GBps_per_gpu": wb / ms / 1e6,
-            "logits_finite": bool(np.isfinite(logits).all())}
+            "logits_finite": bool(np.isfinite(logits).all()), "logits_head": [float(v) for v in logits]}
 
 
 def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier):
@@ -344,4 +353,10 @@ def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier):
     out["kmeans_4Mx8_k256"] = _kmeans(lib, ctx, rank, world, max_over_ranks, barrier)
     out["decode_7b_b1"] = _decode(lib, host, ctx, 1, max_over_ranks, barrier)
     out["decode_7b_b8"] = _decode(lib, host, ctx, 8, max_over_ranks, barrier)
+    if world > 1:
+        # the same step with every gather through NCCL: the logits must be the same bits, only the transport differs
+        lib.ibcu_window_enable(ctx, 0)
+        out["decode_7b_b1_nccl_gathers"] = _decode(lib, host, ctx, 1, max_over_ranks, barrier)
+        lib.ibcu_window_enable(ctx, 1)
+        out["push_gather_matches_nccl"] = out["decode_7b_b1"]["logits_head"] == out["decode_7b_b1_nccl_gathers"]["logits_head"]
     return out

@@ -53,6 +53,10 @@ static_assert(sizeof(ncclUniqueId) <= IBCU_COMM_ID_BYTES, "communicator id does 
 
 void ibcu_comm_destroy_internal(ibcu_ctx* ctx) {
     if (ctx->comm && g_nccl.ok) { ncclCommDestroy((ncclComm_t)ctx->comm); ctx->comm = nullptr; }
+    for (int r = 0; r < IBCU_MAX_RANKS; r++)
+        if (ctx->win_peer[r] && ctx->win_peer[r] != ctx->win_base) { cudaIpcCloseMemHandle(ctx->win_peer[r]); ctx->win_peer[r] = nullptr; }
+    if (ctx->win_base) { cudaFree(ctx->win_base); ctx->win_base = nullptr; }
+    if (ctx->win_err) { cudaFreeHost(ctx->win_err); ctx->win_err = nullptr; }
 }
 
 extern "C" int ibcu_comm_get_id(void* id_out) {
@@ -109,6 +113,7 @@ extern "C" int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride,
     IBCU_REQUIRE(ctx, buf && M >= 0 && stride >= M && B >= 1, "ibcu_allgather_rows: bad arguments");
     if (ctx->world == 1 || M == 0) return IBCU_OK;
     if (!ctx->comm) return ibcu_fail(ctx, IBCU_ERR_STATE, "ibcu_allgather_rows: no communicator");
+    for (int j = 0; j < 4; j++) ctx->win_last[j] = nullptr;    // an NCCL gather in between ends the no-repeat rule
     ncclComm_t comm = (ncclComm_t)ctx->comm;
     int r0, rn;
     ibcu_shard_rows(M, ctx->world, 0, align, &r0, &rn);
@@ -128,6 +133,168 @@ extern "C" int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride,
     }
     IBCU_NCCL(ctx, ncclGroupEnd());
     return IBCU_OK;
+}
+
+// ── push all-gather over peer memory ────────────────────────────────────────────────────
+// Every rank owns a window of its own HBM that the other ranks have mapped (CUDA IPC). A buffer that
+// lives at the same offset in every rank's window is gathered by ONE small kernel per rank: it stores
+// this rank's row slice straight into the peers' copies over NVLink (plain peer stores), publishes an
+// epoch number in each peer's flag word (release, system scope) and then waits, with a limit, until
+// every peer's flag in its own window has reached the same epoch. No NCCL launch, no staging copy.
+// The epoch is device state, so a captured launch replays correctly.
+// Window header: flags[IBCU_MAX_RANKS] (flags[r] written by rank r), then this rank's epoch counter.
+constexpr size_t WIN_HEADER = 4096;
+constexpr int WIN_EPOCH_SLOT = IBCU_MAX_RANKS;
+constexpr long WIN_SPIN_LIMIT = 4L * 1000 * 1000;            // about a second of polling
+
+struct PushDesc { float* buf; int stride, row0, rows; };
+struct PushParams {
+    PushDesc d[4];
+    int n, B, rank, world;
+    char* base;
+    char* peer[IBCU_MAX_RANKS];
+    int* err;
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(1024) allgather_push_kernel(const PushParams p) {
+    __shared__ unsigned long long s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int i = 0; i < p.n; i++) {
+        const PushDesc d = p.d[i];
+        const size_t off0 = (size_t)((char*)d.buf - p.base);
+        const bool vec = ((d.row0 | d.rows | d.stride) & 3) == 0 && (off0 & 15) == 0;
+        for (int b = 0; b < p.B; b++) {
+            const float* src = d.buf + (size_t)b * d.stride + d.row0;
+            const size_t off = off0 + ((size_t)b * d.stride + d.row0) * sizeof(float);
+            if (vec) {
+                for (int e = threadIdx.x; e < d.rows / 4; e += blockDim.x) {
+                    const float4 v = reinterpret_cast<const float4*>(src)[e];
+                    for (int q = 0; q < p.world; q++)
+                        if (q != p.rank) reinterpret_cast<float4*>(p.peer[q] + off)[e] = v;
+                }
+            } else {
+                for (int e = threadIdx.x; e < d.rows; e += blockDim.x) {
+                    const float v = src[e];
+                    for (int q = 0; q < p.world; q++)
+                        if (q != p.rank) reinterpret_cast<float*>(p.peer[q] + off)[e] = v;
+                }
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    unsigned long long* my_flags = reinterpret_cast<unsigned long long*>(p.base);
+    if (threadIdx.x == 0) {
+        const unsigned long long e = my_flags[WIN_EPOCH_SLOT] + 1;
+        my_flags[WIN_EPOCH_SLOT] = e;
+        s_epoch = e;
+        for (int q = 0; q < p.world; q++)
+            if (q != p.rank) st_release_sys(reinterpret_cast<unsigned long long*>(p.peer[q]) + p.rank, e);
+    }
+    __syncthreads();
+    const unsigned long long e = s_epoch;
+    if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+        long it = 0;
+        while (ld_acquire_sys(my_flags + threadIdx.x) < e) {
+            if (++it > WIN_SPIN_LIMIT) { *p.err = (int)e; break; }       // give up: the host reports it at the next sync
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+}
+
+extern "C" int ibcu_window_create(ibcu_ctx* ctx, size_t bytes, void* handle_out) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, handle_out && bytes > 0, "ibcu_window_create: bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) <= IBCU_WINDOW_HANDLE_BYTES, "IPC handle does not fit the ABI token");
+    if (ctx->win_base) return ibcu_fail(ctx, IBCU_ERR_STATE, "window already created");
+    IBCU_REQUIRE(ctx, ctx->world <= IBCU_MAX_RANKS, "ibcu_window_create: %d ranks, at most %d", ctx->world, IBCU_MAX_RANKS);
+    IBCU_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t total = WIN_HEADER + ((bytes + 255) & ~(size_t)255);
+    void* base = nullptr;
+    IBCU_CUDA(ctx, cudaMalloc(&base, total));
+    IBCU_CUDA(ctx, cudaMemset(base, 0, total));
+    IBCU_CUDA(ctx, cudaDeviceSynchronize());
+    IBCU_CUDA(ctx, cudaHostAlloc((void**)&ctx->win_err, sizeof(int), cudaHostAllocMapped));
+    *ctx->win_err = 0;
+    cudaIpcMemHandle_t h;
+    IBCU_CUDA(ctx, cudaIpcGetMemHandle(&h, base));
+    memset(handle_out, 0, IBCU_WINDOW_HANDLE_BYTES);
+    memcpy(handle_out, &h, sizeof h);
+    ctx->win_base = (char*)base; ctx->win_bytes = total; ctx->win_used = WIN_HEADER;
+    ctx->win_peer[ctx->rank] = ctx->win_base; ctx->win_open = 1; ctx->win_enabled = 1;
+    return IBCU_OK;
+}
+
+extern "C" int ibcu_window_open(ibcu_ctx* ctx, int peer, const void* handle) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, handle && peer >= 0 && peer < ctx->world && peer < IBCU_MAX_RANKS, "ibcu_window_open: peer %d of %d", peer, ctx->world);
+    if (!ctx->win_base) return ibcu_fail(ctx, IBCU_ERR_STATE, "ibcu_window_open before ibcu_window_create");
+    if (peer == ctx->rank || ctx->win_peer[peer]) return IBCU_OK;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void* ptr = nullptr;
+    IBCU_CUDA(ctx, cudaSetDevice(ctx->device));
+    IBCU_CUDA(ctx, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    ctx->win_peer[peer] = (char*)ptr;
+    ctx->win_open++;
+    return IBCU_OK;
+}
+
+extern "C" int ibcu_window_alloc(ibcu_ctx* ctx, size_t bytes, void** dptr) {
+    IBCU_CHECK_CTX(ctx);
+    if (!dptr) return IBCU_ERR_PARAM;
+    *dptr = nullptr;
+    if (!ctx->win_base) return IBCU_ERR_STATE;               // not an error state of the context: callers fall back to ibcu_malloc
+    const size_t need = (bytes + 255) & ~(size_t)255;
+    if (ctx->win_used + need > ctx->win_bytes) return IBCU_ERR_NOMEM;
+    *dptr = ctx->win_base + ctx->win_used;
+    ctx->win_used += need;
+    return IBCU_OK;
+}
+
+extern "C" void ibcu_window_enable(ibcu_ctx* ctx, int on) { if (ctx) ctx->win_enabled = on ? 1 : 0; }
+
+static bool in_window(const ibcu_ctx* ctx, const void* p) {
+    return ctx->win_base && (const char*)p >= ctx->win_base + WIN_HEADER && (const char*)p < ctx->win_base + ctx->win_bytes;
+}
+
+extern "C" int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const int* M, const int* stride, int n, int B, int align) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, bufs && M && stride && n >= 1 && n <= 4 && B >= 1, "ibcu_allgather_rows_n: bad arguments");
+    if (ctx->world == 1) return IBCU_OK;
+    bool push = ctx->win_enabled && ctx->win_open == ctx->world;
+    for (int i = 0; i < n && push; i++) {
+        push = in_window(ctx, bufs[i]);
+        for (int j = 0; j < 4; j++) if (ctx->win_last[j] == bufs[i]) push = false;   // the peers may still be reading the previous gather of it
+    }
+    if (!push) {
+        for (int j = 0; j < 4; j++) ctx->win_last[j] = nullptr;
+        for (int i = 0; i < n; i++) { int rc = ibcu_allgather_rows(ctx, bufs[i], M[i], stride[i], B, align); if (rc) return rc; }
+        return IBCU_OK;
+    }
+    PushParams p;
+    memset(&p, 0, sizeof p);
+    p.n = n; p.B = B; p.rank = ctx->rank; p.world = ctx->world; p.base = ctx->win_base; p.err = ctx->win_err;
+    for (int r = 0; r < ctx->world; r++) p.peer[r] = ctx->win_peer[r];
+    for (int i = 0; i < n; i++) {
+        IBCU_REQUIRE(ctx, bufs[i] && M[i] >= 0 && stride[i] >= M[i], "ibcu_allgather_rows_n: tensor %d", i);
+        int r0, rn;
+        ibcu_shard_rows(M[i], ctx->world, ctx->rank, align, &r0, &rn);
+        p.d[i] = { bufs[i], stride[i], r0, rn };
+    }
+    for (int j = 0; j < 4; j++) ctx->win_last[j] = j < n ? bufs[j] : nullptr;
+    return ibcu_launch(ctx, allgather_push_kernel, dim3(1), dim3(1024), 0, 1, true, p);
 }
 
 static int allreduce(ibcu_ctx* ctx, void* buf, size_t n, ncclDataType_t ty) {

@@ -10,6 +10,7 @@
 
 #define IBCU_MAX_GRAPHS 16
 #define IBCU_MAX_EVENTS 16
+#define IBCU_MAX_RANKS 16
 
 struct ncclComm;
 
@@ -31,6 +32,13 @@ struct ibcu_ctx {
     // communicator (NULL when single GPU)
     ncclComm* comm;
     int rank, world;
+    // peer window: a slab of this GPU's memory that the other ranks map and write their row slices into
+    char*  win_base;   size_t win_bytes, win_used;
+    char*  win_peer[IBCU_MAX_RANKS];               // win_peer[rank] == win_base
+    int    win_open;                                // peers mapped so far
+    int    win_enabled;
+    int*   win_err;                                 // pinned, mapped: a push kernel that gave up waiting writes its epoch here
+    const void* win_last[4];                        // buffers of the previous push (a buffer is not pushed twice in a row)
 };
 
 int ibcu_fail(ibcu_ctx* ctx, int code, const char* fmt, ...);

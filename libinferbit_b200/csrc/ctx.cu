@@ -94,6 +94,7 @@ extern "C" int ibcu_malloc(ibcu_ctx* ctx, size_t bytes, void** dptr) {
 extern "C" int ibcu_free(ibcu_ctx* ctx, void* dptr) {
     IBCU_CHECK_CTX(ctx);
     if (!dptr) return IBCU_OK;
+    if (ctx->win_base && (char*)dptr >= ctx->win_base && (char*)dptr < ctx->win_base + ctx->win_bytes) return IBCU_OK;   // window memory goes with the window
     IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     IBCU_CUDA(ctx, cudaFree(dptr));
     return IBCU_OK;
@@ -133,6 +134,11 @@ extern "C" int ibcu_memset(ibcu_ctx* ctx, void* dst, int byte, size_t bytes) {
 extern "C" int ibcu_sync(ibcu_ctx* ctx) {
     IBCU_CHECK_CTX(ctx);
     IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->win_err && *(volatile int*)ctx->win_err) {
+        const int e = *(volatile int*)ctx->win_err;
+        *(volatile int*)ctx->win_err = 0;
+        return ibcu_fail(ctx, IBCU_ERR_COMM, "all-gather %d: a peer's rows did not arrive within the wait limit", e);
+    }
     return ctx->status;
 }
 

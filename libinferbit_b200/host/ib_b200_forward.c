@@ -45,6 +45,12 @@ struct ib_b200_model {
 #define AMAX_PARTS 28
 
 static int dmalloc(ib_b200_model* m, void** p, size_t bytes) { return ibcu_malloc(m->ctx, bytes ? bytes : 16, p); }
+/* activations that are all-gathered live in the peer window when the context has one (same order, hence same
+ * offsets, on every rank), so that the gather is a push over NVLink; elsewhere ordinary device memory */
+static int amalloc(ib_b200_model* m, void** p, size_t bytes) {
+    if (m->world > 1 && ibcu_window_alloc(m->ctx, bytes ? bytes : 16, p) == 0) return 0;
+    return dmalloc(m, p, bytes);
+}
 
 static int lin_alloc(ib_b200_model* m, lin* t, int M, int N, int bits) {
     t->M = M; t->N = N; t->bits = bits;
@@ -86,7 +92,7 @@ ib_b200_model* ib_b200_model_create(ibcu_ctx* ctx, const ib_b200_model_cfg* cfg)
     if (!rc) rc = dmalloc(m, &m->final_norm, (size_t)H * 2);
     void** act[] = { (void**)&m->x, (void**)&m->xb, (void**)&m->q, (void**)&m->k, (void**)&m->v, (void**)&m->att, (void**)&m->hg, (void**)&m->hu, (void**)&m->logits };
     const size_t asz[] = { (size_t)H, (size_t)H, (size_t)H, (size_t)kv, (size_t)kv, (size_t)H, (size_t)I, (size_t)I, (size_t)c.vocab };
-    for (int i = 0; i < 9 && !rc; i++) rc = dmalloc(m, act[i], asz[i] * BMAX * sizeof(float));
+    for (int i = 0; i < 9 && !rc; i++) rc = amalloc(m, act[i], asz[i] * BMAX * sizeof(float));
     if (!rc) rc = dmalloc(m, (void**)&m->tokens, BMAX * sizeof(int32_t));
     if (!rc) rc = dmalloc(m, (void**)&m->amax, (size_t)BMAX * AMAX_PARTS * sizeof(float));
     m->pin_bytes = (size_t)BMAX * c.vocab * sizeof(float) + 256;
@@ -207,7 +213,14 @@ static ibcu_linear_t desc(const lin* t, float* out, int epilogue) {
     return d;
 }
 static int gather(ib_b200_model* m, const lin* t, float* buf, int B) {
-    return m->world > 1 ? ibcu_allgather_rows(m->ctx, buf, t->M, t->M, B, ROW_ALIGN) : 0;
+    if (m->world == 1) return 0;
+    float* bufs[1] = { buf }; int M[1] = { t->M };
+    return ibcu_allgather_rows_n(m->ctx, bufs, M, M, 1, B, ROW_ALIGN);
+}
+static int gather3(ib_b200_model* m, const lin* t0, float* b0, const lin* t1, float* b1, const lin* t2, float* b2, int B) {
+    if (m->world == 1) return 0;
+    float* bufs[3] = { b0, b1, b2 }; int M[3] = { t0->M, t1->M, t2 ? t2->M : 0 };
+    return ibcu_allgather_rows_n(m->ctx, bufs, M, M, t2 ? 3 : 2, B, ROW_ALIGN);
 }
 
 /* the launch sequence of one step; everything stays on the device */
@@ -222,9 +235,7 @@ static int issue(ib_b200_model* m, int pos0, int B) {
         ibcu_prologue_t n1 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->in_norm, c->eps, NULL, 0 };
         ibcu_linear_t qkv[3] = { desc(&y->t[IB_B200_Q], m->q, 0), desc(&y->t[IB_B200_K], m->k, 0), desc(&y->t[IB_B200_V], m->v, 0) };
         rc = ibcu_linear_ex(ctx, qkv, 3, m->x, H, B, c->attn_bits, &n1);
-        if (!rc) rc = gather(m, &y->t[IB_B200_Q], m->q, B);
-        if (!rc) rc = gather(m, &y->t[IB_B200_K], m->k, B);
-        if (!rc) rc = gather(m, &y->t[IB_B200_V], m->v, B);
+        if (!rc) rc = gather3(m, &y->t[IB_B200_Q], m->q, &y->t[IB_B200_K], m->k, &y->t[IB_B200_V], m->v, B);
         /* RoPE, the KV-cache write and the attention itself are one step on the device */
         if (!rc) rc = ibcu_attention_decode(ctx, m->q, m->k, m->v, (float*)y->k_cache, (float*)y->v_cache, m->att,
                                             c->n_heads, c->n_kv_heads, c->head_dim, pos0, B, c->theta);
@@ -235,8 +246,7 @@ static int issue(ib_b200_model* m, int pos0, int B) {
         ibcu_prologue_t n2 = { IBCU_PRO_RMSNORM, NULL, (const uint16_t*)y->post_norm, c->eps, NULL, 0 };
         ibcu_linear_t gu[2] = { desc(&y->t[IB_B200_GATE], m->hg, 0), desc(&y->t[IB_B200_UP], m->hu, 0) };
         if (!rc) rc = ibcu_linear_ex(ctx, gu, 2, m->x, H, B, c->mlp_bits, &n2);
-        if (!rc) rc = gather(m, &y->t[IB_B200_GATE], m->hg, B);
-        if (!rc) rc = gather(m, &y->t[IB_B200_UP], m->hu, B);
+        if (!rc) rc = gather3(m, &y->t[IB_B200_GATE], m->hg, &y->t[IB_B200_UP], m->hu, NULL, NULL, B);
         /* silu(gate) * up (src/forward.c:637-640) in one small launch that also leaves max|h| for down_proj,
          * whose blocks then turn h into their integer operand without a reduction of their own */
         if (!rc) rc = ibcu_silu_mul_amax(ctx, m->hg, m->hg, m->hu, c->inter, B, m->amax, AMAX_PARTS);

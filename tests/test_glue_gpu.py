@@ -98,3 +98,35 @@ def test_rope_kv_write_and_attention(backend, cpu_libs, n_heads, n_kv, hd, pos0,
     assert _cpu.close(be.download(dkc, np.float32, ctx_len * kv_dim).reshape(ctx_len, kv_dim), kcr, RTOL, ATOL)
     assert np.array_equal(be.download(dvc, np.float32, ctx_len * kv_dim).reshape(ctx_len, kv_dim), vcr)
     assert _cpu.close(be.download(dout, np.float32, B * H).reshape(B, H), want, RTOL, ATOL)
+
+
+def test_peer_window_single_rank():
+    """The peer-window calls on a one-rank context: create, bump allocation with equal alignment, window
+    memory survives ibcu_free, the gather of one rank is a no-op, and a second window is refused. (The
+    push over NVLink itself needs two GPUs; the multi-rank bench checks it against the NCCL gather.)"""
+    from libinferbit_b200 import Backend
+    be = Backend(0)
+    try:
+        lib = be.lib
+        p = C.c_void_p()
+        assert lib.ibcu_window_alloc(be.ctx, 1024, C.byref(p)) != 0 and lib.ibcu_status(be.ctx) == 0     # no window yet: plain refusal
+        h = (C.c_ubyte * 64)()
+        be._check(lib.ibcu_window_create(be.ctx, 1 << 20, h))
+        assert any(h)
+        a, b = C.c_void_p(), C.c_void_p()
+        be._check(lib.ibcu_window_alloc(be.ctx, 1000, C.byref(a)))
+        be._check(lib.ibcu_window_alloc(be.ctx, 4096, C.byref(b)))
+        assert b.value - a.value == 1024 and a.value % 256 == 0
+        x = np.arange(1024, dtype=np.float32)
+        be._check(lib.ibcu_memcpy_h2d(be.ctx, b, x.ctypes.data, x.nbytes))
+        be._check(lib.ibcu_free(be.ctx, b))                          # not returned to the driver: still usable
+        bufs = (C.c_void_p * 1)(b.value); Ms = (C.c_int * 1)(1024)
+        be._check(lib.ibcu_allgather_rows_n(be.ctx, bufs, Ms, Ms, 1, 1, 32))
+        y = np.empty_like(x)
+        be._check(lib.ibcu_memcpy_d2h(be.ctx, y.ctypes.data, b, x.nbytes)); be.sync()
+        assert np.array_equal(x, y)
+        big = C.c_void_p()
+        assert lib.ibcu_window_alloc(be.ctx, 2 << 20, C.byref(big)) != 0
+        assert lib.ibcu_window_create(be.ctx, 1 << 20, h) != 0
+    finally:
+        be.close()
