@@ -65,6 +65,47 @@ def main():
         out[f"km{D}_X"] = X; out[f"km{D}_C"] = Cn; out[f"km{D}_idx"] = idx
     np.savez_compressed(os.path.join(ROOT, "tests", "golden", "ref_vectors.npz"), **out)
     print("wrote", len(out), "arrays")
+    decode_golden(libs)
+
+
+def decode_golden(libs):
+    """tests/golden/decode_ref_logits.npz: logits of the reference's own inferbit_load + inferbit_forward on
+    the seeded mini model of ibf_model.py, fed one token per call from an empty KV cache (one thread,
+    the machine's SIMD table as ibf_load installs it, IB_W4A8=0 so that INT4 layers take the FP32-activation
+    kernel this build's decode step uses)."""
+    import tempfile
+    from tests.golden import ibf_model
+    os.environ["IB_W4A8"] = "0"
+    r = libs.ref
+    r.inferbit_config_create.restype = C.c_void_p
+    r.inferbit_config_set_threads.argtypes = [C.c_void_p, C.c_int]
+    r.inferbit_config_free.argtypes = [C.c_void_p]
+    r.inferbit_load.restype = C.c_void_p; r.inferbit_load.argtypes = [C.c_char_p, C.c_void_p]
+    r.inferbit_free.argtypes = [C.c_void_p]
+    r.inferbit_forward.restype = C.c_int
+    r.inferbit_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+    r.inferbit_last_error.restype = C.c_char_p
+    r.inferbit_kv_length.restype = C.c_int; r.inferbit_kv_length.argtypes = [C.c_void_p]
+    V = ibf_model.CFG["vocab"]
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "mini.ibf")
+        ibf_model.write_ibf(path)
+        cfg = r.inferbit_config_create()
+        r.inferbit_config_set_threads(cfg, 1)
+        m = r.inferbit_load(path.encode(), cfg)
+        assert m, r.inferbit_last_error()
+        toks = np.random.default_rng(5).integers(0, V, 8).astype(np.int32)
+        logits = np.empty((len(toks), V), np.float32)
+        for i in range(len(toks)):
+            rc = r.inferbit_forward(m, p(toks[i:i + 1]), 1, p(logits[i]), V)
+            assert rc == 0, r.inferbit_last_error()
+        assert r.inferbit_kv_length(m) == len(toks)
+        r.inferbit_free(m)
+        r.inferbit_config_free(cfg)
+    assert np.isfinite(logits).all() and float(np.abs(logits).max()) > 1e-2
+    np.savez_compressed(os.path.join(ROOT, "tests", "golden", "decode_ref_logits.npz"), tokens=toks, logits=logits,
+                        seed=np.array([ibf_model.SEED]))
+    print("wrote decode golden: logits", logits.shape, "max |logit|", float(np.abs(logits).max()))
 
 
 if __name__ == "__main__":
