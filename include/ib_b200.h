@@ -31,6 +31,10 @@ const char* ib_b200_last_error(void);
 int  ib_b200_register(const void* host_base, size_t bytes);
 int  ib_b200_unregister(const void* host_base);
 
+/* Bytes the table calls have moved since ib_b200_init: host->device (activations; row scales when first seen
+ * or changed) and device->host (results). */
+void ib_b200_copy_stats(unsigned long long* h2d_bytes, unsigned long long* d2h_bytes);
+
 /* ── ib_kernels-shaped dispatch table (src/inferbit_internal.h:199-277) ─────────────── */
 typedef struct {
     void (*matmul_int4)(float* out, const void* weights, const float* scales, const float* input, int M, int N);

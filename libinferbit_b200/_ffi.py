@@ -173,6 +173,7 @@ HOST_SYMBOLS = {
     "ib_b200_last_error": (C.c_char_p, []),
     "ib_b200_register": (_i, [_vp, C.c_size_t]),
     "ib_b200_unregister": (_i, [_vp]),
+    "ib_b200_copy_stats": (None, [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]),
     "ib_b200_install_kernels": (None, [_vp]),
     "ib_b200_matmul_int4": (None, [_vp, _vp, _vp, _vp, _i, _i]),
     "ib_b200_matmul_int8": (None, [_vp, _vp, _vp, _vp, _i, _i]),

@@ -102,7 +102,7 @@ extern "C" int ibcu_free(ibcu_ctx* ctx, void* dptr) {
 extern "C" int ibcu_host_alloc(ibcu_ctx* ctx, size_t bytes, void** hptr) {
     IBCU_CHECK_CTX(ctx);
     if (!hptr) return ibcu_fail(ctx, IBCU_ERR_PARAM, "ibcu_host_alloc: null out pointer");
-    cudaError_t e = cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocDefault);
+    cudaError_t e = cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocMapped | cudaHostAllocPortable);   // device-visible at the same address
     if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_NOMEM, "cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
     return IBCU_OK;
 }

@@ -714,8 +714,13 @@ int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail)
     auto kern = linear_mma_kernel<BITS, NCG, RT, W, STAGES>;
     const size_t smem = (size_t)STAGES * RT * 16 * lin_ld(W) + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * NCG * 8 * 4 + smem_tail;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
+        static size_t allowed[64];                                 // per device, per kernel instance: raised only when a call needs more
+        size_t& have = allowed[ctx->device & 63];
+        if (smem > have) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
+            have = smem;
+        }
     }
     return ibcu_launch(ctx, kern, dim3(grid), dim3(W * 32), smem, 1, true, p);
 }

@@ -38,9 +38,16 @@ int ib_b200_init(int device) {
     return 0;
 }
 
+static void scale_entry_drop(ib_b200_scale_entry* e) {
+    if (e->dev) ibcu_free(g_ib.ctx, e->dev);
+    free(e->host);
+    memset(e, 0, sizeof *e);
+}
+
 void ib_b200_shutdown(void) {
     if (!g_ib.ctx) return;
     ib_b200_pq_release_all();
+    for (int i = 0; i < IB_B200_SCALE_SLOTS; i++) if (g_ib.scales[i].weights) scale_entry_drop(&g_ib.scales[i]);
     for (int i = 0; i < g_ib.n_ranges; i++) ibcu_free(g_ib.ctx, g_ib.ranges[i].dev);
     for (int i = 0; i < IB_B200_NSTAGE; i++) {
         if (g_ib.stage_dev[i]) ibcu_free(g_ib.ctx, g_ib.stage_dev[i]);
@@ -78,6 +85,20 @@ int ib_b200_register(const void* host_base, size_t bytes) {
 int ib_b200_unregister(const void* host_base) {
     for (int i = 0; i < g_ib.n_ranges; i++)
         if (g_ib.ranges[i].host == (const char*)host_base) {
+            /* scale vectors cached for tensors of this range go with it (the table is rebuilt: open addressing) */
+            ib_b200_scale_entry keep[IB_B200_SCALE_SLOTS];
+            int nkeep = 0;
+            for (int k = 0; k < IB_B200_SCALE_SLOTS; k++) {
+                ib_b200_scale_entry* e = &g_ib.scales[k];
+                if (!e->weights) continue;
+                if ((const char*)e->weights >= g_ib.ranges[i].host && (const char*)e->weights < g_ib.ranges[i].host + g_ib.ranges[i].bytes) scale_entry_drop(e);
+                else { keep[nkeep++] = *e; memset(e, 0, sizeof *e); }
+            }
+            for (int k = 0; k < nkeep; k++) {
+                unsigned h = (unsigned)(((uintptr_t)keep[k].weights >> 6) * 2654435761u) % IB_B200_SCALE_SLOTS;
+                while (g_ib.scales[h].weights) h = (h + 1) % IB_B200_SCALE_SLOTS;
+                g_ib.scales[h] = keep[k];
+            }
             ibcu_free(g_ib.ctx, g_ib.ranges[i].dev);
             g_ib.ranges[i] = g_ib.ranges[--g_ib.n_ranges];
             return 0;
@@ -111,16 +132,44 @@ int ib_b200_stage(int slot, size_t bytes, void** host, void** dev) {
     return 0;
 }
 
+enum { ST_X = 0, ST_SCALE, ST_OUT, ST_AUX };
+
 /* host array -> staging slot -> device; returns the device pointer or NULL */
 static void* push(int slot, const void* src, size_t bytes) {
     void *h, *d;
     if (ib_b200_stage(slot, bytes, &h, &d)) return NULL;
     memcpy(h, src, bytes);
     if (ib_b200_check(ibcu_memcpy_h2d(g_ib.ctx, d, h, bytes), "h2d")) return NULL;
+    g_ib.h2d_bytes += bytes;
     return d;
 }
 
-enum { ST_X = 0, ST_SCALE, ST_OUT, ST_AUX };
+/* device copy of the FP32 row scales of the tensor at `weights`: uploaded when first seen or changed */
+static void* scales_on_device(const void* weights, const float* scales, int M) {
+    const size_t bytes = (size_t)M * sizeof(float);
+    unsigned h = (unsigned)(((uintptr_t)weights >> 6) * 2654435761u) % IB_B200_SCALE_SLOTS;
+    ib_b200_scale_entry* e = NULL;
+    for (int probe = 0; probe < 64; probe++, h = (h + 1) % IB_B200_SCALE_SLOTS) {
+        if (!g_ib.scales[h].weights || (g_ib.scales[h].weights == weights && g_ib.scales[h].M == M)) { e = &g_ib.scales[h]; break; }
+    }
+    if (!e) return push(1 /* ST_SCALE */, scales, bytes);               /* neighbourhood full: no caching for this tensor */
+    if (e->weights && memcmp(e->host, scales, bytes) == 0) return e->dev;
+    if (!e->weights) {
+        e->host = (float*)malloc(bytes);
+        if (!e->host || ib_b200_check(ibcu_malloc(g_ib.ctx, bytes, &e->dev), "scale cache")) { free(e->host); memset(e, 0, sizeof *e); return push(1, scales, bytes); }
+        e->weights = weights; e->M = M;
+    }
+    memcpy(e->host, scales, bytes);
+    void* staged = push(1, scales, bytes);
+    if (!staged || ib_b200_check(ibcu_memcpy_d2d(g_ib.ctx, e->dev, staged, bytes), "scale cache copy")) return staged;
+    return e->dev;
+}
+
+void ib_b200_copy_stats(unsigned long long* h2d_bytes, unsigned long long* d2h_bytes) {
+    if (h2d_bytes) *h2d_bytes = g_ib.h2d_bytes;
+    if (d2h_bytes) *d2h_bytes = g_ib.d2h_bytes;
+}
+
 
 static int ready(const char* who) {
     if (g_ib.ctx) return 1;
@@ -139,15 +188,19 @@ static void linear_fp32(const char* who, float* out, const void* weights, const 
     void* dw = ib_b200_translate(weights, wbytes);
     if (!dw) { ib_b200_set_error(IBCU_ERR_STATE, "%s: weights %p (+%zu) are not inside a registered range; there is no CPU path", who, weights, wbytes); return; }
     void* dx = push(ST_X, input, (size_t)B * N * sizeof(float));
-    void* ds = push(ST_SCALE, scales, (size_t)M * sizeof(float));
+    void* ds = scales_on_device(weights, scales, M);
     void *ho, *dout;
     const size_t obytes = ((size_t)(B - 1) * M_stride + M) * sizeof(float);
     if (!dx || !ds || ib_b200_stage(ST_OUT, obytes, &ho, &dout)) return;
-    ibcu_linear_t t = { dw, ds, (float*)dout, M, M_stride, 1, IBCU_EPI_STORE };
+    /* small results are written by the kernel straight into the pinned host buffer (it is mapped into the
+     * device's address space): no copy launch between the kernel and the host's wait */
+    const int direct = obytes <= (1u << 20);
+    ibcu_linear_t t = { dw, ds, (float*)(direct ? ho : dout), M, M_stride, 1, IBCU_EPI_STORE };
     int rc = ibcu_linear(g_ib.ctx, &t, 1, (const float*)dx, N, B, bits);
-    if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, obytes);
+    if (!rc && !direct) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, obytes);
     if (!rc) rc = ibcu_sync(g_ib.ctx);
     if (ib_b200_check(rc, who)) return;
+    g_ib.d2h_bytes += (size_t)B * M * sizeof(float);
     for (int b = 0; b < B; b++) memcpy(out + (size_t)b * M_stride, (const float*)ho + (size_t)b * M_stride, (size_t)M * sizeof(float));
 }
 

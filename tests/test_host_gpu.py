@@ -60,6 +60,20 @@ def test_dispatch_table_matmuls(host, cpu_libs):
     cpu_libs.oracle.ibo_matmul_w4a8_batch(wantb, w4, s4, q, sa, M, N, B, M)
     table.matmul_w4a8_batch(p(gotb), blob.ctypes.data + M * N, p(s4), p(q), p(sa), M, N, B, M)
     assert np.array_equal(gotb, wantb)
+    # row scales are cached on the device per tensor and re-sent only when the host vector changes
+    h0, d0 = C.c_ulonglong(), C.c_ulonglong(); h1, d1 = C.c_ulonglong(), C.c_ulonglong()
+    cpu_libs.oracle.ibo_matmul_int8(want, w8, s8, x[3], M, N)
+    host.ib_b200_copy_stats(C.byref(h0), C.byref(d0))
+    table.matmul_int8(p(got), blob.ctypes.data, p(s8), p(x[3]), M, N)
+    host.ib_b200_copy_stats(C.byref(h1), C.byref(d1))
+    assert _cpu.close(got, want, RTOL, ATOL)
+    assert h1.value - h0.value == 4 * N and d1.value - d0.value == 4 * M      # activations only; result only
+    s8b = (s8 * np.float32(0.5)).astype(np.float32)
+    cpu_libs.oracle.ibo_matmul_int8(want, w8, s8b, x[3], M, N)
+    table.matmul_int8(p(got), blob.ctypes.data, p(s8b), p(x[3]), M, N)
+    host.ib_b200_copy_stats(C.byref(h0), C.byref(d0))
+    assert _cpu.close(got, want, RTOL, ATOL)
+    assert h0.value - h1.value == 4 * N + 4 * M                                  # changed scales travel again
     # weights outside every registered range: an error, outputs untouched, no CPU path
     other = w8.copy(); got[:] = 9.0
     table.matmul_int8(p(got), p(other), p(s8), p(x[0]), M, N)
