@@ -191,14 +191,21 @@ def main():
         raw = (C.c_ubyte * 128)(*idbuf.tolist())
         assert lib.ibcu_comm_init(ctx, raw, rank, world) == 0, lib.ibcu_last_error(ctx)
         if not os.environ.get("IB_BENCH_NCCL_ONLY"):
-            # peer window: every rank maps the others' slab, gathers become pushes over NVLink
+            # peer window: every rank maps the others' slab, gathers become pushes over NVLink. If any rank
+            # cannot create or map a window, every rank stays on NCCL.
             mine = (C.c_ubyte * 64)()
-            assert lib.ibcu_window_create(ctx, 96 << 20, mine) == 0, lib.ibcu_last_error(ctx)
+            ok = lib.ibcu_window_create(ctx, 96 << 20, mine) == 0
             allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
             dist.all_gather(allh, torch.tensor(list(mine), dtype=torch.uint8))
             for r in range(world):
-                if r != rank:
-                    assert lib.ibcu_window_open(ctx, r, (C.c_ubyte * 64)(*allh[r].tolist())) == 0, lib.ibcu_last_error(ctx)
+                if ok and r != rank:
+                    ok = lib.ibcu_window_open(ctx, r, (C.c_ubyte * 64)(*allh[r].tolist())) == 0
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                lib.ibcu_clear_error(ctx)
+                lib.ibcu_window_enable(ctx, 0)
+                os.environ["IB_BENCH_NCCL_ONLY"] = "window unavailable"
             dist.barrier()
     if args.case:
         sync = lambda: bs.check(lib, ctx, lib.ibcu_sync(ctx))
