@@ -266,3 +266,47 @@ def test_silu_mul_amax_then_known_max_prologue(backend, cpu_libs, bits, M, N, B,
     if N % 16 == 0:                       # the tensor-core path: identical fixed-point operands
         assert np.array_equal(got1, got2)
     assert _cpu.close(got2, oracle_linear(cpu_libs, w, s16, want_h, bits), 2e-3, 2e-4)
+
+
+@pytest.mark.parametrize("bits,Ms,N,B", [
+    (8, [7, 250, 3], 512, 1),            # ragged tensors: runs of rows never cross a tensor, tiles shorter than 16 rows
+    (4, [1, 2, 5000, 33], 1024, 2),      # four tensors, one of them larger than the whole grid's worth of 4-row runs
+    (8, [4096, 1024, 1024], 4096, 1),    # the q,k,v launch of the headline step
+    (4, [14336, 14336], 4096, 1),        # the gate,up launch of the 7B decode step
+    (8, [0, 64, 0], 256, 3),             # empty shards (a rank that owns no rows of a tensor)
+])
+def test_several_tensors_with_ragged_rows(backend, cpu_libs, bits, Ms, N, B):
+    rng = np.random.default_rng(bits + sum(Ms) + N)
+    be = backend
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    dx = be.upload(x)
+    n = len(Ms)
+    descs = (LinearT * n)()
+    keep, wants, outs = [], [], []
+    for i, M in enumerate(Ms):
+        Mr = max(M, 1)
+        w, s16, _ = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, Mr, N, 1)
+        wants.append(oracle_linear(cpu_libs, w, s16, x, bits)[:, :M])
+        dw, ds = be.upload(w), be.upload(s16)
+        do = be.upload(np.full((B, Mr), -3.0, np.float32))
+        keep += [dw, ds]; outs.append(do)
+        descs[i] = LinearT(dw.ptr, ds.ptr, do.ptr, M, Mr, 0, 0)
+    be._check(be.lib.ibcu_linear(be.ctx, descs, n, dx.ptr, N, B, bits))
+    be.sync()
+    for do, want, M in zip(outs, wants, Ms):
+        Mr = max(M, 1)
+        got = be.download(do, np.float32, B * Mr).reshape(B, Mr)
+        assert _cpu.close(got[:, :M], want, RTOL, ATOL), (M, float(np.max(np.abs(got[:, :M] - want))) if M else 0)
+        if M == 0:
+            assert np.all(got == -3.0)
+
+
+@pytest.mark.parametrize("bits,M,N,B", [(8, 32000, 4096, 1), (8, 48, 65536, 2), (4, 40, 131072, 1), (8, 200, 16384, 6)])
+def test_full_size_head_and_rows_longer_than_shared_memory(backend, cpu_libs, bits, M, N, B):
+    """The LM-head shape against the scalar restatement, and rows whose limbs do not fit one block's shared
+    memory (columns split over several blocks, integer partial sums recombined by linear_finalize_kernel)."""
+    rng = np.random.default_rng(bits * 13 + M + N + B)
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    got = backend.linear(w, s16, x, bits)
+    want = oracle_linear(cpu_libs, w, s16, x, bits)
+    assert _cpu.close(got, want, RTOL, ATOL * max(1.0, float(np.abs(want).max()))), float(np.max(np.abs(got - want)))
