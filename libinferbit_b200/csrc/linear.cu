@@ -238,12 +238,19 @@ __device__ __forceinline__ void xconvert_regs(const XSource& src, int N, int b, 
         }
     } else if (src.op == IBCU_PRO_RMSNORM) {                  // 1/sqrt(mean(x^2) + eps) over the whole row (src/kernels/scalar.c:126-138)
         __half2 w[P][4];
+        const bool w16 = ((uintptr_t)(src.norm_w + c0) & 15) == 0;
 #pragma unroll
         for (int i = 0; i < P; i++) {
             const int j = (threadIdx.x + i * nth) * 8;
+            if (j < valid && w16) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src.norm_w + c0 + j);
+                w[i][0] = *reinterpret_cast<const __half2*>(&raw.x); w[i][1] = *reinterpret_cast<const __half2*>(&raw.y);
+                w[i][2] = *reinterpret_cast<const __half2*>(&raw.z); w[i][3] = *reinterpret_cast<const __half2*>(&raw.w);
+            } else {
 #pragma unroll
-            for (int q = 0; q < 4; q++)
-                w[i][q] = j < valid ? *reinterpret_cast<const __half2*>(src.norm_w + c0 + j + 2 * q) : __floats2half2_rn(0.0f, 0.0f);
+                for (int q = 0; q < 4; q++)
+                    w[i][q] = j < valid ? *reinterpret_cast<const __half2*>(src.norm_w + c0 + j + 2 * q) : __floats2half2_rn(0.0f, 0.0f);
+            }
         }
         float ss = 0.0f;
         if (c0 == 0 && valid == N) {
@@ -303,6 +310,7 @@ __device__ __forceinline__ void xconvert_regs(const XSource& src, int N, int b, 
 #pragma unroll
         for (int l = 0; l < LIN_LIMBS; l++) *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk[l];
     }
+    if (!perm8) return;                                       // the limb sums only remove the nibble bias of INT4 weights
 #pragma unroll
     for (int l = 0; l < LIN_LIMBS; l++) {
         int v = lsum[l];
@@ -355,6 +363,7 @@ __device__ __forceinline__ void xconvert_known(const XSource& src, int N, int b,
             for (int l = 0; l < LIN_LIMBS; l++) *reinterpret_cast<uint2*>(dst_b + (size_t)l * xs_ld + j) = pk[l];
         }
     }
+    if (!perm8) return;                                       // the limb sums only remove the nibble bias of INT4 weights
 #pragma unroll
     for (int l = 0; l < LIN_LIMBS; l++) {
         int v = lsum[l];
