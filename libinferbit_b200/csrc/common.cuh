@@ -24,7 +24,7 @@ struct ibcu_ctx {
     int force_generic;
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
-    void*  xpack;      size_t xpack_bytes;      // fp16 activation pieces + per-slice scales of the current linear call
+    void*  xpack;      size_t xpack_bytes;      // activation limbs + per-slice scales and limb sums of the current linear call
     void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, PQ slabs, k-means per-block partials)
     cudaEvent_t events[IBCU_MAX_EVENTS];
     cudaGraphExec_t graphs[IBCU_MAX_GRAPHS];

@@ -3,9 +3,9 @@
 // Data in HBM: weights keep the reference layout bit for bit (INT8 row-major; INT4 two columns per
 // byte, low nibble first, bias 8), scales are FP16 (or FP32) per output row.
 //
-// Arithmetic of the fast path: integer tensor cores, exactly. xprep_kernel turns every slice of an
-// FP32 activation into a 32-bit fixed-point integer X = rint(x * 2^s) (s per slice, so that the
-// slice maximum sits just under 2^30) and splits X into four signed base-256 digits (int8 "limbs").
+// Arithmetic of the fast path: integer tensor cores, exactly. Every slice of an FP32 activation becomes
+// a 32-bit fixed-point integer X = rint(x * 2^s) (s per slice, so that the slice maximum sits just
+// under 2^30), split into four signed base-256 digits (int8 "limbs").
 // linear_mma_kernel feeds the weights - INT8 bytes as they are, INT4 nibbles masked in place with
 // one LOP3 per four weights - and the limbs to mma.sync.m16n8k32 (s8/u8 x s8 -> s32): every product
 // and every sum is an exact integer. The four limb sums are recombined in 64-bit, converted to
@@ -15,16 +15,24 @@
 // Because a dot product is invariant under a permutation of k applied to both operands, each lane
 // simply owns 16 contiguous bytes of a row; no transpose or ldmatrix is needed for the weights.
 //
-// Work split: xprep_kernel runs one block per (activation, column slice). linear_mma_kernel is
-// persistent: a block is bound to one column slice, copies that slice's limbs into shared memory
-// once, and then walks row blocks of RT*16 rows. Weights reach shared memory through a cp.async ring
-// whose stages are RT*16 rows x 512 bytes, written in row-linear order (every warp instruction covers
-// 512 contiguous bytes of one row, which is what HBM wants; lane-owns-a-row-fragment register loads
-// measured 2-3 TB/s, this pattern 6+ TB/s). The W warps of a block take one 64-byte k-block of each
-// stage each and meet in a shared-memory reduction per row block. When the columns are split over
-// several blocks (only when a row's limbs do not fit shared memory), each writes its integer partial
+// Activation conversion (xconvert_*): short rows are converted by every block of linear_mma_kernel for
+// itself, straight into shared memory, with all of the block's loads issued before the first is used;
+// long rows once, by xprep_kernel (one block per activation and column slice), into a scratch buffer
+// the blocks copy from. RMSNorm and silu(x)*x2 can be folded into the conversion; a caller that knows
+// max|x| (IBCU_PRO_KNOWN_MAX) spares the blocks their reduction.
+//
+// Work split: linear_mma_kernel is persistent, one wave of blocks. A block is bound to one column slice,
+// whose limbs it holds in shared memory, and to one tensor of the launch, of which it owns one contiguous
+// run of rows; the runs are equal to within a row (blocks are allotted to the tensors in proportion to
+// their rows), so every SM streams the same number of bytes. A run is walked in tiles of up to RT*16
+// rows; rows a tile lacks are zero-filled without fetching anything. Weights reach shared memory through
+// a cp.async ring whose stages are (tile rows) x 64*W bytes, written in row-linear order (every warp
+// instruction covers contiguous bytes of one row, which is what HBM wants; lane-owns-a-row-fragment
+// register loads measured 2-3 TB/s, this pattern 6+ TB/s). The W warps of a block take one 64-byte
+// k-block of each stage each and meet in a shared-memory reduction per tile. When the columns are split
+// over several blocks (only when a row's limbs do not fit shared memory), each writes its integer partial
 // sums to scratch and linear_finalize_kernel recombines them (a fence + arrival-counter epilogue
-// inside the main kernel cost ~3 us per row block and slice, a second small launch costs ~2 us once).
+// inside the main kernel cost ~3 us per tile and slice, a second small launch costs ~2 us once).
 //
 // Portable path (linear_generic_kernel): one warp per output row, plain FP32 FMAs; used for shapes
 // the fast path does not take (row bytes not a multiple of 16, unaligned pointers) and by tests.
@@ -413,7 +421,7 @@ __device__ __forceinline__ void imma_u8(int* c, uint32_t a0, uint32_t a1, uint32
 __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 // ── fast path ───────────────────────────────────────────────────────────────────────────
-// BITS: 4 or 8. NCG: groups of 8 MMA columns (ceil(4B/8)). RT: 16-row tiles per row block.
+// BITS: 4 or 8. NCG: groups of 8 MMA columns (ceil(4B/8)). RT: 16-row MMA tiles per tile of rows.
 // W: warps per block. STAGES: shared-memory ring depth.
 // MMA operands (m16n8k32, lane = 4g + t): A regs a0/a2 = row g, a1/a3 = row g+8, four bytes of k each;
 // B regs b0/b1 = column g. INT8: a 16-byte lane chunk is four words w0..w3 -> two MMAs (w0,w1), (w2,w3)
@@ -442,7 +450,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 template <int BITS, int NCG, int RT, int W, int STAGES>
 __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p) {
-    constexpr int R = RT * 16;                                // rows per row block
+    constexpr int R = RT * 16;                                // most rows per tile
     constexpr int COLS = NCG * 8;
     constexpr int NACC = BITS == 4 ? 2 : 1;                   // INT4 keeps low- and high-nibble sums apart
     constexpr int XB = BITS == 8 ? 64 : 128;                  // limb bytes (= columns) per k-block
@@ -602,7 +610,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
 
         TRACE(4);
-        // ── row block done: every warp holds integer partial sums of all R rows over its k-blocks ──
+        // ── tile done: every warp holds integer partial sums of all R rows over its k-blocks ──
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
             int* mine = red + ((size_t)a * W + warp) * R * COLS;
@@ -849,8 +857,8 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
             row_start += tensors[i].M;
         }
     }
-    // Shared memory per block: stage ring + reduction buffer + the slice's fp16 pieces. Columns are
-    // split over several blocks only when the pieces of a whole row do not fit.
+    // Shared memory per block: stage ring + reduction buffer + the slice's limbs. Columns are
+    // split over several blocks only when the limbs of a whole row do not fit.
     const int kbs = w;
     const int LIN_LD = lin_ld(w);
     // ring depth: the deeper ring when two blocks per SM still fit with it, else the shallower one
