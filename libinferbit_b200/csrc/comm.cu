@@ -1,6 +1,7 @@
-// Multi-GPU plumbing: one process per GPU, NCCL over NVLink/NVSwitch. The hot path has exactly two
-// exchange steps: the all-gather of row-sharded linear outputs and the all-reduce of k-means
-// centroid sums / counts. Everything else is replicated.
+// Multi-GPU plumbing: one process per GPU over NVLink/NVSwitch. The hot path has exactly two exchange
+// steps: the all-gather of row-sharded linear outputs (a push over peer memory when the ranks have
+// mapped each other's windows, else NCCL) and the all-reduce of k-means centroid sums / counts (NCCL).
+// Everything else is replicated.
 #include "common.cuh"
 #include <nccl.h>
 #include <dlfcn.h>
