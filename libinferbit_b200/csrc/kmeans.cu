@@ -15,6 +15,7 @@
 // then combined in index order.
 #include "common.cuh"
 #include <stdlib.h>
+#include <stdint.h>
 
 namespace {
 
@@ -270,6 +271,57 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const float* __restrict
     // coalesced loads, lane l fetches the code (and distance) of point p+l, then the warp walks the
     // 32 points in order with lanes acting as dimensions
     float* stage = reinterpret_cast<float*>(wcnt + (size_t)nwarp * K) + (size_t)warp * 32 * D;   // [32][D]
+    if ((D & 3) == 0 && 32 % (D >> 2) == 0 && ((uintptr_t)X & 15) == 0 && ((uintptr_t)stage & 15) == 0) {
+        // D/4 lanes per point (one float4 each), 32/(D/4) points per step. Points of a step that share a
+        // cluster are applied in rounds: a point goes in round r when r lower points of the step have its
+        // cluster, so every table entry still sees its points in index order. The next 32 points are
+        // fetched while the current ones are applied.
+        const int lpp = D >> 2, pps = 32 / lpp, q = lane / lpp, part = lane - q * lpp;
+        float4* stage4 = reinterpret_cast<float4*>(stage);
+        const float4* X4 = reinterpret_cast<const float4*>(X);
+        int code_n = 0; float dist_n = 0.0f; float4 xn[KM_MAX_D / 4];
+        auto fetch = [&](long p) {
+            const long mine = p + lane;
+            code_n = mine < p1 ? idx[mine] : 0;
+            dist_n = (dist && mine < p1) ? dist[mine] : 0.0f;
+            const long lim = (p1 - p) * lpp;                      // float4s that exist
+#pragma unroll
+            for (int u = 0; u < KM_MAX_D / 4; u++) {
+                const int e = lane + 32 * u;
+                xn[u] = (u < lpp && e < lim) ? X4[(size_t)p * lpp + e] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        };
+        if (p0 < p1) fetch(p0);
+        for (long p = p0; p < p1; p += 32) {
+            const int n = (int)((p1 - p) < 32 ? (p1 - p) : 32);
+            const int code = code_n;
+            inert += (double)dist_n;
+            __syncwarp();                                         // the previous pass's reads of the stage are done
+#pragma unroll
+            for (int u = 0; u < KM_MAX_D / 4; u++) if (u < lpp) stage4[lane + 32 * u] = xn[u];
+            if (p + 32 < p1) fetch(p + 32);
+            __syncwarp();
+            for (int j = 0; j < n; j += pps) {
+                const int pt = j + q;
+                const bool act = pt < n;
+                const int k = __shfl_sync(0xffffffffu, code, act ? pt : j);
+                const unsigned same = __match_any_sync(0xffffffffu, act ? k : -1 - lane);
+                const int rank = __popc(same & ((1u << lane) - 1u)) / lpp;
+                const int rounds = __reduce_max_sync(0xffffffffu, act ? rank : 0);
+                for (int r = 0; r <= rounds; r++) {
+                    if (act && rank == r) {
+                        float4* dst = reinterpret_cast<float4*>(ms + (size_t)k * D) + part;
+                        const float4 v = stage4[pt * lpp + part];
+                        float4 a = *dst;
+                        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                        *dst = a;
+                        if (part == 0) mc[k] += 1;
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else
     for (long p = p0; p < p1; p += 32) {
         const long mine = p + lane;
         const int n = (int)((p1 - p) < 32 ? (p1 - p) : 32);
