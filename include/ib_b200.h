@@ -121,24 +121,37 @@ enum { IB_B200_Q = 0, IB_B200_K, IB_B200_V, IB_B200_O, IB_B200_GATE, IB_B200_UP,
 /* A model lives on one context; with a communicator on the context every linear is row-sharded over
  * the ranks (the reference's row slices, src/threading.c:220-241) and gathered after each layer op. */
 ib_b200_model* ib_b200_model_create(ibcu_ctx* ctx, const ib_b200_model_cfg* cfg);
+/* Same with a bit width (4 or 8) per tensor, as a model file gives them: linear_bits[layer * 7 + which] for
+ * which = IB_B200_Q..IB_B200_DOWN, then linear_bits[n_layers * 7] for the head (NULL: the widths of cfg).
+ * embed_bits: storage form of the embedding rows, 8, 4 or 16 (src/forward.c:90-135). */
+ib_b200_model* ib_b200_model_create_bits(ibcu_ctx* ctx, const ib_b200_model_cfg* cfg, const int* linear_bits, int embed_bits);
 void           ib_b200_model_free(ib_b200_model* m);
 /* Random weights written straight into HBM (counter-based generator), norms near 1, KV cache
- * positions [0, kv_fill) filled with a hashed pattern in [-1, 1). */
+ * positions [0, kv_fill) filled with bell-shaped values of unit variance. Every tensor is a function of the
+ * seed and its place in the model only: N ranks together hold exactly the model one rank would hold. */
 int  ib_b200_model_fill_random(ib_b200_model* m, uint64_t seed, int kv_fill);
 /* Upload one full (unsharded) tensor from host memory; each rank keeps its row slice.
- * layer is ignored for IB_B200_HEAD. w: int8 [M*N] or packed nibbles [M*N/2]; scales: fp16 [M]. */
+ * layer is ignored for IB_B200_HEAD. w: int8 [M*N] or packed nibbles [M*N/2]; scales: fp16 [M], or NULL for
+ * a tensor stored without scales (scale 1, src/forward.c:152-156). */
 int  ib_b200_model_set_linear(ib_b200_model* m, int layer, int which, const void* w, const uint16_t* scales);
 int  ib_b200_model_set_norms(ib_b200_model* m, int layer, const uint16_t* input_norm, const uint16_t* post_attn_norm);
-int  ib_b200_model_set_embedding(ib_b200_model* m, const int8_t* embed, const uint16_t* embed_scale, const uint16_t* final_norm);
+/* embed: rows in the model's embedding storage form; embed_scale: fp16 [vocab] or NULL (rows used as they are). */
+int  ib_b200_model_set_embedding(ib_b200_model* m, const void* embed, const uint16_t* embed_scale, const uint16_t* final_norm);
 int  ib_b200_model_set_kv(ib_b200_model* m, int layer, const float* k, const float* v, int n_pos);
 int  ib_b200_model_get_kv(ib_b200_model* m, int layer, float* k, float* v, int n_pos);
 /* B consecutive positions pos0.. of one sequence (B == 1: forward_single_ex, src/forward.c:518-664;
  * B > 1: forward_batch, :682-846). tokens and logits are host arrays; logits [B*vocab] may be NULL.
- * The launch sequence is captured into a CUDA graph per (pos0, B) on first use and replayed. */
+ * The launch sequence is captured into a CUDA graph per batch size on first use and replayed for every
+ * position (the position is read on the device); the call that captures runs the step eagerly first. */
 int  ib_b200_forward_step(ib_b200_model* m, const int32_t* tokens, int pos0, int B, float* logits);
+/* Same step, but only the last position goes through the output head: logits_last [vocab] (what ib_forward
+ * keeps of a multi-token call, src/forward.c:872-901). */
+int  ib_b200_forward_step_last(ib_b200_model* m, const int32_t* tokens, int pos0, int B, float* logits_last);
 /* Same without host traffic: tokens already in the model's device token buffer (ib_b200_model_tokens),
  * logits left in ib_b200_model_logits. */
 int    ib_b200_forward_step_device(ib_b200_model* m, int pos0, int B);
+/* 0: issue the launches of a step one by one instead of replaying a graph (for per-kernel profiles). */
+void   ib_b200_model_use_graph(ib_b200_model* m, int on);
 void*  ib_b200_model_tokens(ib_b200_model* m);
 float* ib_b200_model_logits(ib_b200_model* m);
 /* Bytes of weights + scales this rank streams per decoded position. */

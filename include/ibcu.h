@@ -50,13 +50,23 @@ int  ibcu_memcpy_d2h(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);  
 int  ibcu_memcpy_d2d(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);   /* async */
 int  ibcu_memset(ibcu_ctx* ctx, void* dst, int byte, size_t bytes);              /* async */
 int  ibcu_sync(ibcu_ctx* ctx);
+/* *dst = value on the context's stream (a one-thread kernel: the value travels as a launch argument, so
+ * the host may change its own copy at once). */
+int  ibcu_store_i32(ibcu_ctx* ctx, int32_t* dst, int32_t value);
 /* Fill a device buffer with counter-based pseudo-random bytes: byte i = low 8 bits of
  * mix64(seed, i / 8) >> (8 * (i % 8)) (mix64 = splitmix64 finaliser). Used to build random-weight
  * models in HBM without a host copy; ibcu_hash_bytes_host computes the same bytes on the CPU. */
 int  ibcu_fill_hash_bytes(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed);
+/* The slice [first_byte, first_byte + bytes) of that stream (first_byte a multiple of 8): a rank that holds some
+ * rows of a tensor gets exactly the bytes the whole tensor would have there. */
+int  ibcu_fill_hash_bytes_at(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed, size_t first_byte);
 void ibcu_hash_bytes_host(void* dst, size_t bytes, uint64_t seed, size_t first_byte);
 /* fp16 values lo + (hi-lo)*u, u from the same generator (one 16-bit draw per element). */
 int  ibcu_fill_hash_fp16_uniform(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi);
+int  ibcu_fill_hash_fp16_uniform_at(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi, size_t first);
+/* FP32 values mean + std * z with z bell-shaped of unit variance (the centred sum of four 16-bit draws), element
+ * first + i of the stream; used to fill synthetic KV caches. */
+int  ibcu_fill_hash_f32_normal_at(ibcu_ctx* ctx, float* dst, size_t count, uint64_t seed, float mean, float std, size_t first);
 void ibcu_hash_fp16_uniform_host(uint16_t* dst, size_t count, uint64_t seed, float lo, float hi, size_t first);
 
 /* Device timing on the context's stream (CUDA events). slot in [0,16). */
@@ -197,6 +207,10 @@ int ibcu_kmeans_lloyd_iter(ibcu_ctx* ctx, const float* X, long N, int D, float* 
 /* x[b*hidden + i] = embed[token_b*hidden + i] * fp16(scale[token_b])  (src/forward.c:94-106) */
 int ibcu_embed_int8(ibcu_ctx* ctx, const int8_t* embed, const uint16_t* scale, const int32_t* tokens,
                     float* x, int hidden, int B);
+/* The same for the three embedding storage forms of embedding_lookup (src/forward.c:90-135): bits 8, bits 4
+ * (two columns per byte, low nibble first, bias 8) - both with fp16 row scales - and bits 16 (fp16 rows). */
+int ibcu_embed_rows(ibcu_ctx* ctx, const void* embed, const uint16_t* scale, const int32_t* tokens,
+                    float* x, int hidden, int B, int bits);
 /* out = x * rsqrt(mean(x^2) + eps) * fp16(w), per row of B (src/forward.c:322-327). */
 int ibcu_rmsnorm_fp16w(ibcu_ctx* ctx, float* out, const float* x, const uint16_t* w, float eps, int N, int B);
 /* Same with FP32 weights, the form ib_kernels.rmsnorm receives (src/kernels/scalar.c:126-138). */
@@ -215,6 +229,12 @@ int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const fl
  * place; nothing reads them afterwards). */
 int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
                           int n_heads, int n_kv_heads, int head_dim, int pos0, int B, float theta);
+/* The same step with the position pos0 read from device memory when the kernels run, and grid, shared
+ * memory and scratch sized for max_ctx cache rows: a launch captured into a CUDA graph then serves every
+ * position of an autoregressive decode (pos0 + B <= max_ctx). Needs at most 8 query heads per KV head,
+ * head_dim a multiple of 4 up to 256 and 16-byte aligned q / caches. */
+int ibcu_attention_decode_at(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
+                             int n_heads, int n_kv_heads, int head_dim, const int* pos0_dev, int max_ctx, int B, float theta);
 /* out[b] = silu(gate[b]) * up[b] over rows of N, and amax[b*parts + p] = max|out[b]| over the p-th of `parts`
  * equal column ranges: the element-wise step of the MLP (src/forward.c:637-640) shaped for IBCU_PRO_KNOWN_MAX. */
 int ibcu_silu_mul_amax(ibcu_ctx* ctx, float* out, const float* gate, const float* up, int N, int B, float* amax, int parts);

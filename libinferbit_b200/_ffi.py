@@ -51,7 +51,11 @@ IBCU_SYMBOLS = {
     "ibcu_memcpy_d2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "ibcu_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
     "ibcu_sync": (C.c_int, [C.c_void_p]),
+    "ibcu_store_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "ibcu_fill_hash_bytes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64]),
+    "ibcu_fill_hash_bytes_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_size_t]),
+    "ibcu_fill_hash_fp16_uniform_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float, C.c_size_t]),
+    "ibcu_fill_hash_f32_normal_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float, C.c_size_t]),
     "ibcu_hash_bytes_host": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_size_t]),
     "ibcu_fill_hash_fp16_uniform": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float]),
     "ibcu_hash_fp16_uniform_host": (None, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_float, C.c_float, C.c_size_t]),
@@ -81,6 +85,7 @@ IBCU_SYMBOLS = {
     "ibcu_kmeans_lloyd_iter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_embed_int8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_embed_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "ibcu_rmsnorm_fp16w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
     "ibcu_rmsnorm_f32w": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
     "ibcu_rope_kv_write": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -88,6 +93,8 @@ IBCU_SYMBOLS = {
     "ibcu_silu_mul_amax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "ibcu_attention_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
+    "ibcu_attention_decode_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_float]),
     "ibcu_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "ibcu_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
@@ -193,6 +200,7 @@ HOST_SYMBOLS = {
     "ib_b200_kmeans_assign": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
     "ib_b200_kmeans_lloyd": (_i, [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "ib_b200_model_create": (_vp, [_vp, C.POINTER(ModelCfg)]),
+    "ib_b200_model_create_bits": (_vp, [_vp, C.POINTER(ModelCfg), _vp, _i]),
     "ib_b200_model_free": (None, [_vp]),
     "ib_b200_model_fill_random": (_i, [_vp, C.c_uint64, _i]),
     "ib_b200_model_set_linear": (_i, [_vp, _i, _i, _vp, _vp]),
@@ -201,7 +209,9 @@ HOST_SYMBOLS = {
     "ib_b200_model_set_kv": (_i, [_vp, _i, _vp, _vp, _i]),
     "ib_b200_model_get_kv": (_i, [_vp, _i, _vp, _vp, _i]),
     "ib_b200_forward_step": (_i, [_vp, _vp, _i, _i, _vp]),
+    "ib_b200_forward_step_last": (_i, [_vp, _vp, _i, _i, _vp]),
     "ib_b200_forward_step_device": (_i, [_vp, _i, _i]),
+    "ib_b200_model_use_graph": (None, [_vp, _i]),
     "ib_b200_model_tokens": (_vp, [_vp]),
     "ib_b200_model_logits": (_vp, [_vp]),
     "ib_b200_model_weight_bytes": (C.c_size_t, [_vp]),
@@ -224,3 +234,51 @@ def load_host():
             fn.argtypes = args
         _libhost = lib
     return _libhost
+
+
+FRONT_PATH = os.path.join(_HERE, "libinferbit.so")
+_sz = C.c_size_t
+FRONT_SYMBOLS = {
+    "inferbit_last_error": (C.c_char_p, []),
+    "inferbit_config_create": (_vp, []),
+    "inferbit_config_free": (None, [_vp]),
+    "inferbit_config_set_threads": (None, [_vp, _i]),
+    "inferbit_config_set_context_length": (None, [_vp, _i]),
+    "inferbit_config_set_kv_cache_dynamic": (None, [_vp, _i]),
+    "inferbit_config_set_native_parse": (None, [_vp, _i]),
+    "inferbit_config_set_native_bits": (None, [_vp, _i]),
+    "inferbit_load": (_vp, [C.c_char_p, _vp]),
+    "inferbit_free": (None, [_vp]),
+    "inferbit_forward": (_i, [_vp, _vp, _i, _vp, _i]),
+    "inferbit_kv_clear": (None, [_vp]),
+    "inferbit_kv_truncate": (None, [_vp, _i]),
+    "inferbit_kv_length": (_i, [_vp]),
+    "inferbit_model_architecture": (C.c_char_p, [_vp]),
+    "inferbit_model_num_layers": (_i, [_vp]),
+    "inferbit_model_hidden_size": (_i, [_vp]),
+    "inferbit_model_vocab_size": (_i, [_vp]),
+    "inferbit_model_max_context": (_i, [_vp]),
+    "inferbit_model_default_bits": (_i, [_vp]),
+    "inferbit_model_weight_memory": (_sz, [_vp]),
+    "inferbit_model_kv_memory": (_sz, [_vp]),
+    "inferbit_model_total_memory": (_sz, [_vp]),
+}
+
+_libfront = None
+
+
+def load_front():
+    """Load libinferbit.so, the reference-named entry points (include/inferbit_gpu.h). Loaded with local
+    symbol scope: the names are the reference's own, and a process may hold the reference library too."""
+    global _libfront
+    if _libfront is None:
+        load_host()
+        if not os.path.exists(FRONT_PATH):
+            raise OSError(f"{FRONT_PATH} not found: build it with `make -C libinferbit_b200`")
+        lib = C.CDLL(FRONT_PATH, mode=C.RTLD_LOCAL)
+        for name, (res, args) in FRONT_SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _libfront = lib
+    return _libfront

@@ -11,6 +11,7 @@
 #define IBCU_MAX_GRAPHS 16
 #define IBCU_MAX_EVENTS 16
 #define IBCU_MAX_RANKS 16
+#define IBCU_MAX_RETIRED 64
 
 struct ncclComm;
 
@@ -22,10 +23,12 @@ struct ibcu_ctx {
     char msg[512];
     int pdl;                       // programmatic dependent launch between our kernels
     int force_generic;
+    int kmeans_exact;              // tests: every distance in the exact form (no tensor-core filter)
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
     void*  xpack;      size_t xpack_bytes;      // activation limbs + per-slice scales and limb sums of the current linear call
     void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, PQ slabs, k-means per-block partials)
+    void*  retired[IBCU_MAX_RETIRED]; int n_retired;   // outgrown scratch that an instantiated graph may still use
     cudaEvent_t events[IBCU_MAX_EVENTS];
     cudaGraphExec_t graphs[IBCU_MAX_GRAPHS];
     int capturing;
@@ -48,7 +51,9 @@ int ibcu_fail(ibcu_ctx* ctx, int code, const char* fmt, ...);
     return ibcu_fail((ctx), IBCU_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
 #define IBCU_REQUIRE(ctx, cond, ...) do { if (!(cond)) return ibcu_fail((ctx), IBCU_ERR_PARAM, __VA_ARGS__); } while (0)
 
-// Grow-only scratch. Growing frees and reallocates, so it must not happen during stream capture.
+// Grow-only scratch. Growing reallocates, so it must not happen during stream capture. While the context
+// holds instantiated graphs the outgrown buffer is kept (their kernels carry its address) until the
+// last graph is destroyed.
 int ibcu_reserve(ibcu_ctx* ctx, void** buf, size_t* have, size_t want);
 
 // Launch `kernel` on the context's stream. With pdl_ok and ctx->pdl the launch carries the

@@ -18,7 +18,16 @@ int ibcu_reserve(ibcu_ctx* ctx, void** buf, size_t* have, size_t want) {
     if (*have >= want) return IBCU_OK;
     if (ctx->capturing) return ibcu_fail(ctx, IBCU_ERR_STATE, "scratch would have to grow to %zu bytes during graph capture; run the call once before capturing", want);
     IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (*buf) IBCU_CUDA(ctx, cudaFree(*buf));
+    if (*buf) {
+        bool graphs = false;
+        for (int i = 0; i < IBCU_MAX_GRAPHS; i++) graphs = graphs || ctx->graphs[i];
+        if (graphs) {
+            if (ctx->n_retired == IBCU_MAX_RETIRED)
+                return ibcu_fail(ctx, IBCU_ERR_STATE, "scratch would have to grow to %zu bytes while %d outgrown buffers are still held for "
+                                 "instantiated graphs; destroy the graphs first", want, IBCU_MAX_RETIRED);
+            ctx->retired[ctx->n_retired++] = *buf;
+        } else IBCU_CUDA(ctx, cudaFree(*buf));
+    }
     *buf = nullptr; *have = 0;
     size_t sz = (want + 255) & ~(size_t)255;
     cudaError_t e = cudaMalloc(buf, sz);
@@ -69,6 +78,7 @@ extern "C" void ibcu_ctx_destroy(ibcu_ctx* ctx) {
     for (int i = 0; i < IBCU_MAX_GRAPHS; i++) if (ctx->graphs[i]) { cudaGraphExecDestroy(ctx->graphs[i]); ctx->graphs[i] = nullptr; }
     ibcu_comm_destroy_internal(ctx);
     for (int i = 0; i < IBCU_MAX_EVENTS; i++) cudaEventDestroy(ctx->events[i]);
+    for (int i = 0; i < ctx->n_retired; i++) cudaFree(ctx->retired[i]);
     if (ctx->xpack) cudaFree(ctx->xpack);
     if (ctx->scratch) cudaFree(ctx->scratch);
     cudaStreamDestroy(ctx->stream);
@@ -142,6 +152,13 @@ extern "C" int ibcu_sync(ibcu_ctx* ctx) {
     return ctx->status;
 }
 
+__global__ void store_i32_kernel(int32_t* dst, int32_t value) { *dst = value; }
+extern "C" int ibcu_store_i32(ibcu_ctx* ctx, int32_t* dst, int32_t value) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, dst, "ibcu_store_i32: null pointer");
+    return ibcu_launch(ctx, store_i32_kernel, dim3(1), dim3(1), 0, 1, false, dst, value);
+}
+
 // ── timing and graphs ───────────────────────────────────────────────────────────────────
 extern "C" int ibcu_event_record(ibcu_ctx* ctx, int slot) {
     IBCU_CHECK_CTX(ctx);
@@ -190,24 +207,33 @@ extern "C" int ibcu_graph_destroy(ibcu_ctx* ctx, int id) {
     IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     IBCU_CUDA(ctx, cudaGraphExecDestroy(ctx->graphs[id]));
     ctx->graphs[id] = nullptr;
+    bool graphs = false;
+    for (int i = 0; i < IBCU_MAX_GRAPHS; i++) graphs = graphs || ctx->graphs[i];
+    if (!graphs) {                                            // nothing can refer to the outgrown scratch buffers any more
+        for (int i = 0; i < ctx->n_retired; i++) cudaFree(ctx->retired[i]);
+        ctx->n_retired = 0;
+    }
     return IBCU_OK;
 }
 
 // ── counter-based fills ─────────────────────────────────────────────────────────────────
+// word w of the destination holds mix64(seed, first_word + w): a slice of a larger array gets the bytes
+// the whole array would have at that place
 __global__ void fill_hash_bytes_kernel(uint64_t* __restrict__ dst, size_t words, uint8_t* __restrict__ tail_dst,
-                                       int tail, uint64_t seed) {
+                                       int tail, uint64_t seed, size_t first_word) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t w = i; w < words; w += stride) dst[w] = ibcu_mix64(seed, w);
+    for (size_t w = i; w < words; w += stride) dst[w] = ibcu_mix64(seed, first_word + w);
     if (i == 0 && tail) {
-        uint64_t v = ibcu_mix64(seed, words);
+        uint64_t v = ibcu_mix64(seed, first_word + words);
         for (int t = 0; t < tail; t++) tail_dst[t] = (uint8_t)(v >> (8 * t));
     }
 }
 
-extern "C" int ibcu_fill_hash_bytes(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed) {
+extern "C" int ibcu_fill_hash_bytes_at(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed, size_t first_byte) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, dst && ((uintptr_t)dst & 7) == 0, "ibcu_fill_hash_bytes: dst must be 8-byte aligned");
+    IBCU_REQUIRE(ctx, (first_byte & 7) == 0, "ibcu_fill_hash_bytes_at: first_byte must be a multiple of 8");
     if (!bytes) return IBCU_OK;
     size_t words = bytes / 8;
     int tail = (int)(bytes % 8);
@@ -215,7 +241,10 @@ extern "C" int ibcu_fill_hash_bytes(ibcu_ctx* ctx, void* dst, size_t bytes, uint
     if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
     if (blocks < 1) blocks = 1;
     return ibcu_launch(ctx, fill_hash_bytes_kernel, dim3(blocks), dim3(256), 0, 1, false,
-                       (uint64_t*)dst, words, (uint8_t*)dst + words * 8, tail, seed);
+                       (uint64_t*)dst, words, (uint8_t*)dst + words * 8, tail, seed, first_byte / 8);
+}
+extern "C" int ibcu_fill_hash_bytes(ibcu_ctx* ctx, void* dst, size_t bytes, uint64_t seed) {
+    return ibcu_fill_hash_bytes_at(ctx, dst, bytes, seed, 0);
 }
 
 extern "C" void ibcu_hash_bytes_host(void* dst, size_t bytes, uint64_t seed, size_t first_byte) {
@@ -238,18 +267,40 @@ __host__ __device__ static inline float hash_uniform(uint64_t seed, size_t i, fl
 #endif
 }
 
-__global__ void fill_hash_fp16_kernel(__half* __restrict__ dst, size_t count, uint64_t seed, float lo, float hi) {
+__global__ void fill_hash_fp16_kernel(__half* __restrict__ dst, size_t count, uint64_t seed, float lo, float hi, size_t first) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (; i < count; i += stride) dst[i] = __float2half_rn(hash_uniform(seed, i, lo, hi));
+    for (; i < count; i += stride) dst[i] = __float2half_rn(hash_uniform(seed, first + i, lo, hi));
 }
 
-extern "C" int ibcu_fill_hash_fp16_uniform(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi) {
+extern "C" int ibcu_fill_hash_fp16_uniform_at(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi, size_t first) {
     IBCU_CHECK_CTX(ctx);
     if (!count) return IBCU_OK;
     int blocks = (int)((count + 255) / 256);
     if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
-    return ibcu_launch(ctx, fill_hash_fp16_kernel, dim3(blocks), dim3(256), 0, 1, false, (__half*)dst, count, seed, lo, hi);
+    return ibcu_launch(ctx, fill_hash_fp16_kernel, dim3(blocks), dim3(256), 0, 1, false, (__half*)dst, count, seed, lo, hi, first);
+}
+extern "C" int ibcu_fill_hash_fp16_uniform(ibcu_ctx* ctx, void* dst, size_t count, uint64_t seed, float lo, float hi) {
+    return ibcu_fill_hash_fp16_uniform_at(ctx, dst, count, seed, lo, hi, 0);
+}
+
+// FP32 values mean + std * z, z the centred sum of the four 16-bit pieces of mix64(seed, i) scaled to unit
+// variance (Irwin-Hall with n = 4: bell-shaped, |z| <= 3.46)
+__global__ void fill_hash_f32_normal_kernel(float* __restrict__ dst, size_t count, uint64_t seed, float mean, float std, size_t first) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < count; i += stride) {
+        const uint64_t r = ibcu_mix64(seed, first + i);
+        const float u = (float)((uint32_t)(r & 0xFFFF) + (uint32_t)((r >> 16) & 0xFFFF) + (uint32_t)((r >> 32) & 0xFFFF) + (uint32_t)(r >> 48)) * (1.0f / 65536.0f);
+        dst[i] = mean + std * ((u - 2.0f) * 1.7320508f);
+    }
+}
+extern "C" int ibcu_fill_hash_f32_normal_at(ibcu_ctx* ctx, float* dst, size_t count, uint64_t seed, float mean, float std, size_t first) {
+    IBCU_CHECK_CTX(ctx);
+    if (!count) return IBCU_OK;
+    int blocks = (int)((count + 255) / 256);
+    if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+    return ibcu_launch(ctx, fill_hash_f32_normal_kernel, dim3(blocks), dim3(256), 0, 1, false, dst, count, seed, mean, std, first);
 }
 
 static uint16_t host_f32_to_f16_rne(float f) {

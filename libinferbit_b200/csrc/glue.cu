@@ -5,24 +5,26 @@
 #include "common.cuh"
 
 namespace {
-#ifdef IBCU_TRACE
-__device__ unsigned long long att_trace_buf[2][512][8];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define ATRACE(k, i) do { if (threadIdx.x == 0) { int bid = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); if (bid < 512) att_trace_buf[k][bid][i] = gtime(); } } while (0)
-#else
-#define ATRACE(k, i) do { } while (0)
-#endif
 
-__global__ void __launch_bounds__(256) embed_int8_kernel(const int8_t* __restrict__ embed, const __half* __restrict__ scale,
+// BITS 8: INT8 rows; 4: two columns per byte, low nibble first, bias 8; 16: fp16 rows (scale unused)
+template <int BITS>
+__global__ void __launch_bounds__(256) embed_rows_kernel(const void* __restrict__ embed, const __half* __restrict__ scale,
                                                          const int32_t* __restrict__ tokens, float* __restrict__ x, int hidden) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
     const int tok = tokens[b];
-    const float s = __half2float(scale[tok]);
-    const int8_t* row = embed + (size_t)tok * hidden;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x)
-        x[(size_t)b * hidden + i] = (float)row[i] * s;
+    const float s = BITS == 16 ? 1.0f : __half2float(scale[tok]);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
+        float v;
+        if (BITS == 8) v = (float)reinterpret_cast<const int8_t*>(embed)[(size_t)tok * hidden + i] * s;
+        else if (BITS == 16) v = __half2float(reinterpret_cast<const __half*>(embed)[(size_t)tok * hidden + i]);
+        else {
+            const uint8_t byte = reinterpret_cast<const uint8_t*>(embed)[(size_t)tok * (hidden / 2) + (i >> 1)];
+            v = (float)((int)((i & 1) ? (byte >> 4) : (byte & 15)) - 8) * s;
+        }
+        x[(size_t)b * hidden + i] = v;
+    }
 }
 
 // block-wide sum, result broadcast to every thread; red must hold 32 floats
@@ -162,23 +164,41 @@ __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict_
 constexpr int ATT_GMAX = 8;          // query heads per KV head handled by the split path (warps per block)
 constexpr int ATT_CHUNK = 128;       // most cache positions per block
 
+// How `cap` cache positions are cut into chunks: chunks of at most chunk_cap positions, shorter ones
+// (at least 32, a multiple of 4) when that still leaves `want` blocks to cover the machine.
+__host__ __device__ __forceinline__ void att_plan(int cap, int want, int chunk_cap, int& chunk, int& nsplit) {
+    chunk = chunk_cap;
+    nsplit = (cap + chunk - 1) / chunk;
+    if (nsplit < want) {
+        chunk = (cap + want - 1) / want;
+        if (chunk < 32) chunk = 32;
+        chunk = (chunk + 3) & ~3;
+        if (chunk > chunk_cap) chunk = chunk_cap;
+        nsplit = (cap + chunk - 1) / chunk;
+    }
+}
+
 __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                              const float* __restrict__ v_cache, float* __restrict__ part,
                                                              int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit,
                                                              const float* __restrict__ k_new, const float* __restrict__ v_new,
-                                                             float* __restrict__ k_cache_w, float* __restrict__ v_cache_w, float theta) {
+                                                             float* __restrict__ k_cache_w, float* __restrict__ v_cache_w, float theta,
+                                                             const int* __restrict__ pos0_ptr, int want, int chunk_cap) {
     extern __shared__ __align__(16) float asm_[];
     const int group = n_heads / n_kv;               // = warps in the block
     const int ld = hd + 4;                          // padded tile rows: conflict-free float4 reads down a column of rows
     float* qs = asm_;                               // [group][hd]
     float* ps = qs + group * hd;                    // [group][32]
-    float* kt = ps + group * 32;                    // [chunk][ld]
-    float* vt = kt + (size_t)chunk * ld;            // [chunk][ld]
-    ATRACE(0, 0);
+    float* kt = ps + group * 32;                    // [chunk_cap][ld]
+    float* vt = kt + (size_t)chunk_cap * ld;        // [chunk_cap][ld]
     pdl_launch_dependents();
     pdl_wait();
-    ATRACE(0, 1);
+    if (pos0_ptr) {                                 // position read on the device: the same launch serves every position
+        pos0 = *pos0_ptr;
+        att_plan(pos0 + (int)gridDim.z, want, chunk_cap, chunk, nsplit);
+    }
     const int kvh = blockIdx.x, sp = blockIdx.y, b = blockIdx.z, pos = pos0 + b;
+    if (sp >= nsplit) return;                       // the grid is sized for the longest context
     const int kv_dim = n_kv * hd, tid = threadIdx.x, lane = tid & 31, g = tid >> 5, nth = blockDim.x;
     const int t0 = sp * chunk, t1 = min(pos + 1, t0 + chunk), n = max(0, t1 - t0);
     // the K and V rows of this chunk that the cache holds go in flight at once (one memory round trip)
@@ -216,10 +236,8 @@ __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float
     } else {
         for (int d = lane; d < hd; d += 32) qs[g * hd + d] = qh[d];
     }
-    ATRACE(0, 2);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    ATRACE(0, 3);
     const float scale = 1.0f / sqrtf((float)hd);
     const float4* q4 = reinterpret_cast<const float4*>(qs + g * hd);
     const int hd4 = hd / 4, ld4 = ld / 4;
@@ -261,26 +279,24 @@ __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float
             if (own1) { const float4 v = vrow[(size_t)t * ld4 + 32]; acc[1].x = fmaf(pt, v.x, acc[1].x); acc[1].y = fmaf(pt, v.y, acc[1].y); acc[1].z = fmaf(pt, v.z, acc[1].z); acc[1].w = fmaf(pt, v.w, acc[1].w); }
         }
     }
-    ATRACE(0, 5);
-    float* dst = part + (((size_t)b * n_heads + (size_t)kvh * group + g) * nsplit + sp) * (size_t)(hd + 4);
+    float* dst = part + (((size_t)b * n_heads + (size_t)kvh * group + g) * gridDim.y + sp) * (size_t)(hd + 4);
     if (own0) *reinterpret_cast<float4*>(dst + 4 + 4 * lane) = acc[0];
     if (own1) *reinterpret_cast<float4*>(dst + 4 + 4 * (lane + 32)) = acc[1];
     if (lane == 0) { dst[0] = m_run; dst[1] = l_run; }
-    ATRACE(0, 6);
 }
 
 // grid (query heads, B): merges the chunk results of one head. All of them are loaded at once, as float4s.
 constexpr int ATT_CMB_V = 8;
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
-                                                           int n_heads, int hd, int nsplit) {
+                                                           int n_heads, int hd, int nsplit, int part_rows,
+                                                           const int* __restrict__ pos0_ptr, int want, int chunk_cap) {
     extern __shared__ __align__(16) float cs[];      // the head's chunk results: [nsplit][hd + 4], then weights [nsplit]
-    ATRACE(1, 0);
     pdl_launch_dependents();
     pdl_wait();
-    ATRACE(1, 1);
+    if (pos0_ptr) { int chunk; att_plan(*pos0_ptr + (int)gridDim.y, want, chunk_cap, chunk, nsplit); }
     const int h = blockIdx.x, b = blockIdx.y;
     const int pstride = hd + 4, total = nsplit * pstride, total4 = total / 4;
-    const float4* src = reinterpret_cast<const float4*>(part + ((size_t)b * n_heads + h) * (size_t)total);
+    const float4* src = reinterpret_cast<const float4*>(part + ((size_t)b * n_heads + h) * (size_t)part_rows * pstride);
     float4* cs4 = reinterpret_cast<float4*>(cs);
     float* wgt = cs + total;
     for (int e0 = 0; e0 < total4; e0 += ATT_CMB_V * 128) {
@@ -303,7 +319,6 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
         for (int s = 0; s < nsplit; s++) a = fmaf(wgt[s], cs[s * pstride + 4 + d], a);
         out[((size_t)b * n_heads + h) * hd + d] = a * inv;
     }
-    ATRACE(1, 2);
 }
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(float* __restrict__ out, const float* __restrict__ gate,
@@ -366,12 +381,20 @@ int grid_for(ibcu_ctx* ctx, size_t n, int threads) {
 
 }  // namespace
 
+extern "C" int ibcu_embed_rows(ibcu_ctx* ctx, const void* embed, const uint16_t* scale, const int32_t* tokens,
+                               float* x, int hidden, int B, int bits) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, embed && tokens && x && hidden > 0 && B > 0, "ibcu_embed_rows: bad arguments");
+    IBCU_REQUIRE(ctx, bits == 16 || (scale && (bits == 8 || (bits == 4 && (hidden & 1) == 0))), "ibcu_embed_rows: bits=%d (8 or 4 with row scales, or 16)", bits);
+    int gx = (hidden + 255) / 256; if (gx > 16) gx = 16;
+    const dim3 grid(gx, B), block(256);
+    if (bits == 8) return ibcu_launch(ctx, embed_rows_kernel<8>, grid, block, 0, 1, true, embed, (const __half*)scale, tokens, x, hidden);
+    if (bits == 4) return ibcu_launch(ctx, embed_rows_kernel<4>, grid, block, 0, 1, true, embed, (const __half*)scale, tokens, x, hidden);
+    return ibcu_launch(ctx, embed_rows_kernel<16>, grid, block, 0, 1, true, embed, (const __half*)scale, tokens, x, hidden);
+}
 extern "C" int ibcu_embed_int8(ibcu_ctx* ctx, const int8_t* embed, const uint16_t* scale, const int32_t* tokens,
                                float* x, int hidden, int B) {
-    IBCU_CHECK_CTX(ctx);
-    IBCU_REQUIRE(ctx, embed && scale && tokens && x && hidden > 0 && B > 0, "ibcu_embed_int8: bad arguments");
-    int gx = (hidden + 255) / 256; if (gx > 16) gx = 16;
-    return ibcu_launch(ctx, embed_int8_kernel, dim3(gx, B), dim3(256), 0, 1, true, embed, (const __half*)scale, tokens, x, hidden);
+    return ibcu_embed_rows(ctx, embed, scale, tokens, x, hidden, B, 8);
 }
 
 extern "C" int ibcu_rmsnorm_fp16w(ibcu_ctx* ctx, float* out, const float* x, const uint16_t* w, float eps, int N, int B) {
@@ -405,31 +428,43 @@ static bool attn_split_ok(const float* q, const float* k_cache, const float* v_c
 }
 
 // k_new / v_new NULL: q is rotated already and the cache holds rows 0..pos0+B-1. Otherwise the fused decode step.
+// pos0_dev NULL: the position is the argument pos0 and the grid is cut for it. Otherwise the position is read
+// on the device and the grid, shared memory and scratch are sized for max_ctx positions, so that one
+// captured launch serves every position up to max_ctx - B.
 static int attention_split(ibcu_ctx* ctx, const float* q, float* k_cache, float* v_cache, float* out,
-                           int n_heads, int n_kv_heads, int head_dim, int pos0, int B, const float* k_new, const float* v_new, float theta) {
+                           int n_heads, int n_kv_heads, int head_dim, int pos0, int B, const float* k_new, const float* v_new, float theta,
+                           const int* pos0_dev, int max_ctx) {
     const int group = n_heads / n_kv_heads;
-    {
-        // split path: chunks of up to 128 cache positions per block, merged by a second small kernel
-        const int cap = pos0 + B;
-        int nsplit = (cap + ATT_CHUNK - 1) / ATT_CHUNK;
-        const int want = (2 * ctx->sm_count) / (n_kv_heads * B);      // enough blocks to cover the machine
-        int chunk = ATT_CHUNK;
-        if (nsplit < want) { chunk = (cap + want - 1) / want; if (chunk < 32) chunk = 32; chunk = (chunk + 3) & ~3; nsplit = (cap + chunk - 1) / chunk; }
-        const size_t pbytes = (size_t)B * n_heads * nsplit * (head_dim + 4) * sizeof(float);
-        int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, pbytes);
-        if (rc) return rc;
-        const size_t smem = ((size_t)group * head_dim + group * 32 + 2 * (size_t)chunk * (head_dim + 4)) * sizeof(float);
-        if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, nsplit, B), dim3(32 * group), smem, 1, true,
-                         q, (const float*)k_cache, (const float*)v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit,
-                         k_new, v_new, k_cache, v_cache, theta);
-        if (rc) return rc;
-        const size_t csmem = ((size_t)nsplit * (head_dim + 4) + nsplit) * sizeof(float);
-        IBCU_REQUIRE(ctx, csmem <= 200 * 1024, "ibcu_attention: %d chunks of cache positions are more than the merge step holds", nsplit);
-        if (csmem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
-        return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), csmem, 1, true,
-                           (const float*)ctx->scratch, out, n_heads, head_dim, nsplit);
+    int want = (2 * ctx->sm_count) / (n_kv_heads * B);       // enough blocks to cover the machine
+    if (want < 1) want = 1;
+    int chunk, nsplit, grid_y, chunk_cap = ATT_CHUNK;
+    if (pos0_dev) {
+        int c_lo, n_lo;
+        att_plan(B, want, ATT_CHUNK, c_lo, n_lo);              // shortest context
+        att_plan(max_ctx, want, ATT_CHUNK, chunk, nsplit);     // longest context: most chunks, longest chunks
+        grid_y = nsplit > n_lo ? nsplit : n_lo;
+        if (want > grid_y) grid_y = want;
+        chunk_cap = chunk;
+        if (chunk_cap < 32) chunk_cap = 32;
+    } else {
+        att_plan(pos0 + B, want, ATT_CHUNK, chunk, nsplit);
+        grid_y = nsplit;
+        chunk_cap = chunk;
     }
+    const size_t pbytes = (size_t)B * n_heads * grid_y * (head_dim + 4) * sizeof(float);
+    int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, pbytes);
+    if (rc) return rc;
+    const size_t smem = ((size_t)group * head_dim + group * 32 + 2 * (size_t)chunk_cap * (head_dim + 4)) * sizeof(float);
+    if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, grid_y, B), dim3(32 * group), smem, 1, true,
+                     q, (const float*)k_cache, (const float*)v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit,
+                     k_new, v_new, k_cache, v_cache, theta, pos0_dev, want, chunk_cap);
+    if (rc) return rc;
+    const size_t csmem = ((size_t)grid_y * (head_dim + 4) + grid_y) * sizeof(float);
+    IBCU_REQUIRE(ctx, csmem <= 200 * 1024, "ibcu_attention: %d chunks of cache positions are more than the merge step holds", grid_y);
+    if (csmem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+    return ibcu_launch(ctx, attn_combine_kernel, dim3(n_heads, B), dim3(128), csmem, 1, true,
+                       (const float*)ctx->scratch, out, n_heads, head_dim, nsplit, grid_y, pos0_dev, want, chunk_cap);
 }
 
 extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cache, const float* v_cache, float* out,
@@ -439,7 +474,7 @@ extern "C" int ibcu_attention(ibcu_ctx* ctx, const float* q, const float* k_cach
     IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && pos0 >= 0 && B > 0,
                  "ibcu_attention: bad shape");
     if (attn_split_ok(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim))
-        return attention_split(ctx, q, (float*)k_cache, (float*)v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, nullptr, nullptr, 0.0f);
+        return attention_split(ctx, q, (float*)k_cache, (float*)v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, nullptr, nullptr, 0.0f, nullptr, 0);
     int cap = pos0 + B;
     size_t smem = ((size_t)cap + 8 * (size_t)head_dim) * sizeof(float);
     IBCU_REQUIRE(ctx, smem <= 200 * 1024, "ibcu_attention: context %d too long for one block's shared memory", cap);
@@ -455,11 +490,22 @@ extern "C" int ibcu_attention_decode(ibcu_ctx* ctx, float* q, float* k, const fl
     IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && (head_dim & 1) == 0 && pos0 >= 0 && B > 0,
                  "ibcu_attention_decode: bad shape heads=%d kv=%d hd=%d pos0=%d B=%d", n_heads, n_kv_heads, head_dim, pos0, B);
     if (attn_split_ok(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim))
-        return attention_split(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, k, v, theta);
+        return attention_split(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B, k, v, theta, nullptr, 0);
     // shapes the split kernel does not take: the two steps one after the other
     int rc = ibcu_rope_kv_write(ctx, q, k, v, k_cache, v_cache, n_heads, n_kv_heads, head_dim, pos0, B, theta);
     if (rc) return rc;
     return ibcu_attention(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, pos0, B);
+}
+
+extern "C" int ibcu_attention_decode_at(ibcu_ctx* ctx, float* q, float* k, const float* v, float* k_cache, float* v_cache, float* out,
+                                        int n_heads, int n_kv_heads, int head_dim, const int* pos0_dev, int max_ctx, int B, float theta) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, q && k && v && k_cache && v_cache && out && pos0_dev, "ibcu_attention_decode_at: null pointer");
+    IBCU_REQUIRE(ctx, n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && head_dim > 0 && (head_dim & 1) == 0 && B > 0 && max_ctx >= B,
+                 "ibcu_attention_decode_at: bad shape heads=%d kv=%d hd=%d max_ctx=%d B=%d", n_heads, n_kv_heads, head_dim, max_ctx, B);
+    IBCU_REQUIRE(ctx, attn_split_ok(q, k_cache, v_cache, n_heads, n_kv_heads, head_dim),
+                 "ibcu_attention_decode_at: needs at most %d query heads per KV head, head_dim a multiple of 4 up to 256 and 16-byte aligned buffers", ATT_GMAX);
+    return attention_split(ctx, q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim, 0, B, k, v, theta, pos0_dev, max_ctx);
 }
 
 extern "C" int ibcu_silu_mul_amax(ibcu_ctx* ctx, float* out, const float* gate, const float* up, int N, int B, float* amax, int parts) {
@@ -488,7 +534,3 @@ extern "C" int ibcu_softmax(ibcu_ctx* ctx, float* data, int N, int rows) {
     IBCU_REQUIRE(ctx, data && N > 0 && rows > 0, "ibcu_softmax: bad arguments");
     return ibcu_launch(ctx, softmax_rows_kernel, dim3(rows), dim3(256), 0, 1, true, data, N);
 }
-
-#ifdef IBCU_TRACE
-extern "C" int ibcu_att_trace_read(void* dst) { return (int)cudaMemcpyFromSymbol(dst, att_trace_buf, sizeof(att_trace_buf)); }
-#endif

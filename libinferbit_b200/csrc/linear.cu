@@ -73,8 +73,6 @@ struct LinearParams {
     const float* xscale;           // [B][nks] 2^-s of each slice
     const int* xsum;               // [B][nks][4] sum of each limb over the slice (INT4 bias term)
     int* partial;                  // [slice][B*4][total_rows] when nks > 1
-    int trace_slot;
-    int xregs;
     XSource xsrc;                  // FP32 source of the activations when the block converts them itself
     int fused_x;                   // 1: convert in the block, 0: limbs were prepared by xprep_kernel
 };
@@ -431,13 +429,6 @@ __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 
 // The nibble bias of 8 is removed once per output as 8 * (sum of the limb over the slice).
 // Dynamic shared memory: stage ring [STAGES][R][LIN_LD] | reduction buffer [W][R][NCG*8] ints (x2 for
 // INT4) | limbs [ncols][xs_ld] | scale-back factors [32] | limb sums [32][4].
-#ifdef IBCU_TRACE
-__device__ unsigned long long ibcu_trace_buf[16][512][8];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(i) do { if (threadIdx.x == 0 && blockIdx.x < 512) ibcu_trace_buf[p.trace_slot & 15][blockIdx.x][i] = gtime(); } while (0)
-#else
-#define TRACE(i) do { } while (0)
-#endif
 __host__ __device__ constexpr int lin_sk(int W) { return W * 64; }                // bytes per row per stage: one 64-byte k-block per warp
 __host__ __device__ constexpr int lin_ld(int W) { return W * 64 + 64; }           // padded row stride: conflict-free fragment reads
 
@@ -457,12 +448,11 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     constexpr int KBS = W;                                    // k-blocks per stage: one per warp
     constexpr int LIN_SK = lin_sk(W), LIN_LD = lin_ld(W);
     constexpr int CPR = LIN_SK / 16;                          // 16-byte chunks per row per stage; the block copies 8 rows per pass
-    static_assert(W == 4 || W == 8, "4 or 8 warps");
+    static_assert(W == 8, "8 warps");
     constexpr int STAGE_BYTES = R * LIN_LD;
     constexpr int NCP = RT * 2;                               // 16-byte chunks per thread per stage
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    TRACE(0);
     pdl_launch_dependents();
 
     const int ks = blockIdx.x % p.nks;                        // this block's column slice, fixed
@@ -518,10 +508,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     if (pf_row < row_end) pf_setup();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) pf_issue();          // weights first: they do not depend on x
-
-    TRACE(1);
     pdl_wait();
-    TRACE(2);
 
     // ── this slice's limbs, scale-back factors and limb sums ──
     if (p.fused_x) {
@@ -541,7 +528,6 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
     }
     cp_async_wait<0>();
     __syncthreads();
-    TRACE(3);
 
     const int8_t* xcol[NCG];
 #pragma unroll
@@ -608,8 +594,6 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
             }
             slot = slot + 1 == STAGES ? 0 : slot + 1;
         }
-
-        TRACE(4);
         // ── tile done: every warp holds integer partial sums of all R rows over its k-blocks ──
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
@@ -660,7 +644,6 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
     }
     cp_async_wait<0>();
-    TRACE(5);
 }
 
 // When the columns are split over several blocks: one thread per (row, activation) recombines the
@@ -742,31 +725,18 @@ int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail)
     return ibcu_launch(ctx, kern, dim3(grid), dim3(W * 32), smem, 1, true, p);
 }
 
-// Ring depths: 8 warps x 512-byte stages for long streams; 4 warps x 256-byte stages (four blocks per SM) when
-// the launch is short, so that the blocks of the next launch fit beside this one's and fetch their
-// weights while this one still computes.
+// Eight warps and 512-byte stages; the ring is as deep as two resident blocks per SM allow.
 template <int BITS, int NCG>
-int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int w, int stages, size_t smem_tail) {
-    if (w == 4) {
-        if (rt == 2) return launch_mma<BITS, NCG, 2, 4, 4>(ctx, p, grid, smem_tail);
-        return launch_mma<BITS, NCG, 1, 4, 6>(ctx, p, grid, smem_tail);
-    }
+int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int stages, size_t smem_tail) {
     if (rt == 2) {
         if (stages >= 6) return launch_mma<BITS, NCG, 2, 8, 6>(ctx, p, grid, smem_tail);
         return launch_mma<BITS, NCG, 2, 8, 4>(ctx, p, grid, smem_tail);
     }
-    if (stages >= 9) return launch_mma<BITS, NCG, 1, 8, 9>(ctx, p, grid, smem_tail);
     if (stages >= 8) return launch_mma<BITS, NCG, 1, 8, 8>(ctx, p, grid, smem_tail);
     return launch_mma<BITS, NCG, 1, 8, 4>(ctx, p, grid, smem_tail);
 }
 
 }  // namespace
-
-// Tuning knobs read once from the environment (for sweeps; defaults are the measured best).
-static int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
 
 extern "C" void ibcu_linear_force_generic(ibcu_ctx* ctx, int on) { if (ctx) ctx->force_generic = on; }
 
@@ -835,17 +805,13 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     const int nkb = (rowbytes + 63) / 64;
     const int xk = bits == 8 ? 64 : 128;
     const int xpad = bits == 8 ? 64 : 16;                     // keeps limb rows of neighbouring columns on different banks
-    static const int rt_env = env_int("IBCU_LINEAR_RT", 0);
-    static const int nks_env = env_int("IBCU_LINEAR_NKS", 0);
-    static const int stages_env = env_int("IBCU_LINEAR_STAGES", 0);
-    static const int w_env = env_int("IBCU_LINEAR_W", 0);
     long total_rows = 0;
     for (int i = 0; i < n_tensors; i++) total_rows += tensors[i].M;
     if (total_rows == 0) return IBCU_OK;
     // Rows are dealt out evenly: every block of the persistent grid owns one contiguous run of rows and
     // walks it in tiles of up to R = 16 or 32 rows. 32-row tiles once a block's run is longer than 16.
-    const int w = w_env == 4 ? 4 : 8;                        // warps per block; four blocks of 4 warps or two of 8 share an SM
-    int rt = rt_env ? rt_env : ((ncg >= 4 || total_rows <= 16L * (w == 4 ? 4 : 2) * ctx->sm_count) ? 1 : 2);
+    const int w = 8;                                          // warps per block; two blocks share an SM
+    const int rt = (ncg >= 4 || total_rows <= 16L * 2 * ctx->sm_count) ? 1 : 2;
     const int R = 16 * rt;
     LinearParams p;
     memset(&p, 0, sizeof p);
@@ -865,29 +831,21 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * w * R * ncg * 8 * 4;
     const size_t whole_row_pieces = (size_t)ncols * ((size_t)nkb * xk + xpad);
     int stages = rt == 2 ? 6 : 8;
-    if (w == 4) stages = rt == 2 ? 4 : 6;
-    else {
     if (2 * ((size_t)stages * R * LIN_LD + red_bytes + whole_row_pieces + 2048) > 227 * 1024) stages = 4;
-    if (stages_env) stages = rt == 2 ? (stages_env >= 6 ? 6 : 4) : (stages_env >= 9 ? 9 : (stages_env >= 8 ? 8 : 4));
-    }
     const size_t fixed_smem = (size_t)stages * R * LIN_LD + red_bytes + 1024;
     const size_t smem_cap = 200 * 1024;
     long piece_budget = (long)smem_cap - (long)fixed_smem;
     int max_slice_kb = (int)((piece_budget / ncols - xpad) / xk) / kbs * kbs;
     if (max_slice_kb < kbs) max_slice_kb = kbs;
-    int nks = 1;
-    if (nks_env) nks = nks_env;
-    int slice_kb = ((nkb + nks - 1) / nks + kbs - 1) / kbs * kbs;      // whole stages per slice
+    int slice_kb = (nkb + kbs - 1) / kbs * kbs;               // whole stages per slice
     if (slice_kb > max_slice_kb) slice_kb = max_slice_kb;
-    nks = (nkb + slice_kb - 1) / slice_kb;
+    const int nks = (nkb + slice_kb - 1) / slice_kb;
     const int xs_ld = slice_kb * xk + xpad;
     const size_t piece_smem = (((size_t)ncols * xs_ld) + 15) & ~(size_t)15;
     // persistent grid: as many blocks as fit on the machine at once, a multiple of nks, at most one per item
     int fit = (int)((227 * 1024) / (fixed_smem + piece_smem + 1024));
     if (fit < 1) fit = 1;
     if (fit > 4) fit = 4;
-    static const int fit_env = env_int("IBCU_LINEAR_FIT", 0);
-    if (fit_env && fit > fit_env) fit = fit_env;
     const int slots = fit * ctx->sm_count;
     int per_slice = slots / nks;
     if (per_slice < 1) per_slice = 1;
@@ -926,37 +884,30 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
         if (rc) return rc;
         p.partial = (int*)ctx->scratch;
     }
-#ifdef IBCU_TRACE
-    { static int seq = 0; p.trace_slot = seq++; }
-#endif
     XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op,
                      op == IBCU_PRO_KNOWN_MAX ? pro->amax : nullptr, op == IBCU_PRO_KNOWN_MAX ? pro->n_amax : 0 };
     // Cheap conversions are done by every block of the main kernel for itself (no extra launch, no
     // dependency chain); expensive ones (SiLU, several activations, long rows) once, by xprep_kernel.
-    static const int fuse_env = env_int("IBCU_LINEAR_FUSE_X", -1);
     int fused = (op != IBCU_PRO_SILU_MUL && (long)B * slice_kb * xk <= 8192 && nks == 1) ? 1 : 0;
     if (op == IBCU_PRO_KNOWN_MAX && nks == 1 && B <= 2) fused = 1;          // no reduction: cheap at any row length
-    if (fuse_env >= 0) fused = fuse_env && nks == 1;
     p.xsrc = xsrc; p.fused_x = fused;
-    static const int skip_xprep = env_int("IBCU_LINEAR_SKIP_XPREP", 0);   // timing experiments only: results are then stale
     // 512 threads hold up to 16384 columns in registers; longer slices take 1024 threads and the looping conversion
     const int xthreads = slice_kb * xk > XREG_V * 4 * 512 ? 1024 : (slice_kb * xk >= 2048 ? 512 : 256);
-    static const int xregs_env = env_int("IBCU_LINEAR_XREGS", 1);
-    if (!fused && !skip_xprep) {
+    if (!fused) {
         const dim3 xg(nks, B);
         const int perm8 = bits == 4 ? 1 : 0, cols = slice_kb * xk;
         rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum)
-           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, xregs_env, xpack, xscale, xsum)
-                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, xregs_env, xpack, xscale, xsum);
+           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum)
+                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum);
     }
     if (rc) return rc;
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
     switch (ncg) { \
-        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, grid, rt, w, stages, smem); break; \
-        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, grid, rt, w, stages, smem); break; \
-        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, grid, rt, w, stages, smem); break; \
-        default: rc = dispatch_shape<BITS, 8>(ctx, p, grid, rt, w, stages, smem); break; \
+        case 1: rc = dispatch_shape<BITS, 1>(ctx, p, grid, rt, stages, smem); break; \
+        case 2: rc = dispatch_shape<BITS, 2>(ctx, p, grid, rt, stages, smem); break; \
+        case 4: rc = dispatch_shape<BITS, 4>(ctx, p, grid, rt, stages, smem); break; \
+        default: rc = dispatch_shape<BITS, 8>(ctx, p, grid, rt, stages, smem); break; \
     }
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH
@@ -978,7 +929,3 @@ extern "C" int ibcu_linear_gate_up_silu(ibcu_ctx* ctx, const ibcu_linear_t* gate
     return ibcu_silu_mul(ctx, gate_up[0].out, gate_up[0].out, gate_up[1].out,
                          (size_t)(B - 1) * gate_up[0].out_stride + gate_up[0].M);
 }
-
-#ifdef IBCU_TRACE
-extern "C" int ibcu_trace_read(void* dst) { return (int)cudaMemcpyFromSymbol(dst, ibcu_trace_buf, sizeof(ibcu_trace_buf)); }
-#endif

@@ -34,4 +34,6 @@ int   ib_b200_check(int rc, const char* what);
 void* ib_b200_translate(const void* p, size_t bytes);
 int   ib_b200_stage(int slot, size_t bytes, void** host, void** dev);
 void  ib_b200_pq_release_all(void);
+void  ib_b200_lock(void);
+void  ib_b200_unlock(void);
 #endif

@@ -22,8 +22,10 @@ static void pq_drop(pq_entry* e) {
     memset(e, 0, sizeof *e);
 }
 void ib_b200_pq_release(const ib_b200_pq_tensor* t) {
+    ib_b200_lock();
     for (int i = 0; i < g_npq; i++)
-        if (g_pq[i].key == t) { pq_drop(&g_pq[i]); g_pq[i] = g_pq[--g_npq]; memset(&g_pq[g_npq], 0, sizeof g_pq[0]); return; }
+        if (g_pq[i].key == t) { pq_drop(&g_pq[i]); g_pq[i] = g_pq[--g_npq]; memset(&g_pq[g_npq], 0, sizeof g_pq[0]); break; }
+    ib_b200_unlock();
 }
 void ib_b200_pq_release_all(void) {
     for (int i = 0; i < g_npq; i++) pq_drop(&g_pq[i]);
@@ -67,7 +69,7 @@ static pq_entry* pq_get(const ib_b200_pq_tensor* t) {
     return e;
 }
 
-int ib_b200_pq_matmul_fp32_batch(const ib_b200_pq_tensor* t, const float* x, float* out, int B) {
+static int pq_matmul_batch_unlocked(const ib_b200_pq_tensor* t, const float* x, float* out, int B) {
     if (!t || !x || !out || B < 1) return -1;                /* src/pq_decode.c:1506 */
     if (!g_ib.ctx) { ib_b200_set_error(IBCU_ERR_STATE, "ib_b200_pq_matmul_fp32 before ib_b200_init"); return -1; }
     pq_entry* e = pq_get(t);
@@ -83,6 +85,12 @@ int ib_b200_pq_matmul_fp32_batch(const ib_b200_pq_tensor* t, const float* x, flo
     if (ib_b200_check(rc, "ib_b200_pq_matmul_fp32")) return -1;
     memcpy(out, ho, ob);
     return 0;
+}
+int ib_b200_pq_matmul_fp32_batch(const ib_b200_pq_tensor* t, const float* x, float* out, int B) {
+    ib_b200_lock();
+    int r = pq_matmul_batch_unlocked(t, x, out, B);
+    ib_b200_unlock();
+    return r;
 }
 int ib_b200_pq_matmul_fp32(const ib_b200_pq_tensor* t, const float* x, float* out) { return ib_b200_pq_matmul_fp32_batch(t, x, out, 1); }
 int ib_b200_pq_matmul_fp32_threaded(const ib_b200_pq_tensor* t, const float* x, float* out, void* pool) {
@@ -115,7 +123,7 @@ static int km_alloc(km_bufs* b, const float* X, int N, int D, int K) {
     return rc;
 }
 
-int ib_b200_kmeans_assign(const float* X, int N, int D, const float* centers, int K, int32_t* indices_out, void* pool) {
+static int ib_b200_kmeans_assign_unlocked(const float* X, int N, int D, const float* centers, int K, int32_t* indices_out, void* pool) {
     (void)pool;
     if (!X || !centers || !indices_out || N <= 0 || K <= 0 || D <= 0) return -1;      /* src/pq_kmeans.c:403 */
     if (!g_ib.ctx) { ib_b200_set_error(IBCU_ERR_STATE, "ib_b200_kmeans_assign before ib_b200_init"); return -1; }
@@ -130,7 +138,7 @@ int ib_b200_kmeans_assign(const float* X, int N, int D, const float* centers, in
     return rc ? -1 : 0;
 }
 
-int ib_b200_kmeans_lloyd(const float* X, int N, int D, int K, int iters, float tol,
+static int ib_b200_kmeans_lloyd_unlocked(const float* X, int N, int D, int K, int iters, float tol,
                          float* centers, int32_t* indices_out, double* inertia_out) {
     if (!X || !centers || N <= 0 || K <= 0 || D <= 0 || iters <= 0) return -1;
     if (!g_ib.ctx) { ib_b200_set_error(IBCU_ERR_STATE, "ib_b200_kmeans_lloyd before ib_b200_init"); return -1; }
@@ -166,4 +174,19 @@ int ib_b200_kmeans_lloyd(const float* X, int N, int D, int K, int iters, float t
     if (shift_d) ibcu_free(g_ib.ctx, shift_d);
     km_free(&b);
     return rc ? -1 : done;
+}
+
+int ib_b200_kmeans_assign(const float* X, int N, int D, const float* centers, int K, int32_t* indices_out, void* pool) {
+    ib_b200_lock();
+    int r = ib_b200_kmeans_assign_unlocked(X, N, D, centers, K, indices_out, pool);
+    ib_b200_unlock();
+    return r;
+}
+
+int ib_b200_kmeans_lloyd(const float* X, int N, int D, int K, int iters, float tol,
+                         float* centers, int32_t* indices_out, double* inertia_out) {
+    ib_b200_lock();
+    int r = ib_b200_kmeans_lloyd_unlocked(X, N, D, K, iters, tol, centers, indices_out, inertia_out);
+    ib_b200_unlock();
+    return r;
 }

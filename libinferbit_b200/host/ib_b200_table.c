@@ -9,8 +9,16 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <pthread.h>
 
 ib_b200_state g_ib;
+
+/* The reference's pool workers call the table concurrently with row slices of one tensor
+ * (src/threading.c:220-241). The staging buffers, the scale cache, the stream and the sticky error are
+ * process-wide, so every entry runs under this lock: concurrent calls are accepted and serialised. */
+static pthread_mutex_t g_lock = PTHREAD_MUTEX_INITIALIZER;
+void ib_b200_lock(void) { pthread_mutex_lock(&g_lock); }
+void ib_b200_unlock(void) { pthread_mutex_unlock(&g_lock); }
 
 void ib_b200_set_error(int code, const char* fmt, ...) {
     if (g_ib.status != 0) return;                 /* first failure wins */
@@ -205,16 +213,16 @@ static void linear_fp32(const char* who, float* out, const void* weights, const 
 }
 
 void ib_b200_matmul_int4(float* out, const void* w, const float* s, const float* x, int M, int N) {
-    linear_fp32("matmul_int4", out, w, s, x, M, N, 1, M, 4);
+    ib_b200_lock(); linear_fp32("matmul_int4", out, w, s, x, M, N, 1, M, 4); ib_b200_unlock();
 }
 void ib_b200_matmul_int8(float* out, const void* w, const float* s, const float* x, int M, int N) {
-    linear_fp32("matmul_int8", out, w, s, x, M, N, 1, M, 8);
+    ib_b200_lock(); linear_fp32("matmul_int8", out, w, s, x, M, N, 1, M, 8); ib_b200_unlock();
 }
 void ib_b200_matmul_int8_batch(float* out, const void* w, const float* s, const float* x, int M, int N, int B, int M_stride) {
-    linear_fp32("matmul_int8_batch", out, w, s, x, M, N, B, M_stride, 8);
+    ib_b200_lock(); linear_fp32("matmul_int8_batch", out, w, s, x, M, N, B, M_stride, 8); ib_b200_unlock();
 }
 
-void ib_b200_matmul_w4a8_batch(float* out, const void* weights, const float* scales_w, const int8_t* input,
+static void ib_b200_matmul_w4a8_batch_unlocked(float* out, const void* weights, const float* scales_w, const int8_t* input,
                                const float* scales_a, int M, int N, int B, int M_stride) {
     const char* who = "matmul_w4a8_batch";
     if (!ready(who)) return;
@@ -238,10 +246,10 @@ void ib_b200_matmul_w4a8_batch(float* out, const void* weights, const float* sca
     for (int b = 0; b < B; b++) memcpy(out + (size_t)b * M_stride, (const float*)ho + (size_t)b * M_stride, (size_t)M * sizeof(float));
 }
 void ib_b200_matmul_w4a8(float* out, const void* w, const float* sw, const int8_t* xq, const float* sa, int M, int N) {
-    ib_b200_matmul_w4a8_batch(out, w, sw, xq, sa, M, N, 1, M);
+    ib_b200_matmul_w4a8_batch(out, w, sw, xq, sa, M, N, 1, M);                    /* takes the lock */
 }
 
-int ib_b200_quantize_input_int8_g128(const float* input, int8_t* out_q, float* out_scales, int N) {
+static int ib_b200_quantize_input_int8_g128_unlocked(const float* input, int8_t* out_q, float* out_scales, int N) {
     if (!ready("quantize_input_int8_g128") || !input || !out_q || !out_scales || N <= 0) return 0;
     const int groups = (N + 127) / 128;
     void* dx = push(ST_X, input, (size_t)N * sizeof(float));
@@ -258,7 +266,7 @@ int ib_b200_quantize_input_int8_g128(const float* input, int8_t* out_q, float* o
 }
 
 /* ── element-wise entries: operands are O(hidden), moved per call ── */
-void ib_b200_rmsnorm(float* out, const float* input, const float* weight, float eps, int N) {
+static void ib_b200_rmsnorm_unlocked(float* out, const float* input, const float* weight, float eps, int N) {
     if (!ready("rmsnorm") || !out || !input || !weight || N <= 0) return;
     /* the table hands over weights already widened to FP32 (src/forward.c:322-327) */
     void* dx = push(ST_X, input, (size_t)N * sizeof(float));
@@ -272,7 +280,7 @@ void ib_b200_rmsnorm(float* out, const float* input, const float* weight, float 
     memcpy(out, ho, (size_t)N * sizeof(float));
 }
 
-void ib_b200_rope(float* q, float* k, int head_dim, int pos, float theta) {
+static void ib_b200_rope_unlocked(float* q, float* k, int head_dim, int pos, float theta) {
     if (!ready("rope") || !q || !k || head_dim <= 0 || (head_dim & 1)) return;
     const size_t hb = (size_t)head_dim * sizeof(float);
     void *hq, *dq, *hk, *dk;
@@ -289,7 +297,7 @@ void ib_b200_rope(float* q, float* k, int head_dim, int pos, float theta) {
     memcpy(q, hq, hb); memcpy(k, hk, hb);
 }
 
-void ib_b200_softmax(float* data, int N) {
+static void ib_b200_softmax_unlocked(float* data, int N) {
     if (!ready("softmax") || !data || N <= 0) return;
     void *h, *d;
     const size_t nb = (size_t)N * sizeof(float);
@@ -303,7 +311,7 @@ void ib_b200_softmax(float* data, int N) {
     memcpy(data, h, nb);
 }
 
-void ib_b200_silu_mul(float* out, const float* gate, const float* up, int N) {
+static void ib_b200_silu_mul_unlocked(float* out, const float* gate, const float* up, int N) {
     if (!ready("silu_mul") || !out || !gate || !up || N <= 0) return;
     const size_t nb = (size_t)N * sizeof(float);
     void* dg = push(ST_X, gate, nb);
@@ -315,6 +323,45 @@ void ib_b200_silu_mul(float* out, const float* gate, const float* up, int N) {
     if (!rc) rc = ibcu_sync(g_ib.ctx);
     if (ib_b200_check(rc, "silu_mul")) return;
     memcpy(out, ho, nb);
+}
+
+
+void ib_b200_matmul_w4a8_batch(float* out, const void* weights, const float* scales_w, const int8_t* input,
+                               const float* scales_a, int M, int N, int B, int M_stride) {
+    ib_b200_lock();
+    ib_b200_matmul_w4a8_batch_unlocked(out, weights, scales_w, input, scales_a, M, N, B, M_stride);
+    ib_b200_unlock();
+}
+
+int ib_b200_quantize_input_int8_g128(const float* input, int8_t* out_q, float* out_scales, int N) {
+    ib_b200_lock();
+    int r = ib_b200_quantize_input_int8_g128_unlocked(input, out_q, out_scales, N);
+    ib_b200_unlock();
+    return r;
+}
+
+void ib_b200_rmsnorm(float* out, const float* input, const float* weight, float eps, int N) {
+    ib_b200_lock();
+    ib_b200_rmsnorm_unlocked(out, input, weight, eps, N);
+    ib_b200_unlock();
+}
+
+void ib_b200_rope(float* q, float* k, int head_dim, int pos, float theta) {
+    ib_b200_lock();
+    ib_b200_rope_unlocked(q, k, head_dim, pos, theta);
+    ib_b200_unlock();
+}
+
+void ib_b200_softmax(float* data, int N) {
+    ib_b200_lock();
+    ib_b200_softmax_unlocked(data, N);
+    ib_b200_unlock();
+}
+
+void ib_b200_silu_mul(float* out, const float* gate, const float* up, int N) {
+    ib_b200_lock();
+    ib_b200_silu_mul_unlocked(out, gate, up, N);
+    ib_b200_unlock();
 }
 
 void ib_b200_install_kernels(void* table) {

@@ -32,6 +32,17 @@ def test_libib_b200_exports_every_declared_symbol():
     assert sorted(_ffi.HOST_SYMBOLS) == names
 
 
+def test_libinferbit_front_exports_every_declared_symbol():
+    lib = _ffi.load_front()
+    txt = open(os.path.join(ROOT, "include", "inferbit_gpu.h")).read()
+    txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+    names = sorted(set(re.findall(r"\b(inferbit_[a-z0-9_]+)\s*\(", txt)))
+    assert len(names) >= 23
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(_ffi.FRONT_SYMBOLS) == names
+
+
 def test_host_layer_without_gpu_reports_errors():
     import numpy as np
     lib = _ffi.load_host()

@@ -224,3 +224,79 @@ def test_decode_step_matches_forward_restatement(host, cpu_libs, B, pos0):
     # the context limit is an error (src/forward.c:857-862)
     assert host.ib_b200_forward_step(m, p(toks), cfg.max_ctx - B + 1, B, None) != 0
     host.ib_b200_model_free(m)
+
+
+def _build(host, cpu_libs, rng, cfg, kv_fill):
+    """a model with the benchmark's structure on the device and its twin for the CPU restatement"""
+    layers, (hw, hs), emb, es, fn = _tiny_model(rng, cfg)
+    kv = cfg.n_kv_heads * cfg.head_dim
+    m = host.ib_b200_model_create(host.ib_b200_ctx(), C.byref(cfg))
+    assert m
+    om = _cpu.IboModel(); olayers = (_cpu.IboLayer * cfg.n_layers)()
+    for f in ("hidden", "inter", "n_layers", "n_heads", "n_kv_heads", "head_dim", "vocab", "max_ctx", "eps", "theta"):
+        setattr(om, f, getattr(cfg, f))
+    caches = []
+    for l, (lin, norms) in enumerate(layers):
+        for i, (w, s, M, N, bits) in enumerate(lin):
+            assert host.ib_b200_model_set_linear(m, l, i, p(w), p(s)) == 0
+            setattr(olayers[l], ("q", "k", "v", "o", "gate", "up", "down")[i], _cpu.IboLinear(w.ctypes.data, s.ctypes.data, M, N, bits))
+        assert host.ib_b200_model_set_norms(m, l, p(norms[0]), p(norms[1])) == 0
+        kc = np.zeros((cfg.max_ctx, kv), np.float32); vc = np.zeros((cfg.max_ctx, kv), np.float32)
+        kc[:kv_fill] = rng.standard_normal((kv_fill, kv)); vc[:kv_fill] = rng.standard_normal((kv_fill, kv))
+        assert host.ib_b200_model_set_kv(m, l, p(kc), p(vc), cfg.max_ctx) == 0
+        caches.append((kc, vc))
+        olayers[l].input_norm, olayers[l].post_attn_norm = norms[0].ctypes.data, norms[1].ctypes.data
+        olayers[l].k_cache, olayers[l].v_cache = kc.ctypes.data, vc.ctypes.data
+    assert host.ib_b200_model_set_linear(m, 0, 7, p(hw), p(hs)) == 0
+    assert host.ib_b200_model_set_embedding(m, p(emb), p(es), p(fn)) == 0
+    om.embed, om.embed_scale, om.final_norm = emb.ctypes.data, es.ctypes.data, fn.ctypes.data
+    om.head = _cpu.IboLinear(hw.ctypes.data, hs.ctypes.data, cfg.vocab, cfg.hidden, 8)
+    om.layers = olayers
+    om._keep = (layers, hw, hs, emb, es, fn, caches, olayers)
+    return m, om
+
+
+def test_one_graph_serves_every_position_and_survives_scratch_growth(host, cpu_libs):
+    """Autoregressive decoding replays one captured graph per batch size (the position lives on the device),
+    and a graph captured early stays valid after later calls made the context's scratch grow: single
+    tokens at positions 3..5, then a batch of 8 (needs more scratch), then single tokens again, every step
+    against the restatement, which runs the same sequence on its own cache."""
+    rng = np.random.default_rng(77)
+    cfg = _ffi.ModelCfg(256, 512, 2, 8, 2, 32, 320, 96, 1e-5, 10000.0, 8, 4, 8)
+    m, om = _build(host, cpu_libs, rng, cfg, 3)
+    lib = _ffi.load_ibcu()
+    pos = 3
+    plan = [1, 1, 1, 8, 1, 1, 16, 1]
+    launches = []
+    for B in plan:
+        toks = rng.integers(0, cfg.vocab, B).astype(np.int32)
+        want = np.empty((B, cfg.vocab), np.float32); got = np.empty((B, cfg.vocab), np.float32)
+        assert cpu_libs.oracle.ibo_decode_step(C.byref(om), toks, pos, B, p(want), None) == 0
+        before = lib.ibcu_launch_count(host.ib_b200_ctx())
+        assert host.ib_b200_forward_step(m, p(toks), pos, B, p(got)) == 0, host.ib_b200_last_error()
+        launches.append(int(lib.ibcu_launch_count(host.ib_b200_ctx()) - before))
+        scale = float(np.abs(want).max())
+        assert _cpu.close(got, want, 2e-3, 2e-4 * max(1.0, scale)), (B, pos, float(np.max(np.abs(got - want))))
+        pos += B
+    # the first call of a batch size issues the step twice (eagerly, then into the capture); a replay issues
+    # only the kernel that stores the position
+    assert launches[0] > 20 and launches[1] == 1 and launches[2] == 1 and launches[4] == 1 and launches[7] == 1, launches
+    host.ib_b200_model_free(m)
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_decode_step_at_7b_layer_shapes(host, cpu_libs, B):
+    """One layer and the LM head at the Mistral-7B shapes of the decode configuration (hidden 4096, MLP 14336,
+    GQA 32/8 x 128, vocabulary 32000, INT8 attention, INT4 MLP, INT8 head) at context position 512."""
+    rng = np.random.default_rng(7000 + B)
+    cfg = _ffi.ModelCfg(4096, 14336, 1, 32, 8, 128, 32000, 544, 1e-5, 10000.0, 8, 4, 8)
+    m, om = _build(host, cpu_libs, rng, cfg, 512)
+    toks = rng.integers(0, cfg.vocab, B).astype(np.int32)
+    want = np.empty((B, cfg.vocab), np.float32); got = np.empty((B, cfg.vocab), np.float32)
+    assert cpu_libs.oracle.ibo_decode_step(C.byref(om), toks, 512, B, p(want), None) == 0
+    assert np.isfinite(want).all() and float(np.abs(want).max()) > 1e-3
+    for rep in range(2):                                               # eager + capture, then a replay over the same cache rows
+        assert host.ib_b200_forward_step(m, p(toks), 512, B, p(got)) == 0, host.ib_b200_last_error()
+        scale = float(np.abs(want).max())
+        assert _cpu.close(got, want, 2e-3, 2e-4 * max(1.0, scale)), (rep, float(np.max(np.abs(got - want))))
+    host.ib_b200_model_free(m)

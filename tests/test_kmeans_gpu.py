@@ -2,6 +2,8 @@
 src/pq_kmeans.c, through the C ABI. Codes must be bit-identical."""
 import ctypes as C
 
+import os
+
 import numpy as np
 import pytest
 
@@ -146,3 +148,34 @@ def test_full_size_properties(backend):
     for d in range(0, D, 3):
         ref = np.bincount(h["idx"], weights=X[:, d].astype(np.float64), minlength=K)
         assert np.allclose(h["sums"][:, d], ref, rtol=1e-4, atol=1e-5)
+
+
+def test_full_size_codes_against_the_reference(backend, cpu_libs):
+    """The benchmark configuration itself: 4 Mi points x 8, K = 256, centroids = the first 256 points, then
+    one more assignment with the centroids of one CPU update (teacher-forced): codes bit-equal to the
+    unmodified reference's ib_kmeans_assign run on its own thread pool (src/pq_kmeans.c:399-413), or to
+    the restatement where the reference library did not travel."""
+    rng = np.random.default_rng(1234)
+    N, D, K = 1 << 22, 8, 256
+    X = (rng.standard_normal((N, D)) * 0.02).astype(np.float32)
+    Cn = X[:K].copy()
+    want = np.empty(N, np.int32)
+    pool = None
+    if cpu_libs.ref is not None:
+        pool = cpu_libs.ref.ib_pool_create(min(32, os.cpu_count() or 1))
+    for step in range(2):
+        if cpu_libs.ref is not None:
+            assert cpu_libs.ref.ib_kmeans_assign(X, N, D, Cn, K, want, pool) == 0
+        else:
+            cpu_libs.oracle.ibo_kmeans_assign(X, N, D, Cn, K, want, None, 2)
+        got = backend.kmeans_assign(X, Cn)
+        bad = np.flatnonzero(got != want)
+        assert bad.size == 0, (step, bad[:10], got[bad[:10]], want[bad[:10]])
+        # centroids of the next iteration from the reference's own codes (float64 means rounded to FP32: any
+        # centroid set will do for a teacher-forced check)
+        cnt = np.bincount(want, minlength=K)
+        for d in range(D):
+            s = np.bincount(want, weights=X[:, d].astype(np.float64), minlength=K)
+            Cn[:, d] = np.where(cnt > 0, s / np.maximum(cnt, 1), Cn[:, d]).astype(np.float32)
+    if pool:
+        cpu_libs.ref.ib_pool_destroy(pool)

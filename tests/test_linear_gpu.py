@@ -28,6 +28,7 @@ def oracle_linear(libs, w, s16, x, bits):
 @pytest.mark.parametrize("M,N,B", [
     (5632, 2048, 1),      # TinyLlama up_proj
     (1024, 4096, 1), (1024, 4096, 4), (1024, 4096, 16),     # k/v proj
+    (4096, 4096, 4), (4096, 4096, 16),                      # q/o proj at the batch sizes of the attention configuration
     (512, 4096, 2), (512, 4096, 3), (512, 4096, 8), (256, 4096, 32),
     (4096, 14336, 1),     # down_proj shape
     (100, 320, 5),        # rows not a multiple of the tile, short rows
