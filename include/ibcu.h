@@ -154,31 +154,36 @@ typedef struct {
     const uint8_t*  idx_l;            /* [M * C] row-major, as in the reference */
     const uint8_t*  idx_r;
     const uint16_t* row_scale;        /* fp16 [M] */
-    const uint8_t*  idx_t;            /* subspace-major copy made by ibcu_pq_prepare: [2*C][M_pad] */
+    const uint8_t*  idx_t;            /* regrouped copy of the codes made by ibcu_pq_prepare */
     int             M_pad;
 } ibcu_pq_t;
 
-/* One-off per tensor (like the reference's ib_pq_lut_cache transposed index layout,
- * src/pq_decode.c:2687-2737): writes the subspace-major code plane into idx_t_out, which must hold
- * ibcu_pq_idx_t_bytes(M, N, G) bytes, and fills t->idx_t / t->M_pad. */
+/* One-off per tensor (like the reference's ib_pq_lut_cache regrouped index layout,
+ * src/pq_decode.c:2687-2737): writes the codes regrouped into slabs of 32 subspaces
+ * ([slab][group of 16 rows][lane][16 rows], subspace 2 * chunk + side = 32 * slab + lane) and, after them,
+ * the largest codebook magnitude into idx_t_out, which must hold ibcu_pq_idx_t_bytes(M, N, G) bytes, and
+ * fills t->idx_t / t->M_pad. Needs the tensor's codebooks as well as its codes. */
 size_t ibcu_pq_idx_t_bytes(int M, int N, int G);
 int    ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out);
 /* out[b*M + r] = row_scale[r] * sum_c (TL[c][idx_l[r,c]] + TR[c][idx_r[r,c]]) for B activations
- * x[b*N + j]; applies the reference's 1 %-of-max chunk skip rule per activation. */
+ * x[b*N + j]; applies the reference's 1 %-of-max chunk skip rule per activation. One launch; the sums of a
+ * row over slabs of 32 subspaces are added as 64-bit fixed-point integers (quantum 2^-62 of a bound on the
+ * row sums), so the result is the same bits from run to run. An activation that holds NaN or Inf gives NaN
+ * in every output of that call. */
 int    ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
 /* Same result as ibcu_pq_matmul_fp32 for callers that must not allocate device memory: serving
  * loops that cannot take cudaMalloc's device-wide synchronisation, plugins living inside a fixed
  * memory budget, processes whose allocator belongs to another runtime. This entry point has no
  * counterpart in the reference (its matmul_impl mallocs its tables on every call,
- * src/pq_decode.c:1519-1680). It calls no cudaMalloc / cudaFree or any allocating routine: the slab
- * partial sums live in an array built into the library, ibcu_pq_noalloc_max_floats() floats (4 MiB)
- * held by every GPU that loads the library from load to exit. A call that needs more (activations x
- * slabs x padded rows floats) is refused with IBCU_ERR_PARAM and a message giving both numbers.
- * The first call on a device looks up the array's device address; make that call before any stream
- * capture. All calls on a device share the one array and it keeps the previous call's contents
- * (nothing in it needs clearing: every value read is written first by the same call), so two calls
- * whose kernels may overlap on the GPU - different contexts or streams on the same device - race and
- * must be serialised by the caller. */
+ * src/pq_decode.c:1519-1680). It calls no cudaMalloc / cudaFree or any allocating routine: the row
+ * accumulators and arrival counters live in an array built into the library, ibcu_pq_noalloc_max_floats()
+ * four-byte words (4 MiB) held by every GPU that loads the library from load to exit. A call that needs
+ * more (4096 words for counters plus 2 words per activation and padded row) is refused with IBCU_ERR_PARAM
+ * and a message giving both numbers. The first call on a device looks up the array's device address; make
+ * that call before any stream capture. All calls on a device share the one array and it keeps the
+ * previous call's contents; the part a call uses must start at zero, so the call clears it on the stream
+ * before its kernel. Two calls whose kernels may overlap on the GPU - different contexts or streams on the
+ * same device - race and must be serialised by the caller. */
 int    ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
 size_t ibcu_pq_noalloc_max_floats(void);
 

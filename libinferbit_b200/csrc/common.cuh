@@ -27,7 +27,8 @@ struct ibcu_ctx {
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
     void*  xpack;      size_t xpack_bytes;      // activation limbs + per-slice scales and limb sums of the current linear call
-    void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, PQ slabs, k-means per-block partials)
+    void*  scratch;    size_t scratch_bytes;    // partial sums (split-K slices, attention chunks, k-means per-block partials)
+    void*  pq_acc;     size_t pq_acc_bytes;     // PQ matvec: arrival counters + fixed-point row accumulators, zero between calls
     void*  retired[IBCU_MAX_RETIRED]; int n_retired;   // outgrown scratch that an instantiated graph may still use
     cudaEvent_t events[IBCU_MAX_EVENTS];
     cudaGraphExec_t graphs[IBCU_MAX_GRAPHS];

@@ -81,6 +81,7 @@ extern "C" void ibcu_ctx_destroy(ibcu_ctx* ctx) {
     for (int i = 0; i < ctx->n_retired; i++) cudaFree(ctx->retired[i]);
     if (ctx->xpack) cudaFree(ctx->xpack);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->pq_acc) cudaFree(ctx->pq_acc);
     cudaStreamDestroy(ctx->stream);
     free(ctx);
 }

@@ -33,16 +33,27 @@ def test_pq_matches_reference_restatement(backend, cpu_libs, M, N, G, K, B):
     assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
 
 
-def test_transposed_code_plane_is_a_faithful_copy(backend):
+def test_packed_code_plane_is_a_faithful_copy(backend):
+    """ibcu_pq_prepare regroups the codes as [slab of 32 subspaces][group of 16 rows][lane][16 rows]
+    (subspace 2 * chunk + side = 32 * slab + lane); padding rows and padding subspaces hold zeros, and the tail
+    of the array holds the largest codebook magnitude."""
     rng = np.random.default_rng(3)
     M, N, G, K = 77, 160, 16, 256
     cb_l, cb_r, il, ir, rs, _ = _cpu.make_pq_case(rng, M, N, G, K, 1)
     t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
     Cn = N // G
-    plane = backend.download(t.idx_t, np.uint8, 2 * Cn * t.M_pad).reshape(2 * Cn, t.M_pad)
     assert t.M_pad == 80
-    assert np.array_equal(plane[0::2, :M], il.T) and np.array_equal(plane[1::2, :M], ir.T)
-    assert np.all(plane[:, M:] == 0)
+    nslab = (2 * Cn + 31) // 32
+    total = backend.lib.ibcu_pq_idx_t_bytes(M, N, G)
+    assert total == nslab * 32 * t.M_pad + 256
+    raw = backend.download(t.idx_t, np.uint8, total)
+    plane = raw[:nslab * 32 * t.M_pad].reshape(nslab, t.M_pad // 16, 32, 16)          # [slab][group][lane][row in group]
+    sub = plane.transpose(0, 2, 1, 3).reshape(nslab * 32, t.M_pad)                        # [subspace][row]
+    assert np.array_equal(sub[0:2 * Cn:2, :M], il.T) and np.array_equal(sub[1:2 * Cn:2, :M], ir.T)
+    assert np.all(sub[:, M:] == 0) and np.all(sub[2 * Cn:] == 0)
+    cbmax = raw[nslab * 32 * t.M_pad:][:4].view(np.float32)[0]
+    want = max(float(np.abs(cb_l.view(np.float16).astype(np.float32)).max()), float(np.abs(cb_r.view(np.float16).astype(np.float32)).max()))
+    assert cbmax == np.float32(want)
 
 
 def test_codes_select_the_right_table_entries(backend):
