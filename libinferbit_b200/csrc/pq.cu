@@ -8,7 +8,7 @@
 // A warp instruction that loads 16 bytes per lane reads 512 contiguous bytes: 16 rows x 32 subspaces.
 // The last 256 bytes of the array hold the largest magnitude of any codebook entry.
 //
-// pq_slab_kernel: grid = (blocks of rows) x (slabs). A block builds the lookup table of its slab in shared
+// pq_slab_kernel: grid = (blocks of rows) x (slabs) x (passes of one or two activations). A block builds the lookup table of its slab in shared
 // memory in the bank-per-lane layout, word (k * 32 + l): lane l only ever touches bank l, so neither the
 // build nor the gather has a bank conflict whatever the codes are. A warp then walks its groups of 16
 // rows: one 16-byte code load per lane, 16 table reads, and a butterfly over the lanes that leaves each
@@ -25,6 +25,7 @@ namespace {
 
 constexpr int PQ_THREADS = 512;
 constexpr int PQ_WARPS = PQ_THREADS / 32;
+constexpr size_t PQ_COUNTER_BYTES = 16384;   // 4096 four-byte slots ahead of the accumulators: arrival counters, the last 64 for max|x|
 constexpr int PQ_TAIL = 256;                 // bytes after the code array: [0] = max |codebook entry| as float bits
 
 struct PqParams {
@@ -36,6 +37,7 @@ struct PqParams {
     float* out;                                // [B][M]
     unsigned long long* acc;                   // [B][M_pad] fixed-point sums, zero between calls
     unsigned int* arrive;                      // [passes][row blocks] arrival counters, zero between calls
+    const unsigned* amax_bits;                 // [B] bit patterns of max|x[b]| when pq_amax_kernel ran ahead, else NULL
 };
 
 // codes [M][C] x 2 planes -> slabs of 32 subspaces, 16 rows per lane (see the head of the file)
@@ -71,6 +73,32 @@ __global__ void __launch_bounds__(256) pq_absmax_kernel(const __half* __restrict
     if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));     // non-negative floats order like ints
 }
 
+// grid (B): the bit pattern of max|x[b]| (NaN and Inf sort above every finite value)
+__global__ void __launch_bounds__(512) pq_amax_kernel(const float* __restrict__ x, int N, unsigned* __restrict__ out) {
+    __shared__ unsigned red[16];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* xb = x + (size_t)blockIdx.x * N;
+    unsigned m = 0u;
+    if ((N & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+        const uint4* x4 = reinterpret_cast<const uint4*>(xb);
+#pragma unroll 8
+        for (int j = threadIdx.x; j < (N >> 2); j += 512) {
+            const uint4 v = x4[j];
+            m = max(max(m, v.x & 0x7fffffffu), max(max(v.y & 0x7fffffffu, v.z & 0x7fffffffu), v.w & 0x7fffffffu));
+        }
+    } else {
+        for (int j = threadIdx.x; j < N; j += 512) m = max(m, __float_as_uint(xb[j]) & 0x7fffffffu);
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 16; w++) m = max(m, red[w]);
+        out[blockIdx.x] = m;
+    }
+}
+
 // one halving step of the butterfly: N values per lane -> N/2, each the sum over the lane pair {l, l ^ o}
 template <int N>
 __device__ __forceinline__ void fold(float* v, int o, int lane) {
@@ -83,108 +111,141 @@ __device__ __forceinline__ void fold(float* v, int o, int lane) {
     }
 }
 
-// BT activations share one pass over the codes: table entries are BT floats wide (1 or 4)
+// BT activations (1 or 2) share a pass over the codes: table entries are BT floats wide. grid = (blocks of rows,
+// blocks of slabs, passes); pass z serves activations BT z .. BT z + BT - 1.
 template <int BT>
-__global__ void __launch_bounds__(PQ_THREADS, BT == 1 ? 2 : 1) pq_slab_kernel(const PqParams p) {
+__global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p) {
+    constexpr int PQ_NG = BT == 1 ? 4 : 2;                   // groups of 16 rows whose codes a warp keeps in flight
     extern __shared__ __align__(16) float lut[];            // [256][32][BT]
     __shared__ float xs[BT][32][17];                         // this slab's activation slices, one row per lane (half <= 16)
-    __shared__ float red[BT][PQ_WARPS];
-    __shared__ int bad_s[PQ_WARPS];
-    __shared__ unsigned char live[BT][32];
+    __shared__ __align__(16) float4 cbf[256][2][2];          // [k][side][half of the entry]: the two shared codebooks (half == 8) widened to FP32, staged once;
+                                                             // even and odd lanes (sides L and R) of a warp read neighbouring 32-byte pieces
+    __shared__ unsigned red[BT][PQ_WARPS];
     __shared__ int last_s;
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int half = p.G >> 1, nsub = 2 * p.C;
+    const int b0 = blockIdx.z * BT, nb = min(BT, p.B - b0);
     const int row_lo = blockIdx.x * p.rows_per_block;
     const int row_hi = min(p.M_pad, row_lo + p.rows_per_block);
     const int G16 = p.M_pad >> 4;
     const int g_lo = row_lo >> 4, g_hi = row_hi >> 4;
+    const int ngw = g_lo + warp < g_hi ? (g_hi - g_lo - warp + PQ_WARPS - 1) / PQ_WARPS : 0;     // this warp's groups: g_lo + warp + 16 i
+    const int nj = (p.nslab - (int)blockIdx.y + (int)gridDim.y - 1) / (int)gridDim.y;             // this block's slabs: blockIdx.y + gridDim.y j
+    const bool cb_smem = half == 8 && p.cb_stride == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
+    const bool cb_vec = half == 8 && (p.cb_stride & 7) == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
+
+    // weights first, they do not depend on the previous kernel: the first codes, the shared codebooks, the row scales
+    auto load_codes = [&](int slab, int c0, uint4* cd) {
+        const uint4* codes = reinterpret_cast<const uint4*>(p.idx_t) + (size_t)slab * G16 * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < PQ_NG; i++) {
+            const int g = g_lo + warp + PQ_WARPS * (c0 + i);
+            cd[i] = (c0 + i < ngw) ? ld_stream_u4(codes + (size_t)g * 32) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    uint4 cd[PQ_NG];
+    if (nj > 0) load_codes(blockIdx.y, 0, cd);
+    if (cb_smem) {
+        const int side = tid >> 8, k = tid & 255;
+        const uint4 raw = k < p.K ? reinterpret_cast<const uint4*>(side ? p.cb_r : p.cb_l)[k] : make_uint4(0, 0, 0, 0);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        cbf[k][side][0] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        cbf[k][side][1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
     const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
+    // the rows this thread would finish if its block turns out to arrive last (PQ_FIN at a time)
+    constexpr int PQ_FIN = 4;
+    const int rows = max(0, min(row_hi, p.M) - row_lo);
+    float rsc[PQ_FIN];
+#pragma unroll
+    for (int u = 0; u < PQ_FIN; u++) {
+        const int e = tid + u * PQ_THREADS;
+        rsc[u] = e < rows * nb ? __half2float(p.row_scale[row_lo + e % rows]) : 0.0f;
+    }
 
     pdl_wait();
     const bool vec_x = (p.N & 3) == 0 && ((uintptr_t)p.x & 15) == 0;
-    for (int b0 = 0; b0 < p.B; b0 += BT) {
-        const int nb = min(BT, p.B - b0);
-        // ── max |x| of each activation (the reference's 1 %-of-max rule and the fixed-point scale need it) ──
-        float am[BT]; int bad = 0;
-#pragma unroll
-        for (int t = 0; t < BT; t++) {
-            am[t] = 0.0f;
-            if (t >= nb) continue;
-            const float* xb = p.x + (size_t)(b0 + t) * p.N;
-            if (vec_x) {
-                const float4* x4 = reinterpret_cast<const float4*>(xb);
-                const int n4 = p.N >> 2;
-#pragma unroll 8
-                for (int j = tid; j < n4; j += PQ_THREADS) {
-                    const float4 v = x4[j];
-                    const float m4 = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-                    am[t] = fmaxf(am[t], m4);
-                    bad |= !(fabsf(v.x) <= 3.0e38f) | !(fabsf(v.y) <= 3.0e38f) | !(fabsf(v.z) <= 3.0e38f) | !(fabsf(v.w) <= 3.0e38f);
-                }
-            } else {
-#pragma unroll 8
-                for (int j = tid; j < p.N; j += PQ_THREADS) { const float v = xb[j]; am[t] = fmaxf(am[t], fabsf(v)); bad |= !(fabsf(v) <= 3.0e38f); }
+    auto fill_xs = [&](int s0) {                            // this slab's slices of x: subspace s covers x[s * half, (s + 1) * half)
+        if (half == 8) {
+            for (int e = tid; e < BT * 256; e += PQ_THREADS) {
+                const int t = e >> 8, l = (e >> 3) & 31, i = e & 7, s = s0 + l;
+                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (size_t)s * 8 + i] : 0.0f;
             }
+            return;
         }
-#pragma unroll
-        for (int t = 0; t < BT; t++) am[t] = warp_max(am[t]);
-        bad = __any_sync(0xffffffffu, bad);
-        __syncthreads();                                     // the previous pass is done with the table and xs
-        if (lane == 0) {
-#pragma unroll
-            for (int t = 0; t < BT; t++) red[t][warp] = am[t];
-            bad_s[warp] = bad;
+        for (int e = tid; e < BT * 32 * half; e += PQ_THREADS) {
+            const int t = e / (32 * half), r = e - t * 32 * half, l = r / half, i = r - l * half;
+            const int s = s0 + l;
+            xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (size_t)s * half + i] : 0.0f;
         }
-        for (int j = 0; j < (p.nslab - (int)blockIdx.y + (int)gridDim.y - 1) / (int)gridDim.y; j++) {
-            const int slab = blockIdx.y + j * gridDim.y;
-            const int s0 = slab * 32;
-            if (j) __syncthreads();
-            // this slab's slices of x: subspace s covers x[s * half, (s + 1) * half)
-            for (int e = tid; e < BT * 32 * half; e += PQ_THREADS) {
-                const int t = e / (32 * half), r = e - t * 32 * half, l = r / half, i = r - l * half;
-                const int s = s0 + l;
-                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (size_t)s * half + i] : 0.0f;
+    };
+    // ── max |x| of each activation (the reference's 1 %-of-max rule and the fixed-point scale need it), as the
+    //    largest bit pattern of |x|: patterns of non-negative floats order like the floats, and NaN / Inf sort last.
+    //    The loads are issued here and first used after the table has been built. ──
+    unsigned ab[BT];
+#pragma unroll
+    for (int t = 0; t < BT; t++) {
+        ab[t] = 0u;
+        if (t >= nb) continue;
+        if (p.amax_bits) { ab[t] = p.amax_bits[b0 + t]; continue; }            // made by pq_amax_kernel ahead of this launch
+        const float* xb = p.x + (size_t)(b0 + t) * p.N;
+        if (vec_x) {
+            const uint4* x4 = reinterpret_cast<const uint4*>(xb);
+            const int n4 = p.N >> 2;
+#pragma unroll 8
+            for (int j = tid; j < n4; j += PQ_THREADS) {
+                const uint4 v = x4[j];
+                ab[t] = max(max(ab[t], v.x & 0x7fffffffu), max(max(v.y & 0x7fffffffu, v.z & 0x7fffffffu), v.w & 0x7fffffffu));
             }
-            __syncthreads();
-            float amax[BT];
-            int anybad = 0;
+        } else {
+#pragma unroll 8
+            for (int j = tid; j < p.N; j += PQ_THREADS) ab[t] = max(ab[t], __float_as_uint(xb[j]) & 0x7fffffffu);
+        }
+    }
+    float amax[BT], inv_q[BT];
+    int anybad = 0;
+    for (int j = 0; j < nj; j++) {
+        const int slab = blockIdx.y + j * gridDim.y;
+        const int s0 = slab * 32;
+        if (j) {
+            __syncthreads();                                 // the gather of the previous slab is done with the table and xs
+            load_codes(slab, 0, cd);
+        }
+        fill_xs(s0);
+        __syncthreads();
+        // ── lookup table of the slab: thread (k, lane) for k = warp, warp + 16, ...; word (k * 32 + lane). Padding
+        //    subspaces have zero slices, hence zero tables; subspaces the 1 % rule drops are dealt with in the gather ──
+        {
+            const int s = s0 + lane;
+            const bool sub_ok = s < nsub;
+            const __half* cb = ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride;
+            if (cb_vec) {
+                float xr[BT][8];
 #pragma unroll
-            for (int w = 0; w < PQ_WARPS; w++) anybad |= bad_s[w];
+                for (int t = 0; t < BT; t++)
 #pragma unroll
-            for (int t = 0; t < BT; t++) {
-                amax[t] = red[t][0];
+                    for (int i = 0; i < 8; i++) xr[t][i] = xs[t][lane][i];
+                if (cb_smem) {
+                    const int side = s & 1;
+#pragma unroll 4
+                    for (int k = warp; k < 256; k += PQ_WARPS) {
+                        const float4 ca = cbf[k][side][0], cc = cbf[k][side][1];
+                        float v[BT];
 #pragma unroll
-                for (int w = 1; w < PQ_WARPS; w++) amax[t] = fmaxf(amax[t], red[t][w]);
-            }
-            if (tid < 32 * BT) {
-                const int t = tid >> 5, l = tid & 31;
-                bool keep = t < nb && s0 + l < nsub;
-                if (keep && amax[t] > 0.0f) {                // a chunk (both halves) whose largest |x| is under 1 % of the largest overall is dropped
-                    const int l0 = l & ~1;
-                    float cm = 0.0f;
-                    for (int i = 0; i < half; i++) cm = fmaxf(cm, fmaxf(fabsf(xs[t][l0][i]), fabsf(xs[t][l0 + 1][i])));
-                    keep = cm >= amax[t] * 0.01f;
-                }
-                live[t][l] = keep;
-            }
-            __syncthreads();
-            // ── lookup table of the slab: thread (k, lane) for k = warp, warp + 16, ...; word (k * 32 + lane) ──
-            {
-                const int s = s0 + lane;
-                const bool sub_ok = s < nsub;
-                const __half* cb = ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride;
-                const bool vec_cb = half == 8 && (p.cb_stride & 7) == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
-                bool lv[BT];
-#pragma unroll
-                for (int t = 0; t < BT; t++) lv[t] = live[t][lane];
-                if (vec_cb) {
+                        for (int t = 0; t < BT; t++) {
+                            float a = 0.0f;
+                            a = fmaf(ca.x, xr[t][0], a); a = fmaf(ca.y, xr[t][1], a); a = fmaf(ca.z, xr[t][2], a); a = fmaf(ca.w, xr[t][3], a);
+                            a = fmaf(cc.x, xr[t][4], a); a = fmaf(cc.y, xr[t][5], a); a = fmaf(cc.z, xr[t][6], a); a = fmaf(cc.w, xr[t][7], a);
+                            v[t] = a;
+                        }
+                        float* dst = lut + ((size_t)k * 32 + lane) * BT;
+                        if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+                        else dst[0] = v[0];
+                    }
+                } else {
                     constexpr int U = 4;
-                    float xr[BT][8];
-#pragma unroll
-                    for (int t = 0; t < BT; t++)
-#pragma unroll
-                        for (int i = 0; i < 8; i++) xr[t][i] = xs[t][lane][i];
                     for (int k0 = warp; k0 < 256; k0 += PQ_WARPS * U) {
                         uint4 raw[U];
 #pragma unroll
@@ -203,131 +264,186 @@ __global__ void __launch_bounds__(PQ_THREADS, BT == 1 ? 2 : 1) pq_slab_kernel(co
                                 float a = 0.0f;
                                 a = fmaf(f0.x, xr[t][0], a); a = fmaf(f0.y, xr[t][1], a); a = fmaf(f1.x, xr[t][2], a); a = fmaf(f1.y, xr[t][3], a);
                                 a = fmaf(f2.x, xr[t][4], a); a = fmaf(f2.y, xr[t][5], a); a = fmaf(f3.x, xr[t][6], a); a = fmaf(f3.y, xr[t][7], a);
-                                v[t] = lv[t] ? a : 0.0f;
+                                v[t] = a;
                             }
                             float* dst = lut + ((size_t)k * 32 + lane) * BT;
-                            if constexpr (BT == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                            if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
                             else dst[0] = v[0];
                         }
                     }
-                } else {
-                    for (int k = warp; k < 256; k += PQ_WARPS) {
-                        float v[BT];
+                }
+            } else {
+                for (int k = warp; k < 256; k += PQ_WARPS) {
+                    float v[BT];
 #pragma unroll
-                        for (int t = 0; t < BT; t++) v[t] = 0.0f;
-                        if (sub_ok && k < p.K) {
-                            for (int i = 0; i < half; i++) {
-                                const float c = __half2float(cb[(size_t)k * half + i]);
+                    for (int t = 0; t < BT; t++) v[t] = 0.0f;
+                    if (sub_ok && k < p.K) {
+                        for (int i = 0; i < half; i++) {
+                            const float c = __half2float(cb[(size_t)k * half + i]);
 #pragma unroll
-                                for (int t = 0; t < BT; t++) v[t] = fmaf(c, xs[t][lane][i], v[t]);
-                            }
-#pragma unroll
-                            for (int t = 0; t < BT; t++) v[t] = lv[t] ? v[t] : 0.0f;
+                            for (int t = 0; t < BT; t++) v[t] = fmaf(c, xs[t][lane][i], v[t]);
                         }
-                        float* dst = lut + ((size_t)k * 32 + lane) * BT;
-#pragma unroll
-                        for (int t = 0; t < BT; t++) dst[t] = v[t];
                     }
+                    float* dst = lut + ((size_t)k * 32 + lane) * BT;
+#pragma unroll
+                    for (int t = 0; t < BT; t++) dst[t] = v[t];
                 }
             }
-            __syncthreads();
-            // ── fixed-point scale: 2^e >= N * max|codebook| * max|x| bounds every row sum ──
-            float inv_q[BT];
+        }
+        if (j == 0) {
+            if (!p.amax_bits) {
+#pragma unroll
+                for (int t = 0; t < BT; t++) ab[t] = __reduce_max_sync(0xffffffffu, ab[t]);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int t = 0; t < BT; t++) red[t][warp] = ab[t];
+            }
+        }
+        __syncthreads();                                     // the table is complete (and, for the first slab, the maxima are in place)
+        if (j == 0) {
 #pragma unroll
             for (int t = 0; t < BT; t++) {
+                unsigned m = red[t][0];
+#pragma unroll
+                for (int w = 1; w < PQ_WARPS; w++) m = max(m, red[t][w]);
+                anybad |= m > 0x7f7fffffu;                                         // a NaN or an Inf among the activations of this pass
+                amax[t] = __uint_as_float(m);
+                // fixed-point scale: 2^e >= N * max|codebook| * max|x| bounds every row sum
                 const float bound = (float)p.N * cbmax * amax[t];
-                int e = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;       // bound < 2^e
+                int e = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;         // bound < 2^e
                 e = max(-60, min(120, e));
-                inv_q[t] = __uint_as_float((uint32_t)(127 + 62 - e) << 23);          // 2^(62 - e)
+                inv_q[t] = __uint_as_float((uint32_t)(127 + 62 - e) << 23);            // 2^(62 - e)
             }
-            // ── gather: a warp per group of 16 rows ──
-            const uint4* codes = reinterpret_cast<const uint4*>(p.idx_t) + (size_t)slab * G16 * 32 + lane;
-            for (int g = g_lo + warp; g < g_hi; g += PQ_WARPS) {
-                const uint4 cd = ld_stream_u4(codes + (size_t)g * 32);
+        }
+        // the reference drops a chunk (both of its subspaces) whose largest |x| is under 1 % of the largest overall:
+        // this lane's subspace then contributes nothing
+        bool dead[BT];
+        unsigned any_dead = 0;
+#pragma unroll
+        for (int t = 0; t < BT; t++) {
+            dead[t] = false;
+            if (t < nb && s0 + lane < nsub && amax[t] > 0.0f) {
+                const int l0 = lane & ~1;
+                float cm = 0.0f;
+                for (int i = 0; i < half; i++) cm = fmaxf(cm, fmaxf(fabsf(xs[t][l0][i]), fabsf(xs[t][l0 + 1][i])));
+                dead[t] = !(cm >= amax[t] * 0.01f);
+            }
+            any_dead |= __ballot_sync(0xffffffffu, dead[t]);
+        }
+        // ── gather: a warp per group of 16 rows, the codes of the next PQ_NG groups in flight meanwhile ──
+        for (int c0 = 0; c0 < ngw; c0 += PQ_NG) {
+            uint4 nx[PQ_NG];
+            if (c0 + PQ_NG < ngw) load_codes(slab, c0 + PQ_NG, nx);
+#pragma unroll
+            for (int q4 = 0; q4 < PQ_NG; q4++) {
+                if (c0 + q4 >= ngw) break;
+                const int g = g_lo + warp + PQ_WARPS * (c0 + q4);
+                const uint4 cw = cd[q4];
                 float v[16 * BT];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const uint32_t w = i < 4 ? cd.x : (i < 8 ? cd.y : (i < 12 ? cd.z : cd.w));
+                    const uint32_t w = i < 4 ? cw.x : (i < 8 ? cw.y : (i < 12 ? cw.z : cw.w));
                     const uint32_t code = (w >> (8 * (i & 3))) & 0xFF;
-                    if constexpr (BT == 4) {
-                        const float4 q = *reinterpret_cast<const float4*>(lut + ((size_t)code * 32 + lane) * 4);
-                        v[i] = q.x; v[16 + i] = q.y; v[32 + i] = q.z; v[48 + i] = q.w;       // index = t * 16 + row
+                    if constexpr (BT == 2) {
+                        const float2 q = *reinterpret_cast<const float2*>(lut + ((size_t)code * 32 + lane) * 2);
+                        v[i] = q.x; v[16 + i] = q.y;                                        // index = t * 16 + row
                     } else v[i] = lut[code * 32 + lane];
                 }
-                if constexpr (BT == 4) { fold<64>(v, 16, lane); fold<32>(v, 8, lane); fold<16>(v, 4, lane); fold<8>(v, 2, lane); fold<4>(v, 1, lane); }
+                if (any_dead) {
+#pragma unroll
+                    for (int t = 0; t < BT; t++)
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[t * 16 + i] = dead[t] ? 0.0f : v[t * 16 + i];
+                }
+                if constexpr (BT == 2) { fold<32>(v, 16, lane); fold<16>(v, 8, lane); fold<8>(v, 4, lane); fold<4>(v, 2, lane); fold<2>(v, 1, lane); }
                 else { fold<16>(v, 16, lane); fold<8>(v, 8, lane); fold<4>(v, 4, lane); fold<2>(v, 2, lane); v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1); }
                 // which (activation, row) a lane ends up with: bit 16 of the lane picked the upper half of the
                 // index range in the first step, bit 8 the upper half of that half, and so on
-                if constexpr (BT == 4) {
-                    const int base = ((lane & 16) ? 32 : 0) + ((lane & 8) ? 16 : 0) + ((lane & 4) ? 8 : 0) + ((lane & 2) ? 4 : 0) + ((lane & 1) ? 2 : 0);
-#pragma unroll
-                    for (int q = 0; q < 2; q++) {
-                        const int idx = base + q, t = idx >> 4, r = 16 * g + (idx & 15);
-                        if (t < nb) atomicAdd(p.acc + (size_t)(b0 + t) * p.M_pad + r, (unsigned long long)__float2ll_rn(v[q] * inv_q[t]));
-                    }
+                if constexpr (BT == 2) {
+                    const int t = lane >> 4, r = 16 * g + (lane & 15);                     // index = lane
+                    if (t < nb) atomicAdd(p.acc + (size_t)(b0 + t) * p.M_pad + r, (unsigned long long)__float2ll_rn(v[0] * inv_q[t]));
                 } else if ((lane & 1) == 0) {
                     const int r = 16 * g + (lane >> 1);
                     atomicAdd(p.acc + (size_t)b0 * p.M_pad + r, (unsigned long long)__float2ll_rn(v[0] * inv_q[0]));
                 }
             }
-        }
-        // ── the block that arrives last for these rows turns the sums into the result ──
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            unsigned int* cnt = p.arrive + (size_t)(b0 / BT) * gridDim.x + blockIdx.x;     // one counter per pass and block of rows
-            const unsigned int n = atomicAdd(cnt, 1u);
-            last_s = n == gridDim.y - 1;
-            if (last_s) *cnt = 0;
-        }
-        __syncthreads();
-        if (last_s) {
-            __threadfence();
-            float amax[BT]; int anybad = 0;
+            if (c0 + PQ_NG < ngw) {
 #pragma unroll
-            for (int w = 0; w < PQ_WARPS; w++) anybad |= bad_s[w];
-#pragma unroll
-            for (int t = 0; t < BT; t++) {
-                amax[t] = red[t][0];
-#pragma unroll
-                for (int w = 1; w < PQ_WARPS; w++) amax[t] = fmaxf(amax[t], red[t][w]);
-            }
-            const int rows = min(row_hi, p.M) - row_lo;
-            for (int e = tid; e < rows * nb; e += PQ_THREADS) {
-                const int t = e / rows, r = row_lo + (e - t * rows);
-                const float bound = (float)p.N * cbmax * amax[t];
-                int ex = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;
-                ex = max(-60, min(120, ex));
-                const long long s = (long long)atomicExch(p.acc + (size_t)(b0 + t) * p.M_pad + r, 0ull);
-                const double q = __longlong_as_double((long long)(1023 + ex - 62) << 52);          // 2^(ex - 62)
-                float y = (float)((double)s * q) * __half2float(p.row_scale[r]);
-                if (anybad) y = __int_as_float(0x7fc00000);                                         // an activation held NaN or Inf
-                p.out[(size_t)(b0 + t) * p.M + r] = y;
-            }
-            // padded rows of the last group also received sums
-            for (int e = tid; e < (row_hi - min(row_hi, p.M)) * nb; e += PQ_THREADS) {
-                const int pad = row_hi - min(row_hi, p.M), t = e / pad, r = min(row_hi, p.M) + (e - t * pad);
-                p.acc[(size_t)(b0 + t) * p.M_pad + r] = 0ull;
+                for (int i = 0; i < PQ_NG; i++) cd[i] = nx[i];
             }
         }
-        __syncthreads();
+    }
+    // ── the block that arrives last for these rows turns the sums into the result ──
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned int* cnt = p.arrive + (size_t)blockIdx.z * gridDim.x + blockIdx.x;        // one counter per pass and block of rows
+        const unsigned int n = atomicAdd(cnt, 1u);
+        last_s = n == gridDim.y - 1;
+        if (last_s) *cnt = 0;
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    if (nj == 0) {                                            // a block without slabs saw no maxima; it cannot be last unless it is alone
+#pragma unroll
+        for (int t = 0; t < BT; t++) { amax[t] = 0.0f; }
+    }
+    for (int e0 = 0; e0 < rows * nb; e0 += PQ_FIN * PQ_THREADS) {
+        long long sum[PQ_FIN];
+#pragma unroll
+        for (int u = 0; u < PQ_FIN; u++) {
+            const int e = e0 + tid + u * PQ_THREADS;
+            sum[u] = 0;
+            if (e < rows * nb) sum[u] = (long long)atomicExch(p.acc + (size_t)(b0 + e / rows) * p.M_pad + row_lo + e % rows, 0ull);
+        }
+#pragma unroll
+        for (int u = 0; u < PQ_FIN; u++) {
+            const int e = e0 + tid + u * PQ_THREADS;
+            if (e >= rows * nb) continue;
+            const int t = e / rows, r = row_lo + e % rows;
+            const float bound = (float)p.N * cbmax * amax[t];
+            int ex = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;
+            ex = max(-60, min(120, ex));
+            const double q = __longlong_as_double((long long)(1023 + ex - 62) << 52);              // 2^(ex - 62)
+            const float sc = e0 == 0 ? rsc[u] : __half2float(p.row_scale[r]);
+            float y = (float)((double)sum[u] * q) * sc;
+            if (anybad) y = __int_as_float(0x7fc00000);                                             // an activation held NaN or Inf
+            p.out[(size_t)(b0 + t) * p.M + r] = y;
+        }
+    }
+    // padded rows of the last group also received sums
+    const int pad = row_hi - min(row_hi, p.M);
+    for (int e = tid; e < pad * nb; e += PQ_THREADS) {
+        const int t = e / pad, r = min(row_hi, p.M) + (e - t * pad);
+        p.acc[(size_t)(b0 + t) * p.M_pad + r] = 0ull;
     }
 }
 
-struct PqPlan { int C, nslab, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
+struct PqPlan { int C, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
 
 PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     PqPlan pl;
     pl.C = t->N / t->G;
     pl.nslab = (2 * pl.C + 31) / 32;
-    const int per_sm = B >= 2 ? 1 : 2;
-    const int slots = ctx->sm_count * per_sm;
-    pl.slab_blocks = pl.nslab < slots ? pl.nslab : slots;                    // more slabs than blocks: a block walks several
-    int rb = slots / pl.slab_blocks;
+    pl.bt = B >= 2 ? 2 : 1;
+    pl.passes = (B + pl.bt - 1) / pl.bt;
+    const int slots = ctx->sm_count * 2;
     const int groups = t->M_pad / 16;
-    if (rb > groups) rb = groups;
-    if (rb < 1) rb = 1;
-    const int gpb = (groups + rb - 1) / rb;
+    pl.slab_blocks = pl.nslab < slots ? pl.nslab : slots;                    // more slabs than blocks: a block walks several
+    // Blocks of rows: every one of them builds the tables of its slab again, so few are cheap in arithmetic, but the
+    // grid should fill whole rounds of the machine. Cost model in warp instructions: a table ~ 3000 * bt, the
+    // gather of all rows ~ groups * 125 * bt, per slab and pass.
+    const long units = (long)pl.slab_blocks * pl.passes;
+    const long slabs_per_block = (pl.nslab + pl.slab_blocks - 1) / pl.slab_blocks;
+    int best_rb = 1; double best = 1e30;
+    for (int rb = 1; rb <= 16 && rb <= groups; rb++) {
+        const long rounds = (units * rb + slots - 1) / slots;
+        const double cost = (double)rounds * slabs_per_block * (3000.0 + 125.0 * ((groups + rb - 1) / rb));
+        if (cost < best * 0.98) { best = cost; best_rb = rb; }
+    }
+    const int gpb = (groups + best_rb - 1) / best_rb;
     pl.rows_per_block = gpb * 16;
     pl.row_blocks = (groups + gpb - 1) / gpb;
     pl.acc_words = (size_t)B * t->M_pad;
@@ -341,14 +457,24 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
     p.rows_per_block = pl.rows_per_block;
     p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
     p.idx_t = t->idx_t; p.row_scale = (const __half*)t->row_scale; p.x = x; p.out = out; p.acc = acc; p.arrive = arrive;
-    const dim3 grid(pl.row_blocks, pl.slab_blocks), block(PQ_THREADS);
-    if (B >= 2) {
-        const size_t smem = (size_t)256 * 32 * 4 * sizeof(float);
-        static std::once_flag once[64];
-        cudaError_t e = cudaSuccess;
-        std::call_once(once[ctx->device & 63], [&] { e = cudaFuncSetAttribute(pq_slab_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
-        if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
-        return ibcu_launch(ctx, pq_slab_kernel<4>, grid, block, smem, 1, true, p);
+    p.amax_bits = nullptr;
+    const dim3 grid(pl.row_blocks, pl.slab_blocks, pl.passes), block(PQ_THREADS);
+    // static plus dynamic shared memory passes 48 KB: opt in once per device
+    static std::once_flag once[64];
+    cudaError_t e = cudaSuccess;
+    std::call_once(once[ctx->device & 63], [&] {
+        e = cudaFuncSetAttribute(pq_slab_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 2 * (int)sizeof(float));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
+    });
+    if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
+    if (pl.bt == 2) {
+        // with several activations every block would scan all of them for their maxima: one small launch does it once;
+        // its results sit in the last 64 counter slots, which no pass uses
+        unsigned* amax_bits = arrive + (PQ_COUNTER_BYTES / sizeof(unsigned) - 64);
+        int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits);
+        if (rc) return rc;
+        p.amax_bits = amax_bits;
+        return ibcu_launch(ctx, pq_slab_kernel<2>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
     }
     return ibcu_launch(ctx, pq_slab_kernel<1>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p);
 }
@@ -364,8 +490,6 @@ int pq_check(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int 
 }
 
 }  // namespace
-
-constexpr size_t PQ_COUNTER_BYTES = 16384;                   // 4096 arrival counters ahead of the accumulators
 
 static size_t pq_scratch_bytes(const PqPlan& pl) { return PQ_COUNTER_BYTES + pl.acc_words * sizeof(unsigned long long); }
 
