@@ -193,6 +193,13 @@ size_t ibcu_pq_noalloc_max_floats(void);
  * dist (may be NULL) receives the winning distance. D <= 32, K <= 1024. */
 int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, const float* C, int K,
                        int32_t* idx, float* dist);
+/* Which assignment kernel ibcu_kmeans_assign may take; every one gives the same codes and distances. For tests
+ * and comparisons: AUTO = the fastest the shape allows (D == 8: tcgen05 tensor-core filter for K a multiple of 32
+ * up to 256, else the mma.sync filter for K a multiple of 8; other shapes the exact kernel). */
+#define IBCU_KMEANS_AUTO     0
+#define IBCU_KMEANS_EXACT    1   /* every distance in the exact form on the CUDA cores */
+#define IBCU_KMEANS_MMA_SYNC 2   /* never the tcgen05 kernel */
+void ibcu_kmeans_set_path(ibcu_ctx* ctx, int path);
 /* The accumulate half of pq_assign_task (src/pq_kmeans.c:183-201): sums[K*D] (FP32), counts[K],
  * inertia (double, sum of dist) over this context's N points, deterministic for a given N. */
 int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int D, int K,

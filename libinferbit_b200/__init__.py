@@ -158,13 +158,18 @@ class Backend:
         self.sync()
         return self.download(do, np.float32, B * t.M).reshape(B, t.M)
 
-    def kmeans_assign(self, X, Cn, want_dist=False):
+    def kmeans_assign(self, X, Cn, want_dist=False, path=0):
+        """path: IBCU_KMEANS_AUTO (0), _EXACT (1) or _MMA_SYNC (2)"""
         X = np.ascontiguousarray(X, np.float32); Cn = np.ascontiguousarray(Cn, np.float32)
         N, D = X.shape; K = Cn.shape[0]
         dX, dC = self.upload(X), self.upload(Cn)
         di = self.alloc(N * 4); dd = self.alloc(N * 4)
-        self._check(self.lib.ibcu_kmeans_assign(self.ctx, dX.ptr, N, D, dC.ptr, K, di.ptr, dd.ptr))
-        self.sync()
+        self.lib.ibcu_kmeans_set_path(self.ctx, path)
+        try:
+            self._check(self.lib.ibcu_kmeans_assign(self.ctx, dX.ptr, N, D, dC.ptr, K, di.ptr, dd.ptr))
+            self.sync()
+        finally:
+            self.lib.ibcu_kmeans_set_path(self.ctx, 0)
         idx = self.download(di, np.int32, N)
         dist = self.download(dd, np.float32, N) if want_dist else None
         for b in (dX, dC, di, dd):

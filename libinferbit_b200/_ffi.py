@@ -79,6 +79,7 @@ IBCU_SYMBOLS = {
     "ibcu_pq_matmul_fp32_noalloc": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pq_noalloc_max_floats": (C.c_size_t, []),
     "ibcu_kmeans_assign": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ibcu_kmeans_set_path": (None, [C.c_void_p, C.c_int]),
     "ibcu_kmeans_accumulate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_kmeans_update": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),

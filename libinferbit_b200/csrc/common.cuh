@@ -23,7 +23,7 @@ struct ibcu_ctx {
     char msg[512];
     int pdl;                       // programmatic dependent launch between our kernels
     int force_generic;
-    int kmeans_exact;              // tests: every distance in the exact form (no tensor-core filter)
+    int kmeans_path;               // IBCU_KMEANS_*: which assignment kernel ibcu_kmeans_assign may take (tests)
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)
     void*  xpack;      size_t xpack_bytes;      // activation limbs + per-slice scales and limb sums of the current linear call
@@ -42,6 +42,7 @@ struct ibcu_ctx {
     int    win_open;                                // peers mapped so far
     int    win_enabled;
     int*   win_err;                                 // pinned, mapped: a push kernel that gave up waiting writes its epoch here
+    int*   kern_err;                                // pinned, mapped, made with the context: a kernel whose bounded wait ran out writes a code here
     const void* win_last[4];                        // buffers of the previous push (a buffer is not pushed twice in a row)
 };
 

@@ -63,6 +63,8 @@ extern "C" int ibcu_ctx_create(int device, ibcu_ctx** out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { free(ctx); return IBCU_ERR_CUDA; }
     for (int i = 0; i < IBCU_MAX_EVENTS; i++)
         if (cudaEventCreate(&ctx->events[i]) != cudaSuccess) { free(ctx); return IBCU_ERR_CUDA; }
+    if (cudaHostAlloc((void**)&ctx->kern_err, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { free(ctx); return IBCU_ERR_NOMEM; }
+    *ctx->kern_err = 0;
     *out = ctx;
     return IBCU_OK;
 }
@@ -82,6 +84,7 @@ extern "C" void ibcu_ctx_destroy(ibcu_ctx* ctx) {
     if (ctx->xpack) cudaFree(ctx->xpack);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->pq_acc) cudaFree(ctx->pq_acc);
+    if (ctx->kern_err) cudaFreeHost(ctx->kern_err);
     cudaStreamDestroy(ctx->stream);
     free(ctx);
 }
@@ -149,6 +152,11 @@ extern "C" int ibcu_sync(ibcu_ctx* ctx) {
         const int e = *(volatile int*)ctx->win_err;
         *(volatile int*)ctx->win_err = 0;
         return ibcu_fail(ctx, IBCU_ERR_COMM, "all-gather %d: a peer's rows did not arrive within the wait limit", e);
+    }
+    if (ctx->kern_err && *(volatile int*)ctx->kern_err) {
+        const int e = *(volatile int*)ctx->kern_err;
+        *(volatile int*)ctx->kern_err = 0;
+        return ibcu_fail(ctx, IBCU_ERR_CUDA, "a kernel gave up a bounded wait (code %d): its results are not valid", e);
     }
     return ctx->status;
 }

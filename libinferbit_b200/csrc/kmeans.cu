@@ -14,40 +14,13 @@
 // each warp adds its points in index order into a private shared-memory table, warps and blocks are
 // then combined in index order.
 #include "common.cuh"
+#include "kmeans_ref.cuh"
 #include <stdlib.h>
 #include <stdint.h>
 
 namespace {
 
 constexpr int KM_MAX_D = 32;
-
-template <int DT>   // DT > 0: compile-time D; DT == 0: run-time D
-__device__ __forceinline__ float ref_sqdist(const float* x, const float* c, int D) {
-    float s = 0.0f;
-    if (DT > 0) {
-#pragma unroll
-        for (int d = 0; d < (DT & ~3); d++) {
-            const float v = __fsub_rn(x[d], c[d]);
-            s = __fadd_rn(s, __fmul_rn(v, v));
-        }
-#pragma unroll
-        for (int d = (DT & ~3); d < DT; d++) {
-            const float v = __fsub_rn(x[d], c[d]);
-            s = __fmaf_rn(v, v, s);
-        }
-    } else {
-        const int body = D & ~3;
-        for (int d = 0; d < body; d++) {
-            const float v = __fsub_rn(x[d], c[d]);
-            s = __fadd_rn(s, __fmul_rn(v, v));
-        }
-        for (int d = body; d < D; d++) {
-            const float v = __fsub_rn(x[d], c[d]);
-            s = __fmaf_rn(v, v, s);
-        }
-    }
-    return s;
-}
 
 // One thread per point, centroids broadcast from shared memory.
 template <int DT>
@@ -475,14 +448,25 @@ int assign_exact_launch(ibcu_ctx* ctx, const float* X, long N, int D, const floa
 
 }  // namespace
 
+int ibcu_kmeans_assign_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist);   // kmeans_tc.cu
+
+extern "C" void ibcu_kmeans_set_path(ibcu_ctx* ctx, int path) { if (ctx) ctx->kmeans_path = path; }
+
 extern "C" int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, const float* C, int K,
                                   int32_t* idx, float* dist) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, X && C && idx, "ibcu_kmeans_assign: null pointer");
     IBCU_REQUIRE(ctx, N > 0 && D >= 1 && D <= KM_MAX_D && K >= 1 && K <= 1024, "ibcu_kmeans_assign: N=%ld D=%d K=%d out of range", N, D, K);
     IBCU_REQUIRE(ctx, (size_t)K * D * sizeof(float) <= 128 * 1024, "ibcu_kmeans_assign: K*D=%d too large", K * D);
-    static const int no_filter = getenv("IBCU_KMEANS_EXACT_ONLY") != nullptr;
-    if (D == 8 && K % 8 == 0 && K >= 8 && !no_filter && ((uintptr_t)X & 15) == 0) {
+    // D == 8: scores on the tensor cores as a filter, exact re-evaluation of the candidates. The tcgen05 kernel takes
+    // K a multiple of 32 up to 256; other multiples of 8 take the register-operand (mma.sync) filter.
+    if (D == 8 && ctx->kmeans_path != IBCU_KMEANS_EXACT && ((uintptr_t)X & 15) == 0) {
+        if (ctx->kmeans_path != IBCU_KMEANS_MMA_SYNC) {
+            const int rc = ibcu_kmeans_assign_tc(ctx, X, N, C, K, idx, dist);
+            if (rc != IBCU_ERR_STATE) return rc;
+        }
+    }
+    if (D == 8 && K % 8 == 0 && K >= 8 && ctx->kmeans_path != IBCU_KMEANS_EXACT && ((uintptr_t)X & 15) == 0) {
         const size_t smem = ((size_t)K * 16 + K + (size_t)K * 8 + 4) * sizeof(float);
         if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_filter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         long tiles = (N + 15) / 16;

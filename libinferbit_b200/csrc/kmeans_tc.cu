@@ -1,0 +1,393 @@
+// k-means assignment for D == 8 on the fifth-generation tensor cores (tcgen05.mma, accumulators in TMEM).
+//
+// Scores s_k = x.c_k - |c_k|^2 / 2 (the nearest centroid maximises s_k) for a tile of 128 points against up to
+// 256 centroids are one accumulator tile in tensor memory. x and c are split into two TF32 terms each
+// (x = xh + xl, c = ch + cl); one tile is four tcgen05.mma steps of K = 8:
+//     xh.ch  +  xl.ch  +  xh.cl  +  [1 1 1 0 0 0 0 0] . [nh0 nh1 nh2 0 0 0 0 0]
+// where nh0 + nh1 + nh2 = -|c|^2 / 2 split into three TF32 terms, so the bias rides in the contraction.
+// Operands sit in shared memory in the canonical K-major layout without swizzle (8 rows x 16 bytes core
+// matrices); the centroid operand is built once per block, the point operand per tile by a loader warp
+// (cp.async ring of raw tiles, converted to the two TF32 terms). One thread issues the MMAs; two
+// accumulator tiles (2 x 256 of the 512 TMEM columns) alternate, so the tensor cores fill one while eight
+// epilogue warps drain the other with tcgen05.ld (32x32b: a thread owns one point, i.e. one row).
+//
+// The scores only FILTER. A thread reduces its row to the best and second-best maxima over groups of 8
+// centroids (three-input max). If the best group leads by more than 2^-14 (|x|^2 + max |c|^2) - far above
+// the error of the split product and of the reference's own FP32 distances - the reference's nearest
+// centroid lies in that group, and its 8 centroids are evaluated in the reference binary's exact order and
+// rounding, lowest index winning ties. Otherwise (near ties, NaN, Inf) the warp evaluates all centroids in
+// that exact form. Codes and distances are therefore bit-identical to the reference, as with the other
+// assignment kernels.
+//
+// Every wait (mbarrier) is bounded: when one runs out the block raises a flag in shared memory, every role
+// leaves its loop, tensor memory is released and a host-visible error word is set; nothing spins for ever.
+#include "common.cuh"
+#include "kmeans_ref.cuh"
+
+namespace {
+
+constexpr int TC_TILE = 128;                 // points per accumulator tile
+constexpr int TC_STAGES = 4;                 // raw / operand tiles in flight
+constexpr int TC_EPI_WARPS = 8;              // warps 0..7 drain accumulators; warp 8 loads points; warp 9 issues MMAs
+constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
+constexpr int TC_A_CHUNK = 16 * 128;         // one 16-byte K chunk of 128 rows: 16 core matrices of 128 bytes
+constexpr int TC_A_STAGE = 4 * TC_A_CHUNK;   // xh (two chunks), xl (two chunks)
+constexpr int TC_RAW_STAGE = TC_TILE * 32;   // 128 points x 8 floats
+constexpr long TC_SPIN_LIMIT = 1L << 22;     // tries of a wait before the block gives up (each try can itself block for a while)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t tf32_of(float v) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v)); return r; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when the block is giving up (this wait ran out, or another role's did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (long it = 0; it < TC_SPIN_LIMIT; it++) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = code;
+    return false;
+}
+
+// shared-memory matrix descriptor: K-major, no swizzle; lbo = bytes between the two 16-byte K chunks of a step,
+// sbo = bytes between groups of 8 rows; bits 46-47 = 1 (descriptor version of this architecture)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) { float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r; }
+
+// two FP32 lanes per instruction (round to nearest, each lane rounded like the scalar operation)
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) { unsigned long long r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+
+constexpr int TC_GROUP_STRIDE = 64 + 4;      // floats per group of 8 centroids in the group table: the 4-float skew spreads groups over the banks
+
+struct TcShared {
+    unsigned long long full_a[TC_STAGES], empty_a[TC_STAGES];     // loader -> MMA, MMA -> loader
+    unsigned long long full_acc[2], empty_acc[2];                  // MMA -> epilogue, epilogue -> MMA
+    unsigned long long drained;                                    // every MMA of the block has completed
+    uint32_t tmem_base;
+    int abort_flag;
+    unsigned cmax2_bits;
+};
+
+__device__ __forceinline__ void tmem_wait_ld(uint32_t* r) {
+    // the registers of the load are operands of the wait, so that nothing reads them ahead of it
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
+
+// best and second-best of the maxima over groups of 8 scores; g1 = index of the best group
+__device__ __forceinline__ void top2_groups(const uint32_t* r, int gid0, float& m1, float& m2, int& g1) {
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const float* v = reinterpret_cast<const float*>(r) + 8 * q;
+        float g = max3(v[0], v[1], v[2]);
+        g = max3(g, v[3], v[4]);
+        g = max3(g, v[5], v[6]);
+        g = fmaxf(g, v[7]);
+        m2 = fmaxf(m2, fminf(m1, g));
+        g1 = g > m1 ? gid0 + q : g1;
+        m1 = fmaxf(m1, g);
+    }
+}
+
+// Dynamic shared memory: centroid operand [ch | cl | bias][2 chunks][K rows x 16 B] | constant point chunk pair
+// (1 1 1 0 / 0 0 0 0 per row) | TC_STAGES point operands (xh, xl) | TC_STAGES raw point tiles | exact centroids [K][8] |
+// the same centroids by group [K/8][8 dims][8] | TcShared
+__global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* __restrict__ X, long N, const float* __restrict__ C, int K,
+                                                                  int32_t* __restrict__ idx, float* __restrict__ dist, int* __restrict__ err) {
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t b_chunk = (uint32_t)K * 16u, b_piece = 2u * b_chunk;
+    unsigned char* sB = tc_smem;
+    unsigned char* sAug = sB + 3 * b_piece;
+    unsigned char* sA = sAug + 2 * TC_A_CHUNK;
+    unsigned char* sRaw = sA + TC_STAGES * TC_A_STAGE;
+    float* cex = reinterpret_cast<float*>(sRaw + TC_STAGES * TC_RAW_STAGE);     // [K][8] as given
+    float* cgrp = cex + (size_t)K * 8;                                           // [K / 8 groups][8 dims][8 centroids], groups TC_GROUP_STRIDE apart
+    TcShared* sh = reinterpret_cast<TcShared*>(cgrp + (size_t)(K / 8) * TC_GROUP_STRIDE);
+    volatile int* abort_flag = &sh->abort_flag;
+    pdl_launch_dependents();
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(smem_u32(&sh->full_a[s]), 1); mbar_init(smem_u32(&sh->empty_a[s]), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&sh->full_acc[b]), 1); mbar_init(smem_u32(&sh->empty_acc[b]), 4); }
+        mbar_init(smem_u32(&sh->drained), 1);
+        sh->abort_flag = 0;
+        sh->cmax2_bits = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_EPI_WARPS + 1) {          // all 512 columns of tensor memory: two accumulator tiles of up to 256 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pdl_wait();
+
+    // ── centroids: exact copy, the three operand pieces, max |c|^2 ──
+    for (int e = tid; e < K * 8; e += TC_THREADS) {
+        const float c = C[e];
+        const int k = e >> 3, d = e & 7;
+        cex[e] = c;
+        cgrp[(k >> 3) * TC_GROUP_STRIDE + d * 8 + (k & 7)] = c;
+    }
+    for (int e = tid; e < 128; e += TC_THREADS) {             // constant chunk pair of the point operand: row e = (1 1 1 0 | 0 0 0 0)
+        const uint32_t one = tf32_of(1.0f);
+        *reinterpret_cast<uint4*>(sAug + (e >> 3) * 128 + (e & 7) * 16) = make_uint4(one, one, one, 0u);
+        *reinterpret_cast<uint4*>(sAug + TC_A_CHUNK + (e >> 3) * 128 + (e & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    unsigned cm_bits = 0u;
+    for (int n = tid; n < K; n += TC_THREADS) {
+        uint32_t h[8], l[8];
+        float nn = 0.0f;
+#pragma unroll
+        for (int d = 0; d < 8; d++) {
+            const float c = cex[n * 8 + d];
+            h[d] = tf32_of(c);
+            l[d] = tf32_of(c - __uint_as_float(h[d]));
+            nn = fmaf(c, c, nn);
+        }
+        cm_bits = max(cm_bits, __float_as_uint(nn));         // nn >= 0 or NaN: NaN and Inf sort above everything finite
+        const float nh = -0.5f * nn;
+        const uint32_t n0 = tf32_of(nh);
+        const float r1 = nh - __uint_as_float(n0);
+        const uint32_t n1 = tf32_of(r1);
+        const uint32_t n2 = tf32_of(r1 - __uint_as_float(n1));
+        const uint32_t row = (uint32_t)(n >> 3) * 128u + (uint32_t)(n & 7) * 16u;
+        *reinterpret_cast<uint4*>(sB + row) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(sB + b_chunk + row) = make_uint4(h[4], h[5], h[6], h[7]);
+        *reinterpret_cast<uint4*>(sB + b_piece + row) = make_uint4(l[0], l[1], l[2], l[3]);
+        *reinterpret_cast<uint4*>(sB + b_piece + b_chunk + row) = make_uint4(l[4], l[5], l[6], l[7]);
+        *reinterpret_cast<uint4*>(sB + 2 * b_piece + row) = make_uint4(n0, n1, n2, 0u);
+        *reinterpret_cast<uint4*>(sB + 2 * b_piece + b_chunk + row) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    cm_bits = __reduce_max_sync(0xffffffffu, cm_bits);
+    if (lane == 0) atomicMax(&sh->cmax2_bits, cm_bits);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the operands written above are read by the tensor cores
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sh->tmem_base;
+    const float cm2 = __uint_as_float(sh->cmax2_bits);
+
+    const long ntile = (N + TC_TILE - 1) / TC_TILE;
+    const long n_my = (long)blockIdx.x < ntile ? (ntile - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;      // tiles blockIdx.x + i gridDim.x
+
+    if (warp == TC_EPI_WARPS) {
+        // ── loader: raw tiles by cp.async (TC_STAGES - 1 ahead), then the two TF32 terms into the operand stage ──
+        auto issue = [&](long i) {
+            if (i < n_my) {
+                const long p0 = (blockIdx.x + i * gridDim.x) * TC_TILE;
+                const uint32_t dst = smem_u32(sRaw + (i % TC_STAGES) * TC_RAW_STAGE);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int e = lane + 32 * j;                     // 16-byte piece e of the tile: point e / 2, half e % 2
+                    const long pt = p0 + (e >> 1);
+                    const int nbytes = pt < N ? 16 : 0;              // points past the end read as zeros
+                    const float* src = X + (pt < N ? pt : 0) * 8 + (e & 1) * 4;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst + e * 16), "l"(src), "r"(nbytes) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        for (int i = 0; i < TC_STAGES - 1; i++) issue(i);
+        for (long i = 0; i < n_my; i++) {
+            const int s = (int)(i % TC_STAGES);
+            __syncwarp();                                            // the raw stage about to be refilled has been read by every lane
+            issue(i + TC_STAGES - 1);
+            asm volatile("cp.async.wait_group %0;" :: "n"(TC_STAGES - 1) : "memory");
+            __syncwarp();
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_a[s]), (uint32_t)(((i / TC_STAGES) & 1) ^ 1), abort_flag, 1))) break;   // the whole warp leaves or stays
+            const unsigned char* raw = sRaw + s * TC_RAW_STAGE;
+            unsigned char* dstA = sA + s * TC_A_STAGE;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int r = lane + 32 * j;
+                const float4 a = *reinterpret_cast<const float4*>(raw + r * 32), c = *reinterpret_cast<const float4*>(raw + r * 32 + 16);
+                const float v[8] = { a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w };
+                uint32_t h[8], l[8];
+#pragma unroll
+                for (int d = 0; d < 8; d++) { h[d] = tf32_of(v[d]); l[d] = tf32_of(v[d] - __uint_as_float(h[d])); }
+                const uint32_t row = (uint32_t)(r >> 3) * 128u + (uint32_t)(r & 7) * 16u;
+                *reinterpret_cast<uint4*>(dstA + row) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(dstA + TC_A_CHUNK + row) = make_uint4(h[4], h[5], h[6], h[7]);
+                *reinterpret_cast<uint4*>(dstA + 2 * TC_A_CHUNK + row) = make_uint4(l[0], l[1], l[2], l[3]);
+                *reinterpret_cast<uint4*>(dstA + 3 * TC_A_CHUNK + row) = make_uint4(l[4], l[5], l[6], l[7]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[s]));
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (warp == TC_EPI_WARPS + 1) {
+        // ── MMA issue: one thread ──
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(K >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
+            const uint64_t b_h = smem_desc(smem_u32(sB), b_chunk, 128), b_l = smem_desc(smem_u32(sB + b_piece), b_chunk, 128);
+            const uint64_t b_n = smem_desc(smem_u32(sB + 2 * b_piece), b_chunk, 128), a_one = smem_desc(smem_u32(sAug), TC_A_CHUNK, 128);
+            bool ok = true;
+            for (long i = 0; i < n_my && ok; i++) {
+                const int s = (int)(i % TC_STAGES), b = (int)(i & 1);
+                ok = mbar_wait(smem_u32(&sh->full_a[s]), (uint32_t)((i / TC_STAGES) & 1), abort_flag, 2) &&
+                     mbar_wait(smem_u32(&sh->empty_acc[b]), (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, 3);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem_base + (uint32_t)b * 256u;
+                const uint64_t a_h = smem_desc(smem_u32(sA + s * TC_A_STAGE), TC_A_CHUNK, 128);
+                const uint64_t a_l = smem_desc(smem_u32(sA + s * TC_A_STAGE + 2 * TC_A_CHUNK), TC_A_CHUNK, 128);
+                mma_tf32_ss(d, a_h, b_h, idesc, 0u);
+                mma_tf32_ss(d, a_l, b_h, idesc, 1u);
+                mma_tf32_ss(d, a_h, b_l, idesc, 1u);
+                mma_tf32_ss(d, a_one, b_n, idesc, 1u);
+                mma_commit(smem_u32(&sh->empty_a[s]));               // the operand stage is free once these MMAs have read it
+                mma_commit(smem_u32(&sh->full_acc[b]));              // and the accumulator tile is complete
+            }
+            mma_commit(smem_u32(&sh->drained));
+            mbar_wait(smem_u32(&sh->drained), 0u, abort_flag, 4);    // nothing of this block is left in the tensor pipe
+        }
+    } else {
+        // ── epilogue: warp w drains accumulator tile w / 4, rows 32 (w % 4) .. + 31 ──
+        const int b = warp >> 2, q = warp & 3;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)b * 256u;
+        for (long i = b; i < n_my; i += 2) {
+            const long row = (blockIdx.x + i * gridDim.x) * TC_TILE + q * 32 + lane;
+            const bool have = row < N;
+            float xr[8];
+            {
+                const float4 u = have ? *reinterpret_cast<const float4*>(X + row * 8) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 v = have ? *reinterpret_cast<const float4*>(X + row * 8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xr[0] = u.x; xr[1] = u.y; xr[2] = u.z; xr[3] = u.w; xr[4] = v.x; xr[5] = v.y; xr[6] = v.z; xr[7] = v.w;
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_acc[b]), (uint32_t)((i >> 1) & 1), abort_flag, 5))) break;            // the whole warp leaves or stays
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float m1 = -INFINITY, m2 = -INFINITY;
+            int g1 = 0;
+            uint32_t ra[32], rb[32];
+            tmem_ld32(taddr, ra);
+            for (int c0 = 0; c0 < K; c0 += 64) {
+                tmem_wait_ld(ra);
+                if (c0 + 32 < K) tmem_ld32(taddr + c0 + 32, rb);
+                top2_groups(ra, c0 >> 3, m1, m2, g1);
+                if (c0 + 32 < K) {
+                    tmem_wait_ld(rb);
+                    if (c0 + 64 < K) tmem_ld32(taddr + c0 + 64, ra);
+                    top2_groups(rb, (c0 >> 3) + 4, m1, m2, g1);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->empty_acc[b]));  // the tensor cores may overwrite this tile
+            // the margin that makes the filter safe: false for NaN / Inf as well
+            float xn = 0.0f;
+#pragma unroll
+            for (int d = 0; d < 8; d++) xn = fmaf(xr[d], xr[d], xn);
+            const bool sure = (m1 - m2) > 6.103515625e-5f * (xn + cm2);
+            // the best group in the exact form (subtract, multiply, add, each rounded, in dimension order), then ascending
+            // with strict '<': the lowest index wins ties as in the reference
+            int win = g1 * 8;
+            float best;
+            {
+                const float* cg = cgrp + g1 * TC_GROUP_STRIDE;
+                // subtract and multiply go two centroids at a time; the add stays scalar, because the assembler contracts
+                // a packed multiply followed by a packed add into a fused multiply-add, which rounds differently
+                float dk[8] = { 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+                for (int d = 0; d < 8; d++) {
+                    const ulonglong2 ca = *reinterpret_cast<const ulonglong2*>(cg + d * 8), cb = *reinterpret_cast<const ulonglong2*>(cg + d * 8 + 4);
+                    const unsigned long long xx = pack2(xr[d], xr[d]);
+                    const unsigned long long c2[4] = { ca.x, ca.y, cb.x, cb.y };
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const unsigned long long v = sub2(xx, c2[j]);
+                        float m0, m1;
+                        unpack2(mul2(v, v), m0, m1);
+                        dk[2 * j] = __fadd_rn(dk[2 * j], m0);
+                        dk[2 * j + 1] = __fadd_rn(dk[2 * j + 1], m1);
+                    }
+                }
+                best = dk[0];
+#pragma unroll
+                for (int j = 1; j < 8; j++) if (dk[j] < best) { best = dk[j]; win = g1 * 8 + j; }
+            }
+            // rows the filter could not decide: the whole warp evaluates all centroids exactly
+            unsigned todo = __ballot_sync(0xffffffffu, have && !sure);
+            while (todo) {
+                const int rl = __ffs(todo) - 1;
+                todo &= todo - 1;
+                float xq[8];
+#pragma unroll
+                for (int d = 0; d < 8; d++) xq[d] = __shfl_sync(0xffffffffu, xr[d], rl);
+                float bd = INFINITY; int bk = 0x7fffffff;
+                for (int k = lane; k < K; k += 32) {
+                    const float dk = ref_sqdist<8>(xq, cex + k * 8, 8);
+                    if (dk < bd) { bd = dk; bk = k; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {                   // lexicographic (distance, index) minimum
+                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                    const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+                    if (od < bd || (od == bd && ok < bk)) { bd = od; bk = ok; }
+                }
+                if (lane == rl) {
+                    if (bk == 0x7fffffff) { bk = 0; bd = ref_sqdist<8>(xr, cex, 8); }      // every distance NaN: centroid 0 (the reference's seed)
+                    win = bk; best = bd;
+                }
+            }
+            if (have) { idx[row] = win; if (dist) dist[row] = best; }
+        }
+    }
+    // ── teardown: every role is out of its loop (all waits are bounded); release tensor memory ──
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == TC_EPI_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512u) : "memory");
+    }
+    if (tid == 0 && sh->abort_flag) *err = 100 + sh->abort_flag;
+}
+
+}  // namespace
+
+// D == 8, K a multiple of 32 up to 256, 16-byte aligned X: the tensor-memory kernel. Returns IBCU_ERR_STATE without
+// touching the context's error when the shape is not its own (the caller takes another kernel).
+int ibcu_kmeans_assign_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist) {
+    if (K < 32 || K > 256 || (K & 31) || ((uintptr_t)X & 15)) return IBCU_ERR_STATE;
+    const size_t smem = 1024 + (size_t)3 * 2 * K * 16 + 2 * TC_A_CHUNK + (size_t)TC_STAGES * (TC_A_STAGE + TC_RAW_STAGE) + (size_t)K * 8 * sizeof(float) + (size_t)(K / 8) * TC_GROUP_STRIDE * sizeof(float) + sizeof(TcShared) + 64;
+    IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const long ntile = (N + TC_TILE - 1) / TC_TILE;
+    long blocks = ntile < ctx->sm_count ? ntile : ctx->sm_count;
+    if (blocks < 1) blocks = 1;
+    return ibcu_launch(ctx, assign_tc_kernel, dim3((unsigned)blocks), dim3(TC_THREADS), smem, 1, true, X, N, C, K, idx, dist, ctx->kern_err);
+}
