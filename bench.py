@@ -81,23 +81,41 @@ class ClockSampler:
 
 
 # ── CPU baseline: the reference's own kernels when its library was built, else this repo's port ──
+def _time_calls(fn, budget_s=2.0, min_reps=2, max_reps=50):
+    """best of repeated calls (the reference's own benches report the minimum, tests/bench_pq_decode.c:74-108)"""
+    fn()
+    best, reps, t_all = 1e30, 0, time.perf_counter()
+    while reps < min_reps or (reps < max_reps and time.perf_counter() - t_all < budget_s):
+        t0 = time.perf_counter(); fn(); best = min(best, time.perf_counter() - t0); reps += 1
+    return best, reps
+
+
 class CpuBaseline:
     def __init__(self):
         ref = os.path.join(ROOT, "oracle", "_ref", "libinferbit_ref.so")
         self.threads = os.cpu_count() or 1
         if os.path.exists(ref):
             self.kind, self.lib = "reference", C.CDLL(ref)
-            self.lib.ib_detect_simd.restype = C.c_int
-            self.lib.ib_init_kernels(self.lib.ib_detect_simd())          # AVX2 table on x86-64
-            self.lib.ib_pool_create.restype = C.c_void_p
-            self.lib.ib_pool_create.argtypes = [C.c_int]
-            self.pool = self.lib.ib_pool_create(self.threads)
-            self.lib.ib_parallel_matmul.argtypes = [C.c_void_p] * 5 + [C.c_int] * 3
+            L = self.lib
+            L.ib_detect_simd.restype = C.c_int
+            L.ib_init_kernels(L.ib_detect_simd())          # AVX2 table on x86-64
+            L.ib_pool_create.restype = C.c_void_p
+            L.ib_pool_create.argtypes = [C.c_int]
+            self.pool = L.ib_pool_create(self.threads)
+            L.ib_parallel_matmul.argtypes = [C.c_void_p] * 5 + [C.c_int] * 3
+            L.ib_parallel_matmul_int8_batch.argtypes = [C.c_void_p] * 5 + [C.c_int] * 3
+            L.ib_kmeans_assign.restype = C.c_int
+            L.ib_kmeans_assign.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+            L.ib_pq_matmul_fp32_threaded.restype = C.c_int
+            L.ib_pq_matmul_fp32_threaded.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         else:
             port = os.path.join(ROOT, "oracle", "libib_oracle.so")
             if not os.path.exists(port):
                 subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "oracle"], check=True)
             self.kind, self.lib, self.threads = "port", C.CDLL(port), 1
+
+    def _base(self, value, unit, sample):
+        return {"value": value, "unit": unit, "cores": self.threads, "kind": self.kind, "sample": sample}
 
     def matvec_int8(self, out, w, s32, x, M, N):
         if self.kind == "reference":
@@ -124,6 +142,116 @@ class CpuBaseline:
         dt = (time.perf_counter() - t0) / steps
         return dt, STEP_BYTES / dt / 1e9
 
+    # the secondary configurations: the reference's own entry point for each, on its pool with every host thread
+    def linear(self, bits, M, N, B, algo_bytes):
+        rng = np.random.default_rng(1)
+        w = rng.integers(0, 256, (M, N if bits == 8 else N // 2), dtype=np.uint8)
+        s = rng.uniform(0.002, 0.02, M).astype(np.float32)
+        x = rng.standard_normal((B, N)).astype(np.float32)
+        out = np.empty((B, M), np.float32)
+        L, p = self.lib, lambda a: a.ctypes.data
+        if self.kind != "reference":
+            fn = (lambda: L.ibo_matmul_int8(p(out), p(w), p(s), p(x), M, N)) if bits == 8 else (lambda: L.ibo_matmul_int4(p(out), p(w), p(s), p(x), M, N))
+            t, reps = _time_calls(fn, 1.0)
+            return self._base(algo_bytes / (t * B) / 1e9, "GB/s", f"best of {reps} single-activation calls of the scalar port, scaled to batch {B}")
+        single = lambda: [L.ib_parallel_matmul(self.pool, p(out) + 4 * b * M, p(w), p(s), p(x) + 4 * b * N, M, N, bits) for b in range(B)]
+        t, reps = _time_calls(single, 1.5)
+        r = self._base(algo_bytes / t / 1e9, "GB/s", f"best of {reps}: ib_parallel_matmul x {B} (bits {bits}; the AVX2 table has no batched kernel, so this is what forward.c runs per position)")
+        if bits == 8 and B > 1:
+            t2, reps2 = _time_calls(lambda: L.ib_parallel_matmul_int8_batch(self.pool, p(out), p(w), p(s), p(x), M, N, B), 1.5)
+            r["int8_batch_entry_GBps"] = algo_bytes / t2 / 1e9
+            r["sample"] += f"; ib_parallel_matmul_int8_batch (scalar on x86-64): best of {reps2}"
+        return r
+
+    def pq(self, M, N, G, K, B, algo_bytes):
+        if self.kind != "reference":
+            return None
+        sys.path.insert(0, ROOT)
+        from tests import _cpu
+        rng = np.random.default_rng(3)
+        cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, B, scale_one=True)
+        t = _cpu.RefPqTensor()
+        t.M, t.N, t.G, t.K, t.K_l2, t.n_levels, t.rotate, t.n_outlier, t.format = M, N, G, K, 0, 1, 0, 0, 0
+        t.codebook_l1_l, t.codebook_l1_r = cb_l.ctypes.data, cb_r.ctypes.data
+        t.indices_l1_l, t.indices_l1_r = il.ctypes.data, ir.ctypes.data
+        t.C, t.l2_idx_bytes, t.row_scale = N // G, 1, rs.ctypes.data
+        out = np.empty((B, M), np.float32)
+        fn = lambda: [self.lib.ib_pq_matmul_fp32_threaded(C.byref(t), x.ctypes.data + 4 * b * N, out.ctypes.data + 4 * b * M, self.pool) for b in range(B)]
+        tt, reps = _time_calls(fn, 1.5)
+        return self._base(algo_bytes / tt / 1e9, "GB/s", f"best of {reps}: ib_pq_matmul_fp32_threaded x {B}")
+
+    def kmeans_assign(self, N, D, K):
+        if self.kind != "reference":
+            return None
+        rng = np.random.default_rng(1234)
+        X = (rng.standard_normal((N, D)) * 0.02).astype(np.float32)
+        Cn = X[:K].copy()
+        idx = np.empty(N, np.int32)
+        tt, reps = _time_calls(lambda: self.lib.ib_kmeans_assign(X.ctypes.data, N, D, Cn.ctypes.data, K, idx.ctypes.data, self.pool), 2.0, 2, 5)
+        return self._base(N / tt / 1e6, "Mpoints/s", f"best of {reps}: ib_kmeans_assign on {N} points with the pool (the assignment is all but the whole of an iteration; "
+                          "the reference's update loop sits inside ib_kmeans_fit, which cannot take initial centroids)")
+
+    def decode(self, B):
+        """tokens/s of the reference's own inferbit_forward (B == 1) / ib_forward_positions (B > 1) on 7B-shape IBF-v1 files
+        of one and of two layers, extrapolated to 32 layers: t32 = t1 + 31 (t2 - t1). IB_W4A8=0 is set at process start."""
+        if self.kind != "reference":
+            return None
+        import tempfile
+        sys.path.insert(0, ROOT)
+        from oracle import ibf_writer
+        L = self.lib
+        L.inferbit_config_create.restype = C.c_void_p
+        L.inferbit_config_set_threads.argtypes = [C.c_void_p, C.c_int]
+        L.inferbit_load.restype = C.c_void_p; L.inferbit_load.argtypes = [C.c_char_p, C.c_void_p]
+        L.inferbit_free.argtypes = [C.c_void_p]
+        L.inferbit_forward.restype = C.c_int; L.inferbit_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+        L.ib_forward_positions.restype = C.c_int; L.ib_forward_positions.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.inferbit_kv_clear.argtypes = [C.c_void_p]
+        H, I, V, kv = 4096, 14336, 32000, 1024
+        rng = np.random.default_rng(7)
+        f16 = lambda a: np.asarray(a, np.float32).astype(np.float16).view(np.uint16)
+
+        def lin(M, N, bits):
+            w = rng.integers(0, 256, (M, N if bits == 8 else N // 2), dtype=np.uint8)
+            lo = 0.001 if bits == 8 else 0.002
+            return (w.view(np.int8) if bits == 8 else w), f16(rng.uniform(lo * 0.05, lo * 0.5, M)), M, N, bits
+        shapes = [(H, H, 8), (kv, H, 8), (kv, H, 8), (H, H, 8), (I, H, 4), (I, H, 4), (H, I, 4)]
+        layers = [([lin(*sh) for sh in shapes], (f16(rng.uniform(0.9, 1.1, H)), f16(rng.uniform(0.9, 1.1, H)))) for _ in range(2)]
+        head = lin(V, H, 8)
+        emb = (rng.integers(-127, 128, (V, H), dtype=np.int8), f16(rng.uniform(0.001, 0.01, V)), f16(rng.uniform(0.9, 1.1, H)))
+        times = []
+        with tempfile.TemporaryDirectory() as d:
+            for nl in (1, 2):
+                cfg = dict(hidden=H, inter=I, n_layers=nl, n_heads=32, n_kv_heads=8, head_dim=128, vocab=V, max_ctx=64, eps=1e-5, theta=10000.0, attn_bits=8, mlp_bits=4)
+                path = os.path.join(d, f"l{nl}.ibf")
+                ibf_writer.write_ibf(path, cfg, layers[:nl], head, emb, name="bench-7b-shape")
+                c = L.inferbit_config_create()
+                L.inferbit_config_set_threads(c, self.threads)
+                m = L.inferbit_load(path.encode(), c)
+                assert m, "reference inferbit_load failed"
+                toks = (np.arange(B, dtype=np.int32) * 7 + 11)
+                logits = np.empty((B, V), np.float32)
+
+                def step():
+                    L.inferbit_kv_clear(m)
+                    if B == 1:
+                        assert L.inferbit_forward(m, toks.ctypes.data, 1, logits.ctypes.data, V) == 0
+                    else:
+                        assert L.ib_forward_positions(m, toks.ctypes.data, B, logits.ctypes.data) == 0
+                tt, reps = _time_calls(step, 1.5, 2, 10)
+                times.append(tt)
+                L.inferbit_free(m)
+        t32 = times[0] + 31 * (times[1] - times[0])
+        return self._base(B / t32, "tok/s", f"inferbit_forward / ib_forward_positions of the unmodified reference on 1- and 2-layer 7B-shape files at positions 0..{B - 1} "
+                          f"({times[0] * 1e3:.1f} / {times[1] * 1e3:.1f} ms per step), extrapolated to 32 layers; attention over 512 cached positions would add under 2 %")
+
+
+def bench_config(n_gpus):
+    """the same dictionary in both arms: what is measured, not how"""
+    return {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1, "bytes_per_step": STEP_BYTES,
+            "l2": "inputs larger than the cache: consecutive steps walk a ring of distinct weight sets",
+            "parallelism": "1 GPU" if n_gpus == 1 else f"rows/{n_gpus} + all-gather"}
+
 
 def run_reference(args, rank):
     if rank != 0:
@@ -134,9 +262,9 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": "int8_matvec_weight_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": max(3, min(args.warmup, 10)), "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 weights x f32 activations, f32 accumulate",
-            "data": "synthetic", "config": {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1},
+            "data": "synthetic", "config": bench_config(args.gpus),
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind,
-                             "sample": f"{steps} steps of q,k,v,o over a ring of 4 host-resident weight sets"},
+                             "sample": f"{steps} steps of q,k,v,o over a ring of 4 host-resident weight sets (168 MB)"},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -166,9 +294,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-other", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--case", default=None, help="run one small secondary case alone (for profiler captures): "
-                    "int8_4096x4096_b1, int8_32000x4096_b1, int4_14336x4096_b1, pq_4096x14336_b1, pq_4096x14336_b8, timeline_int8_4096x4096_b1 (trace build only), kmeans_4Mx8_k256, decode_7b_b1")
+                    "int8_4096x4096_b1, int8_4096x4096_b16, int8_32000x4096_b1, int4_14336x4096_b1, int4_5632x2048_b1, pq_4096x14336_b1, pq_4096x14336_b8, "
+                    "kmeans_4Mx8_k256, decode_7b_b1, decode_7b_b1_eager (launches issued one by one, for per-kernel profiles)")
     args = ap.parse_args()
     rank, world, local, dist = dist_setup(args.gpus)
+    os.environ.setdefault("IB_W4A8", "0")                    # the reference reads it once: INT4 layers on FP32 activations, as configured
     if args.impl == "reference":
         run_reference(args, rank)
         return
@@ -182,7 +312,6 @@ def main():
     ctx = host.ib_b200_ctx()
     if world > 1:
         import torch
-        os.environ["NCCL_DEBUG"] = os.environ.get("IB_NCCL_DEBUG", "WARN")     # keep stdout to the one JSON line
         idbuf = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
             raw = (C.c_ubyte * 128)(); assert lib.ibcu_comm_get_id(raw) == 0
@@ -213,11 +342,13 @@ def main():
             "int8_4096x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 1, reps_target_bytes=300e6),
             "int8_32000x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 1, reps_target_bytes=400e6),
             "int4_14336x4096_b1": lambda: bs._linear_ring(lib, ctx, 4, 14336, 4096, 1, reps_target_bytes=300e6),
-            "timeline_int8_4096x4096_b1": lambda: bs._timeline_linear(lib, ctx, 8, 4096, 4096, 1),
+            "int8_4096x4096_b16": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 16, reps_target_bytes=300e6),
+            "int4_5632x2048_b1": lambda: bs._linear_ring(lib, ctx, 4, 5632, 2048, 1, reps_target_bytes=300e6),
             "pq_4096x14336_b1": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 1),
             "pq_4096x14336_b8": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 8),
             "kmeans_4Mx8_k256": lambda: bs._kmeans(lib, ctx, 0, 1, lambda v: v, sync, iters=2),
-            "decode_7b_b1": lambda: bs._decode(lib, host, ctx, 1, lambda v: v, sync, steps=3),
+            "decode_7b_b1": lambda: bs._decode(lib, host, ctx, 1, 0, 1, lambda v: v, sync, steps=3),
+            "decode_7b_b1_eager": lambda: bs._decode(lib, host, ctx, 1, 0, 1, lambda v: v, sync, steps=3, warm=4, graph=False),
         }
         print(json.dumps({"case": args.case, **cases[args.case]()}), flush=True)
         host.ib_b200_shutdown()
@@ -267,6 +398,18 @@ def main():
     t_step = max_over_ranks(ms.value / K) * 1e-3
     value = STEP_BYTES / t_step / 1e9
     mma_launches_per_step = 2
+    # the same region five more times: how much one event pair scatters (value above is the first, timed as the contract says)
+    repeats = []
+    for _ in range(5):
+        lib.ibcu_event_record(ctx, 4)
+        for _ in range(n_replay):
+            wl.replay(gid)
+        lib.ibcu_event_record(ctx, 5)
+        r_ms = C.c_float()
+        bs.check(lib, ctx, lib.ibcu_event_elapsed_ms(ctx, 4, 5, C.byref(r_ms)))
+        repeats.append(max_over_ranks(r_ms.value / K))
+        barrier()
+    single = wl.matches_single_gpu() if world > 1 else None
     # end to end through the reference-shaped table: host buffers, copies inside the timed region
     e2e = wl.time_table_calls(host, min(K, 300), W)
     e2e_t = max_over_ranks(e2e["t_step"])
@@ -276,9 +419,10 @@ def main():
         "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 weights x int8 limbs of 32-bit fixed-point activations, s32 accumulate (exact); f32 in/out",
         "data": "synthetic",
-        "config": {"workload": "int8_attn_proj_b1", "shapes": "q,o 4096x4096; k,v 1024x4096", "batch": 1,
-                   "bytes_per_step": STEP_BYTES, "l2": f"ring of {RING} distinct weight sets ({RING * STEP_BYTES >> 20} MiB) > L2",
-                   "parallelism": (f"rows/{world} + " + ("NCCL all-gather" if os.environ.get("IB_BENCH_NCCL_ONLY") else "push all-gather over peer memory (NVLink)")) if world > 1 else "1 GPU"},
+        "config": bench_config(world),
+        "timing": {"ring": f"{RING} distinct weight sets ({RING * STEP_BYTES >> 20} MiB) > L2", "steps_per_graph": per_graph,
+                   "transport": ("NCCL all-gather" if os.environ.get("IB_BENCH_NCCL_ONLY") else "push all-gather over peer memory (NVLink)") if world > 1 else None,
+                   "repeat_ms_per_step": repeats, "median_ms_per_step": sorted(repeats)[len(repeats) // 2], "min_ms_per_step": min(repeats)},
         "clocks": clk.summary(),
         "gpu_launches": int(launches_per_graph * n_replay),
         "e2e": {"value": STEP_BYTES / e2e_t / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
@@ -291,13 +435,33 @@ def main():
                              "traffic = DRAM bytes of a step, scaled from the ncu capture of one 4096x4096 launch "
                              "(16.873 MB read + 0 written for 16.777 MB of weights; the 32000x4096 launch gives the same ratio)"},
     }
+    if single is not None:
+        line["matches_single_gpu"] = single
+    cpu = None
     if rank == 0 and world == 1:
         cpu = CpuBaseline()
         dt, gbs = cpu.time_steps(60, 5)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cpu.threads, "kind": cpu.kind,
                                 "sample": "60 steps of q,k,v,o over a ring of 4 host-resident weight sets"}
     if not args.no_other:
-        line["other"] = bs.other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier)
+        other = bs.other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier, peaks)
+        if cpu is not None:
+            # the reference's own entry point for each configuration, timed here on the host cores (a reported baseline)
+            for name, e in other.items():
+                if not isinstance(e, dict):
+                    continue
+                try:
+                    if name.startswith(("int4_", "int8_")):
+                        sh = e["shape"]; e["cpu_baseline"] = cpu.linear(sh["bits"], sh["M"], sh["N"], sh["B"], e["algorithmic_bytes"])
+                    elif name.startswith("pq_"):
+                        sh = e["shape"]; e["cpu_baseline"] = cpu.pq(sh["M"], sh["N"], sh["G"], sh["K"], sh["B"], e["algorithmic_bytes"])
+                    elif name.startswith("kmeans_"):
+                        e["cpu_baseline"] = cpu.kmeans_assign(e["points"], e["D"], e["K"])
+                    elif name.startswith("decode_7b_b") and "nccl" not in name:
+                        e["cpu_baseline"] = cpu.decode(e["batch"])
+                except Exception as ex:                        # a baseline that cannot be taken must not cost the GPU numbers
+                    e["cpu_baseline"] = {"error": repr(ex)[:200]}
+        line["other"] = other
     wl.close()
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -194,7 +194,7 @@ size_t ibcu_pq_noalloc_max_floats(void);
 int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, const float* C, int K,
                        int32_t* idx, float* dist);
 /* Which assignment kernel ibcu_kmeans_assign may take; every one gives the same codes and distances. For tests
- * and comparisons: AUTO = the fastest the shape allows (D == 8: tcgen05 tensor-core filter for K a multiple of 32
+ * and comparisons: AUTO = the fastest the shape allows (D == 8: tcgen05 tensor-core filter for K a multiple of 64
  * up to 256, else the mma.sync filter for K a multiple of 8; other shapes the exact kernel). */
 #define IBCU_KMEANS_AUTO     0
 #define IBCU_KMEANS_EXACT    1   /* every distance in the exact form on the CUDA cores */

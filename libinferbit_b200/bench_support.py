@@ -99,21 +99,27 @@ class AttnProjWorkload:
         self.dev = Dev(lib, ctx)
         self.N = proj[0][2]
         rng = np.random.default_rng(seed)
-        self.x = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
-        self.x2 = self.dev.upload(rng.standard_normal((B, self.N)).astype(np.float32))
+        self.xh = rng.standard_normal((B, self.N)).astype(np.float32)
+        self.x2h = rng.standard_normal((B, self.N)).astype(np.float32)
+        self.x = self.dev.upload(self.xh)
+        self.x2 = self.dev.upload(self.x2h)
         self.out = {name: self.dev.alloc_gathered(B * M * 4) for name, M, _ in proj}
         self.sets = []
-        s = seed * 977 + rank
-        for r in range(ring):
-            ent = {}
+        self.seeds = []
+        s = seed * 977                                       # a tensor is a function of the seed and its place alone: every rank
+        for r in range(ring):                                # fills its rows with the bytes the whole tensor has there
+            ent, sd = {}, {}
             for name, M, N in proj:
                 r0, rn = shard(lib, M, world, rank)
                 w = self.dev.alloc(rn * N)
                 sc = self.dev.alloc(rn * 2)
-                s += 1; check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, w, rn * N, s))
-                s += 1; check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, sc, rn, s, 0.001, 0.01))
+                s += 2; sd[name] = (s - 1, s)
+                check(lib, ctx, lib.ibcu_fill_hash_bytes_at(ctx, w, rn * N, s - 1, r0 * N))
+                check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform_at(ctx, sc, rn, s, 0.001, 0.01, r0))
                 ent[name] = (w, sc, M, r0, rn)
             self.sets.append(ent)
+            self.seeds.append(sd)
+        self.x_host = None
         check(lib, ctx, lib.ibcu_sync(ctx))
 
     def _desc(self, ent, name):
@@ -133,6 +139,48 @@ class AttnProjWorkload:
         if self.world > 1:
             bufs = (C.c_void_p * 1)(self.out["o"]); Ms = (C.c_int * 1)(ent["o"][2])
             check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 1, self.B, 32))
+
+    def matches_single_gpu(self):
+        """The sharded step against the same step on one GPU: set 0 is run once by all ranks (with its gathers), then rank 0
+        builds the unsharded tensors of set 0 from the same seeds on a context of its own without a communicator, runs
+        q, k, v, o there and compares all four outputs. Returns a dict on rank 0, None elsewhere."""
+        lib = self.lib
+        self.step(0)
+        check(lib, self.ctx, lib.ibcu_sync(self.ctx))
+        if self.rank != 0:
+            return None
+        got = {}
+        for name, M, _ in self.proj:
+            a = np.empty((self.B, M), np.float32)
+            check(lib, self.ctx, lib.ibcu_memcpy_d2h(self.ctx, a.ctypes.data, self.out[name], a.nbytes))
+            got[name] = a
+        check(lib, self.ctx, lib.ibcu_sync(self.ctx))
+        ctx1 = C.c_void_p()
+        dev_id = C.c_int()
+        assert lib.ibcu_ctx_create(self._device(), C.byref(ctx1)) == 0
+        d1 = Dev(lib, ctx1)
+        res = {"max_abs_diff": 0.0, "bit_equal": True, "within_tolerance": True}
+        for name, M, N in self.proj:
+            w = d1.alloc(M * N); sc = d1.alloc(M * 2); o = d1.alloc(self.B * M * 4)
+            sw, ss = self.seeds[0][name]
+            check(lib, ctx1, lib.ibcu_fill_hash_bytes(ctx1, w, M * N, sw))
+            check(lib, ctx1, lib.ibcu_fill_hash_fp16_uniform(ctx1, sc, M, ss, 0.001, 0.01))
+            x = d1.upload(self.xh if name != "o" else self.x2h)
+            t = LinearT(w, sc, o, M, M, 0, 0)
+            check(lib, ctx1, lib.ibcu_linear(ctx1, C.byref(t), 1, x, N, self.B, 8))
+            ref = np.empty((self.B, M), np.float32)
+            check(lib, ctx1, lib.ibcu_memcpy_d2h(ctx1, ref.ctypes.data, o, ref.nbytes))
+            check(lib, ctx1, lib.ibcu_sync(ctx1))
+            diff = np.abs(got[name].astype(np.float64) - ref)
+            res["max_abs_diff"] = max(res["max_abs_diff"], float(diff.max()))
+            res["bit_equal"] = res["bit_equal"] and bool(np.array_equal(got[name], ref))
+            res["within_tolerance"] = res["within_tolerance"] and bool(np.all(diff <= 1e-4 + 1e-3 * np.abs(ref)))
+        d1.free_all()
+        lib.ibcu_ctx_destroy(ctx1)
+        return res
+
+    def _device(self):
+        return int(os.environ.get("LOCAL_RANK", "0"))
 
     def capture(self, n):
         self.step(0)
@@ -218,44 +266,8 @@ def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
     lib.ibcu_graph_destroy(ctx, gid)
     dev.free_all()
     algo = wbytes + 2 * M + 4 * B * N + 4 * B * M
-    return {"us": ms * 1e3, "GBps": algo / ms / 1e6}
-
-
-def _timeline_linear(lib, ctx, bits, M, N, B):
-    """Phase times of back-to-back linear launches from the kernels' own %globaltimer stamps. Needs the
-    library built with `make -C libinferbit_b200 clean all TRACE=1`; a number from that build is a timeline,
-    not a benchmark."""
-    if not hasattr(lib, "ibcu_trace_read"):
-        raise SystemExit("timeline cases need the trace build: make -C libinferbit_b200 clean all TRACE=1")
-    dev = Dev(lib, ctx)
-    rowbytes = N if bits == 8 else N // 2
-    wbytes, R = M * rowbytes, 16
-    dW = dev.alloc(R * wbytes); check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, dW, R * wbytes, 7))
-    dS = dev.alloc(M * 2); check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, dS, M, 8, 0.002, 0.02))
-    dx = dev.upload(np.random.default_rng(0).standard_normal((B, N)).astype(np.float32))
-    do = dev.alloc(B * M * 4)
-    descs = [LinearT(dW + r * wbytes, dS, do, M, M, 0, 0) for r in range(R)]
-
-    def run():
-        for d in descs:
-            check(lib, ctx, lib.ibcu_linear(ctx, C.byref(d), 1, dx, N, B, bits))
-    gid = dev.graph(run)
-    dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
-    buf = np.zeros((16, 512, 8), np.uint64)
-    lib.ibcu_trace_read.argtypes = [C.c_void_p]
-    assert lib.ibcu_trace_read(buf.ctypes.data) == 0
-    t = buf.astype(np.int64)
-    nb = int((t[0, :, 0] > 0).sum())
-    order = np.argsort(t[:, :nb, 0].min(axis=1))
-    base = t[order[0], :nb, 0].min()
-    names = ["start", "prefetch_issued", "wait_done", "x_ready", "loop_done", "end"]
-    out = {"blocks": nb, "unit": "us since the first block of the first launch; min..max over blocks", "launches": []}
-    for j in order:
-        out["launches"].append({names[i]: [round(float((t[j, :nb, i] - base).min()) / 1e3, 2), round(float((t[j, :nb, i] - base).max()) / 1e3, 2)]
-                                for i in range(6)})
-    lib.ibcu_graph_destroy(ctx, gid)
-    dev.free_all()
-    return out
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
+            "shape": {"bits": bits, "M": M, "N": N, "B": B}}
 
 
 def _pq(lib, ctx, M, N, G, K, B):
@@ -289,19 +301,25 @@ def _pq(lib, ctx, M, N, G, K, B):
     lib.ibcu_graph_destroy(ctx, gid)
     dev.free_all()
     algo = 2 * M * Cn + 2 * K * half * 2 + 2 * M + 4 * B * N + 4 * B * M
-    return {"us": ms * 1e3, "GBps": algo / ms / 1e6}
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
+            "shape": {"M": M, "N": N, "G": G, "K": K, "B": B}}
+
+
+def _kmeans_shard(r, world, N_total, D, K, C0):
+    n0 = N_total * r // world; n1 = N_total * (r + 1) // world
+    X = (np.random.default_rng(5000 + r).standard_normal((n1 - n0, D)) * 0.02).astype(np.float32)
+    if r == 0:
+        X[:K] = C0
+    return X
 
 
 def _kmeans(lib, ctx, rank, world, max_over_ranks, barrier, N_total=1 << 22, D=8, K=256, iters=10):
     dev = Dev(lib, ctx)
-    n0 = N_total * rank // world; n1 = N_total * (rank + 1) // world
     rng = np.random.default_rng(1234)
     C0 = (rng.standard_normal((K, D)) * 0.02).astype(np.float32)        # stands for X[:K]; same on every rank
-    X = (np.random.default_rng(5000 + rank).standard_normal((n1 - n0, D)) * 0.02).astype(np.float32)
-    if rank == 0:
-        X[:K] = C0
+    X = _kmeans_shard(rank, world, N_total, D, K, C0)
     dX = dev.upload(X); dC = dev.upload(C0)
-    n = n1 - n0
+    n = len(X)
     di, dd = dev.alloc(n * 4), dev.alloc(n * 4)
     ds, dc, dn = dev.alloc(K * D * 4), dev.alloc(K * 4), dev.alloc(16)
 
@@ -314,51 +332,141 @@ def _kmeans(lib, ctx, rank, world, max_over_ranks, barrier, N_total=1 << 22, D=8
     barrier()
     ms = dev.timed(lambda: [it() for _ in range(iters)])
     ms = max_over_ranks(ms)
+    out = {"ms_per_iter": ms / iters, "Mpoints_per_s": N_total / (ms / iters) / 1e3, "points": N_total, "K": K, "D": D, "iters": iters,
+           "algorithmic_bytes": N_total * D * 4 + N_total * 4 + K * D * 4, "flops": 2 * N_total * K * D, "bound": "tensor"}
+    if world > 1:
+        # one iteration from C0, sharded, against the same iteration of all points on one GPU (rank 0, own context)
+        check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, dC, C0.ctypes.data, C0.nbytes))
+        it()
+        cnt = np.empty(K, np.int32); Cs = np.empty((K, D), np.float32)
+        check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, cnt.ctypes.data, dc, cnt.nbytes))
+        check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, Cs.ctypes.data, dC, Cs.nbytes))
+        barrier()
+        if rank == 0:
+            ctx1 = C.c_void_p()
+            assert lib.ibcu_ctx_create(int(os.environ.get("LOCAL_RANK", "0")), C.byref(ctx1)) == 0
+            d1 = Dev(lib, ctx1)
+            Xall = np.concatenate([_kmeans_shard(r, world, N_total, D, K, C0) for r in range(world)])
+            aX, aC = d1.upload(Xall), d1.upload(C0)
+            ai, ad = d1.alloc(N_total * 4), d1.alloc(N_total * 4)
+            a_s, a_c, a_n = d1.alloc(K * D * 4), d1.alloc(K * 4), d1.alloc(16)
+            check(lib, ctx1, lib.ibcu_kmeans_lloyd_iter(ctx1, aX, N_total, D, aC, K, ai, ad, a_s, a_c, a_n))
+            rc = np.empty(K, np.int32); rC = np.empty((K, D), np.float32)
+            check(lib, ctx1, lib.ibcu_memcpy_d2h(ctx1, rc.ctypes.data, a_c, rc.nbytes))
+            check(lib, ctx1, lib.ibcu_memcpy_d2h(ctx1, rC.ctypes.data, aC, rC.nbytes))
+            check(lib, ctx1, lib.ibcu_sync(ctx1))
+            out["matches_single_gpu"] = {"counts_equal": bool(np.array_equal(cnt, rc)), "max_centroid_diff": float(np.abs(Cs - rC).max()),
+                                         "within_tolerance": bool(np.array_equal(cnt, rc) and np.allclose(Cs, rC, rtol=1e-5, atol=1e-7))}
+            d1.free_all()
+            lib.ibcu_ctx_destroy(ctx1)
+        barrier()
     dev.free_all()
-    return {"ms_per_iter": ms / iters, "Mpoints_per_s": N_total / (ms / iters) / 1e3, "points": N_total, "K": K, "D": D, "iters": iters}
+    return out
 
 
-def _decode(lib, host, ctx, B, max_over_ranks, barrier, steps=20, warm=60):
-    cfg = ModelCfg(4096, 14336, 32, 32, 8, 128, 32000, 1024, 1e-5, 10000.0, 8, 4, 8)
+DECODE_CFG = (4096, 14336, 32, 32, 8, 128, 32000, 1024, 1e-5, 10000.0, 8, 4, 8)
+DECODE_NOTE = ("random weights as the configuration says except that the per-row scales are drawn twenty times below its ranges "
+               "(32 random layers otherwise overflow FP32); KV cache rows 0..511 bell-shaped with unit variance; every step is one "
+               "replay of the same CUDA graph (the position is read on the device) at positions 512, 512 + B, ..., 512 + 7 B in turn")
+
+
+def _decode(lib, host, ctx, B, rank, world, max_over_ranks, barrier, steps=20, warm=60, check_single=True):
+    cfg = ModelCfg(*DECODE_CFG)
     m = host.ib_b200_model_create(ctx, C.byref(cfg))
     if not m:
         return {"error": "model allocation failed"}
     assert host.ib_b200_model_fill_random(m, 4321, 512) == 0
     toks = np.arange(B, dtype=np.int32) * 7 + 11
     check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, host.ib_b200_model_tokens(m), toks.ctypes.data, toks.nbytes))
-    for _ in range(warm):                                  # a fixed count, the same on every rank: clocks up
+    V = cfg.vocab
+    out = {}
+    if world > 1 and check_single:
+        # the sharded model is the one-GPU model: same seed, same step at position 512, logits compared on rank 0
         check(lib, ctx, host.ib_b200_forward_step_device(m, 512, B))
+        got = np.empty((B, V), np.float32)
+        check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, got.ctypes.data, host.ib_b200_model_logits(m), got.nbytes))
+        check(lib, ctx, lib.ibcu_sync(ctx))
+        barrier()
+        if rank == 0:
+            ctx1 = C.c_void_p()
+            assert lib.ibcu_ctx_create(int(os.environ.get("LOCAL_RANK", "0")), C.byref(ctx1)) == 0
+            m1 = host.ib_b200_model_create(ctx1, C.byref(cfg))
+            assert m1 and host.ib_b200_model_fill_random(m1, 4321, 512) == 0
+            check(lib, ctx1, lib.ibcu_memcpy_h2d(ctx1, host.ib_b200_model_tokens(m1), toks.ctypes.data, toks.nbytes))
+            check(lib, ctx1, host.ib_b200_forward_step_device(m1, 512, B))
+            ref = np.empty((B, V), np.float32)
+            check(lib, ctx1, lib.ibcu_memcpy_d2h(ctx1, ref.ctypes.data, host.ib_b200_model_logits(m1), ref.nbytes))
+            check(lib, ctx1, lib.ibcu_sync(ctx1))
+            host.ib_b200_model_free(m1)
+            lib.ibcu_ctx_destroy(ctx1)
+            diff = np.abs(got.astype(np.float64) - ref)
+            out["matches_single_gpu"] = {"max_abs_diff": float(diff.max()), "bit_equal": bool(np.array_equal(got, ref)),
+                                         "within_tolerance": bool(np.all(diff <= 1e-4 + 1e-3 * np.abs(ref)))}
+        barrier()
+    span = 8                                               # positions 512, 512 + B, ... 512 + 7 B, then again
+    pos = lambda i: 512 + (i % span) * B
+    for i in range(warm):                                  # a fixed count, the same on every rank: clocks up
+        check(lib, ctx, host.ib_b200_forward_step_device(m, pos(i), B))
     barrier()
     dev = Dev(lib, ctx)
-    ms = dev.timed(lambda: check(lib, ctx, host.ib_b200_forward_step_device(m, 512, B)), reps=steps)
+    k = [0]
+
+    def one():
+        check(lib, ctx, host.ib_b200_forward_step_device(m, pos(k[0]), B)); k[0] += 1
+    ms = dev.timed(one, reps=steps)
     ms = max_over_ranks(ms)
     logits = np.empty(8, np.float32)
     check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, logits.ctypes.data, host.ib_b200_model_logits(m), 32))
     check(lib, ctx, lib.ibcu_sync(ctx))
     wb = host.ib_b200_model_weight_bytes(m)
     host.ib_b200_model_free(m)
-    return {"ms_per_step": ms, "tok_per_s": B / ms * 1e3, "batch": B, "pos": 512, "weight_GBps_per_gpu": wb / ms / 1e6,
-            "logits_finite": bool(np.isfinite(logits).all()), "logits_head": [float(v) for v in logits]}
+    kv_bytes = 32 * 2 * (512 + B) * 1024 * 4
+    out.update({"ms_per_step": ms, "tok_per_s": B / ms * 1e3, "batch": B, "pos": "512 + B * (step % 8)", "weight_GBps_per_gpu": wb / ms / 1e6,
+                "algorithmic_bytes": int(wb * world + kv_bytes), "bound": "hbm", "logits_finite": bool(np.isfinite(logits).all()),
+                "logits_head": [float(v) for v in logits], "note": DECODE_NOTE})
+    return out
 
 
-def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier):
+def with_roofline(entry, peaks, world=1):
+    """adds achieved / peak / frac to an entry that carries its time and algorithmic bytes (or flops)"""
+    if "algorithmic_bytes" not in entry:
+        return entry
+    t = entry["us"] * 1e-6 if "us" in entry else (entry.get("ms_per_iter", entry.get("ms_per_step", 0.0)) * 1e-3)
+    if t <= 0:
+        return entry
+    gbs = entry["algorithmic_bytes"] / t / 1e9 / world           # per GPU
+    r = {"bound": entry.get("bound", "hbm"), "hbm_achieved_GBps": gbs, "hbm_peak_GBps": peaks["hbm_gbs"], "hbm_frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    if "flops" in entry:
+        tf = entry["flops"] / t / 1e12 / world
+        # TF32 is not among the measured peaks; half of the measured dense bf16 rate is the nominal ratio
+        r.update({"tensor_achieved_TFLOPs": tf, "tensor_peak_TFLOPs": peaks["bf16_tflops"] / 2, "tensor_frac": tf / (peaks["bf16_tflops"] / 2) if peaks["bf16_tflops"] else None,
+                  "tensor_peak_note": "half of the measured dense bf16 GEMM rate (TF32 nominal ratio)"})
+    entry["roofline"] = r
+    return entry
+
+
+def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier, peaks):
     out = {}
     if world == 1:
         out["int4_tinyllama_up_5632x2048_b1"] = _linear_ring(lib, ctx, 4, 5632, 2048, 1)
         out["int4_gate_14336x4096_b1"] = _linear_ring(lib, ctx, 4, 14336, 4096, 1)
         out["int4_down_4096x14336_b1"] = _linear_ring(lib, ctx, 4, 4096, 14336, 1)
+        out["int8_q_4096x4096_b1"] = _linear_ring(lib, ctx, 8, 4096, 4096, 1)
         out["int8_q_4096x4096_b4"] = _linear_ring(lib, ctx, 8, 4096, 4096, 4)
         out["int8_q_4096x4096_b16"] = _linear_ring(lib, ctx, 8, 4096, 4096, 16)
         out["int8_head_32000x4096_b1"] = _linear_ring(lib, ctx, 8, 32000, 4096, 1)
         out["pq_down_4096x14336_b1"] = _pq(lib, ctx, 4096, 14336, 16, 256, 1)
         out["pq_down_4096x14336_b8"] = _pq(lib, ctx, 4096, 14336, 16, 256, 8)
     out["kmeans_4Mx8_k256"] = _kmeans(lib, ctx, rank, world, max_over_ranks, barrier)
-    out["decode_7b_b1"] = _decode(lib, host, ctx, 1, max_over_ranks, barrier)
-    out["decode_7b_b8"] = _decode(lib, host, ctx, 8, max_over_ranks, barrier)
+    out["decode_7b_b1"] = _decode(lib, host, ctx, 1, rank, world, max_over_ranks, barrier)
+    out["decode_7b_b8"] = _decode(lib, host, ctx, 8, rank, world, max_over_ranks, barrier)
     if world > 1:
         # the same step with every gather through NCCL: the logits must be the same bits, only the transport differs
         lib.ibcu_window_enable(ctx, 0)
-        out["decode_7b_b1_nccl_gathers"] = _decode(lib, host, ctx, 1, max_over_ranks, barrier)
+        out["decode_7b_b1_nccl_gathers"] = _decode(lib, host, ctx, 1, rank, world, max_over_ranks, barrier, check_single=False)
         lib.ibcu_window_enable(ctx, 1)
         out["push_gather_matches_nccl"] = out["decode_7b_b1"]["logits_head"] == out["decode_7b_b1_nccl_gathers"]["logits_head"]
+    for k, v in out.items():
+        if isinstance(v, dict):
+            with_roofline(v, peaks, world)
     return out

@@ -459,7 +459,7 @@ extern "C" int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, 
     IBCU_REQUIRE(ctx, N > 0 && D >= 1 && D <= KM_MAX_D && K >= 1 && K <= 1024, "ibcu_kmeans_assign: N=%ld D=%d K=%d out of range", N, D, K);
     IBCU_REQUIRE(ctx, (size_t)K * D * sizeof(float) <= 128 * 1024, "ibcu_kmeans_assign: K*D=%d too large", K * D);
     // D == 8: scores on the tensor cores as a filter, exact re-evaluation of the candidates. The tcgen05 kernel takes
-    // K a multiple of 32 up to 256; other multiples of 8 take the register-operand (mma.sync) filter.
+    // K a multiple of 64 up to 256; other multiples of 8 take the register-operand (mma.sync) filter.
     if (D == 8 && ctx->kmeans_path != IBCU_KMEANS_EXACT && ((uintptr_t)X & 15) == 0) {
         if (ctx->kmeans_path != IBCU_KMEANS_MMA_SYNC) {
             const int rc = ibcu_kmeans_assign_tc(ctx, X, N, C, K, idx, dist);

@@ -7,7 +7,7 @@
 // where nh0 + nh1 + nh2 = -|c|^2 / 2 split into three TF32 terms, so the bias rides in the contraction.
 // Operands sit in shared memory in the canonical K-major layout without swizzle (8 rows x 16 bytes core
 // matrices); the centroid operand is built once per block, the point operand per tile by a loader warp
-// (cp.async ring of raw tiles, converted to the two TF32 terms). One thread issues the MMAs; two
+// (four loader warps: cp.async ring of raw tiles, split into the two TF32 terms). One thread issues the MMAs; two
 // accumulator tiles (2 x 256 of the 512 TMEM columns) alternate, so the tensor cores fill one while eight
 // epilogue warps drain the other with tcgen05.ld (32x32b: a thread owns one point, i.e. one row).
 //
@@ -28,8 +28,10 @@ namespace {
 
 constexpr int TC_TILE = 128;                 // points per accumulator tile
 constexpr int TC_STAGES = 4;                 // raw / operand tiles in flight
-constexpr int TC_EPI_WARPS = 8;              // warps 0..7 drain accumulators; warp 8 loads points; warp 9 issues MMAs
-constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
+constexpr int TC_EPI_WARPS = 8;              // warps 0..7 drain accumulators; warps 8..11 load points (32 rows of every tile each); warp 12 issues MMAs
+constexpr int TC_LOAD_WARPS = 4;
+constexpr int TC_MMA_WARP = TC_EPI_WARPS + TC_LOAD_WARPS;
+constexpr int TC_THREADS = (TC_MMA_WARP + 1) * 32;
 constexpr int TC_A_CHUNK = 16 * 128;         // one 16-byte K chunk of 128 rows: 16 core matrices of 128 bytes
 constexpr int TC_A_STAGE = 4 * TC_A_CHUNK;   // xh (two chunks), xl (two chunks)
 constexpr int TC_RAW_STAGE = TC_TILE * 32;   // 128 points x 8 floats
@@ -42,8 +44,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) { asm volatil
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    // the hint lets the thread sleep up to about two microseconds per try instead of spinning on the issue slots
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
 // Bounded wait. Returns false when the block is giving up (this wait ran out, or another role's did).
@@ -108,8 +111,10 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t* r) {
                  :: "memory");
 }
 
-// best and second-best of the maxima over groups of 8 scores; g1 = index of the best group
-__device__ __forceinline__ void top2_groups(const uint32_t* r, int gid0, float& m1, float& m2, int& g1) {
+// Best and second-best of the maxima over groups of 8 scores, kept by four independent trackers (tracker q sees groups
+// q, q + 4, ...) so that the four dependency chains interleave; top2_merge joins two trackers.
+struct Top2 { float m1, m2; int g1; };
+__device__ __forceinline__ void top2_groups(const uint32_t* r, int gid0, Top2* t) {
 #pragma unroll
     for (int q = 0; q < 4; q++) {
         const float* v = reinterpret_cast<const float*>(r) + 8 * q;
@@ -117,10 +122,17 @@ __device__ __forceinline__ void top2_groups(const uint32_t* r, int gid0, float& 
         g = max3(g, v[3], v[4]);
         g = max3(g, v[5], v[6]);
         g = fmaxf(g, v[7]);
-        m2 = fmaxf(m2, fminf(m1, g));
-        g1 = g > m1 ? gid0 + q : g1;
-        m1 = fmaxf(m1, g);
+        t[q].m2 = fmaxf(t[q].m2, fminf(t[q].m1, g));
+        t[q].g1 = g > t[q].m1 ? gid0 + q : t[q].g1;
+        t[q].m1 = fmaxf(t[q].m1, g);
     }
+}
+__device__ __forceinline__ Top2 top2_merge(const Top2& a, const Top2& b) {
+    Top2 r;
+    r.m2 = fmaxf(fmaxf(a.m2, b.m2), fminf(a.m1, b.m1));
+    r.g1 = (b.m1 > a.m1 || (b.m1 == a.m1 && b.g1 < a.g1)) ? b.g1 : a.g1;
+    r.m1 = fmaxf(a.m1, b.m1);
+    return r;
 }
 
 // Dynamic shared memory: centroid operand [ch | cl | bias][2 chunks][K rows x 16 B] | constant point chunk pair
@@ -142,14 +154,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
     pdl_launch_dependents();
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; s++) { mbar_init(smem_u32(&sh->full_a[s]), 1); mbar_init(smem_u32(&sh->empty_a[s]), 1); }
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(smem_u32(&sh->full_a[s]), TC_LOAD_WARPS); mbar_init(smem_u32(&sh->empty_a[s]), 1); }
         for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&sh->full_acc[b]), 1); mbar_init(smem_u32(&sh->empty_acc[b]), 4); }
         mbar_init(smem_u32(&sh->drained), 1);
         sh->abort_flag = 0;
         sh->cmax2_bits = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == TC_EPI_WARPS + 1) {          // all 512 columns of tensor memory: two accumulator tiles of up to 256 columns
+    if (warp == TC_MMA_WARP) {               // all 512 columns of tensor memory: two accumulator tiles of up to 256 columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -205,15 +217,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
     const long ntile = (N + TC_TILE - 1) / TC_TILE;
     const long n_my = (long)blockIdx.x < ntile ? (ntile - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;      // tiles blockIdx.x + i gridDim.x
 
-    if (warp == TC_EPI_WARPS) {
-        // ── loader: raw tiles by cp.async (TC_STAGES - 1 ahead), then the two TF32 terms into the operand stage ──
+    if (warp >= TC_EPI_WARPS && warp < TC_MMA_WARP) {
+        // ── loaders: warp lw owns rows 32 lw .. + 31 of every tile: raw rows by cp.async (TC_STAGES - 1 tiles ahead), then the
+        //    two TF32 terms into the operand stage ──
+        const int lw = warp - TC_EPI_WARPS;
         auto issue = [&](long i) {
             if (i < n_my) {
-                const long p0 = (blockIdx.x + i * gridDim.x) * TC_TILE;
-                const uint32_t dst = smem_u32(sRaw + (i % TC_STAGES) * TC_RAW_STAGE);
+                const long p0 = (blockIdx.x + i * gridDim.x) * TC_TILE + 32 * lw;
+                const uint32_t dst = smem_u32(sRaw + (i % TC_STAGES) * TC_RAW_STAGE + lw * 1024);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int e = lane + 32 * j;                     // 16-byte piece e of the tile: point e / 2, half e % 2
+                for (int j = 0; j < 2; j++) {
+                    const int e = lane + 32 * j;                     // 16-byte piece e of this warp's 1 KB: point e / 2, half e % 2
                     const long pt = p0 + (e >> 1);
                     const int nbytes = pt < N ? 16 : 0;              // points past the end read as zeros
                     const float* src = X + (pt < N ? pt : 0) * 8 + (e & 1) * 4;
@@ -225,21 +239,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
         for (int i = 0; i < TC_STAGES - 1; i++) issue(i);
         for (long i = 0; i < n_my; i++) {
             const int s = (int)(i % TC_STAGES);
-            __syncwarp();                                            // the raw stage about to be refilled has been read by every lane
+            __syncwarp();                                            // the raw rows about to be refilled have been read by every lane
             issue(i + TC_STAGES - 1);
             asm volatile("cp.async.wait_group %0;" :: "n"(TC_STAGES - 1) : "memory");
             __syncwarp();
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_a[s]), (uint32_t)(((i / TC_STAGES) & 1) ^ 1), abort_flag, 1))) break;   // the whole warp leaves or stays
             const unsigned char* raw = sRaw + s * TC_RAW_STAGE;
             unsigned char* dstA = sA + s * TC_A_STAGE;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int r = lane + 32 * j;
+            {
+                const int r = 32 * lw + lane;
                 const float4 a = *reinterpret_cast<const float4*>(raw + r * 32), c = *reinterpret_cast<const float4*>(raw + r * 32 + 16);
                 const float v[8] = { a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w };
                 uint32_t h[8], l[8];
 #pragma unroll
-                for (int d = 0; d < 8; d++) { h[d] = tf32_of(v[d]); l[d] = tf32_of(v[d] - __uint_as_float(h[d])); }
+                for (int d = 0; d < 8; d++) {
+                    // xh = x cut to its TF32 bits; xl = x - xh exactly (the tensor cores read its upper bits): x.c is then
+                    // short by at most 2^-20 |x||c| before the xl.cl term that is left out anyway
+                    h[d] = __float_as_uint(v[d]) & 0xFFFFE000u;
+                    l[d] = __float_as_uint(v[d] - __uint_as_float(h[d]));
+                }
                 const uint32_t row = (uint32_t)(r >> 3) * 128u + (uint32_t)(r & 7) * 16u;
                 *reinterpret_cast<uint4*>(dstA + row) = make_uint4(h[0], h[1], h[2], h[3]);
                 *reinterpret_cast<uint4*>(dstA + TC_A_CHUNK + row) = make_uint4(h[4], h[5], h[6], h[7]);
@@ -251,7 +269,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
             if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[s]));
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else if (warp == TC_EPI_WARPS + 1) {
+    } else if (warp == TC_MMA_WARP) {
         // ── MMA issue: one thread ──
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(K >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
@@ -292,23 +310,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
             }
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_acc[b]), (uint32_t)((i >> 1) & 1), abort_flag, 5))) break;            // the whole warp leaves or stays
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float m1 = -INFINITY, m2 = -INFINITY;
-            int g1 = 0;
-            uint32_t ra[32], rb[32];
+            Top2 tr[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) { tr[q].m1 = -INFINITY; tr[q].m2 = -INFINITY; tr[q].g1 = q; }
+            uint32_t ra[32], rb[32];                                 // 32 columns per load, the next load in flight while one is reduced
             tmem_ld32(taddr, ra);
             for (int c0 = 0; c0 < K; c0 += 64) {
                 tmem_wait_ld(ra);
                 if (c0 + 32 < K) tmem_ld32(taddr + c0 + 32, rb);
-                top2_groups(ra, c0 >> 3, m1, m2, g1);
+                top2_groups(ra, c0 >> 3, tr);
                 if (c0 + 32 < K) {
                     tmem_wait_ld(rb);
                     if (c0 + 64 < K) tmem_ld32(taddr + c0 + 64, ra);
-                    top2_groups(rb, (c0 >> 3) + 4, m1, m2, g1);
+                    top2_groups(rb, (c0 >> 3) + 4, tr);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->empty_acc[b]));  // the tensor cores may overwrite this tile
+            const Top2 top = top2_merge(top2_merge(tr[0], tr[1]), top2_merge(tr[2], tr[3]));
+            const float m1 = top.m1, m2 = top.m2;
+            const int g1 = top.g1;
             // the margin that makes the filter safe: false for NaN / Inf as well
             float xn = 0.0f;
 #pragma unroll
@@ -371,7 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
     // ── teardown: every role is out of its loop (all waits are bounded); release tensor memory ──
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == TC_EPI_WARPS + 1) {
+    if (warp == TC_MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512u) : "memory");
     }
@@ -380,10 +402,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
 
 }  // namespace
 
-// D == 8, K a multiple of 32 up to 256, 16-byte aligned X: the tensor-memory kernel. Returns IBCU_ERR_STATE without
+// D == 8, K a multiple of 64 up to 256, 16-byte aligned X: the tensor-memory kernel. Returns IBCU_ERR_STATE without
 // touching the context's error when the shape is not its own (the caller takes another kernel).
 int ibcu_kmeans_assign_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist) {
-    if (K < 32 || K > 256 || (K & 31) || ((uintptr_t)X & 15)) return IBCU_ERR_STATE;
+    if (K < 64 || K > 256 || (K & 63) || ((uintptr_t)X & 15)) return IBCU_ERR_STATE;
     const size_t smem = 1024 + (size_t)3 * 2 * K * 16 + 2 * TC_A_CHUNK + (size_t)TC_STAGES * (TC_A_STAGE + TC_RAW_STAGE) + (size_t)K * 8 * sizeof(float) + (size_t)(K / 8) * TC_GROUP_STRIDE * sizeof(float) + sizeof(TcShared) + 64;
     IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const long ntile = (N + TC_TILE - 1) / TC_TILE;
