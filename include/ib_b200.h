@@ -58,8 +58,10 @@ typedef struct {
  * ibf_load re-runs ib_init_kernels (src/ibf_loader.c:539-540). */
 void ib_b200_install_kernels(void* table);
 /* Row-sliced, pre-offset calls from pool workers (src/threading.c:220-241) are accepted: weights,
- * scales and out may point inside a tensor. With threads <= 1 the reference makes exactly one call
- * per linear (src/threading.c:247-252), which is the mode this backend wants. */
+ * scales and out may point inside a tensor, and several workers may call at the same time: every
+ * entry takes one process-wide lock, so concurrent calls run one after another on the device. With
+ * threads <= 1 the reference makes exactly one call per linear (src/threading.c:247-252), which is
+ * the mode this backend wants. */
 void ib_b200_matmul_int4(float* out, const void* weights, const float* scales, const float* input, int M, int N);
 void ib_b200_matmul_int8(float* out, const void* weights, const float* scales, const float* input, int M, int N);
 void ib_b200_matmul_int8_batch(float* out, const void* weights, const float* scales_w, const float* input,

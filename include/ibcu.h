@@ -128,9 +128,10 @@ typedef struct {
 } ibcu_prologue_t;
 int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
                    const float* x, int N, int B, int bits, const ibcu_prologue_t* prologue);
-/* Same, plus silu(gate)*up fused into the epilogue of a gate/up pair (src/forward.c:635-637,
- * src/kernels/scalar.c:175-181): tensors[0] = gate, tensors[1] = up, equal M; writes only
- * tensors[0].out[b*out_stride + row] = silu(gate_y) * up_y. */
+/* A gate/up pair in one launch over the shared activation, followed by a second, elementwise launch that forms
+ * silu(gate_y) * up_y (src/forward.c:635-637, src/kernels/scalar.c:175-181): tensors[0] = gate, tensors[1] = up,
+ * equal M. Both outputs are written by the first launch; the second overwrites tensors[0].out[b*out_stride + row]
+ * with the product and leaves tensors[1].out holding up_y. */
 int ibcu_linear_gate_up_silu(ibcu_ctx* ctx, const ibcu_linear_t* gate_up,
                              const float* x, int N, int B, int bits);
 /* Force the portable (non tensor-core) kernel for the next ibcu_linear calls; for tests. */
@@ -286,6 +287,19 @@ int ibcu_window_open(ibcu_ctx* ctx, int peer_rank, const void* handle);
 int ibcu_window_alloc(ibcu_ctx* ctx, size_t bytes, void** dptr);
 void ibcu_window_enable(ibcu_ctx* ctx, int on);
 int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const int* M, const int* stride, int n, int B, int align);
+/* Announces the next ibcu_allgather_rows_n over these buffers ahead of the ibcu_linear* calls that produce this rank's row
+ * slices of them. When the buffers lie in the peer window (and none was part of the previous push), those calls store
+ * their rows into the peers' copies from the kernel's own epilogue, the last block publishes the epoch, and the gather
+ * call that follows has nothing left to launch: the kernel that consumes the gathered rows (a linear, the attention step,
+ * ibcu_silu_mul_amax), or a small waiting kernel ahead of any other consumer, of ibcu_memcpy_d2h and of ibcu_sync, waits
+ * - with the same limit - for the peers' epochs in its prologue. Without a window the call does nothing and the gather
+ * works as before. Invariant for callers: every read of a gathered buffer must be issued before the rank's next gather but
+ * one of that buffer begins, and consecutive gathers must use different buffers (else the slower path is taken). */
+int ibcu_allgather_rows_prepare(ibcu_ctx* ctx, float* const* bufs, const int* stride, int n);
+/* For tests of the bounded wait, on one GPU and without any peer: launches the waiting kernel on a private header in which
+ * one of two ranks never publishes. The kernel gives up at its limit (a second or two); the next ibcu_sync returns
+ * IBCU_ERR_COMM and the context stays usable after ibcu_clear_error. */
+int ibcu_gather_wait_probe(ibcu_ctx* ctx);
 int ibcu_allreduce_f32(ibcu_ctx* ctx, float* buf, size_t n);
 int ibcu_allreduce_i32(ibcu_ctx* ctx, int32_t* buf, size_t n);
 int ibcu_allreduce_f64(ibcu_ctx* ctx, double* buf, size_t n);

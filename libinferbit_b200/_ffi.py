@@ -111,6 +111,8 @@ IBCU_SYMBOLS = {
     "ibcu_window_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "ibcu_window_enable": (None, [C.c_void_p, C.c_int]),
     "ibcu_allgather_rows_n": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]),
+    "ibcu_allgather_rows_prepare": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int]),
+    "ibcu_gather_wait_probe": (C.c_int, [C.c_void_p]),
     "ibcu_allreduce_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ibcu_allreduce_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ibcu_allreduce_f64": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),

@@ -129,15 +129,19 @@ class AttnProjWorkload:
     def step(self, i):
         lib, ctx, ent = self.lib, self.ctx, self.sets[i % self.ring]
         qkv = (LinearT * 3)(self._desc(ent, "q"), self._desc(ent, "k"), self._desc(ent, "v"))
-        check(lib, ctx, lib.ibcu_linear(ctx, qkv, 3, self.x, self.N, self.B, 8))
-        if self.world > 1:
+        if self.world > 1:                                   # announce the gather: the launch pushes its rows from its epilogue
             bufs = (C.c_void_p * 3)(*[self.out[n] for n in ("q", "k", "v")])
             Ms = (C.c_int * 3)(*[ent[n][2] for n in ("q", "k", "v")])
+            check(lib, ctx, lib.ibcu_allgather_rows_prepare(ctx, bufs, Ms, 3))
+        check(lib, ctx, lib.ibcu_linear(ctx, qkv, 3, self.x, self.N, self.B, 8))
+        if self.world > 1:
             check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 3, self.B, 32))
         o = self._desc(ent, "o")
-        check(lib, ctx, lib.ibcu_linear(ctx, C.byref(o), 1, self.x2, self.N, self.B, 8))
         if self.world > 1:
             bufs = (C.c_void_p * 1)(self.out["o"]); Ms = (C.c_int * 1)(ent["o"][2])
+            check(lib, ctx, lib.ibcu_allgather_rows_prepare(ctx, bufs, Ms, 1))
+        check(lib, ctx, lib.ibcu_linear(ctx, C.byref(o), 1, self.x2, self.N, self.B, 8))
+        if self.world > 1:
             check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 1, self.B, 32))
 
     def matches_single_gpu(self):

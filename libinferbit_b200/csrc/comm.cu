@@ -114,6 +114,7 @@ extern "C" int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride,
     IBCU_REQUIRE(ctx, buf && M >= 0 && stride >= M && B >= 1, "ibcu_allgather_rows: bad arguments");
     if (ctx->world == 1 || M == 0) return IBCU_OK;
     if (!ctx->comm) return ibcu_fail(ctx, IBCU_ERR_STATE, "ibcu_allgather_rows: no communicator");
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
     for (int j = 0; j < 4; j++) ctx->win_last[j] = nullptr;    // an NCCL gather in between ends the no-repeat rule
     ncclComm_t comm = (ncclComm_t)ctx->comm;
     int r0, rn;
@@ -144,9 +145,9 @@ extern "C" int ibcu_allgather_rows(ibcu_ctx* ctx, float* buf, int M, int stride,
 // every peer's flag in its own window has reached the same epoch. No NCCL launch, no staging copy.
 // The epoch is device state, so a captured launch replays correctly.
 // Window header: flags[IBCU_MAX_RANKS] (flags[r] written by rank r), then this rank's epoch counter.
-constexpr size_t WIN_HEADER = 4096;
-constexpr int WIN_EPOCH_SLOT = IBCU_MAX_RANKS;
-constexpr long WIN_SPIN_LIMIT = 4L * 1000 * 1000;            // about a second of polling
+constexpr size_t WIN_HEADER = IBCU_WIN_HEADER;
+constexpr int WIN_EPOCH_SLOT = IBCU_WIN_EPOCH_SLOT;
+constexpr long WIN_SPIN_LIMIT = IBCU_WIN_SPIN_LIMIT;
 
 struct PushDesc { float* buf; int stride, row0, rows; };
 struct PushParams {
@@ -157,13 +158,14 @@ struct PushParams {
     int* err;
 };
 
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) { return ld_acquire_sys_u64(p); }
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) { st_release_sys_u64(p, v); }
+
+// The waiting half of a gather whose stores were made by a linear launch, for consumers that do not wait themselves.
+__global__ void __launch_bounds__(32) gather_wait_kernel(const GatherWait g) {
+    pdl_launch_dependents();
+    pdl_wait();
+    gather_wait(g);
 }
 
 __global__ void __launch_bounds__(1024) allgather_push_kernel(const PushParams p) {
@@ -212,6 +214,46 @@ __global__ void __launch_bounds__(1024) allgather_push_kernel(const PushParams p
         }
     }
     __syncthreads();
+}
+
+void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw) {
+    gw->flags = nullptr; gw->world = ctx->world; gw->rank = ctx->rank; gw->err = ctx->win_err;
+    if (!ctx->gather_pending) return;
+    gw->flags = reinterpret_cast<const unsigned long long*>(ctx->win_base);
+    ctx->gather_pending = 0;
+}
+
+int ibcu_flush_gather_wait(ibcu_ctx* ctx) {
+    if (!ctx->gather_pending) return IBCU_OK;
+    GatherWait gw;
+    ibcu_take_gather_wait(ctx, &gw);                          // clears the pending state, so the launch below does not come back here
+    return ibcu_launch(ctx, gather_wait_kernel, dim3(1), dim3(32), 0, 1, true, gw);
+}
+
+// For the linear kernels: do all output slices of a launch belong to buffers of an announced gather? Then the launch
+// stores them into the peers' copies as well and marks those buffers done.
+bool ibcu_push_match(ibcu_ctx* ctx, float* const* outs, int n) {
+    if (ctx->arm_n == 0 || ctx->world <= 1) return false;
+    int hit[4];
+    for (int i = 0; i < n; i++) {
+        hit[i] = -1;
+        for (int j = 0; j < ctx->arm_n; j++) {
+            const char* p = (const char*)outs[i];
+            if (p >= ctx->arm_buf[j] && p < ctx->arm_buf[j] + (size_t)ctx->arm_stride[j] * sizeof(float)) hit[i] = j;
+        }
+        if (hit[i] < 0) return false;
+    }
+    for (int i = 0; i < n; i++) ctx->arm_done[hit[i]] = 1;
+    return true;                                              // the caller raises gather_pending once its pushing kernel is launched
+}
+void ibcu_push_fill(ibcu_ctx* ctx, GatherPush* gp, size_t bytes) {
+    memset(gp, 0, sizeof *gp);
+    gp->world = ctx->world; gp->rank = ctx->rank;
+    gp->err = ctx->win_err;
+    long P = (long)(bytes / (16 * 1024));                     // one pushing block per 16 KB, at most 16
+    gp->pushers = P < 1 ? 1 : P > 16 ? 16 : (int)P;
+    gp->header = reinterpret_cast<unsigned long long*>(ctx->win_base);
+    for (int r = 0; r < ctx->world; r++) gp->peer[r] = ctx->win_peer[r];
 }
 
 extern "C" int ibcu_window_create(ibcu_ctx* ctx, size_t bytes, void* handle_out) {
@@ -266,14 +308,61 @@ extern "C" int ibcu_window_alloc(ibcu_ctx* ctx, size_t bytes, void** dptr) {
 
 extern "C" void ibcu_window_enable(ibcu_ctx* ctx, int on) { if (ctx) ctx->win_enabled = on ? 1 : 0; }
 
+
 static bool in_window(const ibcu_ctx* ctx, const void* p) {
     return ctx->win_base && (const char*)p >= ctx->win_base + WIN_HEADER && (const char*)p < ctx->win_base + ctx->win_bytes;
+}
+
+// A wait that cannot be satisfied, on one GPU: a private header whose own epoch says 1 while the flag word of a
+// "peer" that does not exist stays 0. The waiting kernel must give up at its limit and raise the error word.
+extern "C" int ibcu_gather_wait_probe(ibcu_ctx* ctx) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->win_err) {
+        IBCU_CUDA(ctx, cudaHostAlloc((void**)&ctx->win_err, sizeof(int), cudaHostAllocMapped));
+        *ctx->win_err = 0;
+    }
+    unsigned long long host_hdr[IBCU_WIN_HEADER / 8];
+    memset(host_hdr, 0, sizeof host_hdr);
+    host_hdr[IBCU_WIN_EPOCH_SLOT] = 1;
+    int rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, IBCU_WIN_HEADER);
+    if (rc) return rc;
+    IBCU_CUDA(ctx, cudaMemcpyAsync(ctx->scratch, host_hdr, sizeof host_hdr, cudaMemcpyHostToDevice, ctx->stream));
+    IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    GatherWait gw = { (const unsigned long long*)ctx->scratch, 2, 0, ctx->win_err };
+    return ibcu_launch(ctx, gather_wait_kernel, dim3(1), dim3(32), 0, 1, true, gw);
+}
+
+extern "C" int ibcu_allgather_rows_prepare(ibcu_ctx* ctx, float* const* bufs, const int* stride, int n) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, bufs && stride && n >= 1 && n <= 4, "ibcu_allgather_rows_prepare: bad arguments");
+    ctx->arm_n = 0;
+    if (ctx->world <= 1 || !ctx->win_enabled || ctx->win_open != ctx->world) return IBCU_OK;
+    for (int i = 0; i < n; i++) {
+        if (!in_window(ctx, bufs[i])) return IBCU_OK;
+        for (int j = 0; j < 4; j++) if (ctx->win_last[j] == bufs[i]) return IBCU_OK;      // the peers may still be reading the previous gather of it
+    }
+    for (int i = 0; i < n; i++) { ctx->arm_buf[i] = (const char*)bufs[i]; ctx->arm_stride[i] = stride[i]; ctx->arm_done[i] = 0; }
+    ctx->arm_n = n;
+    return IBCU_OK;
 }
 
 extern "C" int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const int* M, const int* stride, int n, int B, int align) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, bufs && M && stride && n >= 1 && n <= 4 && B >= 1, "ibcu_allgather_rows_n: bad arguments");
     if (ctx->world == 1) return IBCU_OK;
+    if (ctx->arm_n) {
+        // announced ahead (ibcu_allgather_rows_prepare): the linear launches that produced these rows may already have
+        // stored them into the peers' copies; then only the waiting is left, and the next kernel or copy does it
+        bool done = ctx->arm_n == n;
+        for (int i = 0; i < n && done; i++) done = ctx->arm_buf[i] == (const char*)bufs[i] && ctx->arm_done[i];
+        ctx->arm_n = 0;
+        if (done) {
+            for (int j = 0; j < 4; j++) ctx->win_last[j] = j < n ? bufs[j] : nullptr;
+            return IBCU_OK;
+        }
+    }
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
     bool push = ctx->win_enabled && ctx->win_open == ctx->world;
     for (int i = 0; i < n && push; i++) {
         push = in_window(ctx, bufs[i]);
@@ -302,9 +391,45 @@ static int allreduce(ibcu_ctx* ctx, void* buf, size_t n, ncclDataType_t ty) {
     IBCU_CHECK_CTX(ctx);
     if (ctx->world == 1 || n == 0) return IBCU_OK;
     if (!ctx->comm) return ibcu_fail(ctx, IBCU_ERR_STATE, "all-reduce requested without a communicator");
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
     IBCU_NCCL(ctx, ncclAllReduce(buf, buf, n, ty, ncclSum, (ncclComm_t)ctx->comm, ctx->stream));
     return IBCU_OK;
 }
+int ibcu_allreduce_kmeans(ibcu_ctx* ctx, float* sums, size_t n_sums, int32_t* counts, size_t n_counts, double* inertia) {
+    IBCU_CHECK_CTX(ctx);
+    if (ctx->world == 1) return IBCU_OK;
+    if (!ctx->comm) return ibcu_fail(ctx, IBCU_ERR_STATE, "all-reduce requested without a communicator");
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
+    ncclComm_t comm = (ncclComm_t)ctx->comm;
+    IBCU_NCCL(ctx, ncclGroupStart());
+    IBCU_NCCL(ctx, ncclAllReduce(sums, sums, n_sums, ncclFloat, ncclSum, comm, ctx->stream));
+    IBCU_NCCL(ctx, ncclAllReduce(counts, counts, n_counts, ncclInt32, ncclSum, comm, ctx->stream));
+    if (inertia) IBCU_NCCL(ctx, ncclAllReduce(inertia, inertia, 1, ncclDouble, ncclSum, comm, ctx->stream));
+    IBCU_NCCL(ctx, ncclGroupEnd());
+    return IBCU_OK;
+}
+
+// The exchange area: two buffers of `world` slots, taken from the window the first time (or when a larger slot is asked
+// for). Every rank calls this at the same point of the same sequence of window allocations, so the area has the same
+// offset in every window. Two buffers used in turn are enough: a rank can only write buffer t again after it has waited
+// for the exchange in between, which its peers publish only after their kernels that read buffer t have finished.
+int ibcu_exchange_begin(ibcu_ctx* ctx, size_t slot_bytes, ExchSlots* ex) {
+    if (ctx->world <= 1 || !ctx->win_base || !ctx->win_enabled || ctx->win_open != ctx->world) return 0;
+    const size_t slot = (slot_bytes + 255) & ~(size_t)255;
+    if (slot > ctx->exch_slot) {
+        void* area = nullptr;
+        if (ibcu_window_alloc(ctx, 2 * slot * ctx->world, &area) != IBCU_OK) return 0;
+        ctx->exch_off = (size_t)((char*)area - ctx->win_base);
+        ctx->exch_slot = slot;
+        ctx->exch_turn = 0;
+    }
+    ibcu_push_fill(ctx, &ex->gp, slot_bytes);
+    ex->slot = ctx->exch_slot;
+    ex->off = ctx->exch_off + (size_t)(ctx->exch_turn & 1u) * ctx->exch_slot * ctx->world;
+    ctx->exch_turn++;
+    return 1;
+}
+
 extern "C" int ibcu_allreduce_f32(ibcu_ctx* ctx, float* buf, size_t n) { return allreduce(ctx, buf, n, ncclFloat); }
 extern "C" int ibcu_allreduce_i32(ibcu_ctx* ctx, int32_t* buf, size_t n) { return allreduce(ctx, buf, n, ncclInt32); }
 extern "C" int ibcu_allreduce_f64(ibcu_ctx* ctx, double* buf, size_t n) { return allreduce(ctx, buf, n, ncclDouble); }

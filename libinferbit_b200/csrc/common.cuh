@@ -44,7 +44,40 @@ struct ibcu_ctx {
     int*   win_err;                                 // pinned, mapped: a push kernel that gave up waiting writes its epoch here
     int*   kern_err;                                // pinned, mapped, made with the context: a kernel whose bounded wait ran out writes a code here
     const void* win_last[4];                        // buffers of the previous push (a buffer is not pushed twice in a row)
+    // gathers announced ahead of the launches that produce their rows (ibcu_allgather_rows_prepare): the buffers, their
+    // row strides, and which of them a linear launch has meanwhile pushed from its epilogue
+    const char* arm_buf[4]; int arm_stride[4]; int arm_done[4]; int arm_n;
+    int    gather_pending;                          // a linear launch has pushed its rows to the peers: the next kernel (or copy to the host) waits for theirs
+    // exchange area inside the window (all-reduce of small tables, k-means): two buffers of world slots each, used in turn
+    size_t exch_off, exch_slot; unsigned exch_turn;
 };
+
+// Window header, in units of 8 bytes: flags[r] is written by rank r (the epoch of its last finished push), then this
+// rank's own epoch counter and the counter of blocks that have finished pushing in the current launch.
+constexpr size_t IBCU_WIN_HEADER = 4096;
+constexpr int IBCU_WIN_EPOCH_SLOT = IBCU_MAX_RANKS;
+constexpr int IBCU_WIN_DONE_SLOT = IBCU_MAX_RANKS + 1;
+constexpr int IBCU_WIN_READY_SLOT = IBCU_MAX_RANKS + 2;
+constexpr int IBCU_WIN_GO_SLOT = IBCU_MAX_RANKS + 3;         // the epoch about to be published once every block of the pushing launch has arrived      // the epoch up to which block 0 of a waiting kernel has seen every peer arrive
+constexpr long IBCU_WIN_SPIN_LIMIT = 4L * 1000 * 1000;       // about a second of polling
+
+// What a kernel needs to wait for the peers' rows of the gather that precedes it (flags == NULL: nothing to wait for).
+struct GatherWait { const unsigned long long* flags; int world, rank; int* err; };
+// What a linear launch needs to store its rows into the peers' copies and to publish that it has (world == 0: no push).
+struct GatherPush { char* peer[IBCU_MAX_RANKS]; unsigned long long* header; int world, rank, pushers; int* err; };
+
+// Every rank's table for a small all-reduce: rank r's copy sits at off + r * slot in every rank's window.
+struct ExchSlots { GatherPush gp; size_t off, slot; };
+// Next turn of the exchange area for tables of slot_bytes per rank. Returns 1 and fills *ex when the window can carry it
+// (every rank mapped, area large enough or newly taken from the window), else 0: the caller uses NCCL.
+int ibcu_exchange_begin(ibcu_ctx* ctx, size_t slot_bytes, ExchSlots* ex);
+// sums, counts and inertia of a k-means iteration in one grouped NCCL call
+int ibcu_allreduce_kmeans(ibcu_ctx* ctx, float* sums, size_t n_sums, int32_t* counts, size_t n_counts, double* inertia);
+
+// Fills *gw when a push is pending and clears the pending state: the caller's kernel does the waiting in its prologue.
+void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw);
+// Launches a one-block kernel that does the waiting (for consumers that cannot: other kernels, copies to the host).
+int ibcu_flush_gather_wait(ibcu_ctx* ctx);
 
 int ibcu_fail(ibcu_ctx* ctx, int code, const char* fmt, ...);
 
@@ -64,6 +97,7 @@ int ibcu_reserve(ibcu_ctx* ctx, void** buf, size_t* have, size_t want);
 template <typename... KArgs, typename... Args>
 static inline int ibcu_launch(ibcu_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block,
                               size_t smem, int cluster_x, bool pdl_ok, Args... args) {
+    if (ctx->gather_pending) { int rc_ = ibcu_flush_gather_wait(ctx); if (rc_) return rc_; }     // this kernel does not wait by itself
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
@@ -116,6 +150,138 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+// Called by every thread of a block after pdl_wait(): the rows the peers pushed in the preceding gather are in place
+// when it returns. The epoch to wait for is this rank's own (its last push, finished before this kernel's dependency
+// wait returned). Bounded: a rank whose peers do not arrive gives up and raises the host-visible error word.
+__device__ __forceinline__ void gather_wait(const GatherWait& g) {
+    if (!g.flags) return;
+    if ((int)threadIdx.x < g.world && (int)threadIdx.x != g.rank) {          // one thread per peer
+        const unsigned long long e = g.flags[IBCU_WIN_EPOCH_SLOT];
+        long it = 0;
+        while (ld_acquire_sys_u64(g.flags + threadIdx.x) < e) {
+            if (++it > IBCU_WIN_SPIN_LIMIT) { *g.err = (int)e; break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+}
+
+// The pushing half of a gather, at the end of the launch that produced the rows. Every block writes its results into
+// this rank's own memory only; the last gp.pushers blocks to arrive (1 for a few KB, up to 16 for the large tables of a
+// batched step) then copy them into the peers' windows, each its share, and the last of those to finish publishes. A
+// system-scope fence in each of a few hundred blocks, every one with stores over NVLink in flight, was measured to
+// spread the blocks' ends over about 8 us; a handful of fences is not.
+//   const int j = push_arrive(gp);
+//   if (j >= 0) { push_span(gp, j, ...); ...; push_finish(gp); }
+// push_arrive is called by every thread of every block. It returns -1 in blocks that are done, and the pusher's index
+// in the pushing blocks once every block of the grid has arrived. The pushing blocks that arrive before the last one
+// wait for it (bounded); they are at most 16, so the blocks still to run always find room.
+__device__ __forceinline__ int push_arrive(const GatherPush& gp) {
+    __shared__ int s_j;
+    __threadfence();                                          // this thread's results, visible to the blocks that will copy them
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* done = reinterpret_cast<unsigned*>(gp.header + IBCU_WIN_DONE_SLOT);
+        unsigned long long* go = gp.header + IBCU_WIN_GO_SLOT;
+        const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+        const unsigned P = (unsigned)gp.pushers < total ? (unsigned)gp.pushers : total;
+        const unsigned long long e = gp.header[IBCU_WIN_EPOCH_SLOT] + 1;       // the epoch this launch will publish
+        const unsigned n = atomicAdd(done, 1u);
+        int j = (int)n - (int)(total - P);
+        if (n == total - 1) {
+            asm volatile("st.release.gpu.global.u64 [%0], %1;" :: "l"(go), "l"(e) : "memory");
+        } else if (j >= 0) {
+            long it = 0;
+            for (;;) {
+                unsigned long long v;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(go) : "memory");
+                if (v >= e) break;
+                if (++it > IBCU_WIN_SPIN_LIMIT) { *gp.err = (int)e; break; }
+                __nanosleep(40);
+            }
+        }
+        s_j = j;
+    }
+    __syncthreads();
+    const int j = s_j;
+    if (j >= 0) __threadfence();
+    return j;
+}
+__device__ __forceinline__ int push_count(const GatherPush& gp) {
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    return (unsigned)gp.pushers < total ? gp.pushers : (int)total;
+}
+// After a pushing block's copies: when the last pusher is through, this rank's epoch goes up by one and is written into
+// every peer's flag word. Thread 0's system-scope fence is cumulative over the block's stores, which the barrier
+// ordered before it; with several pushers the last one fences once more after it has seen the others' counts, which
+// they raised after their own fences. The flag itself is then a plain (relaxed) system-scope store.
+__device__ __forceinline__ void push_finish(const GatherPush& gp) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        unsigned* done = reinterpret_cast<unsigned*>(gp.header + IBCU_WIN_DONE_SLOT);
+        const int P = push_count(gp);
+        bool last = true;
+        if (P > 1) {
+            last = atomicAdd(done + 1, 1u) == (unsigned)P - 1;
+            if (last) __threadfence_system();
+        }
+        if (last) {
+            done[0] = 0u; done[1] = 0u;
+            const unsigned long long e = gp.header[IBCU_WIN_EPOCH_SLOT] + 1;
+            gp.header[IBCU_WIN_EPOCH_SLOT] = e;
+            for (int q = 0; q < gp.world; q++)
+                if (q != gp.rank)
+                    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(reinterpret_cast<unsigned long long*>(gp.peer[q]) + gp.rank), "l"(e) : "memory");
+        }
+    }
+}
+// A table of `rows` spans, span r being n floats at src + r * stride (this rank's memory), into every peer's window at
+// byte offset off + r * stride * 4: pusher j of P takes every P-th block-sized piece. VEC = 4 needs n, stride, src and
+// off in multiples of 16 bytes. Four loads per thread are in flight before the first store.
+template <int VEC>
+__device__ __forceinline__ void push_table(const GatherPush& gp, int j, int P, const float* src, size_t off, int n, int rows, size_t stride) {
+    const int per = n / VEC;
+    const long total = (long)per * rows;
+    const long step = (long)P * blockDim.x;
+    for (long e0 = (long)j * blockDim.x + threadIdx.x; e0 < total; e0 += 4 * step) {
+        float4 v[4];
+        size_t at[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const long e = e0 + u * step;
+            if (e < total) {
+                const int r = (int)(e / per), i = (int)(e % per);
+                at[u] = ((size_t)r * stride + (size_t)i * VEC) * sizeof(float);
+                if (VEC == 4) v[u] = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const char*>(src) + at[u]));
+                else v[u].x = __ldcg(reinterpret_cast<const float*>(reinterpret_cast<const char*>(src) + at[u]));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (e0 + u * step < total) {
+                for (int q = 0; q < gp.world; q++) {
+                    if (q == gp.rank) continue;
+                    if (VEC == 4) *reinterpret_cast<float4*>(gp.peer[q] + off + at[u]) = v[u];
+                    else *reinterpret_cast<float*>(gp.peer[q] + off + at[u]) = v[u].x;
+                }
+            }
+        }
+    }
+}
+__device__ __forceinline__ void push_span(const GatherPush& gp, int j, int P, const float* src, size_t off, int n, int rows, size_t stride) {
+    if ((((uintptr_t)src | off | (stride * sizeof(float))) & 15) == 0 && (n & 3) == 0) push_table<4>(gp, j, P, src, off, n, rows, stride);
+    else push_table<1>(gp, j, P, src, off, n, rows, stride);
 }
 
 __host__ __device__ __forceinline__ uint64_t ibcu_mix64(uint64_t seed, uint64_t ctr) {

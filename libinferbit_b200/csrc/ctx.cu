@@ -132,11 +132,13 @@ extern "C" int ibcu_memcpy_h2d(ibcu_ctx* ctx, void* dst, const void* src, size_t
 }
 extern "C" int ibcu_memcpy_d2h(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes) {
     IBCU_CHECK_CTX(ctx);
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }      // the source may be a gathered buffer whose peers' rows are still on their way
     if (bytes) IBCU_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     return IBCU_OK;
 }
 extern "C" int ibcu_memcpy_d2d(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes) {
     IBCU_CHECK_CTX(ctx);
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
     if (bytes) IBCU_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return IBCU_OK;
 }
@@ -147,6 +149,7 @@ extern "C" int ibcu_memset(ibcu_ctx* ctx, void* dst, int byte, size_t bytes) {
 }
 extern "C" int ibcu_sync(ibcu_ctx* ctx) {
     IBCU_CHECK_CTX(ctx);
+    if (!ctx->capturing) { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }
     IBCU_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->win_err && *(volatile int*)ctx->win_err) {
         const int e = *(volatile int*)ctx->win_err;
@@ -172,6 +175,7 @@ extern "C" int ibcu_store_i32(ibcu_ctx* ctx, int32_t* dst, int32_t value) {
 extern "C" int ibcu_event_record(ibcu_ctx* ctx, int slot) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, slot >= 0 && slot < IBCU_MAX_EVENTS, "event slot %d out of range", slot);
+    { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }      // a timed region ends when its gathers have ended
     IBCU_CUDA(ctx, cudaEventRecord(ctx->events[slot], ctx->stream));
     return IBCU_OK;
 }
@@ -192,6 +196,7 @@ extern "C" int ibcu_graph_begin(ibcu_ctx* ctx) {
 extern "C" int ibcu_graph_end(ibcu_ctx* ctx, int* graph_id) {
     IBCU_CHECK_CTX(ctx);
     if (!ctx->capturing) return ibcu_fail(ctx, IBCU_ERR_STATE, "no graph capture in progress");
+    ibcu_flush_gather_wait(ctx);                              // a replay is complete in itself: it ends with the wait for its last gather
     ctx->capturing = 0;
     cudaGraph_t g = nullptr;
     IBCU_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &g));

@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float
                                                              int n_heads, int n_kv, int hd, int pos0, int chunk, int nsplit,
                                                              const float* __restrict__ k_new, const float* __restrict__ v_new,
                                                              float* __restrict__ k_cache_w, float* __restrict__ v_cache_w, float theta,
-                                                             const int* __restrict__ pos0_ptr, int want, int chunk_cap) {
+                                                             const int* __restrict__ pos0_ptr, int want, int chunk_cap, const GatherWait gw) {
     extern __shared__ __align__(16) float asm_[];
     const int group = n_heads / n_kv;               // = warps in the block
     const int ld = hd + 4;                          // padded tile rows: conflict-free float4 reads down a column of rows
@@ -193,6 +193,7 @@ __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float
     float* vt = kt + (size_t)chunk_cap * ld;        // [chunk_cap][ld]
     pdl_launch_dependents();
     pdl_wait();
+    gather_wait(gw);                                // q, k, v may be rows that peers pushed
     if (pos0_ptr) {                                 // position read on the device: the same launch serves every position
         pos0 = *pos0_ptr;
         att_plan(pos0 + (int)gridDim.z, want, chunk_cap, chunk, nsplit);
@@ -333,10 +334,11 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(float* __restrict__ out, 
 
 // grid (parts, B): silu(gate) * up over one column range of one row, and the largest magnitude written
 __global__ void __launch_bounds__(256) silu_mul_amax_kernel(float* __restrict__ out, const float* __restrict__ gate, const float* __restrict__ up,
-                                                            int N, int chunk, float* __restrict__ amax) {
+                                                            int N, int chunk, float* __restrict__ amax, const GatherWait gw) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
+    gather_wait(gw);                                // gate and up may be rows that peers pushed
     const int p = blockIdx.x, b = blockIdx.y;
     const size_t base = (size_t)b * N;
     const int c1 = min(N, (p + 1) * chunk);
@@ -456,9 +458,11 @@ static int attention_split(ibcu_ctx* ctx, const float* q, float* k_cache, float*
     if (rc) return rc;
     const size_t smem = ((size_t)group * head_dim + group * 32 + 2 * (size_t)chunk_cap * (head_dim + 4)) * sizeof(float);
     if (smem > 48 * 1024) IBCU_CUDA(ctx, cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GatherWait gw;
+    ibcu_take_gather_wait(ctx, &gw);
     rc = ibcu_launch(ctx, attn_partial_kernel, dim3(n_kv_heads, grid_y, B), dim3(32 * group), smem, 1, true,
                      q, (const float*)k_cache, (const float*)v_cache, (float*)ctx->scratch, n_heads, n_kv_heads, head_dim, pos0, chunk, nsplit,
-                     k_new, v_new, k_cache, v_cache, theta, pos0_dev, want, chunk_cap);
+                     k_new, v_new, k_cache, v_cache, theta, pos0_dev, want, chunk_cap, gw);
     if (rc) return rc;
     const size_t csmem = ((size_t)grid_y * (head_dim + 4) + grid_y) * sizeof(float);
     IBCU_REQUIRE(ctx, csmem <= 200 * 1024, "ibcu_attention: %d chunks of cache positions are more than the merge step holds", grid_y);
@@ -512,7 +516,9 @@ extern "C" int ibcu_silu_mul_amax(ibcu_ctx* ctx, float* out, const float* gate, 
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, out && gate && up && amax && N > 0 && B > 0 && parts > 0, "ibcu_silu_mul_amax: bad arguments");
     const int chunk = (N + parts - 1) / parts;
-    return ibcu_launch(ctx, silu_mul_amax_kernel, dim3(parts, B), dim3(256), 0, 1, true, out, gate, up, N, chunk, amax);
+    GatherWait gw;
+    ibcu_take_gather_wait(ctx, &gw);
+    return ibcu_launch(ctx, silu_mul_amax_kernel, dim3(parts, B), dim3(256), 0, 1, true, out, gate, up, N, chunk, amax, gw);
 }
 
 extern "C" int ibcu_silu_mul(ibcu_ctx* ctx, float* out, const float* gate, const float* up, size_t n) {

@@ -353,9 +353,19 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const float* __restrict
 // (g, c) adds partials g, g + 8, ... of column c with its loads in flight eight at a time, then the
 // eight group sums are combined in a fixed order. Blocks [0, nS) do the sums (in double), [nS, nS + nC)
 // the counts, the last one the inertia.
+// With ex.gp.world > 0 the totals also go into this rank's slot of the exchange area (sums, then counts, then the
+// inertia); the last block copies the slot into every peer's window and publishes: every rank then adds the slots up.
+__device__ __forceinline__ size_t exch_counts_off(int KD) { return (size_t)KD * sizeof(float); }
+__device__ __forceinline__ size_t exch_inertia_off(int KD, int K) { return ((size_t)KD * sizeof(float) + (size_t)K * sizeof(int32_t) + 7) & ~(size_t)7; }
+template <typename T>
+__device__ __forceinline__ void exch_store(const ExchSlots& ex, size_t byte_off, T v) {       // into this rank's own window
+    *reinterpret_cast<T*>(ex.gp.peer[ex.gp.rank] + ex.off + (size_t)ex.gp.rank * ex.slot + byte_off) = v;
+}
+
 __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __restrict__ part_sums, const int32_t* __restrict__ part_counts,
                                                                 const double* __restrict__ part_inertia, int nblocks, int KD, int K,
-                                                                float* __restrict__ sums, int32_t* __restrict__ counts, double* __restrict__ inertia) {
+                                                                float* __restrict__ sums, int32_t* __restrict__ counts, double* __restrict__ inertia,
+                                                                const ExchSlots ex) {
     __shared__ double dsh[8][32];
     __shared__ int ish[8][32];
     pdl_launch_dependents();
@@ -371,8 +381,11 @@ __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __r
         }
         dsh[g][c] = s;
         __syncthreads();
-        if (g == 0 && e < KD)
-            sums[e] = (float)(((dsh[0][c] + dsh[1][c]) + (dsh[2][c] + dsh[3][c])) + ((dsh[4][c] + dsh[5][c]) + (dsh[6][c] + dsh[7][c])));
+        if (g == 0 && e < KD) {
+            const float v = (float)(((dsh[0][c] + dsh[1][c]) + (dsh[2][c] + dsh[3][c])) + ((dsh[4][c] + dsh[5][c]) + (dsh[6][c] + dsh[7][c])));
+            sums[e] = v;
+            if (ex.gp.world) exch_store(ex, (size_t)e * sizeof(float), v);
+        }
     } else if ((int)blockIdx.x < nS + nC) {
         const int e = (blockIdx.x - nS) * 32 + c;
         int s = 0;
@@ -382,8 +395,12 @@ __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __r
         }
         ish[g][c] = s;
         __syncthreads();
-        if (g == 0 && e < K) counts[e] = ish[0][c] + ish[1][c] + ish[2][c] + ish[3][c] + ish[4][c] + ish[5][c] + ish[6][c] + ish[7][c];
-    } else if (inertia) {
+        if (g == 0 && e < K) {
+            const int v = ish[0][c] + ish[1][c] + ish[2][c] + ish[3][c] + ish[4][c] + ish[5][c] + ish[6][c] + ish[7][c];
+            counts[e] = v;
+            if (ex.gp.world) exch_store(ex, exch_counts_off(KD) + (size_t)e * sizeof(int32_t), v);
+        }
+    } else if (inertia || ex.gp.world) {
         double s = 0.0;
 #pragma unroll 4
         for (int b = threadIdx.x; b < nblocks; b += 256) s += part_inertia[b];
@@ -392,8 +409,45 @@ __global__ void __launch_bounds__(256) accumulate_finish_kernel(const float* __r
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (c == 0) dsh[0][g] = s;
         __syncthreads();
-        if (threadIdx.x == 0)
-            *inertia = ((dsh[0][0] + dsh[0][1]) + (dsh[0][2] + dsh[0][3])) + ((dsh[0][4] + dsh[0][5]) + (dsh[0][6] + dsh[0][7]));
+        if (threadIdx.x == 0) {
+            const double v = ((dsh[0][0] + dsh[0][1]) + (dsh[0][2] + dsh[0][3])) + ((dsh[0][4] + dsh[0][5]) + (dsh[0][6] + dsh[0][7]));
+            if (inertia) *inertia = v;
+            if (ex.gp.world) exch_store(ex, exch_inertia_off(KD, K), v);
+        }
+    }
+    if (ex.gp.world) {                                        // the whole slot goes to the peers in one piece
+        const int j = push_arrive(ex.gp);
+        if (j >= 0) {
+            const size_t at = ex.off + (size_t)ex.gp.rank * ex.slot;
+            const int words = (int)((exch_inertia_off(KD, K) + 8 + 15) / 16) * 4;
+            push_span(ex.gp, j, push_count(ex.gp), reinterpret_cast<const float*>(ex.gp.peer[ex.gp.rank] + at), at, words, 1, 0);
+            push_finish(ex.gp);
+        }
+    }
+}
+
+// The all-reduce of a sharded iteration, done by the consumer: waits for the peers' slots of the exchange area, adds the
+// ranks' tables in rank order (the same order, hence the same bits, on every rank) into sums, counts and inertia.
+__global__ void __launch_bounds__(1024) exchange_sum_kernel(const ExchSlots ex, const GatherWait gw, int KD, int K,
+                                                            float* __restrict__ sums, int32_t* __restrict__ counts, double* __restrict__ inertia) {
+    pdl_launch_dependents();
+    pdl_wait();
+    gather_wait(gw);
+    const char* base = ex.gp.peer[ex.gp.rank] + ex.off;
+    for (int e = threadIdx.x; e < KD; e += blockDim.x) {
+        float s = 0.0f;
+        for (int r = 0; r < ex.gp.world; r++) s += *reinterpret_cast<const volatile float*>(base + (size_t)r * ex.slot + (size_t)e * sizeof(float));
+        sums[e] = s;
+    }
+    for (int e = threadIdx.x; e < K; e += blockDim.x) {
+        int s = 0;
+        for (int r = 0; r < ex.gp.world; r++) s += *reinterpret_cast<const volatile int*>(base + (size_t)r * ex.slot + exch_counts_off(KD) + (size_t)e * sizeof(int32_t));
+        counts[e] = s;
+    }
+    if (threadIdx.x == 0 && inertia) {
+        double s = 0.0;
+        for (int r = 0; r < ex.gp.world; r++) s += *reinterpret_cast<const volatile double*>(base + (size_t)r * ex.slot + exch_inertia_off(KD, K));
+        *inertia = s;
     }
 }
 
@@ -478,9 +532,8 @@ extern "C" int ibcu_kmeans_assign(ibcu_ctx* ctx, const float* X, long N, int D, 
     return assign_exact_launch(ctx, X, N, D, C, K, idx, dist, nullptr, nullptr, N);
 }
 
-extern "C" int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int D, int K,
-                                      const int32_t* idx, const float* dist,
-                                      float* sums, int32_t* counts, double* inertia) {
+static int kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int D, int K, const int32_t* idx, const float* dist,
+                             float* sums, int32_t* counts, double* inertia, const ExchSlots& ex) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, X && idx && sums && counts, "ibcu_kmeans_accumulate: null pointer");
     IBCU_REQUIRE(ctx, N > 0 && D >= 1 && D <= KM_MAX_D && K >= 1 && K <= 1024, "ibcu_kmeans_accumulate: N=%ld D=%d K=%d out of range", N, D, K);
@@ -508,7 +561,15 @@ extern "C" int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int
     int fin_blocks = (int)((KD + 31) / 32) + (K + 31) / 32 + 1;
     return ibcu_launch(ctx, accumulate_finish_kernel, dim3(fin_blocks), dim3(256), 0, 1, true,
                        (const float*)part_sums, (const int32_t*)part_counts, (const double*)part_inertia, (int)nblocks, (int)KD, K,
-                       sums, counts, inertia);
+                       sums, counts, inertia, ex);
+}
+
+extern "C" int ibcu_kmeans_accumulate(ibcu_ctx* ctx, const float* X, long N, int D, int K,
+                                      const int32_t* idx, const float* dist,
+                                      float* sums, int32_t* counts, double* inertia) {
+    ExchSlots none;
+    memset(&none, 0, sizeof none);
+    return kmeans_accumulate(ctx, X, N, D, K, idx, dist, sums, counts, inertia, none);
 }
 
 extern "C" int ibcu_kmeans_update(ibcu_ctx* ctx, float* C, int K, int D, const float* sums,
@@ -524,12 +585,24 @@ extern "C" int ibcu_kmeans_lloyd_iter(ibcu_ctx* ctx, const float* X, long N, int
     IBCU_REQUIRE(ctx, dist, "ibcu_kmeans_lloyd_iter: dist buffer required");
     int rc = ibcu_kmeans_assign(ctx, X, N, D, C, K, idx, dist);
     if (rc) return rc;
-    rc = ibcu_kmeans_accumulate(ctx, X, N, D, K, idx, dist, sums, counts, inertia);
+    // One exchange per iteration. Through the peer window: the kernel that finishes this rank's tables stores them into
+    // every rank's exchange area and publishes, the next kernel waits for the peers' and adds the tables in rank order.
+    // Without a window: the three all-reduces as one grouped NCCL call.
+    ExchSlots ex;
+    memset(&ex, 0, sizeof ex);
+    const size_t slot_bytes = (size_t)K * D * sizeof(float) + (size_t)K * sizeof(int32_t) + 16;
+    const int windowed = ctx->world > 1 && !ctx->capturing ? ibcu_exchange_begin(ctx, slot_bytes, &ex) : 0;
+    if (!windowed) memset(&ex, 0, sizeof ex);
+    rc = kmeans_accumulate(ctx, X, N, D, K, idx, dist, sums, counts, inertia, ex);
     if (rc) return rc;
-    if (ctx->world > 1) {
-        if ((rc = ibcu_allreduce_f32(ctx, sums, (size_t)K * D))) return rc;
-        if ((rc = ibcu_allreduce_i32(ctx, counts, (size_t)K))) return rc;
-        if (inertia && (rc = ibcu_allreduce_f64(ctx, inertia, 1))) return rc;
+    if (windowed) {
+        ctx->gather_pending = 1;
+        GatherWait gw;
+        ibcu_take_gather_wait(ctx, &gw);
+        rc = ibcu_launch(ctx, exchange_sum_kernel, dim3(1), dim3(1024), 0, 1, true, ex, gw, K * D, K, sums, counts, inertia);
+        if (rc) return rc;
+    } else if (ctx->world > 1) {
+        if ((rc = ibcu_allreduce_kmeans(ctx, sums, (size_t)K * D, counts, (size_t)K, inertia))) return rc;
     }
     return ibcu_kmeans_update(ctx, C, K, D, sums, counts, nullptr);
 }

@@ -38,6 +38,9 @@
 // the fast path does not take (row bytes not a multiple of 16, unaligned pointers) and by tests.
 #include "common.cuh"
 
+bool ibcu_push_match(ibcu_ctx* ctx, float* const* outs, int n);      // comm.cu
+void ibcu_push_fill(ibcu_ctx* ctx, GatherPush* gp, size_t bytes);  // bytes this launch pushes to each peer
+
 namespace {
 
 struct LinTensor {
@@ -47,6 +50,7 @@ struct LinTensor {
     int M, out_stride, scales_fp32, epilogue;
     int row_start;                 // first row of this tensor in the launch's concatenated row space
     int blk_start, rows_per;       // its blocks (per column slice) start at blk_start; each owns rows_per contiguous rows
+    long win_off;                  // byte offset of `out` inside the peer window when the launch pushes its rows to the peers
 };
 
 struct XSource {                   // where an activation value comes from
@@ -75,7 +79,17 @@ struct LinearParams {
     int* partial;                  // [slice][B*4][total_rows] when nks > 1
     XSource xsrc;                  // FP32 source of the activations when the block converts them itself
     int fused_x;                   // 1: convert in the block, 0: limbs were prepared by xprep_kernel
+    GatherWait gw;                 // the activations may be rows that peers pushed: wait for them (flags == NULL: nothing to wait for)
+    GatherPush gp;                 // world > 0: this rank's output rows also go into the peers' copies (row-sharded output of a gather)
 };
+
+// Pushing blocks of a launch: this rank's rows of every output tensor, which all blocks have written locally by now,
+// go into the peers' copies of the buffers.
+__device__ __forceinline__ void push_rows(const GatherPush& gp, int j, const LinTensor* t, int n_tensors, int B) {
+    const int P = push_count(gp);
+    for (int i = 0; i < n_tensors; i++)
+        push_span(gp, j, P, t[i].out, (size_t)t[i].win_off, t[i].M, B, (size_t)t[i].out_stride);
+}
 
 constexpr int LIN_LIMBS = 4;
 
@@ -397,10 +411,12 @@ __device__ __forceinline__ void xconvert_any(const XSource& src, int N, int b, i
 // main kernel would cost more than a launch (several activations, long rows, the SiLU prologue).
 template <int T>
 __global__ void __launch_bounds__(T) xprep_kernel(const XSource src, int N, int slice_cols, int xs_ld, int perm8,
-                                                     int nks, int xregs, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum) {
+                                                     int nks, int xregs, int8_t* __restrict__ xpack, float* __restrict__ xscale, int* __restrict__ xsum,
+                                                     const GatherWait gw) {
     __shared__ XScratch sc;
     pdl_launch_dependents();
     pdl_wait();
+    gather_wait(gw);
     const int ks = blockIdx.x, b = blockIdx.y;
     int8_t* dst = xpack + ((size_t)ks * (gridDim.y * LIN_LIMBS) + (size_t)b * LIN_LIMBS) * xs_ld;
     xconvert_any(src, N, b, ks * slice_cols, slice_cols, dst, xs_ld, perm8, sc, xscale + b * nks + ks, xsum + ((size_t)b * nks + ks) * LIN_LIMBS, xregs);
@@ -509,6 +525,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) pf_issue();          // weights first: they do not depend on x
     pdl_wait();
+    gather_wait(p.gw);
 
     // ── this slice's limbs, scale-back factors and limb sums ──
     if (p.fused_x) {
@@ -634,7 +651,8 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
                     const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
                                                    : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
                     float* o = T.out + (size_t)b * T.out_stride + row;
-                    *o = T.epilogue == IBCU_EPI_ADD ? *o + y * sc : y * sc;
+                    const float v = T.epilogue == IBCU_EPI_ADD ? *o + y * sc : y * sc;
+                    *o = v;
                 }
             } else {
 #pragma unroll
@@ -644,6 +662,10 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
     }
     cp_async_wait<0>();
+    if (p.gp.world && p.nks == 1) {
+        const int j = push_arrive(p.gp);
+        if (j >= 0) { push_rows(p.gp, j, p.t, p.n_tensors, p.B); push_finish(p.gp); }
+    }
 }
 
 // When the columns are split over several blocks: one thread per (row, activation) recombines the
@@ -671,7 +693,12 @@ __global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams
         const float sc = T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row]
                                        : __half2float(reinterpret_cast<const __half*>(T.scales)[row]);
         float* o = T.out + (size_t)b * T.out_stride + row;
-        *o = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
+        const float v = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
+        *o = v;
+    }
+    if (p.gp.world) {
+        const int j = push_arrive(p.gp);
+        if (j >= 0) { push_rows(p.gp, j, p.t, p.n_tensors, p.B); push_finish(p.gp); }
     }
 }
 
@@ -819,8 +846,22 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
         int row_start = 0;
         for (int i = 0; i < n_tensors; i++) {
             p.t[i] = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
-                       tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, row_start, 0, 0 };
+                       tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, row_start, 0, 0, -1 };
             row_start += tensors[i].M;
+        }
+    }
+    // multi-GPU: the activation may be a buffer whose rows the peers pushed (wait in the first kernel of this call), and
+    // the outputs may be this rank's slices of an announced gather (store them into the peers' copies from the epilogue)
+    GatherWait gw;
+    ibcu_take_gather_wait(ctx, &gw);
+    {
+        float* outs[4];
+        for (int i = 0; i < n_tensors; i++) outs[i] = tensors[i].out;
+        if (ibcu_push_match(ctx, outs, n_tensors)) {
+            size_t bytes = 0;
+            for (int i = 0; i < n_tensors; i++) bytes += (size_t)tensors[i].M * B * sizeof(float);
+            ibcu_push_fill(ctx, &p.gp, bytes);
+            for (int i = 0; i < n_tensors; i++) p.t[i].win_off = (long)((const char*)tensors[i].out - ctx->win_base);
         }
     }
     // Shared memory per block: stage ring + reduction buffer + the slice's limbs. Columns are
@@ -896,10 +937,12 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     if (!fused) {
         const dim3 xg(nks, B);
         const int perm8 = bits == 4 ? 1 : 0, cols = slice_kb * xk;
-        rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum)
-           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum)
-                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum);
+        rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum, gw)
+           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw)
+                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw);
+        gw.flags = nullptr;                                   // the conversion kernel has waited; the main kernel follows it
     }
+    p.gw = gw;
     if (rc) return rc;
     const size_t smem = piece_smem + 32 * sizeof(float) + 32 * LIN_LIMBS * sizeof(int);
 #define IBCU_DISPATCH(BITS) \
@@ -911,11 +954,14 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     }
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH
-    if (rc || nks == 1) return rc;
+    if (rc) return rc;
+    if (nks == 1) { if (p.gp.world) ctx->gather_pending = 1; return rc; }
     long outs = total_rows * B;
     int fgrid = (int)((outs + 255) / 256);
     if (fgrid > 4 * ctx->sm_count) fgrid = 4 * ctx->sm_count;
-    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p);
+    rc = ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p);
+    if (!rc && p.gp.world) ctx->gather_pending = 1;           // the peers' rows of this gather are awaited by whatever comes next
+    return rc;
 }
 
 // v1: the two projections in one launch, then the element-wise kernel over gate.out.

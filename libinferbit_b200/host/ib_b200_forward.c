@@ -258,6 +258,10 @@ static ibcu_linear_t desc(const lin* t, float* out, int epilogue) {
 static int linear_group(ib_b200_model* m, lin* const* ts, float* const* outs, int n, const float* x, int N, int B,
                         const ibcu_prologue_t* pro, int epilogue) {
     int done[3] = { 0, 0, 0 }, rc = 0;
+    float* bufs[3]; int M[3];
+    for (int i = 0; i < n; i++) { bufs[i] = outs[i]; M[i] = ts[i]->M; }
+    /* announce the gather: launches that can store their rows into the peers' copies from their epilogue then do */
+    if (m->world > 1) rc = ibcu_allgather_rows_prepare(m->ctx, bufs, M, n);
     for (int i = 0; i < n && !rc; i++) {
         if (done[i]) continue;
         ibcu_linear_t d[3];
@@ -267,8 +271,6 @@ static int linear_group(ib_b200_model* m, lin* const* ts, float* const* outs, in
         rc = ibcu_linear_ex(m->ctx, d, nd, x, N, B, ts[i]->bits, pro);
     }
     if (rc || m->world == 1) return rc;
-    float* bufs[3]; int M[3];
-    for (int i = 0; i < n; i++) { bufs[i] = outs[i]; M[i] = ts[i]->M; }
     return ibcu_allgather_rows_n(m->ctx, bufs, M, M, n, B, ROW_ALIGN);
 }
 

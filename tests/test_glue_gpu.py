@@ -130,3 +130,23 @@ def test_peer_window_single_rank():
         assert lib.ibcu_window_create(be.ctx, 1 << 20, h) != 0
     finally:
         be.close()
+
+
+def test_bounded_wait_runs_out_and_reports(backend, cpu_libs):
+    """A rank whose peer never publishes: the waiting kernel gives up at its limit, the next sync reports a communication
+    error, and after clearing it the context works as before (nothing hangs, nothing is lost)."""
+    import time
+    be = backend
+    assert be.lib.ibcu_gather_wait_probe(be.ctx) == 0
+    t0 = time.time()
+    rc = be.lib.ibcu_sync(be.ctx)
+    dt = time.time() - t0
+    assert rc == -4, rc                                              # IBCU_ERR_COMM
+    assert b"did not arrive within the wait limit" in be.lib.ibcu_last_error(be.ctx)
+    assert dt < 30.0
+    be.lib.ibcu_clear_error(be.ctx)
+    rng = np.random.default_rng(0)
+    w, s16, x = _cpu.make_int8_case(rng, 64, 256, 1)
+    s = np.empty(64, np.float32); cpu_libs.oracle.ibo_fp16_array_to_fp32(s16, s, 64)
+    want = np.empty((1, 64), np.float32); cpu_libs.oracle.ibo_matmul_int8_batch(want, w, s, x, 64, 256, 1, 64)
+    assert _cpu.close(be.linear(w, s16, x, 8), want)
