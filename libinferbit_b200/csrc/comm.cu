@@ -216,6 +216,62 @@ __global__ void __launch_bounds__(1024) allgather_push_kernel(const PushParams p
     __syncthreads();
 }
 
+// The receiving half of a tagged gather: polls the twins of the rows this rank does not own until they carry the tag of
+// this gather (bounded), copies the values into the plain buffers and, in the last block to finish, counts the gather.
+struct TagDesc { size_t off; int stride, M, row0, rows; };     // plain buffer at byte offset off; [row0, row0 + rows) is this rank's own slice
+struct TagParams { TagDesc d[4]; int n, B; char* base; size_t twin0; int* err; };
+
+__device__ __forceinline__ uint2 ld_volatile_u2(const void* p) {       // one 8-byte load: value and tag as they were stored together
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) tag_unpack_kernel(const TagParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    unsigned long long* header = reinterpret_cast<unsigned long long*>(p.base);
+    const unsigned long long count = header[IBCU_WIN_TAG_SLOT];
+    const unsigned tag = (unsigned)count + 1u;
+    const long step = (long)gridDim.x * blockDim.x;
+    for (int i = 0; i < p.n; i++) {
+        const TagDesc d = p.d[i];
+        const int remote = d.M - d.rows;
+        const long total = (long)p.B * remote;
+        float* plain = reinterpret_cast<float*>(p.base + d.off);
+        const uint2* twin = reinterpret_cast<const uint2*>(p.base + p.twin0 + 2 * (d.off - IBCU_WIN_HEADER));
+        for (long e0 = (long)blockIdx.x * blockDim.x + threadIdx.x; e0 < total; e0 += 4 * step) {
+            size_t idx[4];
+            unsigned pending = 0;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const long e = e0 + u * step;
+                idx[u] = 0;
+                if (e < total) {
+                    const int b = (int)(e / remote), rr = (int)(e % remote);
+                    idx[u] = (size_t)b * d.stride + (rr < d.row0 ? rr : rr + d.rows);
+                    pending |= 1u << u;
+                }
+            }
+            long it = 0;
+            while (pending) {
+                uint2 w[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) if (pending >> u & 1u) w[u] = ld_volatile_u2(twin + idx[u]);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if ((pending >> u & 1u) && w[u].y == tag) { plain[idx[u]] = __uint_as_float(w[u].x); pending &= ~(1u << u); }
+                if (pending && ++it > IBCU_WIN_SPIN_LIMIT / 4) { *p.err = (int)tag; break; }       // give up: the host reports it at the next sync
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* done = reinterpret_cast<unsigned*>(header + IBCU_WIN_TAG_DONE_SLOT);
+        if (atomicAdd(done, 1u) == gridDim.x - 1) { *done = 0u; header[IBCU_WIN_TAG_SLOT] = count + 1; }
+    }
+}
+
 void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw) {
     gw->flags = nullptr; gw->world = ctx->world; gw->rank = ctx->rank; gw->err = ctx->win_err;
     if (!ctx->gather_pending) return;
@@ -250,6 +306,7 @@ void ibcu_push_fill(ibcu_ctx* ctx, GatherPush* gp, size_t bytes) {
     memset(gp, 0, sizeof *gp);
     gp->world = ctx->world; gp->rank = ctx->rank;
     gp->err = ctx->win_err;
+    gp->twin0 = ctx->win_bytes;
     long P = (long)(bytes / (16 * 1024));                     // one pushing block per 16 KB, at most 16
     gp->pushers = P < 1 ? 1 : P > 16 ? 16 : (int)P;
     gp->header = reinterpret_cast<unsigned long long*>(ctx->win_base);
@@ -263,10 +320,12 @@ extern "C" int ibcu_window_create(ibcu_ctx* ctx, size_t bytes, void* handle_out)
     if (ctx->win_base) return ibcu_fail(ctx, IBCU_ERR_STATE, "window already created");
     IBCU_REQUIRE(ctx, ctx->world <= IBCU_MAX_RANKS, "ibcu_window_create: %d ranks, at most %d", ctx->world, IBCU_MAX_RANKS);
     IBCU_CUDA(ctx, cudaSetDevice(ctx->device));
-    const size_t total = WIN_HEADER + ((bytes + 255) & ~(size_t)255);
+    // header, then the plain part that buffers are taken from, then the tagged part: an 8-byte {value, tag} twin of every float
+    const size_t plain = (bytes + 255) & ~(size_t)255;
+    const size_t total = WIN_HEADER + plain;
     void* base = nullptr;
-    IBCU_CUDA(ctx, cudaMalloc(&base, total));
-    IBCU_CUDA(ctx, cudaMemset(base, 0, total));
+    IBCU_CUDA(ctx, cudaMalloc(&base, total + 2 * plain));
+    IBCU_CUDA(ctx, cudaMemset(base, 0, total + 2 * plain));
     IBCU_CUDA(ctx, cudaDeviceSynchronize());
     IBCU_CUDA(ctx, cudaHostAlloc((void**)&ctx->win_err, sizeof(int), cudaHostAllocMapped));
     *ctx->win_err = 0;
@@ -358,8 +417,22 @@ extern "C" int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const in
         for (int i = 0; i < n && done; i++) done = ctx->arm_buf[i] == (const char*)bufs[i] && ctx->arm_done[i];
         ctx->arm_n = 0;
         if (done) {
+            // every rank's rows are on their way, tagged, to every other rank's window: receive this rank's copies
             for (int j = 0; j < 4; j++) ctx->win_last[j] = j < n ? bufs[j] : nullptr;
-            return IBCU_OK;
+            TagParams tp;
+            memset(&tp, 0, sizeof tp);
+            tp.n = n; tp.B = B; tp.base = ctx->win_base; tp.twin0 = ctx->win_bytes; tp.err = ctx->win_err;
+            long elems = 0;
+            for (int i = 0; i < n; i++) {
+                int r0, rn;
+                ibcu_shard_rows(M[i], ctx->world, ctx->rank, align, &r0, &rn);
+                tp.d[i] = { (size_t)((const char*)bufs[i] - ctx->win_base), stride[i], M[i], r0, rn };
+                elems += (long)B * (M[i] - rn);
+            }
+            long blocks = (elems + 2047) / 2048;              // 8 elements per thread
+            if (blocks < 1) blocks = 1;
+            if (blocks > 64) blocks = 64;
+            return ibcu_launch(ctx, tag_unpack_kernel, dim3((unsigned)blocks), dim3(256), 0, 1, true, tp);
         }
     }
     { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }

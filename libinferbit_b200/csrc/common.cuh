@@ -37,7 +37,7 @@ struct ibcu_ctx {
     ncclComm* comm;
     int rank, world;
     // peer window: a slab of this GPU's memory that the other ranks map and write their row slices into
-    char*  win_base;   size_t win_bytes, win_used;
+    char*  win_base;   size_t win_bytes, win_used;   // win_bytes: header + plain part (buffers); the tagged part of twice that size follows
     char*  win_peer[IBCU_MAX_RANKS];               // win_peer[rank] == win_base
     int    win_open;                                // peers mapped so far
     int    win_enabled;
@@ -57,14 +57,15 @@ struct ibcu_ctx {
 constexpr size_t IBCU_WIN_HEADER = 4096;
 constexpr int IBCU_WIN_EPOCH_SLOT = IBCU_MAX_RANKS;
 constexpr int IBCU_WIN_DONE_SLOT = IBCU_MAX_RANKS + 1;
-constexpr int IBCU_WIN_READY_SLOT = IBCU_MAX_RANKS + 2;
-constexpr int IBCU_WIN_GO_SLOT = IBCU_MAX_RANKS + 3;         // the epoch about to be published once every block of the pushing launch has arrived      // the epoch up to which block 0 of a waiting kernel has seen every peer arrive
+constexpr int IBCU_WIN_GO_SLOT = IBCU_MAX_RANKS + 2;         // the epoch about to be published once every block of the pushing launch has arrived
+constexpr int IBCU_WIN_TAG_SLOT = IBCU_MAX_RANKS + 3;        // number of tagged gathers this rank has received in full
+constexpr int IBCU_WIN_TAG_DONE_SLOT = IBCU_MAX_RANKS + 4;   // blocks of the receiving kernel that are through
 constexpr long IBCU_WIN_SPIN_LIMIT = 4L * 1000 * 1000;       // about a second of polling
 
 // What a kernel needs to wait for the peers' rows of the gather that precedes it (flags == NULL: nothing to wait for).
 struct GatherWait { const unsigned long long* flags; int world, rank; int* err; };
 // What a linear launch needs to store its rows into the peers' copies and to publish that it has (world == 0: no push).
-struct GatherPush { char* peer[IBCU_MAX_RANKS]; unsigned long long* header; int world, rank, pushers; int* err; };
+struct GatherPush { char* peer[IBCU_MAX_RANKS]; unsigned long long* header; int world, rank, pushers; int* err; size_t twin0; };
 
 // Every rank's table for a small all-reduce: rank r's copy sits at off + r * slot in every rank's window.
 struct ExchSlots { GatherPush gp; size_t off, slot; };
@@ -174,6 +175,22 @@ __device__ __forceinline__ void gather_wait(const GatherWait& g) {
         }
     }
     __syncthreads();
+}
+
+// Tagged gather (the low-latency path of a gather whose rows a linear launch produces). The window has a second part
+// of twice the size of the first: the float at byte offset off of the first part has an 8-byte twin at
+// twin0 + 2 * (off - IBCU_WIN_HEADER), holding the value and a tag. The producing launch stores every result into its
+// own buffer and, as {value, tag} in ONE 8-byte store, into the twin in every peer's window: no fence and no flag, the
+// tag travels with the value. tag = number of tagged gathers received so far + 1, the same on every rank because every
+// rank takes part in every gather; the receiving kernel (tag_unpack_kernel) polls the twins of the rows it does not own
+// until they carry the tag, copies the values into the plain buffer and counts the gather. A zeroed window never
+// matches (tags start at 1); the count wraps after 2^32 gathers.
+__device__ __forceinline__ unsigned tag_current(const GatherPush& gp) { return (unsigned)gp.header[IBCU_WIN_TAG_SLOT] + 1u; }
+__device__ __forceinline__ void tag_push(const GatherPush& gp, size_t off, float v, unsigned tag) {
+    const size_t at = gp.twin0 + 2 * (off - IBCU_WIN_HEADER);
+    const uint2 w = make_uint2(__float_as_uint(v), tag);
+    for (int q = 0; q < gp.world; q++)
+        if (q != gp.rank) asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" :: "l"(gp.peer[q] + at), "r"(w.x), "r"(w.y) : "memory");
 }
 
 // The pushing half of a gather, at the end of the launch that produced the rows. Every block writes its results into

@@ -83,14 +83,6 @@ struct LinearParams {
     GatherPush gp;                 // world > 0: this rank's output rows also go into the peers' copies (row-sharded output of a gather)
 };
 
-// Pushing blocks of a launch: this rank's rows of every output tensor, which all blocks have written locally by now,
-// go into the peers' copies of the buffers.
-__device__ __forceinline__ void push_rows(const GatherPush& gp, int j, const LinTensor* t, int n_tensors, int B) {
-    const int P = push_count(gp);
-    for (int i = 0; i < n_tensors; i++)
-        push_span(gp, j, P, t[i].out, (size_t)t[i].win_off, t[i].M, B, (size_t)t[i].out_stride);
-}
-
 constexpr int LIN_LIMBS = 4;
 
 // ── activation split ────────────────────────────────────────────────────────────────────
@@ -625,6 +617,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
         __syncthreads();
         const int B = p.B;
+        const unsigned tag = p.gp.world ? tag_current(p.gp) : 0u;
         // one thread per (row, activation): limb sums over the warps, bias, recombination
         for (int e = threadIdx.x; e < R * B; e += W * 32) {
             const int r = e % R, b = e / R;
@@ -653,6 +646,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
                     float* o = T.out + (size_t)b * T.out_stride + row;
                     const float v = T.epilogue == IBCU_EPI_ADD ? *o + y * sc : y * sc;
                     *o = v;
+                    if (p.gp.world) tag_push(p.gp, (size_t)T.win_off + ((size_t)b * T.out_stride + row) * sizeof(float), v, tag);
                 }
             } else {
 #pragma unroll
@@ -662,10 +656,6 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
     }
     cp_async_wait<0>();
-    if (p.gp.world && p.nks == 1) {
-        const int j = push_arrive(p.gp);
-        if (j >= 0) { push_rows(p.gp, j, p.t, p.n_tensors, p.B); push_finish(p.gp); }
-    }
 }
 
 // When the columns are split over several blocks: one thread per (row, activation) recombines the
@@ -675,6 +665,7 @@ __global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams
     pdl_wait();
     const int B = p.B;
     const long total = (long)p.total_rows * B;
+    const unsigned tag = p.gp.world ? tag_current(p.gp) : 0u;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
         const int vrow = (int)(e % p.total_rows);
         const int b = (int)(e / p.total_rows);
@@ -695,10 +686,7 @@ __global__ void __launch_bounds__(256) linear_finalize_kernel(const LinearParams
         float* o = T.out + (size_t)b * T.out_stride + row;
         const float v = T.epilogue == IBCU_EPI_ADD ? *o + (float)y * sc : (float)y * sc;
         *o = v;
-    }
-    if (p.gp.world) {
-        const int j = push_arrive(p.gp);
-        if (j >= 0) { push_rows(p.gp, j, p.t, p.n_tensors, p.B); push_finish(p.gp); }
+        if (p.gp.world) tag_push(p.gp, (size_t)T.win_off + ((size_t)b * T.out_stride + row) * sizeof(float), v, tag);
     }
 }
 
@@ -850,8 +838,8 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
             row_start += tensors[i].M;
         }
     }
-    // multi-GPU: the activation may be a buffer whose rows the peers pushed (wait in the first kernel of this call), and
-    // the outputs may be this rank's slices of an announced gather (store them into the peers' copies from the epilogue)
+    // multi-GPU: a windowed exchange may be pending (wait in the first kernel of this call), and the outputs may be this
+    // rank's slices of an announced gather (every result also goes, tagged, into the peers' windows from the epilogue)
     GatherWait gw;
     ibcu_take_gather_wait(ctx, &gw);
     {
@@ -955,13 +943,11 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     if (bits == 8) { IBCU_DISPATCH(8) } else { IBCU_DISPATCH(4) }
 #undef IBCU_DISPATCH
     if (rc) return rc;
-    if (nks == 1) { if (p.gp.world) ctx->gather_pending = 1; return rc; }
+    if (nks == 1) return rc;
     long outs = total_rows * B;
     int fgrid = (int)((outs + 255) / 256);
     if (fgrid > 4 * ctx->sm_count) fgrid = 4 * ctx->sm_count;
-    rc = ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p);
-    if (!rc && p.gp.world) ctx->gather_pending = 1;           // the peers' rows of this gather are awaited by whatever comes next
-    return rc;
+    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, p);
 }
 
 // v1: the two projections in one launch, then the element-wise kernel over gate.out.
