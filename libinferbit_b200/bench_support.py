@@ -374,12 +374,14 @@ DECODE_NOTE = ("random weights as the configuration says except that the per-row
                "replay of the same CUDA graph (the position is read on the device) at positions 512, 512 + B, ..., 512 + 7 B in turn")
 
 
-def _decode(lib, host, ctx, B, rank, world, max_over_ranks, barrier, steps=20, warm=60, check_single=True):
+def _decode(lib, host, ctx, B, rank, world, max_over_ranks, barrier, steps=20, warm=60, check_single=True, graph=True):
     cfg = ModelCfg(*DECODE_CFG)
     m = host.ib_b200_model_create(ctx, C.byref(cfg))
     if not m:
         return {"error": "model allocation failed"}
     assert host.ib_b200_model_fill_random(m, 4321, 512) == 0
+    if not graph:
+        host.ib_b200_model_use_graph(m, 0)                 # launches issued one by one (a profiler then sees kernels)
     toks = np.arange(B, dtype=np.int32) * 7 + 11
     check(lib, ctx, lib.ibcu_memcpy_h2d(ctx, host.ib_b200_model_tokens(m), toks.ctypes.data, toks.nbytes))
     V = cfg.vocab
