@@ -163,6 +163,27 @@ class CpuBaseline:
             r["sample"] += f"; ib_parallel_matmul_int8_batch (scalar on x86-64): best of {reps2}"
         return r
 
+    def w4a8(self, M, N, B, algo_bytes):
+        """the reference's default route for an INT4 linear: ib_quantize_input_int8_g128 per activation, then
+        ib_parallel_matmul_w4a8 on the pool (src/forward.c:175-246)"""
+        if self.kind != "reference":
+            return None
+        rng = np.random.default_rng(1)
+        w = rng.integers(0, 256, (M, N // 2), dtype=np.uint8)
+        s = rng.uniform(0.002, 0.02, M).astype(np.float32)
+        x = rng.standard_normal((B, N)).astype(np.float32)
+        q = np.empty((B, N), np.int8); sa = np.empty((B, (N + 127) // 128), np.float32)
+        out = np.empty((B, M), np.float32)
+        L, p = self.lib, lambda a: a.ctypes.data
+        L.ib_parallel_matmul_w4a8.argtypes = [C.c_void_p] * 6 + [C.c_int] * 2
+        L.ib_quantize_input_int8_g128.argtypes = [C.c_void_p] * 3 + [C.c_int]
+        def fn():
+            for b in range(B):
+                L.ib_quantize_input_int8_g128(p(x) + 4 * b * N, p(q) + b * N, p(sa) + 4 * b * sa.shape[1], N)
+                L.ib_parallel_matmul_w4a8(self.pool, p(out) + 4 * b * M, p(w), p(s), p(q) + b * N, p(sa) + 4 * b * sa.shape[1], M, N)
+        t, reps = _time_calls(fn, 1.5)
+        return self._base(algo_bytes / t / 1e9, "GB/s", f"best of {reps}: ib_quantize_input_int8_g128 + ib_parallel_matmul_w4a8 x {B}")
+
     def pq(self, M, N, G, K, B, algo_bytes):
         if self.kind != "reference":
             return None
@@ -342,6 +363,9 @@ def main():
             "int8_4096x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 1, reps_target_bytes=300e6),
             "int8_32000x4096_b1": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 1, reps_target_bytes=400e6),
             "int4_14336x4096_b1": lambda: bs._linear_ring(lib, ctx, 4, 14336, 4096, 1, reps_target_bytes=300e6),
+            "w4a8_14336x4096_b1": lambda: bs._w4a8_ring(lib, ctx, 14336, 4096, 1),
+            "w4a8_4096x14336_b1": lambda: bs._w4a8_ring(lib, ctx, 4096, 14336, 1),
+            "w4a8_14336x4096_b8": lambda: bs._w4a8_ring(lib, ctx, 14336, 4096, 8),
             "int8_4096x4096_b16": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 16, reps_target_bytes=300e6),
             "int4_5632x2048_b1": lambda: bs._linear_ring(lib, ctx, 4, 5632, 2048, 1, reps_target_bytes=300e6),
             "pq_4096x14336_b1": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 1),
@@ -451,7 +475,9 @@ def main():
                 if not isinstance(e, dict):
                     continue
                 try:
-                    if name.startswith(("int4_", "int8_")):
+                    if name.startswith("w4a8_"):
+                        sh = e["shape"]; e["cpu_baseline"] = cpu.w4a8(sh["M"], sh["N"], sh["B"], e["algorithmic_bytes"])
+                    elif name.startswith(("int4_", "int8_")):
                         sh = e["shape"]; e["cpu_baseline"] = cpu.linear(sh["bits"], sh["M"], sh["N"], sh["B"], e["algorithmic_bytes"])
                     elif name.startswith("pq_"):
                         sh = e["shape"]; e["cpu_baseline"] = cpu.pq(sh["M"], sh["N"], sh["G"], sh["K"], sh["B"], e["algorithmic_bytes"])

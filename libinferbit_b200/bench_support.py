@@ -274,6 +274,33 @@ def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
             "shape": {"bits": bits, "M": M, "N": N, "B": B}}
 
 
+def _w4a8_ring(lib, ctx, M, N, B, reps_target_bytes=300e6):
+    """The reference's default route for an INT4 linear (src/forward.c:175-246 with IB_W4A8 on): quantise the activation per
+    128-column group, then the INT4 x INT8 matvec; both launches are inside the timed call."""
+    dev = Dev(lib, ctx)
+    wbytes = M * N // 2
+    R = max(2, int(reps_target_bytes // wbytes))
+    groups = (N + 127) // 128
+    dW = dev.alloc(R * wbytes); check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, dW, R * wbytes, 17))
+    dS = dev.alloc(M * 2); check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, dS, M, 18, 0.002, 0.02))
+    dx = dev.upload(np.random.default_rng(0).standard_normal((B, N)).astype(np.float32))
+    dq, dsa, do = dev.alloc(B * N), dev.alloc(B * groups * 4), dev.alloc(B * M * 4)
+    descs = [LinearT(dW + r * wbytes, dS, do, M, M, 0, 0) for r in range(R)]
+
+    def run():
+        for d in descs:
+            check(lib, ctx, lib.ibcu_quantize_input_int8_g128(ctx, dx, dq, dsa, N, B))
+            check(lib, ctx, lib.ibcu_linear_w4a8(ctx, C.byref(d), dq, dsa, N, B))
+    gid = dev.graph(run)
+    dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
+    ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid), reps=5) for _ in range(3)) / R
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    algo = wbytes + 2 * M + 4 * B * N + 4 * B * M
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
+            "shape": {"bits": 4, "activation_bits": 8, "M": M, "N": N, "B": B}, "route": "quantize_input_int8_g128 + matmul_w4a8"}
+
+
 def _pq(lib, ctx, M, N, G, K, B):
     dev = Dev(lib, ctx)
     rng = np.random.default_rng(3)
@@ -457,6 +484,8 @@ def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier, pe
         out["int4_tinyllama_up_5632x2048_b1"] = _linear_ring(lib, ctx, 4, 5632, 2048, 1)
         out["int4_gate_14336x4096_b1"] = _linear_ring(lib, ctx, 4, 14336, 4096, 1)
         out["int4_down_4096x14336_b1"] = _linear_ring(lib, ctx, 4, 4096, 14336, 1)
+        out["w4a8_gate_14336x4096_b1"] = _w4a8_ring(lib, ctx, 14336, 4096, 1)
+        out["w4a8_down_4096x14336_b1"] = _w4a8_ring(lib, ctx, 4096, 14336, 1)
         out["int8_q_4096x4096_b1"] = _linear_ring(lib, ctx, 8, 4096, 4096, 1)
         out["int8_q_4096x4096_b4"] = _linear_ring(lib, ctx, 8, 4096, 4096, 4)
         out["int8_q_4096x4096_b16"] = _linear_ring(lib, ctx, 8, 4096, 4096, 16)

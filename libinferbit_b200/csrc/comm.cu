@@ -325,12 +325,18 @@ extern "C" int ibcu_window_create(ibcu_ctx* ctx, size_t bytes, void* handle_out)
     const size_t total = WIN_HEADER + plain;
     void* base = nullptr;
     IBCU_CUDA(ctx, cudaMalloc(&base, total + 2 * plain));
-    IBCU_CUDA(ctx, cudaMemset(base, 0, total + 2 * plain));
-    IBCU_CUDA(ctx, cudaDeviceSynchronize());
-    IBCU_CUDA(ctx, cudaHostAlloc((void**)&ctx->win_err, sizeof(int), cudaHostAllocMapped));
-    *ctx->win_err = 0;
+    int* err_word = nullptr;
     cudaIpcMemHandle_t h;
-    IBCU_CUDA(ctx, cudaIpcGetMemHandle(&h, base));
+    cudaError_t e = cudaMemset(base, 0, total + 2 * plain);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess && !ctx->win_err) e = cudaHostAlloc((void**)&err_word, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, base);
+    if (e != cudaSuccess) {                                   // nothing is kept of a window that could not be made
+        cudaFree(base);
+        if (err_word) cudaFreeHost(err_word);
+        return ibcu_fail(ctx, IBCU_ERR_CUDA, "ibcu_window_create: %s", cudaGetErrorString(e));
+    }
+    if (err_word) { *err_word = 0; ctx->win_err = err_word; }
     memset(handle_out, 0, IBCU_WINDOW_HANDLE_BYTES);
     memcpy(handle_out, &h, sizeof h);
     ctx->win_base = (char*)base; ctx->win_bytes = total; ctx->win_used = WIN_HEADER;

@@ -84,6 +84,10 @@ struct LinearParams {
 };
 
 constexpr int LIN_LIMBS = 4;
+// Row length of the reduction buffer in words. With more than one group of 8 columns the rows are padded by 4 words:
+// rows then start 4 banks apart and the 128-bit reads of a (row, activation)'s four limbs never collide. One group keeps
+// its 8 words (a two-way collision there costs less than the shared memory the padding would take from the ring).
+__host__ __device__ constexpr int lin_rld(int ncg) { return ncg == 1 ? 8 : ncg * 8 + 4; }
 
 // ── activation split ────────────────────────────────────────────────────────────────────
 // grid (nks, B), one block per slice of one activation: X = rint(x * 2^s) with 2^s * max|x| in
@@ -451,6 +455,7 @@ template <int BITS, int NCG, int RT, int W, int STAGES>
 __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p) {
     constexpr int R = RT * 16;                                // most rows per tile
     constexpr int COLS = NCG * 8;
+    constexpr int RLD = lin_rld(NCG);                         // words per row of the reduction buffer
     constexpr int NACC = BITS == 4 ? 2 : 1;                   // INT4 keeps low- and high-nibble sums apart
     constexpr int XB = BITS == 8 ? 64 : 128;                  // limb bytes (= columns) per k-block
     constexpr int KBS = W;                                    // k-blocks per stage: one per warp
@@ -477,7 +482,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
 
     unsigned char* ring = smem_raw;
     int* red = reinterpret_cast<int*>(smem_raw + STAGES * STAGE_BYTES);
-    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw + STAGES * STAGE_BYTES + NACC * W * R * COLS * 4);
+    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw + STAGES * STAGE_BYTES + NACC * W * R * RLD * 4);
     float* s_back = reinterpret_cast<float*>(xs + (((size_t)p.ncols * p.xs_ld + 15) & ~(size_t)15));
     int* s_xsum = reinterpret_cast<int*>(s_back + 32);
 
@@ -606,13 +611,13 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         // ── tile done: every warp holds integer partial sums of all R rows over its k-blocks ──
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
-            int* mine = red + ((size_t)a * W + warp) * R * COLS;
+            int* mine = red + ((size_t)a * W + warp) * R * RLD;
 #pragma unroll
             for (int i = 0; i < RT; i++)
 #pragma unroll
                 for (int c = 0; c < NCG; c++) {
-                    *reinterpret_cast<int2*>(mine + (i * 16 + g) * COLS + c * 8 + 2 * t) = make_int2(acc[a][i][c][0], acc[a][i][c][1]);
-                    *reinterpret_cast<int2*>(mine + (i * 16 + g + 8) * COLS + c * 8 + 2 * t) = make_int2(acc[a][i][c][2], acc[a][i][c][3]);
+                    *reinterpret_cast<int2*>(mine + (i * 16 + g) * RLD + c * 8 + 2 * t) = make_int2(acc[a][i][c][0], acc[a][i][c][1]);
+                    *reinterpret_cast<int2*>(mine + (i * 16 + g + 8) * RLD + c * 8 + 2 * t) = make_int2(acc[a][i][c][2], acc[a][i][c][3]);
                 }
         }
         __syncthreads();
@@ -624,18 +629,26 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
             if (r >= tile_rows) continue;
             const int row = row0 + r;
             int limb[LIN_LIMBS];
+            {                                                 // the four limbs of (row, activation) sit side by side: one 128-bit read per warp
+                int4 lo = make_int4(0, 0, 0, 0);
 #pragma unroll
-            for (int l = 0; l < LIN_LIMBS; l++) {
-                int v = 0;
-#pragma unroll
-                for (int w = 0; w < W; w++) v += red[((size_t)w * R + r) * COLS + b * LIN_LIMBS + l];
-                if (BITS == 4) {
-                    int hi = 0;
-#pragma unroll
-                    for (int w = 0; w < W; w++) hi += red[((size_t)(W + w) * R + r) * COLS + b * LIN_LIMBS + l];
-                    v += (hi >> 4) - 8 * s_xsum[b * LIN_LIMBS + l];
+                for (int w = 0; w < W; w++) {
+                    const int4 v = *reinterpret_cast<const int4*>(red + ((size_t)w * R + r) * RLD + b * LIN_LIMBS);
+                    lo.x += v.x; lo.y += v.y; lo.z += v.z; lo.w += v.w;
                 }
-                limb[l] = v;
+                if (BITS == 4) {
+                    int4 hi = make_int4(0, 0, 0, 0);
+#pragma unroll
+                    for (int w = 0; w < W; w++) {
+                        const int4 v = *reinterpret_cast<const int4*>(red + ((size_t)(W + w) * R + r) * RLD + b * LIN_LIMBS);
+                        hi.x += v.x; hi.y += v.y; hi.z += v.z; hi.w += v.w;
+                    }
+                    lo.x += (hi.x >> 4) - 8 * s_xsum[b * LIN_LIMBS + 0];
+                    lo.y += (hi.y >> 4) - 8 * s_xsum[b * LIN_LIMBS + 1];
+                    lo.z += (hi.z >> 4) - 8 * s_xsum[b * LIN_LIMBS + 2];
+                    lo.w += (hi.w >> 4) - 8 * s_xsum[b * LIN_LIMBS + 3];
+                }
+                limb[0] = lo.x; limb[1] = lo.y; limb[2] = lo.z; limb[3] = lo.w;
             }
             if (p.nks == 1) {
                 {
@@ -727,7 +740,7 @@ __global__ void __launch_bounds__(256) linear_generic_kernel(LinTensor T, const 
 template <int BITS, int NCG, int RT, int W, int STAGES>
 int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail) {
     auto kern = linear_mma_kernel<BITS, NCG, RT, W, STAGES>;
-    const size_t smem = (size_t)STAGES * RT * 16 * lin_ld(W) + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * NCG * 8 * 4 + smem_tail;
+    const size_t smem = (size_t)STAGES * RT * 16 * lin_ld(W) + (size_t)(BITS == 4 ? 2 : 1) * W * RT * 16 * lin_rld(NCG) * 4 + smem_tail;   // ring + reduction buffer + limbs
     if (smem > 48 * 1024) {
         static size_t allowed[64];                                 // per device, per kernel instance: raised only when a call needs more
         size_t& have = allowed[ctx->device & 63];
@@ -857,7 +870,7 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     const int kbs = w;
     const int LIN_LD = lin_ld(w);
     // ring depth: the deeper ring when two blocks per SM still fit with it, else the shallower one
-    const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * w * R * ncg * 8 * 4;
+    const size_t red_bytes = (size_t)(bits == 4 ? 2 : 1) * w * R * lin_rld(ncg) * 4;
     const size_t whole_row_pieces = (size_t)ncols * ((size_t)nkb * xk + xpad);
     int stages = rt == 2 ? 6 : 8;
     if (2 * ((size_t)stages * R * LIN_LD + red_bytes + whole_row_pieces + 2048) > 227 * 1024) stages = 4;

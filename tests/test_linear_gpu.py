@@ -175,14 +175,18 @@ def test_bad_arguments_are_refused(backend):
     assert be.lib.ibcu_status(be.ctx) == 0
 
 
-@pytest.mark.parametrize("N", [128, 4096, 200])
-def test_w4a8_route_bit_exact(backend, cpu_libs, N):
+@pytest.mark.parametrize("N,B,M", [(128, 3, 70), (4096, 3, 70), (200, 3, 70), (14336, 1, 333), (4096, 8, 512), (2048, 11, 100),
+                                   (4096, 1, 4096)])
+def test_w4a8_route_bit_exact(backend, cpu_libs, N, B, M):
     """Activation quantiser (src/threading.c:401-432) and INT4 x INT8 kernel (src/kernels/scalar.c:43-124):
-    integer work, so the bar is bit-exact, including the FP32 accumulation order."""
-    rng = np.random.default_rng(N)
-    B, M = 3, 70
+    integer work, so the bar is bit-exact, including the FP32 accumulation order. Whole groups of 128 columns
+    take the tensor-core kernel (more than 8 activations in chunks of 8), N = 200 the row-per-warp kernel;
+    both are also run against each other."""
+    rng = np.random.default_rng(N + B)
     be = backend
-    x = rng.standard_normal((B, N)).astype(np.float32); x[1, :64] = 0; x[2, :] *= 1e-12
+    x = rng.standard_normal((B, N)).astype(np.float32)
+    if B >= 3:
+        x[1, :64] = 0; x[2, :] *= 1e-12
     groups = (N + 127) // 128
     q = np.empty((B, N), np.int8); sa = np.empty((B, groups), np.float32)
     for b in range(B):
@@ -200,6 +204,14 @@ def test_w4a8_route_bit_exact(backend, cpu_libs, N):
     t = LinearT(be.upload(w).ptr, be.upload(s16).ptr, do.ptr, M, M, 0, 0)
     be._check(be.lib.ibcu_linear_w4a8(be.ctx, C.byref(t), dq.ptr, dsa.ptr, N, B)); be.sync()
     assert np.array_equal(be.download(do, np.float32, B * M).reshape(B, M), want)
+    be.lib.ibcu_linear_force_generic(be.ctx, 1)             # the row-per-warp kernel on the same inputs
+    try:
+        do2 = be.alloc(B * M * 4)
+        t2 = LinearT(t.w, t.scales, do2.ptr, M, M, 0, 0)
+        be._check(be.lib.ibcu_linear_w4a8(be.ctx, C.byref(t2), dq.ptr, dsa.ptr, N, B)); be.sync()
+        assert np.array_equal(be.download(do2, np.float32, B * M).reshape(B, M), want)
+    finally:
+        be.lib.ibcu_linear_force_generic(be.ctx, 0)
 
 
 @pytest.mark.parametrize("bits,N", [(8, 1024), (4, 2048), (8, 200)])
