@@ -145,8 +145,9 @@ int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* tensor, const int8_t* x
 
 /* ── PQ matvec ───────────────────────────────────────────────────────────────────────── */
 /* Stands in for ib_pq_matmul_fp32 / _threaded / _streaming (src/pq_decode.h:189-222; body
- * src/pq_decode.c:1504-1682) for single-level tensors without outlier columns. Field meanings
- * follow ib_pq_tensor (src/pq_decode.h:39-87). All pointers are device pointers. */
+ * src/pq_decode.c:1504-1682), including the second residual level with one-byte or 4-bit packed indices
+ * (K_l2 <= 256; src/pq_decode.c:1058-1075, :1441-1496) and the int8 outlier sidecar (:1394-1409). Field
+ * meanings follow ib_pq_tensor (src/pq_decode.h:39-87). All pointers are device pointers. */
 typedef struct {
     int M, N, G, K;                   /* K <= 256, G even, N % G == 0, C = N / G chunks */
     const uint16_t* codebook_l;       /* fp16 [K * G/2] (shared by all chunks) */
@@ -157,6 +158,17 @@ typedef struct {
     const uint16_t* row_scale;        /* fp16 [M] */
     const uint8_t*  idx_t;            /* regrouped copy of the codes made by ibcu_pq_prepare */
     int             M_pad;
+    /* production extras; all zero / NULL for a plain single-level tensor */
+    int             K_l2;             /* > 0: a second residual level with K_l2 <= 256 entries per shared codebook */
+    const uint16_t* codebook2_l;      /* fp16 [K_l2 * G/2] */
+    const uint16_t* codebook2_r;
+    const uint8_t*  idx2_l;           /* [M * C] bytes, or [M * (C+1)/2] bytes of two 4-bit indices (low nibble = even chunk) when K_l2 == 16 */
+    const uint8_t*  idx2_r;
+    int             n_outlier;        /* > 0: that many columns of x bypass the tables; then C = (N - n_outlier) / G */
+    const int32_t*  outlier_cols;     /* [n_outlier] ascending */
+    const int8_t*   outlier_sidecar;  /* [M * n_outlier] */
+    const uint16_t* outlier_scale;    /* fp16 [n_outlier] */
+    const int32_t*  inner_cols;       /* [N - n_outlier] the other columns, made by ibcu_pq_prepare */
 } ibcu_pq_t;
 
 /* One-off per tensor (like the reference's ib_pq_lut_cache regrouped index layout,
@@ -165,6 +177,8 @@ typedef struct {
  * the largest codebook magnitude into idx_t_out, which must hold ibcu_pq_idx_t_bytes(M, N, G) bytes, and
  * fills t->idx_t / t->M_pad. Needs the tensor's codebooks as well as its codes. */
 size_t ibcu_pq_idx_t_bytes(int M, int N, int G);
+/* the same for any tensor: both levels' regrouped codes, the tail, and the list of inner columns when there are outliers */
+size_t ibcu_pq_prepared_bytes(const ibcu_pq_t* t);
 int    ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out);
 /* out[b*M + r] = row_scale[r] * sum_c (TL[c][idx_l[r,c]] + TR[c][idx_r[r,c]]) for B activations
  * x[b*N + j]; applies the reference's 1 %-of-max chunk skip rule per activation. One launch; the sums of a

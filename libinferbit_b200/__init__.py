@@ -147,6 +147,30 @@ class Backend:
         t._keep = bufs + [dt]
         return t
 
+    def make_pq_ex(self, d):
+        """Upload a PQ tensor given as a dict of arrays in the reference's layout: cb1_l/r, idx1_l/r, rs, and optionally the
+        second level (cb2_l/r, idx2_l/r, K_l2; 4-bit packed indices when K_l2 == 16) and the outlier sidecar (ocols, oside,
+        oscale, n_outlier)."""
+        t = PqT()
+        t.M, t.N, t.G, t.K = d["M"], d["N"], d["G"], d["K"]
+        keep = []
+        def up(name):
+            if name not in d:
+                return None
+            b = self.upload(d[name]); keep.append(b)
+            return b.ptr
+        t.codebook_l, t.codebook_r, t.idx_l, t.idx_r, t.row_scale = up("cb1_l"), up("cb1_r"), up("idx1_l"), up("idx1_r"), up("rs")
+        t.cb_chunk_stride = 0
+        t.K_l2 = d.get("K_l2", 0)
+        t.codebook2_l, t.codebook2_r, t.idx2_l, t.idx2_r = up("cb2_l"), up("cb2_r"), up("idx2_l"), up("idx2_r")
+        t.n_outlier = d.get("n_outlier", 0)
+        t.outlier_cols, t.outlier_sidecar, t.outlier_scale = up("ocols"), up("oside"), up("oscale")
+        dt = self.alloc(self.lib.ibcu_pq_prepared_bytes(C.byref(t)))
+        self._check(self.lib.ibcu_pq_prepare(self.ctx, C.byref(t), dt.ptr))
+        self.sync()
+        t._keep = keep + [dt]
+        return t
+
     def pq_matmul(self, t, x):
         x = np.ascontiguousarray(x, dtype=np.float32)
         if x.ndim == 1:

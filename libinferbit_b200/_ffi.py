@@ -30,7 +30,10 @@ class PqT(C.Structure):
     _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K", C.c_int),
                 ("codebook_l", C.c_void_p), ("codebook_r", C.c_void_p), ("cb_chunk_stride", C.c_long),
                 ("idx_l", C.c_void_p), ("idx_r", C.c_void_p), ("row_scale", C.c_void_p),
-                ("idx_t", C.c_void_p), ("M_pad", C.c_int)]
+                ("idx_t", C.c_void_p), ("M_pad", C.c_int),
+                ("K_l2", C.c_int), ("codebook2_l", C.c_void_p), ("codebook2_r", C.c_void_p), ("idx2_l", C.c_void_p), ("idx2_r", C.c_void_p),
+                ("n_outlier", C.c_int), ("outlier_cols", C.c_void_p), ("outlier_sidecar", C.c_void_p), ("outlier_scale", C.c_void_p),
+                ("inner_cols", C.c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/ibcu.h declares
@@ -74,6 +77,7 @@ IBCU_SYMBOLS = {
     "ibcu_quantize_input_int8_g128": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "ibcu_linear_w4a8": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "ibcu_pq_idx_t_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "ibcu_pq_prepared_bytes": (C.c_size_t, [C.POINTER(PqT)]),
     "ibcu_pq_prepare": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p]),
     "ibcu_pq_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pq_matmul_fp32_noalloc": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),

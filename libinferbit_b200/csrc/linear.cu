@@ -454,7 +454,6 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 template <int BITS, int NCG, int RT, int W, int STAGES>
 __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p) {
     constexpr int R = RT * 16;                                // most rows per tile
-    constexpr int COLS = NCG * 8;
     constexpr int RLD = lin_rld(NCG);                         // words per row of the reduction buffer
     constexpr int NACC = BITS == 4 ? 2 : 1;                   // INT4 keeps low- and high-nibble sums apart
     constexpr int XB = BITS == 8 ? 64 : 128;                  // limb bytes (= columns) per k-block

@@ -38,11 +38,18 @@ struct PqParams {
     unsigned long long* acc;                   // [B][M_pad] fixed-point sums, zero between calls
     unsigned int* arrive;                      // [passes][row blocks] arrival counters, zero between calls
     const unsigned* amax_bits;                 // [B] bit patterns of max|x[b]| when pq_amax_kernel ran ahead, else NULL
+    // production extras (src/pq_decode.c:1441-1496, :1538-1546): slabs [nslab1, nslab) hold the codes of a second
+    // residual level over the same activation slices, with shared codebooks of K2 entries; inner != NULL lists the
+    // columns of x that the tables are built from (the others are outlier columns), n_inner = C * G of them
+    int nslab1, K2;
+    const __half* cb2_l; const __half* cb2_r;
+    const int* inner; int n_inner;
 };
 
 // codes [M][C] x 2 planes -> slabs of 32 subspaces, 16 rows per lane (see the head of the file)
+// packed != 0: two 4-bit codes per byte, low nibble = even chunk, rows of (C + 1) / 2 bytes (second level with 16 entries)
 __global__ void __launch_bounds__(256) pq_pack_kernel(const uint8_t* __restrict__ idx_l, const uint8_t* __restrict__ idx_r,
-                                                      int M, int C, int M_pad, int nslab, uint8_t* __restrict__ idx_t) {
+                                                      int M, int C, int M_pad, int nslab, uint8_t* __restrict__ idx_t, int packed) {
     const int G16 = M_pad / 16;
     const long total = (long)nslab * G16 * 32;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
@@ -55,7 +62,11 @@ __global__ void __launch_bounds__(256) pq_pack_kernel(const uint8_t* __restrict_
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int r = 16 * g + i;
-            const uint32_t v = (c < C && r < M) ? src[(size_t)r * C + c] : 0u;
+            uint32_t v = 0u;
+            if (c < C && r < M) {
+                if (packed) { const uint32_t b = src[(size_t)r * ((C + 1) / 2) + (c >> 1)]; v = (c & 1) ? (b >> 4) & 15u : b & 15u; }
+                else v = src[(size_t)r * C + c];
+            }
             w[i >> 2] |= v << (8 * (i & 3));
         }
         reinterpret_cast<uint4*>(idx_t)[e] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -73,14 +84,20 @@ __global__ void __launch_bounds__(256) pq_absmax_kernel(const __half* __restrict
     if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));     // non-negative floats order like ints
 }
 
+// tail[0] += tail[1]: the bound used for the fixed-point scale covers one entry of each level
+__global__ void pq_add_tail_kernel(float* tail) { if (threadIdx.x == 0) tail[0] += tail[1]; }
+
 // grid (B): the bit pattern of max|x[b]| (NaN and Inf sort above every finite value)
-__global__ void __launch_bounds__(512) pq_amax_kernel(const float* __restrict__ x, int N, unsigned* __restrict__ out) {
+__global__ void __launch_bounds__(512) pq_amax_kernel(const float* __restrict__ x, int N, unsigned* __restrict__ out,
+                                                      const int* __restrict__ inner, int n_inner) {
     __shared__ unsigned red[16];
     pdl_launch_dependents();
     pdl_wait();
     const float* xb = x + (size_t)blockIdx.x * N;
     unsigned m = 0u;
-    if ((N & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+    if (inner) {
+        for (int j = threadIdx.x; j < n_inner; j += 512) m = max(m, __float_as_uint(xb[inner[j]]) & 0x7fffffffu);
+    } else if ((N & 3) == 0 && ((uintptr_t)x & 15) == 0) {
         const uint4* x4 = reinterpret_cast<const uint4*>(xb);
 #pragma unroll 8
         for (int j = threadIdx.x; j < (N >> 2); j += 512) {
@@ -132,8 +149,21 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     const int g_lo = row_lo >> 4, g_hi = row_hi >> 4;
     const int ngw = g_lo + warp < g_hi ? (g_hi - g_lo - warp + PQ_WARPS - 1) / PQ_WARPS : 0;     // this warp's groups: g_lo + warp + 16 i
     const int nj = (p.nslab - (int)blockIdx.y + (int)gridDim.y - 1) / (int)gridDim.y;             // this block's slabs: blockIdx.y + gridDim.y j
-    const bool cb_smem = half == 8 && p.cb_stride == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
-    const bool cb_vec = half == 8 && (p.cb_stride & 7) == 0 && ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
+    const bool cb1_al = ((uintptr_t)p.cb_l & 15) == 0 && ((uintptr_t)p.cb_r & 15) == 0;
+    const bool cb2_al = ((uintptr_t)p.cb2_l & 15) == 0 && ((uintptr_t)p.cb2_r & 15) == 0;
+    // per level (0: first, 1: second residual level): may the two shared codebooks be staged in shared memory, may they be read 16 bytes at a time
+    auto lvl_smem = [&](int lvl) { return half == 8 && (lvl ? cb2_al : (p.cb_stride == 0 && cb1_al)); };
+    auto lvl_vec = [&](int lvl) { return half == 8 && (lvl ? cb2_al : ((p.cb_stride & 7) == 0 && cb1_al)); };
+    auto stage_cb = [&](int lvl) {                            // every thread: one entry of one side, widened to FP32
+        const int side = tid >> 8, k = tid & 255;
+        const __half* src = lvl ? (side ? p.cb2_r : p.cb2_l) : (side ? p.cb_r : p.cb_l);
+        const uint4 raw = k < (lvl ? p.K2 : p.K) ? reinterpret_cast<const uint4*>(src)[k] : make_uint4(0, 0, 0, 0);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        cbf[k][side][0] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        cbf[k][side][1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    };
+    int staged = -1;                                          // the level whose codebooks sit in cbf
 
     // weights first, they do not depend on the previous kernel: the first codes, the shared codebooks, the row scales
     auto load_codes = [&](int slab, int c0, uint4* cd) {
@@ -145,14 +175,10 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         }
     };
     uint4 cd[PQ_NG];
-    if (nj > 0) load_codes(blockIdx.y, 0, cd);
-    if (cb_smem) {
-        const int side = tid >> 8, k = tid & 255;
-        const uint4 raw = k < p.K ? reinterpret_cast<const uint4*>(side ? p.cb_r : p.cb_l)[k] : make_uint4(0, 0, 0, 0);
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-        cbf[k][side][0] = make_float4(f0.x, f0.y, f1.x, f1.y);
-        cbf[k][side][1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    if (nj > 0) {
+        load_codes(blockIdx.y, 0, cd);
+        const int lvl0 = (int)blockIdx.y >= p.nslab1;
+        if (lvl_smem(lvl0)) { stage_cb(lvl0); staged = lvl0; }
     }
     const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
     // the rows this thread would finish if its block turns out to arrive last (PQ_FIN at a time)
@@ -171,14 +197,14 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         if (half == 8) {
             for (int e = tid; e < BT * 256; e += PQ_THREADS) {
                 const int t = e >> 8, l = (e >> 3) & 31, i = e & 7, s = s0 + l;
-                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (size_t)s * 8 + i] : 0.0f;
+                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (p.inner ? p.inner[s * 8 + i] : s * 8 + i)] : 0.0f;
             }
             return;
         }
         for (int e = tid; e < BT * 32 * half; e += PQ_THREADS) {
             const int t = e / (32 * half), r = e - t * 32 * half, l = r / half, i = r - l * half;
             const int s = s0 + l;
-            xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (size_t)s * half + i] : 0.0f;
+            xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (p.inner ? p.inner[s * half + i] : s * half + i)] : 0.0f;
         }
     };
     // ── max |x| of each activation (the reference's 1 %-of-max rule and the fixed-point scale need it), as the
@@ -191,7 +217,9 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         if (t >= nb) continue;
         if (p.amax_bits) { ab[t] = p.amax_bits[b0 + t]; continue; }            // made by pq_amax_kernel ahead of this launch
         const float* xb = p.x + (size_t)(b0 + t) * p.N;
-        if (vec_x) {
+        if (p.inner) {                                       // outlier columns do not count (src/pq_decode.c:1582-1588)
+            for (int j = tid; j < p.n_inner; j += PQ_THREADS) ab[t] = max(ab[t], __float_as_uint(xb[p.inner[j]]) & 0x7fffffffu);
+        } else if (vec_x) {
             const uint4* x4 = reinterpret_cast<const uint4*>(xb);
             const int n4 = p.N >> 2;
 #pragma unroll 8
@@ -208,10 +236,14 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     int anybad = 0;
     for (int j = 0; j < nj; j++) {
         const int slab = blockIdx.y + j * gridDim.y;
-        const int s0 = slab * 32;
+        const int lvl = slab >= p.nslab1;                    // slabs of the second level follow those of the first, over the same slices of x
+        const int s0 = (lvl ? slab - p.nslab1 : slab) * 32;
+        const int Kl = lvl ? p.K2 : p.K;
+        const bool cb_smem = lvl_smem(lvl), cb_vec = lvl_vec(lvl);
         if (j) {
             __syncthreads();                                 // the gather of the previous slab is done with the table and xs
             load_codes(slab, 0, cd);
+            if (cb_smem && staged != lvl) { stage_cb(lvl); staged = lvl; }
         }
         fill_xs(s0);
         __syncthreads();
@@ -220,7 +252,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         {
             const int s = s0 + lane;
             const bool sub_ok = s < nsub;
-            const __half* cb = ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride;
+            const __half* cb = lvl ? ((s & 1) ? p.cb2_r : p.cb2_l) : ((s & 1) ? p.cb_r : p.cb_l) + (size_t)(s >> 1) * p.cb_stride;
             if (cb_vec) {
                 float xr[BT][8];
 #pragma unroll
@@ -251,7 +283,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
 #pragma unroll
                         for (int u = 0; u < U; u++) {
                             const int k = k0 + u * PQ_WARPS;
-                            raw[u] = (sub_ok && k < p.K) ? *reinterpret_cast<const uint4*>(cb + (size_t)k * 8) : make_uint4(0, 0, 0, 0);
+                            raw[u] = (sub_ok && k < Kl) ? *reinterpret_cast<const uint4*>(cb + (size_t)k * 8) : make_uint4(0, 0, 0, 0);
                         }
 #pragma unroll
                         for (int u = 0; u < U; u++) {
@@ -277,7 +309,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
                     float v[BT];
 #pragma unroll
                     for (int t = 0; t < BT; t++) v[t] = 0.0f;
-                    if (sub_ok && k < p.K) {
+                    if (sub_ok && k < Kl) {
                         for (int i = 0; i < half; i++) {
                             const float c = __half2float(cb[(size_t)k * half + i]);
 #pragma unroll
@@ -421,12 +453,34 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     }
 }
 
-struct PqPlan { int C, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
+// Outlier sidecar (src/pq_decode.c:1394-1409): out[r] += sum over j of (sidecar[r][j] * scale[j]) * x[col[j]], added to the finished
+// rows. grid (blocks of 8 rows, activations), a warp per row, lanes over the outlier columns.
+__global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restrict__ side, const int32_t* __restrict__ cols, const __half* __restrict__ scale,
+                                                         int no, const float* __restrict__ x, int N, float* __restrict__ out, int M) {
+    extern __shared__ float xo[];                            // x[col[j]] of this activation
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int j = threadIdx.x; j < no; j += 256) xo[j] = x[(size_t)b * N + cols[j]];
+    __syncthreads();
+    const int r = blockIdx.x * 8 + warp;
+    if (r >= M) return;
+    float acc = 0.0f;
+    for (int j = lane; j < no; j += 32) {
+        const float w = (float)side[(size_t)r * no + j] * __half2float(scale[j]);
+        acc = fmaf(w, xo[j], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[(size_t)b * M + r] += acc;
+}
+
+struct PqPlan { int C, nslab1, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
 
 PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     PqPlan pl;
-    pl.C = t->N / t->G;
-    pl.nslab = (2 * pl.C + 31) / 32;
+    pl.C = (t->N - t->n_outlier) / t->G;
+    pl.nslab1 = (2 * pl.C + 31) / 32;
+    pl.nslab = t->K_l2 > 0 ? 2 * pl.nslab1 : pl.nslab1;
     pl.bt = B >= 2 ? 2 : 1;
     pl.passes = (B + pl.bt - 1) / pl.bt;
     const int slots = ctx->sm_count * 2;
@@ -458,6 +512,8 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
     p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
     p.idx_t = t->idx_t; p.row_scale = (const __half*)t->row_scale; p.x = x; p.out = out; p.acc = acc; p.arrive = arrive;
     p.amax_bits = nullptr;
+    p.nslab1 = pl.nslab1; p.K2 = t->K_l2; p.cb2_l = (const __half*)t->codebook2_l; p.cb2_r = (const __half*)t->codebook2_r;
+    p.inner = t->n_outlier > 0 ? t->inner_cols : nullptr; p.n_inner = t->N - t->n_outlier;
     const dim3 grid(pl.row_blocks, pl.slab_blocks, pl.passes), block(PQ_THREADS);
     // static plus dynamic shared memory passes 48 KB: opt in once per device
     static std::once_flag once[64];
@@ -471,20 +527,30 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         // with several activations every block would scan all of them for their maxima: one small launch does it once;
         // its results sit in the last 64 counter slots, which no pass uses
         unsigned* amax_bits = arrive + (PQ_COUNTER_BYTES / sizeof(unsigned) - 64);
-        int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits);
+        int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits, p.inner, p.n_inner);
         if (rc) return rc;
         p.amax_bits = amax_bits;
-        return ibcu_launch(ctx, pq_slab_kernel<2>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
+        rc = ibcu_launch(ctx, pq_slab_kernel<2>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
+        if (rc) return rc;
+    } else {
+        const int rc = ibcu_launch(ctx, pq_slab_kernel<1>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p);
+        if (rc) return rc;
     }
-    return ibcu_launch(ctx, pq_slab_kernel<1>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p);
+    if (t->n_outlier > 0)                                    // the sidecar's share is added to the finished rows (src/pq_decode.c:1676)
+        return ibcu_launch(ctx, pq_outlier_kernel, dim3((t->M + 7) / 8, B), dim3(256), (size_t)t->n_outlier * sizeof(float), 1, true,
+                           t->outlier_sidecar, t->outlier_cols, (const __half*)t->outlier_scale, t->n_outlier, x, t->N, out, t->M);
+    return IBCU_OK;
 }
 
 int pq_check(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B, const char* who) {
     IBCU_REQUIRE(ctx, t && x && out, "%s: null pointer", who);
     IBCU_REQUIRE(ctx, t->codebook_l && t->codebook_r && t->row_scale, "%s: tensor has a null pointer", who);
     IBCU_REQUIRE(ctx, t->idx_t && t->M_pad >= t->M && (t->M_pad & 15) == 0, "%s: call ibcu_pq_prepare on the tensor first", who);
-    IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->G <= 32 && t->N % t->G == 0 && t->K >= 1 && t->K <= 256,
-                 "%s: bad shape M=%d N=%d G=%d K=%d", who, t->M, t->N, t->G, t->K);
+    IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->G <= 32 && t->n_outlier >= 0 && t->n_outlier < t->N &&
+                      (t->N - t->n_outlier) % t->G == 0 && t->K >= 1 && t->K <= 256,
+                 "%s: bad shape M=%d N=%d G=%d K=%d outliers=%d", who, t->M, t->N, t->G, t->K, t->n_outlier);
+    IBCU_REQUIRE(ctx, t->K_l2 == 0 || (t->K_l2 >= 1 && t->K_l2 <= 256 && t->codebook2_l && t->codebook2_r), "%s: second level with K_l2=%d", who, t->K_l2);
+    IBCU_REQUIRE(ctx, t->n_outlier == 0 || (t->outlier_cols && t->outlier_sidecar && t->outlier_scale && t->inner_cols), "%s: outlier arrays missing", who);
     IBCU_REQUIRE(ctx, B >= 1 && B <= 32, "%s: B=%d not in 1..32", who, B);
     return IBCU_OK;
 }
@@ -500,29 +566,74 @@ extern "C" size_t ibcu_pq_idx_t_bytes(int M, int N, int G) {
     return nslab * 32 * M_pad + PQ_TAIL;
 }
 
+extern "C" size_t ibcu_pq_prepared_bytes(const ibcu_pq_t* t) {
+    if (!t || t->M <= 0 || t->N <= 0 || t->G <= 0 || t->n_outlier < 0 || t->n_outlier >= t->N || (t->N - t->n_outlier) % t->G) return 0;
+    const size_t M_pad = ((size_t)t->M + 15) & ~(size_t)15;
+    const size_t nslab1 = (2 * (size_t)((t->N - t->n_outlier) / t->G) + 31) / 32;
+    const size_t nslab = t->K_l2 > 0 ? 2 * nslab1 : nslab1;
+    return nslab * 32 * M_pad + PQ_TAIL + (t->n_outlier > 0 ? (size_t)(t->N - t->n_outlier) * sizeof(int32_t) : 0);
+}
+
+// inner[k] = k-th column that is not an outlier column (ascending), as src/pq_decode.c:1538-1546 builds it
+__global__ void __launch_bounds__(256) pq_inner_cols_kernel(const int32_t* __restrict__ ocols, int no, int N, int32_t* __restrict__ inner) {
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < N; j += gridDim.x * blockDim.x) {
+        // rank of j among the outlier columns (sorted): columns below j that are outliers
+        int lo = 0, hi = no;
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (ocols[mid] < j) lo = mid + 1; else hi = mid; }
+        if (lo < no && ocols[lo] == j) continue;             // an outlier column itself
+        inner[j - lo] = j;
+    }
+}
+
 extern "C" int ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, t && idx_t_out && t->idx_l && t->idx_r && t->codebook_l && t->codebook_r, "ibcu_pq_prepare: null pointer");
-    IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->N % t->G == 0 && t->K >= 1 && t->K <= 256,
-                 "ibcu_pq_prepare: bad shape M=%d N=%d G=%d K=%d", t->M, t->N, t->G, t->K);
+    IBCU_REQUIRE(ctx, t->M > 0 && t->N > 0 && t->G > 0 && (t->G & 1) == 0 && t->n_outlier >= 0 && t->n_outlier < t->N &&
+                      (t->N - t->n_outlier) % t->G == 0 && t->K >= 1 && t->K <= 256,
+                 "ibcu_pq_prepare: bad shape M=%d N=%d G=%d K=%d outliers=%d", t->M, t->N, t->G, t->K, t->n_outlier);
+    IBCU_REQUIRE(ctx, t->K_l2 == 0 || (t->K_l2 >= 1 && t->K_l2 <= 256 && t->codebook2_l && t->codebook2_r && t->idx2_l && t->idx2_r),
+                 "ibcu_pq_prepare: second level with K_l2=%d (at most 256 entries, one-byte or 4-bit indices)", t->K_l2);
+    IBCU_REQUIRE(ctx, t->n_outlier == 0 || (t->outlier_cols && t->outlier_sidecar && t->outlier_scale), "ibcu_pq_prepare: outlier arrays missing");
+    IBCU_REQUIRE(ctx, t->K_l2 == 0 || t->cb_chunk_stride == 0, "ibcu_pq_prepare: a second level needs shared codebooks");
     IBCU_REQUIRE(ctx, ((uintptr_t)idx_t_out & 15) == 0, "ibcu_pq_prepare: idx_t_out must be 16-byte aligned");
-    const int C = t->N / t->G, half = t->G / 2;
+    const int C = (t->N - t->n_outlier) / t->G, half = t->G / 2;
     const int M_pad = (t->M + 15) & ~15;
-    const int nslab = (2 * C + 31) / 32;
-    const size_t body = (size_t)nslab * 32 * M_pad;
-    const long vecs = (long)(body / 16);
+    const int nslab1 = (2 * C + 31) / 32, nslab = t->K_l2 > 0 ? 2 * nslab1 : nslab1;
+    const size_t plane = (size_t)nslab1 * 32 * M_pad, body = (size_t)nslab * 32 * M_pad;
+    const long vecs = (long)(plane / 16);
     int blocks = (int)((vecs + 255) / 256);
     if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-    int rc = ibcu_launch(ctx, pq_pack_kernel, dim3(blocks), dim3(256), 0, 1, false, t->idx_l, t->idx_r, t->M, C, M_pad, nslab, idx_t_out);
+    int rc = ibcu_launch(ctx, pq_pack_kernel, dim3(blocks), dim3(256), 0, 1, false, t->idx_l, t->idx_r, t->M, C, M_pad, nslab1, idx_t_out, 0);
     if (rc) return rc;
+    if (t->K_l2 > 0) {
+        rc = ibcu_launch(ctx, pq_pack_kernel, dim3(blocks), dim3(256), 0, 1, false, t->idx2_l, t->idx2_r, t->M, C, M_pad, nslab1, idx_t_out + plane,
+                         t->K_l2 == 16 ? 1 : 0);
+        if (rc) return rc;
+    }
     IBCU_CUDA(ctx, cudaMemsetAsync(idx_t_out + body, 0, PQ_TAIL, ctx->stream));
-    // entries of both tables: one pair when the tables are shared, one pair per chunk otherwise
+    // largest magnitude over the entries of all tables: one pair when the tables are shared, one pair per chunk otherwise; then the second level's
     const size_t n = t->cb_chunk_stride ? (size_t)(C - 1) * t->cb_chunk_stride + (size_t)t->K * half : (size_t)t->K * half;
     int ab = (int)((n + 255) / 256);
     if (ab > ctx->sm_count * 4) ab = ctx->sm_count * 4;
     rc = ibcu_launch(ctx, pq_absmax_kernel, dim3(ab), dim3(256), 0, 1, false, (const __half*)t->codebook_l, (const __half*)t->codebook_r, n,
                      reinterpret_cast<float*>(idx_t_out + body));
     if (rc) return rc;
+    if (t->K_l2 > 0) {
+        // the fixed-point bound is N * (largest entry) * max|x| per level: with two levels the sum of both levels' largest entries bounds a pair of terms
+        rc = ibcu_launch(ctx, pq_absmax_kernel, dim3(1), dim3(256), 0, 1, false, (const __half*)t->codebook2_l, (const __half*)t->codebook2_r,
+                         (size_t)t->K_l2 * half, reinterpret_cast<float*>(idx_t_out + body) + 1);
+        if (rc) return rc;
+        rc = ibcu_launch(ctx, pq_add_tail_kernel, dim3(1), dim3(32), 0, 1, false, reinterpret_cast<float*>(idx_t_out + body));
+        if (rc) return rc;
+    }
+    if (t->n_outlier > 0) {
+        int32_t* inner = reinterpret_cast<int32_t*>(idx_t_out + body + PQ_TAIL);
+        int ib = (t->N + 255) / 256;
+        if (ib > ctx->sm_count * 4) ib = ctx->sm_count * 4;
+        rc = ibcu_launch(ctx, pq_inner_cols_kernel, dim3(ib), dim3(256), 0, 1, false, t->outlier_cols, t->n_outlier, t->N, inner);
+        if (rc) return rc;
+        t->inner_cols = inner;
+    }
     t->idx_t = idx_t_out;
     t->M_pad = M_pad;
     return IBCU_OK;

@@ -12,13 +12,13 @@
 typedef struct {
     const ib_b200_pq_tensor* key;
     ibcu_pq_t dev;
-    void* bufs[6];
+    void* bufs[13];
 } pq_entry;
 static pq_entry g_pq[PQ_CACHE];
 static int g_npq;
 
 static void pq_drop(pq_entry* e) {
-    for (int i = 0; i < 6; i++) if (e->bufs[i]) ibcu_free(g_ib.ctx, e->bufs[i]);
+    for (int i = 0; i < 13; i++) if (e->bufs[i]) ibcu_free(g_ib.ctx, e->bufs[i]);
     memset(e, 0, sizeof *e);
 }
 void ib_b200_pq_release(const ib_b200_pq_tensor* t) {
@@ -41,27 +41,49 @@ static int up(void** dst, const void* src, size_t bytes) {
 static pq_entry* pq_get(const ib_b200_pq_tensor* t) {
     for (int i = 0; i < g_npq; i++) if (g_pq[i].key == t) return &g_pq[i];
     if (g_npq == PQ_CACHE) { ib_b200_set_error(IBCU_ERR_NOMEM, "PQ tensor cache full (%d); release some with ib_b200_pq_release", PQ_CACHE); return NULL; }
-    /* the same restrictions the backend has: one level, no outlier sidecar, no rotation bookkeeping */
-    if (t->n_levels != 1 || t->n_outlier != 0 || t->G <= 0 || (t->G & 1) || t->N % t->G || t->K < 1 || t->K > 256 ||
-        !t->codebook_l1_l || !t->codebook_l1_r || !t->indices_l1_l || !t->indices_l1_r || !t->row_scale) {
-        ib_b200_set_error(IBCU_ERR_PARAM, "PQ tensor outside the supported subset (levels=%d outliers=%d G=%d K=%d)", t->n_levels, t->n_outlier, t->G, t->K);
+    /* what the backend takes: one or two levels (second level: at most 256 entries, one-byte or 4-bit packed indices), an
+     * optional int8 outlier sidecar; anything else (uint16 second-level indices, other formats) stays with the caller */
+    const int two = t->n_levels == 2;
+    const int K2 = two ? (t->K_l2 > 0 ? t->K_l2 : t->K) : 0;                 /* src/pq_decode.c:1099-1101 */
+    const int l2_bytes = t->l2_idx_bytes > 0 ? t->l2_idx_bytes : 1;
+    if ((t->n_levels != 1 && t->n_levels != 2) || t->n_outlier < 0 || t->n_outlier >= t->N || t->G <= 0 || (t->G & 1) ||
+        (t->N - t->n_outlier) % t->G || t->K < 1 || t->K > 256 || t->format != 0 ||
+        !t->codebook_l1_l || !t->codebook_l1_r || !t->indices_l1_l || !t->indices_l1_r || !t->row_scale ||
+        (two && (K2 > 256 || (K2 != 16 && l2_bytes != 1) || !t->codebook_l2_l || !t->codebook_l2_r || !t->indices_l2_l || !t->indices_l2_r)) ||
+        (t->n_outlier > 0 && (!t->outlier_cols || !t->outlier_sidecar || !t->outlier_scale))) {
+        ib_b200_set_error(IBCU_ERR_PARAM, "PQ tensor outside the supported subset (levels=%d K_l2=%d l2 index bytes=%d outliers=%d G=%d K=%d format=%d)",
+                          t->n_levels, t->K_l2, t->l2_idx_bytes, t->n_outlier, t->G, t->K, t->format);
         return NULL;
     }
     pq_entry* e = &g_pq[g_npq];
     memset(e, 0, sizeof *e);
-    const int C = t->N / t->G, half = t->G / 2;
+    const int C = (t->N - t->n_outlier) / t->G, half = t->G / 2;
     int rc = up(&e->bufs[0], t->codebook_l1_l, (size_t)t->K * half * 2);
     if (!rc) rc = up(&e->bufs[1], t->codebook_l1_r, (size_t)t->K * half * 2);
     if (!rc) rc = up(&e->bufs[2], t->indices_l1_l, (size_t)t->M * C);
     if (!rc) rc = up(&e->bufs[3], t->indices_l1_r, (size_t)t->M * C);
     if (!rc) rc = up(&e->bufs[4], t->row_scale, (size_t)t->M * 2);
-    if (!rc) rc = ibcu_malloc(g_ib.ctx, ibcu_pq_idx_t_bytes(t->M, t->N, t->G), &e->bufs[5]);
+    if (!rc && two) {
+        const size_t stride = K2 == 16 ? (size_t)(C + 1) / 2 : (size_t)C;
+        rc = up(&e->bufs[6], t->codebook_l2_l, (size_t)K2 * half * 2);
+        if (!rc) rc = up(&e->bufs[7], t->codebook_l2_r, (size_t)K2 * half * 2);
+        if (!rc) rc = up(&e->bufs[8], t->indices_l2_l, (size_t)t->M * stride);
+        if (!rc) rc = up(&e->bufs[9], t->indices_l2_r, (size_t)t->M * stride);
+    }
+    if (!rc && t->n_outlier > 0) {
+        rc = up(&e->bufs[10], t->outlier_cols, (size_t)t->n_outlier * sizeof(int32_t));
+        if (!rc) rc = up(&e->bufs[11], t->outlier_sidecar, (size_t)t->M * t->n_outlier);
+        if (!rc) rc = up(&e->bufs[12], t->outlier_scale, (size_t)t->n_outlier * 2);
+    }
     if (!rc) {
         e->dev.M = t->M; e->dev.N = t->N; e->dev.G = t->G; e->dev.K = t->K;
         e->dev.codebook_l = e->bufs[0]; e->dev.codebook_r = e->bufs[1]; e->dev.cb_chunk_stride = 0;
         e->dev.idx_l = e->bufs[2]; e->dev.idx_r = e->bufs[3]; e->dev.row_scale = e->bufs[4];
-        rc = ibcu_pq_prepare(g_ib.ctx, &e->dev, (uint8_t*)e->bufs[5]);
+        e->dev.K_l2 = K2; e->dev.codebook2_l = e->bufs[6]; e->dev.codebook2_r = e->bufs[7]; e->dev.idx2_l = e->bufs[8]; e->dev.idx2_r = e->bufs[9];
+        e->dev.n_outlier = t->n_outlier; e->dev.outlier_cols = e->bufs[10]; e->dev.outlier_sidecar = e->bufs[11]; e->dev.outlier_scale = e->bufs[12];
+        rc = ibcu_malloc(g_ib.ctx, ibcu_pq_prepared_bytes(&e->dev), &e->bufs[5]);
     }
+    if (!rc) rc = ibcu_pq_prepare(g_ib.ctx, &e->dev, (uint8_t*)e->bufs[5]);
     if (!rc) rc = ibcu_sync(g_ib.ctx);
     if (ib_b200_check(rc, "PQ tensor upload")) { pq_drop(e); return NULL; }
     e->key = t;

@@ -235,6 +235,95 @@ int ibo_pq_matmul_fp32(int M, int N, int G, int K,
     return 0;
 }
 
+/* The same path with the production extras: a second residual level (src/pq_decode.c:1441-1496 TL2/TR2
+ * terms; index forms of :1058-1075: one byte, or two 4-bit indices per byte, low nibble = even chunk, when
+ * K_l2 == 16) and the outlier sidecar (:1394-1409 scalar form): outlier columns are taken out of the
+ * activation before the tables are built (inner_cols, :1538-1546), so N - n_outlier = C * G, and come
+ * back as out[r] += (sidecar[r][j] * scale[j]) * x[col[j]] after the row scale. NULL / 0 switch a part off. */
+int ibo_pq_matmul_fp32_ex(int M, int N, int G, int K, int K_l2,
+                          const uint16_t* cb1_l, const uint16_t* cb1_r, const uint16_t* cb2_l, const uint16_t* cb2_r,
+                          const uint8_t* idx1_l, const uint8_t* idx1_r, const uint8_t* idx2_l, const uint8_t* idx2_r,
+                          const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
+                          const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
+                          const float* x, float* out, int fused) {
+    if (!cb1_l || !cb1_r || !idx1_l || !idx1_r || !row_scale || !x || !out) return -1;
+    if (M <= 0 || N <= 0 || G <= 0 || (G & 1) || G > 32 || K <= 0 || K > 256 || n_outlier < 0 || (N - n_outlier) % G) return -1;
+    const int two = cb2_l && cb2_r && idx2_l && idx2_r;
+    if (two && (K_l2 <= 0 || K_l2 > 256)) return -1;
+    int half = G / 2, n_inner = N - n_outlier, C = n_inner / G;
+    const int packed = two && K_l2 == 16;
+    const size_t l2_stride = packed ? (size_t)((C + 1) / 2) : (size_t)C;
+    int* inner = (int*)malloc((size_t)n_inner * sizeof(int));
+    unsigned char* mask = (unsigned char*)calloc((size_t)N, 1);
+    float* xi = (float*)malloc((size_t)n_inner * sizeof(float));
+    float* t1l = (float*)malloc((size_t)C * K * sizeof(float));
+    float* t1r = (float*)malloc((size_t)C * K * sizeof(float));
+    float* t2l = two ? (float*)malloc((size_t)C * K_l2 * sizeof(float)) : NULL;
+    float* t2r = two ? (float*)malloc((size_t)C * K_l2 * sizeof(float)) : NULL;
+    float* ent = (float*)malloc((size_t)half * sizeof(float));
+    unsigned char* live = (unsigned char*)malloc((size_t)C);
+    int rc = -1;
+    if (!inner || !mask || !xi || !t1l || !t1r || (two && (!t2l || !t2r)) || !ent || !live) goto done;
+    for (int j = 0; j < n_outlier; j++) mask[outlier_cols[j]] = 1;
+    { int kk = 0; for (int j = 0; j < N; j++) if (!mask[j] && kk < n_inner) inner[kk++] = j; }
+    for (int j = 0; j < n_inner; j++) xi[j] = x[inner[j]];
+    {
+        float amax = 0.0f;
+        for (int j = 0; j < n_inner; j++) { float a = xi[j] < 0 ? -xi[j] : xi[j]; if (a > amax) amax = a; }
+        for (int c = 0; c < C; c++) {
+            live[c] = 1;
+            if (amax > 0.0f) {
+                float cmax = 0.0f, thr = amax * 0.01f;
+                for (int i = 0; i < G; i++) { float a = xi[c * G + i]; if (a < 0) a = -a; if (a > cmax) cmax = a; }
+                if (!(cmax >= thr)) live[c] = 0;
+            }
+        }
+    }
+    for (int c = 0; c < C; c++) {
+        if (!live[c]) continue;
+        for (int k = 0; k < K; k++) {
+            for (int i = 0; i < half; i++) ent[i] = ibo_fp16_to_fp32(cb1_l[k * half + i]);
+            t1l[(size_t)c * K + k] = dot_seq(ent, xi + c * G, half, fused);
+            for (int i = 0; i < half; i++) ent[i] = ibo_fp16_to_fp32(cb1_r[k * half + i]);
+            t1r[(size_t)c * K + k] = dot_seq(ent, xi + c * G + half, half, fused);
+        }
+        for (int k = 0; two && k < K_l2; k++) {
+            for (int i = 0; i < half; i++) ent[i] = ibo_fp16_to_fp32(cb2_l[k * half + i]);
+            t2l[(size_t)c * K_l2 + k] = dot_seq(ent, xi + c * G, half, fused);
+            for (int i = 0; i < half; i++) ent[i] = ibo_fp16_to_fp32(cb2_r[k * half + i]);
+            t2r[(size_t)c * K_l2 + k] = dot_seq(ent, xi + c * G + half, half, fused);
+        }
+    }
+    for (int r = 0; r < M; r++) {
+        const uint8_t* il = idx1_l + (size_t)r * C;
+        const uint8_t* ir = idx1_r + (size_t)r * C;
+        const uint8_t* jl = two ? idx2_l + (size_t)r * l2_stride : NULL;
+        const uint8_t* jr = two ? idx2_r + (size_t)r * l2_stride : NULL;
+        float acc = 0.0f;
+        for (int c = 0; c < C; c++) {
+            if (!live[c]) continue;
+            acc += t1l[(size_t)c * K + il[c]] + t1r[(size_t)c * K + ir[c]];
+            if (two) {
+                int a = packed ? ((c & 1) ? (jl[c >> 1] >> 4) & 15 : jl[c >> 1] & 15) : jl[c];
+                int b = packed ? ((c & 1) ? (jr[c >> 1] >> 4) & 15 : jr[c >> 1] & 15) : jr[c];
+                acc += t2l[(size_t)c * K_l2 + a] + t2r[(size_t)c * K_l2 + b];
+            }
+        }
+        out[r] = acc * ibo_fp16_to_fp32(row_scale[r]);
+    }
+    for (int j = 0; j < n_outlier; j++) {
+        float os = ibo_fp16_to_fp32(outlier_scale[j]), xj = x[outlier_cols[j]];
+        for (int r = 0; r < M; r++) {
+            float w = (float)outlier_sidecar[(size_t)r * n_outlier + j] * os;
+            out[r] += w * xj;
+        }
+    }
+    rc = 0;
+done:
+    free(inner); free(mask); free(xi); free(t1l); free(t1r); free(t2l); free(t2r); free(ent); free(live);
+    return rc;
+}
+
 /* src/pq_decode.c:1103-1196 with n_levels == 1, no outliers. */
 int ibo_pq_reconstruct_fp32(int M, int N, int G, int K,
                             const uint16_t* cb_l, const uint16_t* cb_r,

@@ -50,6 +50,14 @@ int ibo_pq_matmul_fp32(int M, int N, int G, int K,
                        const uint16_t* cb_l, const uint16_t* cb_r, long cb_chunk_stride,
                        const uint8_t* idx_l, const uint8_t* idx_r, const uint16_t* row_scale,
                        const float* x, float* out, int fused, int* n_skipped);
+/* The same with a second residual level (one-byte or 4-bit-packed indices) and the outlier sidecar
+ * (src/pq_decode.c:1058-1075, :1394-1409, :1441-1496, :1538-1546); NULL / 0 switch a part off. */
+int ibo_pq_matmul_fp32_ex(int M, int N, int G, int K, int K_l2,
+                          const uint16_t* cb1_l, const uint16_t* cb1_r, const uint16_t* cb2_l, const uint16_t* cb2_r,
+                          const uint8_t* idx1_l, const uint8_t* idx1_r, const uint8_t* idx2_l, const uint8_t* idx2_r,
+                          const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
+                          const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
+                          const float* x, float* out, int fused);
 /* src/pq_decode.c:1103-1196 — dense W[M*N] from codes, every value rounded through fp16. */
 int ibo_pq_reconstruct_fp32(int M, int N, int G, int K,
                             const uint16_t* cb_l, const uint16_t* cb_r,

@@ -84,6 +84,8 @@ class Libs:
         o.ibo_matmul_w4a8_batch.argtypes = [f32, u8, f32, i8, f32, C.c_int, C.c_int, C.c_int, C.c_int]
         o.ibo_pq_matmul_fp32.restype = C.c_int
         o.ibo_pq_matmul_fp32.argtypes = [C.c_int] * 4 + [u16, u16, C.c_long, u8, u8, u16, f32, f32, C.c_int, C.POINTER(C.c_int)]
+        o.ibo_pq_matmul_fp32_ex.restype = C.c_int
+        o.ibo_pq_matmul_fp32_ex.argtypes = [C.c_int] * 5 + [C.c_void_p] * 9 + [C.c_int] + [C.c_void_p] * 5 + [C.c_int]
         o.ibo_pq_reconstruct_fp32.restype = C.c_int
         o.ibo_pq_reconstruct_fp32.argtypes = [C.c_int] * 4 + [u16, u16, u8, u8, u16, f32]
         o.ibo_kmeans_assign.argtypes = [f32, C.c_long, C.c_int, f32, C.c_int, i32, C.c_void_p, C.c_int]
@@ -142,6 +144,60 @@ class Libs:
         t.C = N // G; t.l2_idx_bytes = 1; t.row_scale = row_scale.ctypes.data
         t._keep = (cb_l, cb_r, idx_l, idx_r, row_scale)
         return t
+
+
+def make_pq_case_ex(rng, M, N, G, K, K_l2, n_outlier, B):
+    """A PQ tensor with the production extras: K_l2 > 0 adds a second residual level (4-bit packed indices when
+    K_l2 == 16, else one byte), n_outlier > 0 an int8 sidecar over that many columns. N - n_outlier = C * G."""
+    half = G // 2
+    Cn = (N - n_outlier) // G
+    assert Cn * G == N - n_outlier
+    d = {"M": M, "N": N, "G": G, "K": K, "K_l2": K_l2, "n_outlier": n_outlier, "C": Cn}
+    d["cb1_l"] = fp16_bits(rng.standard_normal((K, half)) * 0.02); d["cb1_r"] = fp16_bits(rng.standard_normal((K, half)) * 0.02)
+    d["idx1_l"] = rng.integers(0, K, size=(M, Cn), dtype=np.uint8); d["idx1_r"] = rng.integers(0, K, size=(M, Cn), dtype=np.uint8)
+    if K_l2:
+        d["cb2_l"] = fp16_bits(rng.standard_normal((K_l2, half)) * 0.004); d["cb2_r"] = fp16_bits(rng.standard_normal((K_l2, half)) * 0.004)
+        if K_l2 == 16:
+            nb = (Cn + 1) // 2
+            d["idx2_l"] = rng.integers(0, 256, size=(M, nb), dtype=np.uint8); d["idx2_r"] = rng.integers(0, 256, size=(M, nb), dtype=np.uint8)
+        else:
+            d["idx2_l"] = rng.integers(0, K_l2, size=(M, Cn), dtype=np.uint8); d["idx2_r"] = rng.integers(0, K_l2, size=(M, Cn), dtype=np.uint8)
+    if n_outlier:
+        d["ocols"] = np.sort(rng.choice(N, n_outlier, replace=False)).astype(np.int32)
+        d["oside"] = rng.integers(-127, 128, size=(M, n_outlier), dtype=np.int8)
+        d["oscale"] = fp16_bits(rng.uniform(0.001, 0.01, n_outlier))
+    d["rs"] = fp16_bits(rng.uniform(0.5, 2.0, M))
+    d["x"] = rng.standard_normal((B, N)).astype(np.float32)
+    return d
+
+
+def _ptr(d, k):
+    return d[k].ctypes.data if k in d else None
+
+
+def oracle_pq_ex(o, d, xb, fused=1):
+    out = np.empty(d["M"], np.float32)
+    rc = o.ibo_pq_matmul_fp32_ex(d["M"], d["N"], d["G"], d["K"], d["K_l2"], _ptr(d, "cb1_l"), _ptr(d, "cb1_r"), _ptr(d, "cb2_l"), _ptr(d, "cb2_r"),
+                                 _ptr(d, "idx1_l"), _ptr(d, "idx1_r"), _ptr(d, "idx2_l"), _ptr(d, "idx2_r"), _ptr(d, "rs"),
+                                 d["n_outlier"], _ptr(d, "ocols"), _ptr(d, "oside"), _ptr(d, "oscale"), xb.ctypes.data, out.ctypes.data, fused)
+    assert rc == 0
+    return out
+
+
+def ref_pq_tensor_ex(d):
+    """the reference's ib_pq_tensor over the arrays of make_pq_case_ex"""
+    t = RefPqTensor()
+    t.M, t.N, t.G, t.K, t.K_l2 = d["M"], d["N"], d["G"], d["K"], d["K_l2"]
+    t.n_levels, t.rotate, t.n_outlier, t.format = (2 if d["K_l2"] else 1), 0, d["n_outlier"], 0
+    t.codebook_l1_l, t.codebook_l1_r = _ptr(d, "cb1_l"), _ptr(d, "cb1_r")
+    t.codebook_l2_l, t.codebook_l2_r = _ptr(d, "cb2_l"), _ptr(d, "cb2_r")
+    t.indices_l1_l, t.indices_l1_r = _ptr(d, "idx1_l"), _ptr(d, "idx1_r")
+    t.indices_l2_l, t.indices_l2_r = _ptr(d, "idx2_l"), _ptr(d, "idx2_r")
+    t.C, t.l2_idx_bytes, t.l2_packed_bits = d["C"], 1, 0
+    t.row_scale = _ptr(d, "rs")
+    t.outlier_cols, t.outlier_sidecar, t.outlier_scale = _ptr(d, "ocols"), _ptr(d, "oside"), _ptr(d, "oscale")
+    t._keep = d
+    return t
 
 
 _libs = None

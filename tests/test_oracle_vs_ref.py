@@ -120,6 +120,24 @@ def test_pq_matmul_and_reconstruct(libs, M, N, G, K):
     assert np.max(np.abs(dense - fused)) < 2e-3 * np.max(np.abs(dense))
 
 
+@pytest.mark.parametrize("M,N,G,K,K_l2,n_out", [(40, 256, 16, 256, 256, 0), (33, 256, 16, 256, 16, 0), (24, 272, 16, 64, 0, 16),
+                                               (40, 528, 16, 256, 16, 16), (16, 104, 8, 32, 64, 8)])
+def test_pq_second_level_and_outliers(libs, M, N, G, K, K_l2, n_out):
+    """Second residual level (byte and 4-bit packed indices) and the outlier sidecar (fewer than 32 columns: the
+    reference then takes its scalar form, src/pq_decode.c:1411-1421) against the compiled reference."""
+    rng = np.random.default_rng(M + N + K_l2 + n_out)
+    d = _cpu.make_pq_case_ex(rng, M, N, G, K, K_l2, n_out, 2)
+    t = _cpu.ref_pq_tensor_ex(d)
+    for b in range(2):
+        xb = d["x"][b].copy()
+        if b == 1:
+            xb[:2 * G] *= 1e-4                                # chunks under the 1 % rule (some of these columns may be outliers)
+        r = np.empty(M, np.float32)
+        assert libs.ref.ib_pq_matmul_fp32(C.byref(t), xb, r) == 0
+        a = _cpu.oracle_pq_ex(libs.oracle, d, xb)
+        assert _cpu.close(a, r, rtol=1e-5, atol=1e-6)
+
+
 def _near_tie_points(rng, D, N):
     Cn = (rng.standard_normal((2, D)) * 0.02).astype(np.float32)
     mid = (Cn[0].astype(np.float64) + Cn[1]) / 2

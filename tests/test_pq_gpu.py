@@ -33,6 +33,49 @@ def test_pq_matches_reference_restatement(backend, cpu_libs, M, N, G, K, B):
     assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
 
 
+@pytest.mark.parametrize("M,N,G,K,K_l2,n_out,B", [
+    (4096, 14336, 16, 256, 256, 0, 1),    # down_proj shape with a full second level
+    (4096, 14336, 16, 256, 16, 0, 2),     # 6-bit-per-weight variant: 16-entry second level, two 4-bit indices per byte
+    (1000, 2048 + 48, 16, 256, 0, 48, 3), # outlier sidecar only; rows not a multiple of 16
+    (4096, 4096 + 64, 16, 256, 16, 64, 1),
+    (77, 8 * 13 + 5, 8, 32, 64, 5, 2), (33, 96, 4, 16, 16, 0, 1),
+])
+def test_pq_second_level_and_outliers(backend, cpu_libs, M, N, G, K, K_l2, n_out, B):
+    """The production forms of the tensor (src/pq_decode.c:1441-1496 second residual level, :1058-1075 index forms, :1394-1409
+    outlier sidecar, :1538-1546 inner columns) against the CPU restatement, which is pinned to the compiled reference."""
+    rng = np.random.default_rng(M + N + K_l2 + n_out + B)
+    d = _cpu.make_pq_case_ex(rng, M, N, G, K, K_l2, n_out, B)
+    d["x"][B - 1, :3 * G] *= 1e-4                            # some chunks fall under the 1 % rule
+    t = backend.make_pq_ex(d)
+    got = backend.pq_matmul(t, d["x"])
+    want = np.stack([_cpu.oracle_pq_ex(cpu_libs.oracle, d, d["x"][b]) for b in range(B)])
+    assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
+    got2 = backend.pq_matmul(t, d["x"])                      # accumulators and counters were left clean
+    assert np.array_equal(got, got2)
+
+
+def test_pq_extras_through_the_host_layer(cpu_libs):
+    """ib_b200_pq_matmul_fp32 takes the reference's own struct with two levels and outliers (host pointers)."""
+    from libinferbit_b200 import _ffi
+    host = _ffi.load_host()
+    assert host.ib_b200_init(0) == 0, host.ib_b200_last_error()
+    try:
+        rng = np.random.default_rng(11)
+        d = _cpu.make_pq_case_ex(rng, 300, 1024 + 32, 16, 256, 16, 32, 1)
+        t = _cpu.ref_pq_tensor_ex(d)
+        out = np.empty(300, np.float32)
+        host.ib_b200_pq_matmul_fp32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        assert host.ib_b200_pq_matmul_fp32(C.byref(t), d["x"][0].ctypes.data, out.ctypes.data) == 0, host.ib_b200_last_error()
+        want = _cpu.oracle_pq_ex(cpu_libs.oracle, d, d["x"][0])
+        assert _cpu.close(out, want, RTOL, ATOL)
+        t.l2_idx_bytes = 2; t.K_l2 = 4096                    # uint16 second-level indices: refused, never computed on the CPU
+        host.ib_b200_pq_release.argtypes = [C.c_void_p]
+        host.ib_b200_pq_release(C.byref(t))
+        assert host.ib_b200_pq_matmul_fp32(C.byref(t), d["x"][0].ctypes.data, out.ctypes.data) == -1
+    finally:
+        host.ib_b200_shutdown()
+
+
 def test_packed_code_plane_is_a_faithful_copy(backend):
     """ibcu_pq_prepare regroups the codes as [slab of 32 subspaces][group of 16 rows][lane][16 rows]
     (subspace 2 * chunk + side = 32 * slab + lane); padding rows and padding subspaces hold zeros, and the tail
