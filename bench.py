@@ -372,6 +372,8 @@ def main():
             "pq_4096x14336_b8": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 8),
             "kmeans_4Mx8_k256": lambda: bs._kmeans(lib, ctx, 0, 1, lambda v: v, sync, iters=2),
             "decode_7b_b1": lambda: bs._decode(lib, host, ctx, 1, 0, 1, lambda v: v, sync, steps=3),
+            "decode_7b_b8": lambda: bs._decode(lib, host, ctx, 8, 0, 1, lambda v: v, sync, steps=3),
+            "decode_7b_b8_eager": lambda: bs._decode(lib, host, ctx, 8, 0, 1, lambda v: v, sync, steps=3, warm=4, graph=False),
             "decode_7b_b1_eager": lambda: bs._decode(lib, host, ctx, 1, 0, 1, lambda v: v, sync, steps=3, warm=4, graph=False),
         }
         print(json.dumps({"case": args.case, **cases[args.case]()}), flush=True)

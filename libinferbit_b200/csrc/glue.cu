@@ -437,7 +437,11 @@ static int attention_split(ibcu_ctx* ctx, const float* q, float* k_cache, float*
                            int n_heads, int n_kv_heads, int head_dim, int pos0, int B, const float* k_new, const float* v_new, float theta,
                            const int* pos0_dev, int max_ctx) {
     const int group = n_heads / n_kv_heads;
-    int want = (2 * ctx->sm_count) / (n_kv_heads * B);       // enough blocks to cover the machine
+    // Enough blocks to cover the machine several times over: a block's shared memory grows with its chunk of positions (two
+    // tiles of chunk x head_dim floats), so short chunks let several blocks share an SM; with B activations every chunk
+    // is staged by B blocks, which long chunks would serialise into waves of one block per SM. (One block serving all B
+    // activations from one staged tile was measured slower: the activations then run one after the other in each warp.)
+    int want = (6 * ctx->sm_count) / (n_kv_heads * B);
     if (want < 1) want = 1;
     int chunk, nsplit, grid_y, chunk_cap = ATT_CHUNK;
     if (pos0_dev) {
