@@ -249,9 +249,10 @@ class AttnProjWorkload:
 
 
 # ── secondary configurations ────────────────────────────────────────────────────────────
-def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
+def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6, tcgen05=0):
     """us per call and weight GB/s of one linear over a ring of distinct weight buffers (graph replay)."""
     dev = Dev(lib, ctx)
+    lib.ibcu_linear_use_tcgen05(ctx, tcgen05)
     rowbytes = N if bits == 8 else N // 2
     wbytes = M * rowbytes
     R = max(2, int(reps_target_bytes // wbytes))
@@ -269,6 +270,7 @@ def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6):
     ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid), reps=5) for _ in range(3)) / R
     lib.ibcu_graph_destroy(ctx, gid)
     dev.free_all()
+    lib.ibcu_linear_use_tcgen05(ctx, 0)
     algo = wbytes + 2 * M + 4 * B * N + 4 * B * M
     return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
             "shape": {"bits": bits, "M": M, "N": N, "B": B}}

@@ -23,6 +23,7 @@ struct ibcu_ctx {
     char msg[512];
     int pdl;                       // programmatic dependent launch between our kernels
     int force_generic;
+    int linear_tc;                 // 0 (default): every batch size on the mma.sync kernel; 1: INT4 calls with 8 to 16 activations on the tcgen05 kernel; 2: INT8 calls too
     int kmeans_path;               // IBCU_KMEANS_*: which assignment kernel ibcu_kmeans_assign may take (tests)
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)

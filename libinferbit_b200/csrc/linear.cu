@@ -37,6 +37,7 @@
 // Portable path (linear_generic_kernel): one warp per output row, plain FP32 FMAs; used for shapes
 // the fast path does not take (row bytes not a multiple of 16, unaligned pointers) and by tests.
 #include "common.cuh"
+#include "tc_common.cuh"
 
 bool ibcu_push_match(ibcu_ctx* ctx, float* const* outs, int n);      // comm.cu
 void ibcu_push_fill(ibcu_ctx* ctx, GatherPush* gp, size_t bytes);  // bytes this launch pushes to each peer
@@ -113,7 +114,8 @@ __device__ __forceinline__ float4 xsrc_load4(const XSource& s, const float* xb, 
 // Balanced base-256 digits of eight fixed-point values, as limb words. With Y = X + 0x00808080 the
 // unsigned bytes u_l of Y satisfy X = sum (u_l - 128) 256^l (l < 3) + (Y >> 24) 2^24, and u_l - 128 as
 // a signed byte is u_l ^ 0x80: so the four digits of X are the four bytes of Y ^ 0x00808080. Two 4x4
-// byte transposes turn eight such words into limb-major words; perm8 picks the INT4 column order.
+// byte transposes turn eight such words into limb-major words; bit 0 of perm8 picks the INT4 column order of the
+// mma.sync kernel, any non-zero perm8 also asks for the limb sums (perm8 == 2: natural order with sums).
 __device__ __forceinline__ void transpose4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t* o) {
     const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
     const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
@@ -124,7 +126,7 @@ __device__ __forceinline__ void limbs8(const int* X, int perm8, uint2* pk, int* 
     uint32_t D[8], lo[4], hi[4];
 #pragma unroll
     for (int i = 0; i < 8; i++) D[i] = ((uint32_t)X[i] + 0x00808080u) ^ 0x00808080u;
-    if (perm8) { transpose4x4_bytes(D[0], D[2], D[4], D[6], lo); transpose4x4_bytes(D[1], D[3], D[5], D[7], hi); }
+    if (perm8 & 1) { transpose4x4_bytes(D[0], D[2], D[4], D[6], lo); transpose4x4_bytes(D[1], D[3], D[5], D[7], hi); }
     else       { transpose4x4_bytes(D[0], D[1], D[2], D[3], lo); transpose4x4_bytes(D[4], D[5], D[6], D[7], hi); }
 #pragma unroll
     for (int l = 0; l < LIN_LIMBS; l++) {
@@ -752,6 +754,407 @@ int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail)
     return ibcu_launch(ctx, kern, dim3(grid), dim3(W * 32), smem, 1, true, p);
 }
 
+// ── batched path on tcgen05 (8 to 16 activations; optional) ─────────────────────────────
+// With eight or more activations the four limbs of every activation make 32 to 64 MMA columns and the product is a
+// small GEMM; mma.sync's integer rate then bounds the large launches. linear_tc_kernel runs the same exact arithmetic on
+// the fifth-generation tensor cores: tiles of 64 weight rows are the A operand, read from shared memory (INT8 bytes as
+// stored; INT4 nibbles widened to bytes by the loader warps), the limbs of a column slice are the B operand, resident in
+// shared memory for the life of the block, and the s32 sums accumulate in tensor memory, two tiles in turn so that the
+// epilogue of one tile overlaps the MMAs of the next.
+//   warps 0-3: epilogue (tcgen05.ld, limb recombination, scale, store / partial sums)   warps 4-7: loaders   warp 8: MMA issue
+// Both operands are K-major. A (weights) uses the 128-byte swizzle: a row's 128 bytes stay one line of shared memory, so a
+// warp's asynchronous copy of 512 contiguous bytes of a row lands in four whole lines (copies scattered in 16-byte pieces
+// were measured to reach L2 as one request per lane and fetched every sector twice). B (limbs) has no swizzle: a 16-byte K
+// chunk of 8 columns is one 128-byte core matrix, the core matrices of a chunk are contiguous (SBO = 128), chunks follow
+// one another (LBO = 16 x columns).
+// A block is bound to one column slice; it walks the row tiles blockIdx.x / nks + j * gridDim.x / nks.
+// Measured on B200 (graph replays, weights from HBM): 28672 x 4096 INT4 at 8 activations 42.8 us against 51.2 us for the
+// mma.sync kernel; 32000 x 4096 INT8 at 8 activations 47.2 against 47.3 us; 4096 x 4096 INT8 at 16 activations 20.5 against
+// 17.1 us (few tiles, and the split columns cost a recombination launch). In-kernel time stamps: a stage of 32 KB takes
+// 3.6 us from copy issue to landing with three stages in flight, so the kernel is bound by bytes in flight per SM (96 KB
+// beside the 64 KB of resident limbs), not by the tensor pipe (10 % active). Hence the option is off by default.
+constexpr int LT_TILE = 64, LT_EPI_WARPS = 4, LT_LOAD_WARPS = 4, LT_MMA_WARP = 8, LT_THREADS = 9 * 32;
+constexpr int LT_KCOLS = 512;                    // weight columns per pipeline step: sixteen MMAs of K = 32; a step reads 512 (INT8) or 256 (INT4) contiguous bytes of each row
+constexpr int LT_CH = LT_KCOLS / 16;             // 16-byte K chunks per step
+constexpr int LT_A_KBLOCK = LT_TILE * 128;       // A operand, K-major with the 128-byte swizzle: a block of 128 columns is 64 rows of 128 bytes (8 KB),
+                                                 // 8-row atoms of 1 KB; chunk c of row r sits at chunk position c ^ (r % 8) of its row
+constexpr int LT_A_STAGE = (LT_KCOLS / 128) * LT_A_KBLOCK;   // 32 KB: 64 rows x 512 bytes
+constexpr int LT_RAW_LD = 256 + 16;              // INT4: bytes per row of a raw stage: the nibbles of a step + 16
+constexpr int LT_RAW_STAGE = LT_TILE * LT_RAW_LD;
+constexpr int LT_MAX_STAGES = 8;
+
+struct LtShared {
+    unsigned long long full_a[LT_MAX_STAGES], empty_a[LT_MAX_STAGES];   // loaders -> MMA, MMA -> loaders
+    unsigned long long full_acc[2], empty_acc[2];                        // MMA -> epilogue, epilogue -> MMA
+    unsigned long long b_full, drained;
+    uint32_t tmem_base;
+    int abort_flag;
+    float back[32];                              // 2^-s of this slice per activation
+    int xsum[32 * LIN_LIMBS];                    // limb sums of this slice (INT4 bias)
+};
+
+struct LtParams {
+    LinTensor t[4];
+    int n_tensors, tile_start[5];                // tiles of tensor i are [tile_start[i], tile_start[i + 1])
+    int total_rows, rowbytes, N, B, NC, nks, slice_steps, total_steps, xs_ld;
+    const int8_t* xpack; const float* xscale; const int* xsum;
+    int* partial;
+    GatherPush gp;
+    int* err;
+};
+
+// shared-memory matrix descriptor, K-major with the 128-byte swizzle: 8-row atoms of 1024 bytes follow one another (SBO = 1024);
+// the K offset inside the 128-byte rows is part of the start address
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+template <int BITS, int STAGES, int RAW_STAGES>
+__global__ void __launch_bounds__(LT_THREADS, 1) linear_tc_kernel(const LtParams p) {
+    extern __shared__ __align__(1024) unsigned char lt_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ks = blockIdx.x % p.nks, tile0 = blockIdx.x / p.nks, tile_step = gridDim.x / p.nks;
+    const int ntiles = p.tile_start[p.n_tensors];
+    const int n_my = tile0 < ntiles ? (ntiles - tile0 + tile_step - 1) / tile_step : 0;
+    const int kbs = min(p.slice_steps, p.total_steps - ks * p.slice_steps);          // pipeline steps (of 128 columns) in this slice
+    const long n_steps = (long)n_my * kbs;
+    const uint32_t b_lbo = (uint32_t)p.NC * 16u;
+    unsigned char* sB = lt_smem;                                                       // [slice chunks][NC / 8][8][16]
+    unsigned char* sA = sB + (((size_t)p.slice_steps * LT_CH * b_lbo + 1023) & ~(size_t)1023);
+    unsigned char* sRaw = sA + STAGES * LT_A_STAGE;
+    LtShared* sh = reinterpret_cast<LtShared*>(sRaw + (BITS == 4 ? RAW_STAGES * LT_RAW_STAGE : 0));
+    volatile int* abort_flag = &sh->abort_flag;
+    pdl_launch_dependents();
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&sh->full_a[s]), LT_LOAD_WARPS); mbar_init(smem_u32(&sh->empty_a[s]), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&sh->full_acc[b]), 1); mbar_init(smem_u32(&sh->empty_acc[b]), LT_EPI_WARPS); }
+        mbar_init(smem_u32(&sh->b_full), LT_EPI_WARPS + 1);
+        mbar_init(smem_u32(&sh->drained), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const uint32_t tmem_cols = 2u * (uint32_t)p.NC;                                   // 64 or 128: a power of two, at least 32
+    if (warp == LT_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sh->tmem_base;
+
+    // which tensor a tile belongs to, and its first row there
+    auto tile_of = [&](int j, int& ti, int& row0) {
+        const int tile = tile0 + j * tile_step;
+        ti = 0;
+#pragma unroll
+        for (int i = 1; i < 4; i++) if (i < p.n_tensors && tile >= p.tile_start[i]) ti = i;
+        row0 = (tile - p.tile_start[ti]) * LT_TILE;
+    };
+
+    if (warp >= LT_EPI_WARPS && warp < LT_MMA_WARP) {
+        // ── loaders: warp lw owns rows 32 lw .. + 31 of every tile. The weights do not depend on the previous kernel:
+        //    no dependency wait here. ──
+        const int lw = warp - LT_EPI_WARPS;                                            // rows 16 lw .. + 15 of every tile
+        constexpr int RING = BITS == 8 ? STAGES : RAW_STAGES;                          // depth of the ring the global loads land in
+        bool alive = true;
+        auto issue = [&](long i) {
+            if (i < n_steps && alive) {
+                const int j = (int)(i / kbs), kb = (int)(i - (long)j * kbs);
+                int ti, row0;
+                tile_of(j, ti, row0);
+                const LinTensor& T = p.t[ti];
+                if (BITS == 8) {
+                    const int s = (int)(i % STAGES);
+                    // the stage is free once the MMAs of its previous use have read it
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_a[s]), (uint32_t)(((i / STAGES) & 1) ^ 1), abort_flag, 1))) { alive = false; }
+                    if (alive) {
+                        // a warp instruction copies one row's 512 bytes: whole lines of global memory into four whole (swizzled) lines of shared memory
+                        const uint32_t dst0 = smem_u32(sA + s * LT_A_STAGE) + (uint32_t)(lane >> 3) * LT_A_KBLOCK;
+                        const uint32_t c = lane & 7;
+#pragma unroll
+                        for (int u = 0; u < 16; u++) {
+                            const int rr = 16 * lw + u;
+                            const bool hv = row0 + rr < T.M;
+                            const uint8_t* sp = T.w + (size_t)(hv ? row0 + rr : 0) * p.rowbytes + (size_t)(ks * p.slice_steps + kb) * LT_KCOLS + lane * 16;
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                                         :: "r"(dst0 + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u + ((c ^ (uint32_t)(rr & 7)) << 4)), "l"(sp), "r"(hv ? 16 : 0) : "memory");
+                        }
+                    }
+                } else {
+                    // the nibbles of the step: 2 rows x 256 bytes per warp instruction
+                    const int piece = lane & 15;
+                    const uint32_t dst0 = smem_u32(sRaw + (int)(i % RAW_STAGES) * LT_RAW_STAGE) + piece * 16;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int rr = 16 * lw + 2 * u + (lane >> 4);
+                        const bool hv = row0 + rr < T.M;
+                        const uint8_t* sp = T.w + (size_t)(hv ? row0 + rr : 0) * p.rowbytes + (size_t)(ks * p.slice_steps + kb) * (LT_KCOLS / 2) + piece * 16;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst0 + (uint32_t)rr * LT_RAW_LD), "l"(sp), "r"(hv ? 16 : 0) : "memory");
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        constexpr int AHEAD = RING - 1;
+        for (int i = 0; i < AHEAD; i++) issue(i);
+        for (long i = 0; i < n_steps && alive; i++) {
+            if (BITS == 4) __syncwarp();                                               // the raw rows about to be refilled have been read by every lane
+            issue(i + AHEAD);
+            asm volatile("cp.async.wait_group %0;" :: "n"(AHEAD) : "memory");
+            if (BITS == 4) __syncwarp();                                               // rows copied by other lanes of the warp
+            const int s = (int)(i % STAGES);
+            if (BITS == 4) {
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_a[s]), (uint32_t)(((i / STAGES) & 1) ^ 1), abort_flag, 1))) break;
+                // widen this row's 128 nibbles to bytes 0..15 in column order: a raw byte holds columns 2i (low) and 2i + 1 (high)
+                // lane = (row, half of the row's 256 raw bytes): 8 pieces of 16 bytes -> 16 chunks of the operand stage
+                const int r = 16 * lw + (lane & 15), hf = lane >> 4;
+                const unsigned char* raw = sRaw + (int)(i % RAW_STAGES) * LT_RAW_STAGE + r * LT_RAW_LD + hf * 128;
+                unsigned char* dst = sA + s * LT_A_STAGE + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+                const uint32_t rx = (uint32_t)(r & 7);
+                auto chunk_at = [&](int kc) { return dst + (kc >> 3) * LT_A_KBLOCK + (((uint32_t)(kc & 7) ^ rx) << 4); };   // K chunk kc of this row
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(raw + q * 16);
+                    const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+                    uint32_t o[8];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const uint32_t lo = w[u] & 0x0F0F0F0Fu, hi = (w[u] >> 4) & 0x0F0F0F0Fu;
+                        o[2 * u] = __byte_perm(lo, hi, 0x5140);
+                        o[2 * u + 1] = __byte_perm(lo, hi, 0x7362);
+                    }
+                    *reinterpret_cast<uint4*>(chunk_at(hf * 16 + 2 * q)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(chunk_at(hf * 16 + 2 * q + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[s]));
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        // ── everyone else: the slice's limbs into the B operand, after the kernel that made them ──
+        pdl_wait();
+        const int ncols = p.B * LIN_LIMBS;
+        const int fill_tid = warp == LT_MMA_WARP ? LT_EPI_WARPS * 32 + lane : tid, fill_n = (LT_EPI_WARPS + 1) * 32;
+        const int cgs = p.NC / 8;
+        const long pieces = (long)kbs * LT_CH * p.NC;                                  // 16-byte pieces: LT_CH K chunks per step, NC columns
+        const int8_t* xp = p.xpack + (size_t)ks * ncols * p.xs_ld;
+        const uint32_t sB_u32 = smem_u32(sB);
+        for (long e = fill_tid; e < pieces; e += fill_n) {
+            // a warp instruction covers 8 columns x 4 K chunks: four 128-byte runs in shared memory, 64 contiguous bytes per
+            // column in global memory. Asynchronous copies: all pieces of a thread are in flight together.
+            const int c8 = (int)(e & 7), kl = (int)((e >> 3) & 3);
+            const long hi = e >> 5;
+            const int cg = (int)(hi % cgs), kc = (int)(hi / cgs) * 4 + kl;
+            const int c = cg * 8 + c8;
+            const bool have = c < ncols;
+            const int8_t* src = xp + (size_t)(have ? c : 0) * p.xs_ld + (size_t)kc * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(sB_u32 + (uint32_t)kc * b_lbo + cg * 128 + c8 * 16), "l"(src), "r"(have ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (fill_tid < p.B) sh->back[fill_tid] = p.xscale[fill_tid * p.nks + ks];
+        if (BITS == 4 && fill_tid < ncols) sh->xsum[fill_tid] = p.xsum[((size_t)(fill_tid / LIN_LIMBS) * p.nks + ks) * LIN_LIMBS + (fill_tid % LIN_LIMBS)];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->b_full));
+
+        if (warp == LT_MMA_WARP) {
+            if (lane == 0) {
+                // s32 accumulate; A: unsigned bytes for widened nibbles (bias 8 removed through the limb sums), signed for INT8; B: signed limbs
+                const uint32_t idesc = (2u << 4) | ((BITS == 8 ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(p.NC >> 3) << 17) | ((uint32_t)(LT_TILE >> 4) << 24);
+                bool ok = mbar_wait(smem_u32(&sh->b_full), 0u, abort_flag, 6);
+                for (int j = 0; j < n_my && ok; j++) {
+                    const int buf = j & 1;
+                    ok = mbar_wait(smem_u32(&sh->empty_acc[buf]), (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, 3);
+                    const uint32_t d = tmem_base + (uint32_t)buf * (uint32_t)p.NC;
+                    for (int kb = 0; kb < kbs && ok; kb++) {
+                        const long i = (long)j * kbs + kb;
+                        const int s = (int)(i % STAGES);
+                        ok = mbar_wait(smem_u32(&sh->full_a[s]), (uint32_t)((i / STAGES) & 1), abort_flag, 2);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int m = 0; m < LT_CH / 2; m++) {
+                            const uint64_t a_desc = smem_desc_sw128(smem_u32(sA + s * LT_A_STAGE + (m >> 2) * LT_A_KBLOCK + (m & 3) * 32));
+                            const uint64_t b_desc = smem_desc(smem_u32(sB + (size_t)(kb * LT_CH + 2 * m) * b_lbo), b_lbo, 128);
+                            mma_i8_ss(d, a_desc, b_desc, idesc, (kb | m) ? 1u : 0u);
+                        }
+                        mma_commit(smem_u32(&sh->empty_a[s]));
+                    }
+                    if (ok) mma_commit(smem_u32(&sh->full_acc[buf]));
+                }
+                mma_commit(smem_u32(&sh->drained));
+                mbar_wait(smem_u32(&sh->drained), 0u, abort_flag, 4);                  // nothing of this block is left in the tensor pipe
+            }
+        } else {
+            // ── epilogue: warp q drains rows 32 q .. + 31 of every tile ──
+            const int q = warp;
+            const unsigned tag = p.gp.world ? tag_current(p.gp) : 0u;
+            for (int j = 0; j < n_my; j++) {
+                const int buf = j & 1;
+                int ti, row0;
+                tile_of(j, ti, row0);
+                const LinTensor& T = p.t[ti];
+                // a 64-row accumulator keeps row r in lane 32 (r / 16) + r % 16 of tensor memory: the first 16 lanes of every warp's quarter
+                const int row = row0 + 16 * q + (lane & 15);
+                const bool have = lane < 16 && row < T.M;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_acc[buf]), (uint32_t)((j >> 1) & 1), abort_flag, 5))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * (uint32_t)p.NC;
+                const float sc = have ? (T.scales_fp32 ? reinterpret_cast<const float*>(T.scales)[row] : __half2float(reinterpret_cast<const __half*>(T.scales)[row])) : 0.0f;
+                for (int c0 = 0; c0 < p.NC; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(taddr + c0, acc);
+                    tmem_wait_ld(acc);
+#pragma unroll
+                    for (int bb = 0; bb < 8; bb++) {
+                        const int b = c0 / 4 + bb;
+                        if (b >= p.B || !have) continue;
+                        int limb[LIN_LIMBS];
+#pragma unroll
+                        for (int l = 0; l < LIN_LIMBS; l++) {
+                            limb[l] = (int)acc[bb * 4 + l];
+                            if (BITS == 4) limb[l] -= 8 * sh->xsum[b * LIN_LIMBS + l];
+                        }
+                        if (p.nks == 1) {
+                            const long long V = (((long long)limb[3] * 256 + limb[2]) * 256 + limb[1]) * 256 + limb[0];
+                            const float y = (float)((double)V * (double)sh->back[b]);
+                            float* o = T.out + (size_t)b * T.out_stride + row;
+                            const float v = T.epilogue == IBCU_EPI_ADD ? *o + y * sc : y * sc;
+                            *o = v;
+                            if (p.gp.world) tag_push(p.gp, (size_t)T.win_off + ((size_t)b * T.out_stride + row) * sizeof(float), v, tag);
+                        } else {
+#pragma unroll
+                            for (int l = 0; l < LIN_LIMBS; l++)
+                                p.partial[((size_t)ks * (p.B * LIN_LIMBS) + b * LIN_LIMBS + l) * p.total_rows + T.row_start + row] = limb[l];
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh->empty_acc[buf]));              // the tensor cores may overwrite this tile
+            }
+        }
+    }
+    // ── the end: tensor memory back, a wait that ran out reported ──
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == LT_MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+    if (tid == 0 && sh->abort_flag) *p.err = 100 + sh->abort_flag;
+}
+
+template <int BITS, int STAGES, int RAW_STAGES>
+int launch_tc(ibcu_ctx* ctx, const LtParams& p, int grid, size_t smem) {
+    auto kern = linear_tc_kernel<BITS, STAGES, RAW_STAGES>;
+    static size_t allowed[64];
+    size_t& have = allowed[ctx->device & 63];
+    if (smem > have) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(linear_tc_kernel, smem=%zu): %s", smem, cudaGetErrorString(e));
+        have = smem;
+    }
+    return ibcu_launch(ctx, kern, dim3(grid), dim3(LT_THREADS), smem, 1, true, p);
+}
+
+constexpr int LT_STAGES8 = 4, LT_STAGES4 = 2, LT_RAW4 = 4;     // stages of weights in flight (INT8: operand stages; INT4: raw stages, widened into 3 operand stages)
+constexpr size_t LT_B_BUDGET = 64 * 1024;                      // shared memory for the resident limbs of a column slice: the rest goes to the weight ring
+
+// 8 to 16 activations, rows of whole 128-column steps: conversion kernel, tcgen05 kernel, and the recombination kernel when
+// the columns had to be split over several blocks. Returns IBCU_ERR_STATE when the shape does not fit (the caller goes on).
+int linear_tc(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors, const float* x, int N, int B, int bits,
+              const ibcu_prologue_t* pro, int op) {
+    const int NC = B <= 8 ? 32 : 64, ncols = B * LIN_LIMBS;
+    const int total_steps = N / LT_KCOLS;
+    const size_t ring = bits == 8 ? (size_t)LT_STAGES8 * LT_A_STAGE : (size_t)LT_STAGES4 * LT_A_STAGE + (size_t)LT_RAW4 * LT_RAW_STAGE;
+    const size_t fixed = ring + sizeof(LtShared) + 2048;
+    const size_t per_step = (size_t)NC * LT_KCOLS;                                     // B-operand bytes per step
+    size_t b_budget = 227 * 1024 - fixed;
+    if (b_budget > LT_B_BUDGET) b_budget = LT_B_BUDGET;
+    const int max_steps = (int)(b_budget / per_step);
+    if (max_steps < 2) return IBCU_ERR_STATE;
+    const int nks = (total_steps + max_steps - 1) / max_steps;
+    const int slice_steps = (total_steps + nks - 1) / nks;
+    const size_t smem = (((size_t)slice_steps * per_step + 1023) & ~(size_t)1023) + ring + sizeof(LtShared);
+    LtParams p;
+    memset(&p, 0, sizeof p);
+    long total_rows = 0;
+    int ntiles = 0;
+    for (int i = 0; i < n_tensors; i++) {
+        p.t[i] = { (const uint8_t*)tensors[i].w, tensors[i].scales, tensors[i].out, tensors[i].M,
+                   tensors[i].out_stride, tensors[i].scales_fp32, tensors[i].epilogue, (int)total_rows, 0, 0, -1 };
+        p.tile_start[i] = ntiles;
+        ntiles += (tensors[i].M + LT_TILE - 1) / LT_TILE;
+        total_rows += tensors[i].M;
+    }
+    for (int i = n_tensors; i <= 4; i++) p.tile_start[i] = ntiles;
+    if (ntiles == 0) return IBCU_OK;
+    GatherWait gw;
+    ibcu_take_gather_wait(ctx, &gw);
+    {
+        float* outs[4];
+        for (int i = 0; i < n_tensors; i++) outs[i] = tensors[i].out;
+        if (ibcu_push_match(ctx, outs, n_tensors)) {
+            size_t bytes = 0;
+            for (int i = 0; i < n_tensors; i++) bytes += (size_t)tensors[i].M * B * sizeof(float);
+            ibcu_push_fill(ctx, &p.gp, bytes);
+            for (int i = 0; i < n_tensors; i++) p.t[i].win_off = (long)((const char*)tensors[i].out - ctx->win_base);
+        }
+    }
+    const int cols = slice_steps * LT_KCOLS, xs_ld = cols + 16;
+    const size_t xpack_bytes = (((size_t)nks * ncols * xs_ld) + 255) & ~(size_t)255;
+    const size_t xscale_bytes = (((size_t)B * nks * sizeof(float)) + 255) & ~(size_t)255;
+    int rc = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, xpack_bytes + xscale_bytes + (size_t)B * nks * LIN_LIMBS * sizeof(int));
+    if (rc) return rc;
+    int8_t* xpack = (int8_t*)ctx->xpack;
+    float* xscale = (float*)((char*)ctx->xpack + xpack_bytes);
+    int* xsum = (int*)((char*)ctx->xpack + xpack_bytes + xscale_bytes);
+    p.n_tensors = n_tensors; p.total_rows = (int)total_rows; p.rowbytes = bits == 8 ? N : N / 2; p.N = N; p.B = B; p.NC = NC;
+    p.nks = nks; p.slice_steps = slice_steps; p.total_steps = total_steps; p.xs_ld = xs_ld;
+    p.xpack = xpack; p.xscale = xscale; p.xsum = xsum; p.err = ctx->kern_err;
+    if (nks > 1) {
+        rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, (size_t)total_rows * nks * B * LIN_LIMBS * sizeof(int));
+        if (rc) return rc;
+        p.partial = (int*)ctx->scratch;
+    }
+    XSource xsrc = { x, pro ? pro->x2 : nullptr, pro ? (const __half*)pro->norm_w : nullptr, pro ? pro->eps : 0.0f, op,
+                     op == IBCU_PRO_KNOWN_MAX ? pro->amax : nullptr, op == IBCU_PRO_KNOWN_MAX ? pro->n_amax : 0 };
+    {
+        const dim3 xg(nks, B);
+        const int perm8 = bits == 4 ? 2 : 0;                                           // natural column order; limb sums for the nibble bias
+        const int xthreads = cols > XREG_V * 4 * 512 ? 1024 : (cols >= 2048 ? 512 : 256);
+        rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum, gw)
+           : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw)
+                              : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw);
+        if (rc) return rc;
+    }
+    int per_slice = ctx->sm_count / nks;                                               // one block per SM
+    if (per_slice < 1) per_slice = 1;
+    if (per_slice > ntiles) per_slice = ntiles;
+    const int grid = per_slice * nks;
+    rc = bits == 8 ? launch_tc<8, LT_STAGES8, 1>(ctx, p, grid, smem) : launch_tc<4, LT_STAGES4, LT_RAW4>(ctx, p, grid, smem);
+    if (rc || nks == 1) return rc;
+    LinearParams fp;
+    memset(&fp, 0, sizeof fp);
+    for (int i = 0; i < n_tensors; i++) fp.t[i] = p.t[i];
+    fp.n_tensors = n_tensors; fp.total_rows = (int)total_rows; fp.B = B; fp.nks = nks; fp.partial = p.partial; fp.xscale = xscale; fp.gp = p.gp;
+    long outs = total_rows * B;
+    int fgrid = (int)((outs + 255) / 256);
+    if (fgrid > 4 * ctx->sm_count) fgrid = 4 * ctx->sm_count;
+    return ibcu_launch(ctx, linear_finalize_kernel, dim3(fgrid), dim3(256), 0, 1, true, fp);
+}
+
 // Eight warps and 512-byte stages; the ring is as deep as two resident blocks per SM allow.
 template <int BITS, int NCG>
 int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int stages, size_t smem_tail) {
@@ -766,6 +1169,7 @@ int dispatch_shape(ibcu_ctx* ctx, const LinearParams& p, int grid, int rt, int s
 }  // namespace
 
 extern "C" void ibcu_linear_force_generic(ibcu_ctx* ctx, int on) { if (ctx) ctx->force_generic = on; }
+extern "C" void ibcu_linear_use_tcgen05(ibcu_ctx* ctx, int on) { if (ctx) ctx->linear_tc = on; }
 
 extern "C" int ibcu_linear(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors,
                            const float* x, int N, int B, int bits) {
@@ -826,6 +1230,10 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
             if (rc2) return rc2;
         }
         return IBCU_OK;
+    }
+    if (B >= 8 && N % LT_KCOLS == 0 && ctx->linear_tc && (bits == 4 || ctx->linear_tc > 1)) {       // enough activations for a GEMM: the tcgen05 kernel
+        const int rc_tc = linear_tc(ctx, tensors, n_tensors, x, N, B, bits, pro, op);
+        if (rc_tc != IBCU_ERR_STATE) return rc_tc;
     }
     const int ncols = B * LIN_LIMBS;
     const int ncg = (ncols + 7) / 8 <= 1 ? 1 : ((ncols + 7) / 8 <= 2 ? 2 : ((ncols + 7) / 8 <= 4 ? 4 : 8));

@@ -43,6 +43,32 @@ def test_linear_matches_scalar_reference(backend, cpu_libs, bits, M, N, B):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("M,N,B", [(4096, 4096, 8), (4096, 4096, 16), (1000, 4096, 11), (130, 256, 8), (4096, 14336, 8), (2048, 14336, 16),
+                                   (300, 1152, 9)])
+def test_batched_tcgen05_path(backend, cpu_libs, bits, M, N, B):
+    """The optional kernel for 8 to 16 activations on the tcgen05 tensor cores (accumulators in tensor memory): against
+    the scalar restatement, and against the mma.sync kernel on the same inputs. Both sum exact
+    integers; they can differ in the last place only where the columns were split into different numbers of slices."""
+    rng = np.random.default_rng(bits * 13 + M + N + B)
+    w, s16, x = (_cpu.make_int8_case if bits == 8 else _cpu.make_int4_case)(rng, M, N, B)
+    init = rng.standard_normal((B, M)).astype(np.float32)
+    want = oracle_linear(cpu_libs, w, s16, x, bits)
+    backend.lib.ibcu_linear_use_tcgen05(backend.ctx, 2)
+    try:
+        before = backend.launches()
+        got = backend.linear(w, s16, x, bits)
+        assert backend.launches() - before >= (2 if N % 512 == 0 else 1)    # conversion kernel + tcgen05 kernel (+ recombination); other rows take the usual kernel
+        assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
+        got_add = backend.linear(w, s16, x, bits, epilogue=1, out_init=init)
+        assert np.allclose(got_add, init + got, rtol=1e-6, atol=1e-6 * float(np.abs(got).max()))    # the residual epilogue adds the same product
+    finally:
+        backend.lib.ibcu_linear_use_tcgen05(backend.ctx, 0)
+    other = backend.linear(w, s16, x, bits)
+    assert np.allclose(got, other, rtol=2e-6, atol=1e-6 * float(np.abs(other).max()))
+    assert backend.lib.ibcu_sync(backend.ctx) == 0           # no wait inside the kernel ran out
+
+
+@pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("M,N,B", [(40, 66, 2), (9, 30, 1), (257, 1000, 3), (64, 4096, 4)])
 def test_portable_kernel(backend, cpu_libs, bits, M, N, B):
     """Shapes the tensor-core path does not take (row bytes not a multiple of 16) and the forced
