@@ -130,7 +130,8 @@ __device__ __forceinline__ void fold(float* v, int o, int lane) {
 
 // BT activations (1 or 2) share a pass over the codes: table entries are BT floats wide. grid = (blocks of rows,
 // blocks of slabs, passes); pass z serves activations BT z .. BT z + BT - 1.
-template <int BT>
+// EX: the tensor has a second level or outlier columns; plain tensors take the instance without that code.
+template <int BT, bool EX>
 __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p) {
     constexpr int PQ_NG = BT == 1 ? 4 : 2;                   // groups of 16 rows whose codes a warp keeps in flight
     extern __shared__ __align__(16) float lut[];            // [256][32][BT]
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     uint4 cd[PQ_NG];
     if (nj > 0) {
         load_codes(blockIdx.y, 0, cd);
-        const int lvl0 = (int)blockIdx.y >= p.nslab1;
+        const int lvl0 = EX && (int)blockIdx.y >= p.nslab1;
         if (lvl_smem(lvl0)) { stage_cb(lvl0); staged = lvl0; }
     }
     const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
@@ -197,14 +198,14 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         if (half == 8) {
             for (int e = tid; e < BT * 256; e += PQ_THREADS) {
                 const int t = e >> 8, l = (e >> 3) & 31, i = e & 7, s = s0 + l;
-                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (p.inner ? p.inner[s * 8 + i] : s * 8 + i)] : 0.0f;
+                xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + ((EX && p.inner) ? p.inner[s * 8 + i] : s * 8 + i)] : 0.0f;
             }
             return;
         }
         for (int e = tid; e < BT * 32 * half; e += PQ_THREADS) {
             const int t = e / (32 * half), r = e - t * 32 * half, l = r / half, i = r - l * half;
             const int s = s0 + l;
-            xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + (p.inner ? p.inner[s * half + i] : s * half + i)] : 0.0f;
+            xs[t][l][i] = (t < nb && s < nsub) ? p.x[(size_t)(b0 + t) * p.N + ((EX && p.inner) ? p.inner[s * half + i] : s * half + i)] : 0.0f;
         }
     };
     // ── max |x| of each activation (the reference's 1 %-of-max rule and the fixed-point scale need it), as the
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         if (t >= nb) continue;
         if (p.amax_bits) { ab[t] = p.amax_bits[b0 + t]; continue; }            // made by pq_amax_kernel ahead of this launch
         const float* xb = p.x + (size_t)(b0 + t) * p.N;
-        if (p.inner) {                                       // outlier columns do not count (src/pq_decode.c:1582-1588)
+        if (EX && p.inner) {                                 // outlier columns do not count (src/pq_decode.c:1582-1588)
             for (int j = tid; j < p.n_inner; j += PQ_THREADS) ab[t] = max(ab[t], __float_as_uint(xb[p.inner[j]]) & 0x7fffffffu);
         } else if (vec_x) {
             const uint4* x4 = reinterpret_cast<const uint4*>(xb);
@@ -236,14 +237,14 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     int anybad = 0;
     for (int j = 0; j < nj; j++) {
         const int slab = blockIdx.y + j * gridDim.y;
-        const int lvl = slab >= p.nslab1;                    // slabs of the second level follow those of the first, over the same slices of x
+        const int lvl = EX && slab >= p.nslab1;              // slabs of the second level follow those of the first, over the same slices of x
         const int s0 = (lvl ? slab - p.nslab1 : slab) * 32;
         const int Kl = lvl ? p.K2 : p.K;
         const bool cb_smem = lvl_smem(lvl), cb_vec = lvl_vec(lvl);
         if (j) {
             __syncthreads();                                 // the gather of the previous slab is done with the table and xs
             load_codes(slab, 0, cd);
-            if (cb_smem && staged != lvl) { stage_cb(lvl); staged = lvl; }
+            if (EX && cb_smem && staged != lvl) { stage_cb(lvl); staged = lvl; }
         }
         fill_xs(s0);
         __syncthreads();
@@ -514,13 +515,16 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
     p.amax_bits = nullptr;
     p.nslab1 = pl.nslab1; p.K2 = t->K_l2; p.cb2_l = (const __half*)t->codebook2_l; p.cb2_r = (const __half*)t->codebook2_r;
     p.inner = t->n_outlier > 0 ? t->inner_cols : nullptr; p.n_inner = t->N - t->n_outlier;
+    const bool ex = t->K_l2 > 0 || t->n_outlier > 0;
     const dim3 grid(pl.row_blocks, pl.slab_blocks, pl.passes), block(PQ_THREADS);
     // static plus dynamic shared memory passes 48 KB: opt in once per device
     static std::once_flag once[64];
     cudaError_t e = cudaSuccess;
     std::call_once(once[ctx->device & 63], [&] {
-        e = cudaFuncSetAttribute(pq_slab_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 2 * (int)sizeof(float));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
+        e = cudaFuncSetAttribute(pq_slab_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 2 * (int)sizeof(float));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 2 * (int)sizeof(float));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
     });
     if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
     if (pl.bt == 2) {
@@ -530,10 +534,12 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits, p.inner, p.n_inner);
         if (rc) return rc;
         p.amax_bits = amax_bits;
-        rc = ibcu_launch(ctx, pq_slab_kernel<2>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
+        rc = ex ? ibcu_launch(ctx, pq_slab_kernel<2, true>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p)
+                : ibcu_launch(ctx, pq_slab_kernel<2, false>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
         if (rc) return rc;
     } else {
-        const int rc = ibcu_launch(ctx, pq_slab_kernel<1>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p);
+        const int rc = ex ? ibcu_launch(ctx, pq_slab_kernel<1, true>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p)
+                          : ibcu_launch(ctx, pq_slab_kernel<1, false>, grid, block, (size_t)256 * 32 * sizeof(float), 1, true, p);
         if (rc) return rc;
     }
     if (t->n_outlier > 0)                                    // the sidecar's share is added to the finished rows (src/pq_decode.c:1676)
