@@ -366,9 +366,9 @@ def main():
             "w4a8_14336x4096_b1": lambda: bs._w4a8_ring(lib, ctx, 14336, 4096, 1),
             "w4a8_4096x14336_b1": lambda: bs._w4a8_ring(lib, ctx, 4096, 14336, 1),
             "w4a8_14336x4096_b8": lambda: bs._w4a8_ring(lib, ctx, 14336, 4096, 8),
-            "int4_28672x4096_b8": lambda: bs._linear_ring(lib, ctx, 4, 28672, 4096, 8, reps_target_bytes=400e6),
+            "int4_28672x4096_b8": lambda: bs._linear_ring(lib, ctx, 4, 28672, 4096, 8, reps_target_bytes=400e6, tcgen05=-1),
             "int4_28672x4096_b8_tcgen05": lambda: bs._linear_ring(lib, ctx, 4, 28672, 4096, 8, reps_target_bytes=400e6, tcgen05=1),
-            "int8_32000x4096_b8": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 8, reps_target_bytes=400e6),
+            "int8_32000x4096_b8": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 8, reps_target_bytes=400e6, tcgen05=-1),
             "int8_32000x4096_b8_tcgen05": lambda: bs._linear_ring(lib, ctx, 8, 32000, 4096, 8, reps_target_bytes=400e6, tcgen05=2),
             "int8_4096x4096_b16_tcgen05": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 16, reps_target_bytes=300e6, tcgen05=2),
             "int8_4096x4096_b16": lambda: bs._linear_ring(lib, ctx, 8, 4096, 4096, 16, reps_target_bytes=300e6),

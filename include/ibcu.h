@@ -136,10 +136,11 @@ int ibcu_linear_gate_up_silu(ibcu_ctx* ctx, const ibcu_linear_t* gate_up,
                              const float* x, int N, int B, int bits);
 /* Force the portable (non tensor-core) kernel for the next ibcu_linear calls; for tests. */
 void ibcu_linear_force_generic(ibcu_ctx* ctx, int on);
-/* A second kernel for calls with 8 to 16 activations and N a multiple of 128 (256 for INT4): the same exact arithmetic on
- * the tcgen05 tensor cores, weights as the A operand from shared memory, limbs as the B operand, s32 accumulators in
- * tensor memory. on = 1: INT4 calls take it, 2: INT8 calls as well, 0 (the default): none - measured on B200 it equals
- * the mma.sync kernel on the large INT4 tensors and is slower on the INT8 ones, so it is kept as an option. */
+/* A second kernel for calls with 5 to 16 activations and N a multiple of 512: the same exact arithmetic on the tcgen05
+ * tensor cores, weights as the A operand from shared memory, limbs as the B operand, s32 accumulators in tensor memory.
+ * on = 0 (the default): only the calls where it was measured faster than the mma.sync kernel on B200 (INT4 tensors of at
+ * least 3072 rows and at most 4096 columns with 5 to 8 activations); 1: every INT4 call it can take; 2: INT8 calls as well;
+ * -1: never. The choice depends on the call's shape only, so every rank of a sharded model takes the same kernel. */
 void ibcu_linear_use_tcgen05(ibcu_ctx* ctx, int on);
 
 /* W4A8 route (src/threading.c:401-432 activation quantiser, src/kernels/scalar.c:43-124 kernels):

@@ -249,7 +249,7 @@ class AttnProjWorkload:
 
 
 # ── secondary configurations ────────────────────────────────────────────────────────────
-def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6, tcgen05=0):
+def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6, tcgen05=0):    # tcgen05: 0 library default, 1 / 2 forced on, -1 off
     """us per call and weight GB/s of one linear over a ring of distinct weight buffers (graph replay)."""
     dev = Dev(lib, ctx)
     lib.ibcu_linear_use_tcgen05(ctx, tcgen05)

@@ -23,7 +23,7 @@ struct ibcu_ctx {
     char msg[512];
     int pdl;                       // programmatic dependent launch between our kernels
     int force_generic;
-    int linear_tc;                 // 0 (default): every batch size on the mma.sync kernel; 1: INT4 calls with 8 to 16 activations on the tcgen05 kernel; 2: INT8 calls too
+    int linear_tc;                 // tcgen05 kernel for batched linears: 0 (default) where it was measured faster, 1 every INT4 call it can take, 2 INT8 calls too, -1 never
     int kmeans_path;               // IBCU_KMEANS_*: which assignment kernel ibcu_kmeans_assign may take (tests)
     uint64_t launches;
     // scratch owned by the context, grown on demand (never shrinks)

@@ -770,9 +770,10 @@ int launch_mma(ibcu_ctx* ctx, const LinearParams& p, int grid, size_t smem_tail)
 // A block is bound to one column slice; it walks the row tiles blockIdx.x / nks + j * gridDim.x / nks.
 // Measured on B200 (graph replays, weights from HBM): 28672 x 4096 INT4 at 8 activations 42.8 us against 51.2 us for the
 // mma.sync kernel; 32000 x 4096 INT8 at 8 activations 47.2 against 47.3 us; 4096 x 4096 INT8 at 16 activations 20.5 against
-// 17.1 us (few tiles, and the split columns cost a recombination launch). In-kernel time stamps: a stage of 32 KB takes
+// 17.1 us (few tiles, and the split columns cost a recombination launch). The 7B step at batch 8 gains 5 % with the gate/up launch on this kernel. In-kernel time stamps: a stage of 32 KB takes
 // 3.6 us from copy issue to landing with three stages in flight, so the kernel is bound by bytes in flight per SM (96 KB
-// beside the 64 KB of resident limbs), not by the tensor pipe (10 % active). Hence the option is off by default.
+// beside the 64 KB of resident limbs), not by the tensor pipe (10 % active). By default it therefore takes only the calls where it was measured ahead: INT4 tensors of
+// at least 3072 rows and at most 4096 columns with 5 to 8 activations; ibcu_linear_use_tcgen05 widens or narrows that.
 constexpr int LT_TILE = 64, LT_EPI_WARPS = 4, LT_LOAD_WARPS = 4, LT_MMA_WARP = 8, LT_THREADS = 9 * 32;
 constexpr int LT_KCOLS = 512;                    // weight columns per pipeline step: sixteen MMAs of K = 32; a step reads 512 (INT8) or 256 (INT4) contiguous bytes of each row
 constexpr int LT_CH = LT_KCOLS / 16;             // 16-byte K chunks per step
@@ -1231,7 +1232,12 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
         }
         return IBCU_OK;
     }
-    if (B >= 8 && N % LT_KCOLS == 0 && ctx->linear_tc && (bits == 4 || ctx->linear_tc > 1)) {       // enough activations for a GEMM: the tcgen05 kernel
+    long rows_all = 0;
+    for (int i = 0; i < n_tensors; i++) rows_all += tensors[i].M;
+    // linear_tc: 0 = automatic (the tcgen05 kernel where it was measured faster: INT4 tensors of many rows whose columns need at most
+    // two slices), 1 = every INT4 call it can take, 2 = INT8 calls too, -1 = never
+    const bool tc_auto = ctx->linear_tc == 0 && bits == 4 && B >= 5 && B <= 8 && N <= 4096 && rows_all >= 3072;
+    if (B >= 5 && N % LT_KCOLS == 0 && (tc_auto || (ctx->linear_tc > 0 && (bits == 4 || ctx->linear_tc > 1)))) {       // enough activations for a GEMM: the tcgen05 kernel
         const int rc_tc = linear_tc(ctx, tensors, n_tensors, x, N, B, bits, pro, op);
         if (rc_tc != IBCU_ERR_STATE) return rc_tc;
     }

@@ -61,9 +61,10 @@ def test_batched_tcgen05_path(backend, cpu_libs, bits, M, N, B):
         assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
         got_add = backend.linear(w, s16, x, bits, epilogue=1, out_init=init)
         assert np.allclose(got_add, init + got, rtol=1e-6, atol=1e-6 * float(np.abs(got).max()))    # the residual epilogue adds the same product
+        backend.lib.ibcu_linear_use_tcgen05(backend.ctx, -1)
+        other = backend.linear(w, s16, x, bits)
     finally:
         backend.lib.ibcu_linear_use_tcgen05(backend.ctx, 0)
-    other = backend.linear(w, s16, x, bits)
     assert np.allclose(got, other, rtol=2e-6, atol=1e-6 * float(np.abs(other).max()))
     assert backend.lib.ibcu_sync(backend.ctx) == 0           # no wait inside the kernel ran out
 
