@@ -148,6 +148,9 @@ void ibcu_linear_use_tcgen05(ibcu_ctx* ctx, int on);
 int ibcu_quantize_input_int8_g128(ibcu_ctx* ctx, const float* x, int8_t* q, float* sa, int N, int B);
 int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* tensor, const int8_t* xq, const float* sa,
                      int N, int B);
+/* Both steps of the reference's INT4 route for FP32 activations (tensor_matmul with IB_W4A8 on, src/forward.c:175-246):
+ * the quantiser and the matvec (one launch for a single activation of up to 4096 columns, else two). Same bits as the two calls. */
+int ibcu_linear_w4a8_fp32(ibcu_ctx* ctx, const ibcu_linear_t* tensor, const float* x, int N, int B);
 
 /* ── PQ matvec ───────────────────────────────────────────────────────────────────────── */
 /* Stands in for ib_pq_matmul_fp32 / _threaded / _streaming (src/pq_decode.h:189-222; body

@@ -77,6 +77,7 @@ IBCU_SYMBOLS = {
     "ibcu_linear_use_tcgen05": (None, [C.c_void_p, C.c_int]),
     "ibcu_quantize_input_int8_g128": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "ibcu_linear_w4a8": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_linear_w4a8_fp32": (C.c_int, [C.c_void_p, C.POINTER(LinearT), C.c_void_p, C.c_int, C.c_int]),
     "ibcu_pq_idx_t_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "ibcu_pq_prepared_bytes": (C.c_size_t, [C.POINTER(PqT)]),
     "ibcu_pq_prepare": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p]),

@@ -278,7 +278,7 @@ def _linear_ring(lib, ctx, bits, M, N, B, reps_target_bytes=700e6, tcgen05=0):  
 
 def _w4a8_ring(lib, ctx, M, N, B, reps_target_bytes=300e6):
     """The reference's default route for an INT4 linear (src/forward.c:175-246 with IB_W4A8 on): quantise the activation per
-    128-column group, then the INT4 x INT8 matvec; both launches are inside the timed call."""
+    128-column group, then the INT4 x INT8 matvec; both steps are inside the timed call."""
     dev = Dev(lib, ctx)
     wbytes = M * N // 2
     R = max(2, int(reps_target_bytes // wbytes))
@@ -291,8 +291,7 @@ def _w4a8_ring(lib, ctx, M, N, B, reps_target_bytes=300e6):
 
     def run():
         for d in descs:
-            check(lib, ctx, lib.ibcu_quantize_input_int8_g128(ctx, dx, dq, dsa, N, B))
-            check(lib, ctx, lib.ibcu_linear_w4a8(ctx, C.byref(d), dq, dsa, N, B))
+            check(lib, ctx, lib.ibcu_linear_w4a8_fp32(ctx, C.byref(d), dx, N, B))
     gid = dev.graph(run)
     dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
     ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid), reps=5) for _ in range(3)) / R
@@ -300,7 +299,7 @@ def _w4a8_ring(lib, ctx, M, N, B, reps_target_bytes=300e6):
     dev.free_all()
     algo = wbytes + 2 * M + 4 * B * N + 4 * B * M
     return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
-            "shape": {"bits": 4, "activation_bits": 8, "M": M, "N": N, "B": B}, "route": "quantize_input_int8_g128 + matmul_w4a8"}
+            "shape": {"bits": 4, "activation_bits": 8, "M": M, "N": N, "B": B}, "route": "quantize_input_int8_g128 + matmul_w4a8 (ibcu_linear_w4a8_fp32)"}
 
 
 def _pq(lib, ctx, M, N, G, K, B):

@@ -110,6 +110,7 @@ struct WtParams {
     const uint8_t* w; const void* scales; int scales_fp32;
     float* out; int M, out_stride, epilogue;
     const int8_t* xq; const float* sa;                        // [B][N], [B][groups]
+    const float* xf;                                          // not NULL: FP32 activations [B][N], quantised per group by every block for itself (xq, sa unused)
     int N, B, groups, rows_per_block, xs_ld;
     int dld;                                                  // words per row of the parked dot products: B made odd, so that rows fall on different banks
 };
@@ -156,23 +157,58 @@ __global__ void __launch_bounds__(WT_W * 32) w4a8_mma_kernel(const WtParams p) {
     pdl_wait();
 
     // activations: bytes of every 8 columns reordered to evens then odds; per group 8 x the sum of its bytes and its scale
-    for (int e = threadIdx.x; e < p.B * (p.N / 8); e += WT_W * 32) {
-        const int b = e / (p.N / 8), c8 = e % (p.N / 8);
-        const uint2 v = *reinterpret_cast<const uint2*>(p.xq + (size_t)b * p.N + (size_t)c8 * 8);
-        const uint2 o = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
-        *reinterpret_cast<uint2*>(xs + (size_t)b * p.xs_ld + (size_t)c8 * 8) = o;
-    }
-    for (int e = threadIdx.x; e < p.B * nk; e += WT_W * 32) {
-        const int b = e / nk, k = e % nk;
-        const int4* q4 = reinterpret_cast<const int4*>(p.xq + (size_t)b * p.N + (size_t)k * 128);
-        int s = 0;
+    if (p.xf) {
+        // the reference's quantiser (src/threading.c:401-432) on the fly: a warp per (activation, group of 128 columns),
+        // scale = max|x| / 127 (1e-10 and all zeros for a dead group), round half away from zero, clamp to +-127
+        for (int e = warp; e < p.B * nk; e += WT_W) {
+            const int b = e / nk, k = e % nk;
+            const float4 v = *reinterpret_cast<const float4*>(p.xf + (size_t)b * p.N + (size_t)k * 128 + 4 * lane);
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            const bool dead = amax < 1e-10f;
+            const float scale = dead ? 1e-10f : __fdiv_rn(amax, 127.0f);
+            const float inv = dead ? 0.0f : __fdiv_rn(1.0f, scale);
+            const float f[4] = { v.x, v.y, v.z, v.w };
+            int q[4];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int4 v = q4[i];
-            s = __dp4a(v.x, 0x01010101, s); s = __dp4a(v.y, 0x01010101, s); s = __dp4a(v.z, 0x01010101, s); s = __dp4a(v.w, 0x01010101, s);
+            for (int i = 0; i < 4; i++) {
+                int qi = 0;
+                if (!dead) {
+                    qi = __float2int_rz(__fadd_rn(__fmul_rn(f[i], inv), f[i] >= 0.0f ? 0.5f : -0.5f));
+                    qi = max(-127, min(127, qi));
+                }
+                q[i] = qi;
+            }
+            // lane holds columns 4 lane .. 4 lane + 3: the even lane of a pair has c0..c3 of its 8 columns, the odd lane c4..c7
+            const uint32_t mine = (uint32_t)(q[0] & 255) | ((uint32_t)(q[1] & 255) << 8) | ((uint32_t)(q[2] & 255) << 16) | ((uint32_t)(q[3] & 255) << 24);
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            const uint32_t lo = (lane & 1) ? other : mine, hi = (lane & 1) ? mine : other;
+            if ((lane & 1) == 0)
+                *reinterpret_cast<uint2*>(xs + (size_t)b * p.xs_ld + (size_t)k * 128 + 4 * lane) =
+                    make_uint2(__byte_perm(lo, hi, 0x6420), __byte_perm(lo, hi, 0x7531));
+            int ssum = q[0] + q[1] + q[2] + q[3];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+            if (lane == 0) { qsum[e] = 8 * ssum; s_sa[e] = scale; }
         }
-        qsum[e] = 8 * s;
-        s_sa[e] = p.sa[e];
+    } else {
+        for (int e = threadIdx.x; e < p.B * (p.N / 8); e += WT_W * 32) {
+            const int b = e / (p.N / 8), c8 = e % (p.N / 8);
+            const uint2 v = *reinterpret_cast<const uint2*>(p.xq + (size_t)b * p.N + (size_t)c8 * 8);
+            const uint2 o = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+            *reinterpret_cast<uint2*>(xs + (size_t)b * p.xs_ld + (size_t)c8 * 8) = o;
+        }
+        for (int e = threadIdx.x; e < p.B * nk; e += WT_W * 32) {
+            const int b = e / nk, k = e % nk;
+            const int4* q4 = reinterpret_cast<const int4*>(p.xq + (size_t)b * p.N + (size_t)k * 128);
+            int s = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int4 v = q4[i];
+                s = __dp4a(v.x, 0x01010101, s); s = __dp4a(v.y, 0x01010101, s); s = __dp4a(v.z, 0x01010101, s); s = __dp4a(v.w, 0x01010101, s);
+            }
+            qsum[e] = 8 * s;
+            s_sa[e] = p.sa[e];
+        }
     }
     __syncthreads();
     const int col = g < p.B ? g : 0;                          // spare MMA columns reread activation 0
@@ -265,13 +301,38 @@ extern "C" int ibcu_quantize_input_int8_g128(ibcu_ctx* ctx, const float* x, int8
     return ibcu_launch(ctx, quantize_g128_kernel, dim3((total + 7) / 8), dim3(256), 0, 1, true, x, q, sa, N, groups, total);
 }
 
+static int w4a8_call(ibcu_ctx* ctx, const ibcu_linear_t* t, const int8_t* xq, const float* sa, const float* xf, int N, int B);
+
 extern "C" int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* t, const int8_t* xq, const float* sa, int N, int B) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, t && t->w && t->scales && t->out && xq && sa, "ibcu_linear_w4a8: null pointer");
+    return w4a8_call(ctx, t, xq, sa, nullptr, N, B);
+}
+
+// FP32 activations in: quantiser and matvec in one launch when the tensor-core kernel takes the shape, else the quantiser
+// kernel into the context's activation buffer and then the matvec.
+extern "C" int ibcu_linear_w4a8_fp32(ibcu_ctx* ctx, const ibcu_linear_t* t, const float* x, int N, int B) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, t && t->w && t->scales && t->out && x, "ibcu_linear_w4a8_fp32: null pointer");
+    // every block of the matvec would quantise all activations for itself: worth it only while that is a few groups
+    // (one 4096-column activation); otherwise the quantiser runs once, as a launch of its own
+    if (N % 128 == 0 && ((uintptr_t)x & 15) == 0 && (long)B * (N / 128) <= 32) return w4a8_call(ctx, t, nullptr, nullptr, x, N, B);
+    const int groups = (N + 127) / 128;
+    const size_t qbytes = ((size_t)B * N + 255) & ~(size_t)255;
+    int rc = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, qbytes + (size_t)B * groups * sizeof(float));
+    if (rc) return rc;
+    int8_t* q = (int8_t*)ctx->xpack;
+    float* sa = (float*)((char*)ctx->xpack + qbytes);
+    rc = ibcu_quantize_input_int8_g128(ctx, x, q, sa, N, B);
+    if (rc) return rc;
+    return w4a8_call(ctx, t, q, sa, nullptr, N, B);
+}
+
+static int w4a8_call(ibcu_ctx* ctx, const ibcu_linear_t* t, const int8_t* xq, const float* sa, const float* xf, int N, int B) {
     IBCU_REQUIRE(ctx, N > 0 && (N & 1) == 0 && B >= 1 && B <= 32 && t->M >= 0 && t->out_stride >= t->M, "ibcu_linear_w4a8: bad shape");
     if (t->M == 0) return IBCU_OK;
     // tensor-core path: whole groups of 128 columns, aligned operands; up to 8 activations per launch
-    if (N % 128 == 0 && !ctx->force_generic && ((uintptr_t)t->w & 15) == 0 && ((uintptr_t)xq & 7) == 0) {
+    if (N % 128 == 0 && !ctx->force_generic && ((uintptr_t)t->w & 15) == 0 && (xf || ((uintptr_t)xq & 7) == 0)) {
         const int groups = N / 128;
         for (int b0 = 0; b0 < B; b0 += 8) {
             const int Bc = B - b0 < 8 ? B - b0 : 8;
@@ -279,7 +340,8 @@ extern "C" int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* t, const int
             memset(&p, 0, sizeof p);
             p.w = (const uint8_t*)t->w; p.scales = t->scales; p.scales_fp32 = t->scales_fp32;
             p.out = t->out + (size_t)b0 * t->out_stride; p.M = t->M; p.out_stride = t->out_stride; p.epilogue = t->epilogue;
-            p.xq = xq + (size_t)b0 * N; p.sa = sa + (size_t)b0 * groups; p.N = N; p.B = Bc; p.groups = groups;
+            p.xq = xq ? xq + (size_t)b0 * N : nullptr; p.sa = sa ? sa + (size_t)b0 * groups : nullptr; p.xf = xf ? xf + (size_t)b0 * N : nullptr;
+            p.N = N; p.B = Bc; p.groups = groups;
             p.xs_ld = N + 16;
             p.dld = Bc | 1;
             // rows per block: one wave of two blocks per SM when shared memory allows; 32-row tiles once a block's run is longer than 16
@@ -306,6 +368,17 @@ extern "C" int ibcu_linear_w4a8(ibcu_ctx* ctx, const ibcu_linear_t* t, const int
             if (rc) return rc;
             if (b0 + Bc >= B) return IBCU_OK;
         }
+    }
+    if (!xq) {                                                // FP32 activations and a shape the kernel above did not take: quantise first
+        const int groups = (N + 127) / 128;
+        const size_t qbytes = ((size_t)B * N + 255) & ~(size_t)255;
+        int rc = ibcu_reserve(ctx, &ctx->xpack, &ctx->xpack_bytes, qbytes + (size_t)B * groups * sizeof(float));
+        if (rc) return rc;
+        int8_t* q = (int8_t*)ctx->xpack;
+        float* sq = (float*)((char*)ctx->xpack + qbytes);
+        rc = ibcu_quantize_input_int8_g128(ctx, xf, q, sq, N, B);
+        if (rc) return rc;
+        xq = q; sa = sq;
     }
     return ibcu_launch(ctx, w4a8_kernel, dim3((t->M + 7) / 8), dim3(256), 0, 1, true, (const uint8_t*)t->w, t->scales, t->scales_fp32,
                        t->out, t->M, t->out_stride, t->epilogue, xq, sa, N, B);

@@ -231,6 +231,10 @@ def test_w4a8_route_bit_exact(backend, cpu_libs, N, B, M):
     t = LinearT(be.upload(w).ptr, be.upload(s16).ptr, do.ptr, M, M, 0, 0)
     be._check(be.lib.ibcu_linear_w4a8(be.ctx, C.byref(t), dq.ptr, dsa.ptr, N, B)); be.sync()
     assert np.array_equal(be.download(do, np.float32, B * M).reshape(B, M), want)
+    do3 = be.alloc(B * M * 4)                               # quantiser and matvec in one call from the FP32 activations
+    t3 = LinearT(t.w, t.scales, do3.ptr, M, M, 0, 0)
+    be._check(be.lib.ibcu_linear_w4a8_fp32(be.ctx, C.byref(t3), dx.ptr, N, B)); be.sync()
+    assert np.array_equal(be.download(do3, np.float32, B * M).reshape(B, M), want)
     be.lib.ibcu_linear_force_generic(be.ctx, 1)             # the row-per-warp kernel on the same inputs
     try:
         do2 = be.alloc(B * M * 4)
