@@ -195,6 +195,10 @@ int    ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out);
  * row sums), so the result is the same bits from run to run. An activation that holds NaN or Inf gives NaN
  * in every output of that call. */
 int    ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
+/* The same with rows of out out_stride floats apart (out[b*out_stride + r]): a rank that holds a slice of the tensor's rows
+ * writes it in place into the full-width result, which ibcu_allgather_rows then completes (the reference's threaded form
+ * splits rows over workers the same way, src/pq_decode.c:1807-1830). */
+int    ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int out_stride, int B);
 /* Same result as ibcu_pq_matmul_fp32 for callers that must not allocate device memory: serving
  * loops that cannot take cudaMalloc's device-wide synchronisation, plugins living inside a fixed
  * memory budget, processes whose allocator belongs to another runtime. This entry point has no

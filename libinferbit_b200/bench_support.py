@@ -337,6 +337,77 @@ def _pq(lib, ctx, M, N, G, K, B):
             "shape": {"M": M, "N": N, "G": G, "K": K, "B": B}}
 
 
+def _pq_sharded(lib, ctx, rank, world, max_over_ranks, barrier, M, N, G, K, B):
+    """The PQ matvec with the rows of every tensor split over the ranks (the reference's threaded form splits rows over
+    workers the same way): a rank computes its rows in place into the full-width result, a gather completes it. The
+    codes are a function of the seed and the global row, so the sharded tensors are the single-GPU ones."""
+    dev = Dev(lib, ctx)
+    rng = np.random.default_rng(3)
+    half, Cn = G // 2, N // G
+    R = 24
+    cbh = [(rng.standard_normal((K, half)) * 0.02).astype(np.float16) for _ in range(2)]
+    cb = [dev.upload(c) for c in cbh]
+    xh = rng.standard_normal((B, N)).astype(np.float32)
+    x = dev.upload(xh)
+    r0, rn = shard(lib, M, world, rank)
+    rs = dev.upload(np.ones(rn, np.float16))
+    outs = [dev.alloc_gathered(B * M * 4) for _ in range(2)]      # two result buffers in turn (a buffer is not gathered twice in a row)
+    ts = []
+    def make(dv, rows, row0, r):
+        t = PqT()
+        t.M, t.N, t.G, t.K = rows, N, G, K
+        t.codebook_l, t.codebook_r, t.cb_chunk_stride = cb[0] if dv is dev else dv.upload(cbh[0]), cb[1] if dv is dev else dv.upload(cbh[1]), 0
+        t.row_scale = rs if dv is dev else dv.upload(np.ones(rows, np.float16))
+        il = dv.alloc(rows * Cn); ir = dv.alloc(rows * Cn)
+        check(dv.lib, dv.ctx, dv.lib.ibcu_fill_hash_bytes_at(dv.ctx, il, rows * Cn, 100 + 2 * r, row0 * Cn))
+        check(dv.lib, dv.ctx, dv.lib.ibcu_fill_hash_bytes_at(dv.ctx, ir, rows * Cn, 101 + 2 * r, row0 * Cn))
+        t.idx_l, t.idx_r = il, ir
+        it = dv.alloc(dv.lib.ibcu_pq_idx_t_bytes(rows, N, G))
+        check(dv.lib, dv.ctx, dv.lib.ibcu_pq_prepare(dv.ctx, C.byref(t), it))
+        return t
+    for r in range(R):
+        ts.append(make(dev, rn, r0, r))
+    k = [0]
+    def one():
+        o = outs[k[0] & 1]
+        check(lib, ctx, lib.ibcu_pq_matmul_fp32_strided(ctx, C.byref(ts[k[0] % R]), x, o + 4 * r0, M, B))
+        bufs = (C.c_void_p * 1)(o); Ms = (C.c_int * 1)(M)
+        check(lib, ctx, lib.ibcu_allgather_rows_n(ctx, bufs, Ms, Ms, 1, B, 32))
+        k[0] += 1
+    for _ in range(200):
+        one()
+    barrier()
+    reps = 240
+    ms = max_over_ranks(dev.timed(one, reps=reps))
+    algo = 2 * M * Cn + 2 * K * half * 2 + 2 * M + 4 * B * N + 4 * B * M
+    out = {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm", "rows_per_rank": rn,
+           "shape": {"M": M, "N": N, "G": G, "K": K, "B": B}}
+    # tensor 0 once more, against the unsharded tensor on one GPU (rank 0, own context)
+    k[0] = 0
+    one()
+    got = np.empty((B, M), np.float32)
+    check(lib, ctx, lib.ibcu_memcpy_d2h(ctx, got.ctypes.data, outs[0], got.nbytes))
+    check(lib, ctx, lib.ibcu_sync(ctx))
+    barrier()
+    if rank == 0:
+        ctx1 = C.c_void_p()
+        assert lib.ibcu_ctx_create(int(os.environ.get("LOCAL_RANK", "0")), C.byref(ctx1)) == 0
+        d1 = Dev(lib, ctx1)
+        t1 = make(d1, M, 0, 0)
+        x1 = d1.upload(xh); o1 = d1.alloc(B * M * 4)
+        check(lib, ctx1, lib.ibcu_pq_matmul_fp32(ctx1, C.byref(t1), x1, o1, B))
+        ref = np.empty((B, M), np.float32)
+        check(lib, ctx1, lib.ibcu_memcpy_d2h(ctx1, ref.ctypes.data, o1, ref.nbytes))
+        check(lib, ctx1, lib.ibcu_sync(ctx1))
+        d1.free_all(); lib.ibcu_ctx_destroy(ctx1)
+        diff = np.abs(got.astype(np.float64) - ref)
+        out["matches_single_gpu"] = {"max_abs_diff": float(diff.max()), "bit_equal": bool(np.array_equal(got, ref)),
+                                     "within_tolerance": bool(np.all(diff <= 1e-4 + 1e-3 * np.abs(ref)))}
+    barrier()
+    dev.free_all()
+    return out
+
+
 def _kmeans_shard(r, world, N_total, D, K, C0):
     n0 = N_total * r // world; n1 = N_total * (r + 1) // world
     X = (np.random.default_rng(5000 + r).standard_normal((n1 - n0, D)) * 0.02).astype(np.float32)
@@ -493,6 +564,8 @@ def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier, pe
         out["int8_head_32000x4096_b1"] = _linear_ring(lib, ctx, 8, 32000, 4096, 1)
         out["pq_down_4096x14336_b1"] = _pq(lib, ctx, 4096, 14336, 16, 256, 1)
         out["pq_down_4096x14336_b8"] = _pq(lib, ctx, 4096, 14336, 16, 256, 8)
+    if world > 1:
+        out["pq_down_4096x14336_b1_row_sharded"] = _pq_sharded(lib, ctx, rank, world, max_over_ranks, barrier, 4096, 14336, 16, 256, 1)
     out["kmeans_4Mx8_k256"] = _kmeans(lib, ctx, rank, world, max_over_ranks, barrier)
     out["decode_7b_b1"] = _decode(lib, host, ctx, 1, rank, world, max_over_ranks, barrier)
     out["decode_7b_b8"] = _decode(lib, host, ctx, 8, rank, world, max_over_ranks, barrier)

@@ -34,7 +34,8 @@ struct PqParams {
     const uint8_t* idx_t;
     const __half* row_scale;
     const float* x;                            // [B][N]
-    float* out;                                // [B][M]
+    float* out;                                // [B][out_stride], the first M of every row written
+    int out_stride;
     unsigned long long* acc;                   // [B][M_pad] fixed-point sums, zero between calls
     unsigned int* arrive;                      // [passes][row blocks] arrival counters, zero between calls
     const unsigned* amax_bits;                 // [B] bit patterns of max|x[b]| when pq_amax_kernel ran ahead, else NULL
@@ -443,7 +444,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
             const float sc = e0 == 0 ? rsc[u] : __half2float(p.row_scale[r]);
             float y = (float)((double)sum[u] * q) * sc;
             if (anybad) y = __int_as_float(0x7fc00000);                                             // an activation held NaN or Inf
-            p.out[(size_t)(b0 + t) * p.M + r] = y;
+            p.out[(size_t)(b0 + t) * p.out_stride + r] = y;
         }
     }
     // padded rows of the last group also received sums
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
 // Outlier sidecar (src/pq_decode.c:1394-1409): out[r] += sum over j of (sidecar[r][j] * scale[j]) * x[col[j]], added to the finished
 // rows. grid (blocks of 8 rows, activations), a warp per row, lanes over the outlier columns.
 __global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restrict__ side, const int32_t* __restrict__ cols, const __half* __restrict__ scale,
-                                                         int no, const float* __restrict__ x, int N, float* __restrict__ out, int M) {
+                                                         int no, const float* __restrict__ x, int N, float* __restrict__ out, int M, int out_stride) {
     extern __shared__ float xo[];                            // x[col[j]] of this activation
     pdl_launch_dependents();
     pdl_wait();
@@ -472,7 +473,7 @@ __global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restric
         acc = fmaf(w, xo[j], acc);
     }
     acc = warp_sum(acc);
-    if (lane == 0) out[(size_t)b * M + r] += acc;
+    if (lane == 0) out[(size_t)b * out_stride + r] += acc;
 }
 
 struct PqPlan { int C, nslab1, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
@@ -505,13 +506,13 @@ PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     return pl;
 }
 
-int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B, const PqPlan& pl,
+int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int out_stride, int B, const PqPlan& pl,
               unsigned long long* acc, unsigned int* arrive) {
     PqParams p;
     p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = pl.C; p.B = B; p.nslab = pl.nslab;
     p.rows_per_block = pl.rows_per_block;
     p.cb_l = (const __half*)t->codebook_l; p.cb_r = (const __half*)t->codebook_r; p.cb_stride = t->cb_chunk_stride;
-    p.idx_t = t->idx_t; p.row_scale = (const __half*)t->row_scale; p.x = x; p.out = out; p.acc = acc; p.arrive = arrive;
+    p.idx_t = t->idx_t; p.row_scale = (const __half*)t->row_scale; p.x = x; p.out = out; p.out_stride = out_stride; p.acc = acc; p.arrive = arrive;
     p.amax_bits = nullptr;
     p.nslab1 = pl.nslab1; p.K2 = t->K_l2; p.cb2_l = (const __half*)t->codebook2_l; p.cb2_r = (const __half*)t->codebook2_r;
     p.inner = t->n_outlier > 0 ? t->inner_cols : nullptr; p.n_inner = t->N - t->n_outlier;
@@ -544,7 +545,7 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
     }
     if (t->n_outlier > 0)                                    // the sidecar's share is added to the finished rows (src/pq_decode.c:1676)
         return ibcu_launch(ctx, pq_outlier_kernel, dim3((t->M + 7) / 8, B), dim3(256), (size_t)t->n_outlier * sizeof(float), 1, true,
-                           t->outlier_sidecar, t->outlier_cols, (const __half*)t->outlier_scale, t->n_outlier, x, t->N, out, t->M);
+                           t->outlier_sidecar, t->outlier_cols, (const __half*)t->outlier_scale, t->n_outlier, x, t->N, out, t->M, out_stride);
     return IBCU_OK;
 }
 
@@ -646,9 +647,14 @@ extern "C" int ibcu_pq_prepare(ibcu_ctx* ctx, ibcu_pq_t* t, uint8_t* idx_t_out) 
 }
 
 extern "C" int ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B) {
+    return ibcu_pq_matmul_fp32_strided(ctx, t, x, out, t ? t->M : 0, B);
+}
+
+extern "C" int ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int out_stride, int B) {
     IBCU_CHECK_CTX(ctx);
     int rc = pq_check(ctx, t, x, out, B, "ibcu_pq_matmul_fp32");
     if (rc) return rc;
+    IBCU_REQUIRE(ctx, out_stride >= t->M, "ibcu_pq_matmul_fp32_strided: out_stride=%d below M=%d", out_stride, t->M);
     const PqPlan pl = pq_plan(ctx, t, B);
     const size_t need = pq_scratch_bytes(pl);
     if (ctx->pq_acc_bytes < need) {
@@ -658,7 +664,7 @@ extern "C" int ibcu_pq_matmul_fp32(ibcu_ctx* ctx, const ibcu_pq_t* t, const floa
         if (rc) return rc;
         IBCU_CUDA(ctx, cudaMemsetAsync(ctx->pq_acc, 0, ctx->pq_acc_bytes, ctx->stream));
     }
-    return pq_launch(ctx, t, x, out, B, pl, (unsigned long long*)((char*)ctx->pq_acc + PQ_COUNTER_BYTES), (unsigned int*)ctx->pq_acc);
+    return pq_launch(ctx, t, x, out, out_stride, B, pl, (unsigned long long*)((char*)ctx->pq_acc + PQ_COUNTER_BYTES), (unsigned int*)ctx->pq_acc);
 }
 
 // ── PQ matvec without any allocation ────────────────────────────────────────────────────
@@ -709,5 +715,5 @@ extern "C" int ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, co
     // array is shared by every caller on the device and one that was cut short may not have: clear the part
     // this call uses (an asynchronous fill on the stream, no allocation).
     IBCU_CUDA(ctx, cudaMemsetAsync(base, 0, need, ctx->stream));
-    return pq_launch(ctx, t, x, out, B, pl, (unsigned long long*)((char*)base + PQ_COUNTER_BYTES), (unsigned int*)base);
+    return pq_launch(ctx, t, x, out, t->M, B, pl, (unsigned long long*)((char*)base + PQ_COUNTER_BYTES), (unsigned int*)base);
 }
