@@ -76,6 +76,27 @@ def test_pq_extras_through_the_host_layer(cpu_libs):
         host.ib_b200_shutdown()
 
 
+def test_row_slices_written_in_place(backend, cpu_libs):
+    """Two tensors that hold the upper and the lower rows of one tensor write their rows straight into the full-width
+    result (ibcu_pq_matmul_fp32_strided): the same bits as the whole tensor in one call."""
+    rng = np.random.default_rng(17)
+    M, N, G, K, B = 200, 512, 16, 256, 3
+    cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, B)
+    whole = backend.pq_matmul(backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs), x)
+    cut = 96
+    top = backend.make_pq(cut, N, G, K, cb_l, cb_r, il[:cut].copy(), ir[:cut].copy(), rs[:cut].copy())
+    bot = backend.make_pq(M - cut, N, G, K, cb_l, cb_r, il[cut:].copy(), ir[cut:].copy(), rs[cut:].copy())
+    dx = backend.upload(x)
+    do = backend.upload(np.full((B, M + 8), -3.0, np.float32))
+    backend._check(backend.lib.ibcu_pq_matmul_fp32_strided(backend.ctx, C.byref(top), dx.ptr, do.ptr, M + 8, B))
+    backend._check(backend.lib.ibcu_pq_matmul_fp32_strided(backend.ctx, C.byref(bot), dx.ptr, do.ptr + 4 * cut, M + 8, B))
+    backend.sync()
+    got = backend.download(do, np.float32, B * (M + 8)).reshape(B, M + 8)
+    assert np.array_equal(got[:, :M], whole) and np.all(got[:, M:] == -3.0)
+    assert backend.lib.ibcu_pq_matmul_fp32_strided(backend.ctx, C.byref(top), dx.ptr, do.ptr, cut - 1, B) == -1      # stride below the rows
+    backend.lib.ibcu_clear_error(backend.ctx)
+
+
 def test_packed_code_plane_is_a_faithful_copy(backend):
     """ibcu_pq_prepare regroups the codes as [slab of 32 subspaces][group of 16 rows][lane][16 rows]
     (subspace 2 * chunk + side = 32 * slab + lane); padding rows and padding subspaces hold zeros, and the tail
