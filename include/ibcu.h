@@ -50,6 +50,10 @@ int  ibcu_memcpy_d2h(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);  
 int  ibcu_memcpy_d2d(ibcu_ctx* ctx, void* dst, const void* src, size_t bytes);   /* async */
 int  ibcu_memset(ibcu_ctx* ctx, void* dst, int byte, size_t bytes);              /* async */
 int  ibcu_sync(ibcu_ctx* ctx);
+/* The same wait for callers that turn a short kernel round: a one-thread kernel writes a sequence number into pinned host
+ * memory when the stream's work is done and the host polls that word (bounded; the driver's wait takes over after about two
+ * seconds or when the launch fails). Returns what ibcu_sync would. */
+int  ibcu_sync_spin(ibcu_ctx* ctx);
 /* *dst = value on the context's stream (a one-thread kernel: the value travels as a launch argument, so
  * the host may change its own copy at once). */
 int  ibcu_store_i32(ibcu_ctx* ctx, int32_t* dst, int32_t value);

@@ -54,6 +54,7 @@ IBCU_SYMBOLS = {
     "ibcu_memcpy_d2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "ibcu_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
     "ibcu_sync": (C.c_int, [C.c_void_p]),
+    "ibcu_sync_spin": (C.c_int, [C.c_void_p]),
     "ibcu_store_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "ibcu_fill_hash_bytes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64]),
     "ibcu_fill_hash_bytes_at": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint64, C.c_size_t]),

@@ -43,6 +43,7 @@ struct ibcu_ctx {
     int    win_open;                                // peers mapped so far
     int    win_enabled;
     int*   win_err;                                 // pinned, mapped: a push kernel that gave up waiting writes its epoch here
+    int*   spin_flag; int spin_seq;                 // pinned, mapped: the word ibcu_sync_spin's kernel writes and the host polls
     int*   kern_err;                                // pinned, mapped, made with the context: a kernel whose bounded wait ran out writes a code here
     const void* win_last[4];                        // buffers of the previous push (a buffer is not pushed twice in a row)
     // gathers announced ahead of the launches that produce their rows (ibcu_allgather_rows_prepare): the buffers, their

@@ -83,7 +83,7 @@ int ib_b200_register(const void* host_base, size_t bytes) {
     int rc = ib_b200_check(ibcu_malloc(g_ib.ctx, bytes, &dev), "ib_b200_register");
     if (rc) return rc;
     rc = ibcu_memcpy_h2d(g_ib.ctx, dev, host_base, bytes);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "ib_b200_register copy")) { ibcu_free(g_ib.ctx, dev); return rc; }
     ib_b200_range* r = &g_ib.ranges[g_ib.n_ranges++];
     r->host = (const char*)host_base; r->bytes = bytes; r->dev = (char*)dev;
@@ -206,7 +206,7 @@ static void linear_fp32(const char* who, float* out, const void* weights, const 
     ibcu_linear_t t = { dw, ds, (float*)(direct ? ho : dout), M, M_stride, 1, IBCU_EPI_STORE };
     int rc = ibcu_linear(g_ib.ctx, &t, 1, (const float*)dx, N, B, bits);
     if (!rc && !direct) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, obytes);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, who)) return;
     g_ib.d2h_bytes += (size_t)B * M * sizeof(float);
     for (int b = 0; b < B; b++) memcpy(out + (size_t)b * M_stride, (const float*)ho + (size_t)b * M_stride, (size_t)M * sizeof(float));
@@ -241,7 +241,7 @@ static void ib_b200_matmul_w4a8_batch_unlocked(float* out, const void* weights, 
     ibcu_linear_t t = { dw, ds, (float*)dout, M, M_stride, 1, IBCU_EPI_STORE };
     int rc = ibcu_linear_w4a8(g_ib.ctx, &t, (const int8_t*)dx, (const float*)da, N, B);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, obytes);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, who)) return;
     for (int b = 0; b < B; b++) memcpy(out + (size_t)b * M_stride, (const float*)ho + (size_t)b * M_stride, (size_t)M * sizeof(float));
 }
@@ -258,7 +258,7 @@ static int ib_b200_quantize_input_int8_g128_unlocked(const float* input, int8_t*
     int rc = ibcu_quantize_input_int8_g128(g_ib.ctx, (const float*)dx, (int8_t*)dq, (float*)ds, N, 1);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, hq, dq, (size_t)N);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, hs, ds, (size_t)groups * sizeof(float));
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "quantize_input_int8_g128")) return 0;
     memcpy(out_q, hq, (size_t)N);
     memcpy(out_scales, hs, (size_t)groups * sizeof(float));
@@ -275,7 +275,7 @@ static void ib_b200_rmsnorm_unlocked(float* out, const float* input, const float
     if (!dx || !dw || ib_b200_stage(ST_OUT, (size_t)N * sizeof(float), &ho, &dout)) return;
     int rc = ibcu_rmsnorm_f32w(g_ib.ctx, (float*)dout, (const float*)dx, (const float*)dw, eps, N, 1);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, (size_t)N * sizeof(float));
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "rmsnorm")) return;
     memcpy(out, ho, (size_t)N * sizeof(float));
 }
@@ -292,7 +292,7 @@ static void ib_b200_rope_unlocked(float* q, float* k, int head_dim, int pos, flo
     if (!rc) rc = ibcu_rope_kv_write(g_ib.ctx, (float*)dq, (float*)dk, NULL, NULL, NULL, 1, 1, head_dim, pos, 1, theta);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, hq, dq, hb);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, hk, dk, hb);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "rope")) return;
     memcpy(q, hq, hb); memcpy(k, hk, hb);
 }
@@ -306,7 +306,7 @@ static void ib_b200_softmax_unlocked(float* data, int N) {
     int rc = ibcu_memcpy_h2d(g_ib.ctx, d, h, nb);
     if (!rc) rc = ibcu_softmax(g_ib.ctx, (float*)d, N, 1);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, h, d, nb);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "softmax")) return;
     memcpy(data, h, nb);
 }
@@ -320,7 +320,7 @@ static void ib_b200_silu_mul_unlocked(float* out, const float* gate, const float
     if (!dg || !du || ib_b200_stage(ST_OUT, nb, &ho, &dout)) return;
     int rc = ibcu_silu_mul(g_ib.ctx, (float*)dout, (const float*)dg, (const float*)du, (size_t)N);
     if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, nb);
-    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (!rc) rc = ibcu_sync_spin(g_ib.ctx);
     if (ib_b200_check(rc, "silu_mul")) return;
     memcpy(out, ho, nb);
 }
