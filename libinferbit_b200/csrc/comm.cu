@@ -216,73 +216,80 @@ __global__ void __launch_bounds__(1024) allgather_push_kernel(const PushParams p
     __syncthreads();
 }
 
-// The receiving half of a tagged gather: polls the twins of the rows this rank does not own until they carry the tag of
-// this gather (bounded), copies the values into the plain buffers and, in the last block to finish, counts the gather.
-struct TagDesc { size_t off; int stride, M, row0, rows; };     // plain buffer at byte offset off; [row0, row0 + rows) is this rank's own slice
-struct TagParams { TagDesc d[4]; int n, B; char* base; size_t twin0; int* err; };
-
-__device__ __forceinline__ uint2 ld_volatile_u2(const void* p) {       // one 8-byte load: value and tag as they were stored together
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-
+// The receiving half of a tagged gather as a kernel of its own (for consumers that cannot receive themselves).
 __global__ void __launch_bounds__(256) tag_unpack_kernel(const TagParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    unsigned long long* header = reinterpret_cast<unsigned long long*>(p.base);
-    const unsigned long long count = header[IBCU_WIN_TAG_SLOT];
-    const unsigned tag = (unsigned)count + 1u;
-    const long step = (long)gridDim.x * blockDim.x;
-    for (int i = 0; i < p.n; i++) {
-        const TagDesc d = p.d[i];
-        const int remote = d.M - d.rows;
-        const long total = (long)p.B * remote;
-        float* plain = reinterpret_cast<float*>(p.base + d.off);
-        const uint2* twin = reinterpret_cast<const uint2*>(p.base + p.twin0 + 2 * (d.off - IBCU_WIN_HEADER));
-        for (long e0 = (long)blockIdx.x * blockDim.x + threadIdx.x; e0 < total; e0 += 4 * step) {
-            size_t idx[4];
-            unsigned pending = 0;
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const long e = e0 + u * step;
-                idx[u] = 0;
-                if (e < total) {
-                    const int b = (int)(e / remote), rr = (int)(e % remote);
-                    idx[u] = (size_t)b * d.stride + (rr < d.row0 ? rr : rr + d.rows);
-                    pending |= 1u << u;
-                }
-            }
-            long it = 0;
-            while (pending) {
-                uint2 w[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) if (pending >> u & 1u) w[u] = ld_volatile_u2(twin + idx[u]);
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if ((pending >> u & 1u) && w[u].y == tag) { plain[idx[u]] = __uint_as_float(w[u].x); pending &= ~(1u << u); }
-                if (pending && ++it > IBCU_WIN_SPIN_LIMIT / 4) { *p.err = (int)tag; break; }       // give up: the host reports it at the next sync
-            }
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned* done = reinterpret_cast<unsigned*>(header + IBCU_WIN_TAG_DONE_SLOT);
-        if (atomicAdd(done, 1u) == gridDim.x - 1) { *done = 0u; header[IBCU_WIN_TAG_SLOT] = count + 1; }
-    }
+    tag_receive(p, blockIdx.x, gridDim.x);
 }
 
-void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw) {
-    gw->flags = nullptr; gw->world = ctx->world; gw->rank = ctx->rank; gw->err = ctx->win_err;
+static int launch_tag_unpack(ibcu_ctx* ctx, const TagParams& tp) {
+    long elems = 0;
+    for (int i = 0; i < tp.n; i++) elems += (long)tp.B * (tp.d[i].M - tp.d[i].rows);
+    long blocks = (elems + 2047) / 2048;                      // 8 elements per thread
+    if (blocks < 1) blocks = 1;
+    if (blocks > 64) blocks = 64;
+    TagParams q = tp;
+    q.all_mask = 0u;
+    return ibcu_launch(ctx, tag_unpack_kernel, dim3((unsigned)blocks), dim3(256), 0, 1, true, q);
+}
+
+static void take_flags(ibcu_ctx* ctx, GatherWait* gw) {
+    memset(gw, 0, sizeof *gw);
+    gw->world = ctx->world; gw->rank = ctx->rank; gw->err = ctx->win_err;
     if (!ctx->gather_pending) return;
     gw->flags = reinterpret_cast<const unsigned long long*>(ctx->win_base);
     ctx->gather_pending = 0;
 }
 
+void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw) {
+    if (ctx->tag_pending) {                                   // the caller's kernel cannot receive: a kernel of its own does
+        ctx->tag_pending = 0;
+        launch_tag_unpack(ctx, ctx->tag_p);                  // a failed launch is recorded in the context; the caller's own launch reports it
+    }
+    take_flags(ctx, gw);
+}
+
+void ibcu_gather_wait_mark(ibcu_ctx* ctx, GatherWait* gw, const void* x, size_t x_bytes);
+void ibcu_take_gather_wait_x(ibcu_ctx* ctx, GatherWait* gw, const void* x, size_t x_bytes) {
+    take_flags(ctx, gw);
+    if (!ctx->tag_pending) return;
+    ctx->tag_pending = 0;
+    gw->tag = ctx->tag_p;
+    gw->tag.all_mask = 0u;
+    ibcu_gather_wait_mark(ctx, gw, x, x_bytes);              // buffers the kernel reads itself: received in full by every block
+}
+
+// After the ranges the kernel reads have been marked: every block repeating the whole receive of those buffers pays only
+// while that is little work; beyond, the receiving kernel of its own is cheaper and the caller's kernel receives nothing.
+void ibcu_gather_wait_settle(ibcu_ctx* ctx, GatherWait* gw) {
+    long repeated = 0;
+    for (int i = 0; i < gw->tag.n; i++)
+        if ((gw->tag.all_mask >> i) & 1u) repeated += (long)gw->tag.B * (gw->tag.d[i].M - gw->tag.d[i].rows);
+    if (repeated > 1024) {
+        TagParams tp = gw->tag;
+        gw->tag.n = 0;
+        launch_tag_unpack(ctx, tp);
+    }
+}
+
+void ibcu_gather_wait_mark(ibcu_ctx* ctx, GatherWait* gw, const void* x, size_t x_bytes) {
+    for (int i = 0; i < gw->tag.n; i++) {
+        const char* lo = ctx->win_base + gw->tag.d[i].off;
+        const char* hi = lo + ((size_t)(gw->tag.B - 1) * gw->tag.d[i].stride + gw->tag.d[i].M) * sizeof(float);
+        if ((const char*)x < hi && (const char*)x + x_bytes > lo) gw->tag.all_mask |= 1u << i;
+    }
+}
+
 int ibcu_flush_gather_wait(ibcu_ctx* ctx) {
+    if (ctx->tag_pending) {
+        ctx->tag_pending = 0;
+        const int rc = launch_tag_unpack(ctx, ctx->tag_p);
+        if (rc) return rc;
+    }
     if (!ctx->gather_pending) return IBCU_OK;
     GatherWait gw;
-    ibcu_take_gather_wait(ctx, &gw);                          // clears the pending state, so the launch below does not come back here
+    take_flags(ctx, &gw);                                     // clears the pending state, so the launch below does not come back here
     return ibcu_launch(ctx, gather_wait_kernel, dim3(1), dim3(32), 0, 1, true, gw);
 }
 
@@ -428,17 +435,15 @@ extern "C" int ibcu_allgather_rows_n(ibcu_ctx* ctx, float* const* bufs, const in
             TagParams tp;
             memset(&tp, 0, sizeof tp);
             tp.n = n; tp.B = B; tp.base = ctx->win_base; tp.twin0 = ctx->win_bytes; tp.err = ctx->win_err;
-            long elems = 0;
             for (int i = 0; i < n; i++) {
                 int r0, rn;
                 ibcu_shard_rows(M[i], ctx->world, ctx->rank, align, &r0, &rn);
                 tp.d[i] = { (size_t)((const char*)bufs[i] - ctx->win_base), stride[i], M[i], r0, rn };
-                elems += (long)B * (M[i] - rn);
             }
-            long blocks = (elems + 2047) / 2048;              // 8 elements per thread
-            if (blocks < 1) blocks = 1;
-            if (blocks > 64) blocks = 64;
-            return ibcu_launch(ctx, tag_unpack_kernel, dim3((unsigned)blocks), dim3(256), 0, 1, true, tp);
+            { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }      // an earlier gather still to be received comes first
+            ctx->tag_p = tp;
+            ctx->tag_pending = 1;                             // received by the next linear call in its first kernel, else by a kernel of its own
+            return IBCU_OK;
         }
     }
     { int rc = ibcu_flush_gather_wait(ctx); if (rc) return rc; }

@@ -15,6 +15,12 @@
 
 struct ncclComm;
 
+// A tagged gather still to be received (n == 0: none): the plain buffers, this rank's own slice of each, and which of
+// them the receiving kernel reads itself (all_mask): those are received in full by every block, the others are dealt
+// out among the blocks.
+struct TagDesc { size_t off; int stride, M, row0, rows; };     // plain buffer at byte offset off; [row0, row0 + rows) is this rank's own slice
+struct TagParams { TagDesc d[4]; int n, B; char* base; size_t twin0; int* err; unsigned all_mask; };
+
 struct ibcu_ctx {
     int device;
     int sm_count;
@@ -50,6 +56,8 @@ struct ibcu_ctx {
     // row strides, and which of them a linear launch has meanwhile pushed from its epilogue
     const char* arm_buf[4]; int arm_stride[4]; int arm_done[4]; int arm_n;
     int    gather_pending;                          // a linear launch has pushed its rows to the peers: the next kernel (or copy to the host) waits for theirs
+    int    tag_pending; TagParams tag_p;            // a tagged gather whose receiving half has not been issued yet: the next linear call does it in its
+                                                    // first kernel, anything else is preceded by the receiving kernel
     // exchange area inside the window (all-reduce of small tables, k-means): two buffers of world slots each, used in turn
     size_t exch_off, exch_slot; unsigned exch_turn;
 };
@@ -64,8 +72,8 @@ constexpr int IBCU_WIN_TAG_SLOT = IBCU_MAX_RANKS + 3;        // number of tagged
 constexpr int IBCU_WIN_TAG_DONE_SLOT = IBCU_MAX_RANKS + 4;   // blocks of the receiving kernel that are through
 constexpr long IBCU_WIN_SPIN_LIMIT = 4L * 1000 * 1000;       // about a second of polling
 
-// What a kernel needs to wait for the peers' rows of the gather that precedes it (flags == NULL: nothing to wait for).
-struct GatherWait { const unsigned long long* flags; int world, rank; int* err; };
+// What a kernel needs to wait for the peers' rows of the gather that precedes it (flags == NULL and tag.n == 0: nothing).
+struct GatherWait { const unsigned long long* flags; int world, rank; int* err; TagParams tag; };
 // What a linear launch needs to store its rows into the peers' copies and to publish that it has (world == 0: no push).
 struct GatherPush { char* peer[IBCU_MAX_RANKS]; unsigned long long* header; int world, rank, pushers; int* err; size_t twin0; };
 
@@ -78,7 +86,14 @@ int ibcu_exchange_begin(ibcu_ctx* ctx, size_t slot_bytes, ExchSlots* ex);
 int ibcu_allreduce_kmeans(ibcu_ctx* ctx, float* sums, size_t n_sums, int32_t* counts, size_t n_counts, double* inertia);
 
 // Fills *gw when a push is pending and clears the pending state: the caller's kernel does the waiting in its prologue.
+// A pending tagged gather is received by a kernel of its own first.
 void ibcu_take_gather_wait(ibcu_ctx* ctx, GatherWait* gw);
+// The same for a kernel that can receive a tagged gather itself (it calls gather_wait after its dependency wait and reads,
+// of the gathered buffers, at most [x, x + x_bytes)): a pending tagged gather goes into *gw instead of a kernel of its own.
+void ibcu_take_gather_wait_x(ibcu_ctx* ctx, GatherWait* gw, const void* x, size_t x_bytes);
+// one more range the kernel reads itself; then, once all ranges are marked, the decision whether the kernel receives at all
+void ibcu_gather_wait_mark(ibcu_ctx* ctx, GatherWait* gw, const void* x, size_t x_bytes);
+void ibcu_gather_wait_settle(ibcu_ctx* ctx, GatherWait* gw);
 // Launches a one-block kernel that does the waiting (for consumers that cannot: other kernels, copies to the host).
 int ibcu_flush_gather_wait(ibcu_ctx* ctx);
 
@@ -100,7 +115,7 @@ int ibcu_reserve(ibcu_ctx* ctx, void** buf, size_t* have, size_t want);
 template <typename... KArgs, typename... Args>
 static inline int ibcu_launch(ibcu_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block,
                               size_t smem, int cluster_x, bool pdl_ok, Args... args) {
-    if (ctx->gather_pending) { int rc_ = ibcu_flush_gather_wait(ctx); if (rc_) return rc_; }     // this kernel does not wait by itself
+    if (ctx->gather_pending || ctx->tag_pending) { int rc_ = ibcu_flush_gather_wait(ctx); if (rc_) return rc_; }     // this kernel does not wait by itself
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
@@ -166,17 +181,80 @@ __device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsign
 // Called by every thread of a block after pdl_wait(): the rows the peers pushed in the preceding gather are in place
 // when it returns. The epoch to wait for is this rank's own (its last push, finished before this kernel's dependency
 // wait returned). Bounded: a rank whose peers do not arrive gives up and raises the host-visible error word.
-__device__ __forceinline__ void gather_wait(const GatherWait& g) {
-    if (!g.flags) return;
-    if ((int)threadIdx.x < g.world && (int)threadIdx.x != g.rank) {          // one thread per peer
-        const unsigned long long e = g.flags[IBCU_WIN_EPOCH_SLOT];
-        long it = 0;
-        while (ld_acquire_sys_u64(g.flags + threadIdx.x) < e) {
-            if (++it > IBCU_WIN_SPIN_LIMIT) { *g.err = (int)e; break; }
-            __nanosleep(64);
+__device__ __forceinline__ uint2 ld_volatile_u2(const void* p) {       // one 8-byte load: value and tag as they were stored together
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// The receiving half of a tagged gather (see below), by all threads of all blocks of a kernel: polls the twins of the
+// rows this rank does not own until they carry the gather's tag (bounded), copies the values into the plain buffers and,
+// in the last block to finish, counts the gather. Elements of a buffer are dealt out among the blocks (blk of nblk), or
+// all taken by every block when the kernel itself reads that buffer (all_mask). Returns the tag received.
+__device__ __forceinline__ unsigned tag_receive(const TagParams& p, unsigned blk, unsigned nblk) {
+    unsigned long long* header = reinterpret_cast<unsigned long long*>(p.base);
+    const unsigned long long count = header[IBCU_WIN_TAG_SLOT];
+    const unsigned tag = (unsigned)count + 1u;
+    for (int i = 0; i < p.n; i++) {
+        const TagDesc d = p.d[i];
+        const int remote = d.M - d.rows;
+        const long total = (long)p.B * remote;
+        float* plain = reinterpret_cast<float*>(p.base + d.off);
+        const uint2* twin = reinterpret_cast<const uint2*>(p.base + p.twin0 + 2 * (d.off - IBCU_WIN_HEADER));
+        const bool all = (p.all_mask >> i) & 1u;
+        const long step = (long)(all ? 1u : nblk) * blockDim.x;
+        for (long e0 = (long)(all ? 0u : blk) * blockDim.x + threadIdx.x; e0 < total; e0 += 4 * step) {
+            size_t idx[4];
+            unsigned pending = 0;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const long e = e0 + u * step;
+                idx[u] = 0;
+                if (e < total) {
+                    const int b = (int)(e / remote), rr = (int)(e % remote);
+                    idx[u] = (size_t)b * d.stride + (rr < d.row0 ? rr : rr + d.rows);
+                    pending |= 1u << u;
+                }
+            }
+            long it = 0;
+            while (pending) {
+                uint2 w[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) if (pending >> u & 1u) w[u] = ld_volatile_u2(twin + idx[u]);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if ((pending >> u & 1u) && w[u].y == tag) { plain[idx[u]] = __uint_as_float(w[u].x); pending &= ~(1u << u); }
+                if (pending && ++it > IBCU_WIN_SPIN_LIMIT / 4) { *p.err = (int)tag; break; }       // give up: the host reports it at the next sync
+            }
         }
     }
-    __syncthreads();
+    __syncthreads();                                          // the block's own copies are in place for its own reads
+    if (threadIdx.x == 0) {
+        unsigned* done = reinterpret_cast<unsigned*>(header + IBCU_WIN_TAG_DONE_SLOT);
+        if (atomicAdd(done, 1u) == nblk - 1) { *done = 0u; header[IBCU_WIN_TAG_SLOT] = count + 1; }
+    }
+    return tag;
+}
+
+// Called by every thread of every block after pdl_wait(). Returns the tag of the tagged gather it received, else 0: a
+// kernel that goes on to push rows of its own must then use that tag + 1 (the count may or may not have moved yet).
+__device__ __forceinline__ unsigned gather_wait(const GatherWait& g) {
+    if (g.flags) {
+        if ((int)threadIdx.x < g.world && (int)threadIdx.x != g.rank) {          // one thread per peer
+            const unsigned long long e = g.flags[IBCU_WIN_EPOCH_SLOT];
+            long it = 0;
+            while (ld_acquire_sys_u64(g.flags + threadIdx.x) < e) {
+                if (++it > IBCU_WIN_SPIN_LIMIT) { *g.err = (int)e; break; }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+    }
+    if (g.tag.n) {
+        const unsigned nblk = gridDim.x * gridDim.y * gridDim.z;
+        const unsigned blk = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        return tag_receive(g.tag, blk, nblk);
+    }
+    return 0u;
 }
 
 // Tagged gather (the low-latency path of a gather whose rows a linear launch produces). The window has a second part

@@ -523,7 +523,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) pf_issue();          // weights first: they do not depend on x
     pdl_wait();
-    gather_wait(p.gw);
+    const unsigned recv_tag = gather_wait(p.gw);             // not 0: this launch received a tagged gather; its own pushes then carry the next tag
 
     // ── this slice's limbs, scale-back factors and limb sums ──
     if (p.fused_x) {
@@ -623,7 +623,7 @@ __global__ void __launch_bounds__(W * 32) linear_mma_kernel(const LinearParams p
         }
         __syncthreads();
         const int B = p.B;
-        const unsigned tag = p.gp.world ? tag_current(p.gp) : 0u;
+        const unsigned tag = p.gp.world ? (recv_tag ? recv_tag + 1u : tag_current(p.gp)) : 0u;
         // one thread per (row, activation): limb sums over the warps, bias, recombination
         for (int e = threadIdx.x; e < R * B; e += W * 32) {
             const int r = e % R, b = e / R;
@@ -1102,7 +1102,9 @@ int linear_tc(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n_tensors, const 
     for (int i = n_tensors; i <= 4; i++) p.tile_start[i] = ntiles;
     if (ntiles == 0) return IBCU_OK;
     GatherWait gw;
-    ibcu_take_gather_wait(ctx, &gw);
+    ibcu_take_gather_wait_x(ctx, &gw, x, (size_t)B * N * sizeof(float));
+    if (pro && pro->x2) ibcu_gather_wait_mark(ctx, &gw, pro->x2, (size_t)B * N * sizeof(float));
+    ibcu_gather_wait_settle(ctx, &gw);
     {
         float* outs[4];
         for (int i = 0; i < n_tensors; i++) outs[i] = tensors[i].out;
@@ -1267,7 +1269,9 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
     // multi-GPU: a windowed exchange may be pending (wait in the first kernel of this call), and the outputs may be this
     // rank's slices of an announced gather (every result also goes, tagged, into the peers' windows from the epilogue)
     GatherWait gw;
-    ibcu_take_gather_wait(ctx, &gw);
+    ibcu_take_gather_wait_x(ctx, &gw, x, (size_t)B * N * sizeof(float));
+    if (pro && pro->x2) ibcu_gather_wait_mark(ctx, &gw, pro->x2, (size_t)B * N * sizeof(float));
+    ibcu_gather_wait_settle(ctx, &gw);
     {
         float* outs[4];
         for (int i = 0; i < n_tensors; i++) outs[i] = tensors[i].out;
@@ -1354,7 +1358,7 @@ extern "C" int ibcu_linear_ex(ibcu_ctx* ctx, const ibcu_linear_t* tensors, int n
         rc = xthreads == 1024 ? ibcu_launch(ctx, xprep_kernel<1024>, xg, dim3(1024), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 0, xpack, xscale, xsum, gw)
            : xthreads == 512  ? ibcu_launch(ctx, xprep_kernel<512>, xg, dim3(512), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw)
                               : ibcu_launch(ctx, xprep_kernel<256>, xg, dim3(256), 0, 1, true, xsrc, N, cols, xs_ld, perm8, nks, 1, xpack, xscale, xsum, gw);
-        gw.flags = nullptr;                                   // the conversion kernel has waited; the main kernel follows it
+        gw.flags = nullptr; gw.tag.n = 0;                     // the conversion kernel has waited and received; the main kernel follows it
     }
     p.gw = gw;
     if (rc) return rc;
