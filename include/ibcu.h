@@ -219,6 +219,13 @@ int    ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, const floa
 int    ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
 size_t ibcu_pq_noalloc_max_floats(void);
 
+/* PQ-compressed KV cache, encode of n_vec vectors of dim values (src/pq_decode.c:5008-5066: the K or the V row of a
+ * position): scale[v] = max|vec| / 7 (at least 1e-12), and per chunk of G normalised values the nearest entry (squared
+ * distance, strict '<') of the left codebook to its first half and of the right codebook to its second half.
+ * idx[v * 2C + c] = left code of chunk c, idx[v * 2C + C + c] = right code; cb_l / cb_r: fp16 [K1 * G/2], K1 <= 256. */
+int ibcu_pqkv_encode(ibcu_ctx* ctx, const float* vec, int dim, int n_vec, int G, int K1,
+                     const uint16_t* cb_l, const uint16_t* cb_r, uint8_t* idx, float* scale);
+
 /* ── k-means ─────────────────────────────────────────────────────────────────────────── */
 /* ib_kmeans_assign (src/pq_kmeans.h:70-74, src/pq_kmeans.c:399-413): idx[i] = nearest centroid of
  * X[i*D..], direct squared distance in the reference binary's rounding order, strict '<'.

@@ -83,6 +83,7 @@ IBCU_SYMBOLS = {
     "ibcu_pq_prepared_bytes": (C.c_size_t, [C.POINTER(PqT)]),
     "ibcu_pq_prepare": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p]),
     "ibcu_pq_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
+    "ibcu_pqkv_encode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_pq_matmul_fp32_strided": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "ibcu_pq_matmul_fp32_noalloc": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pq_noalloc_max_floats": (C.c_size_t, []),

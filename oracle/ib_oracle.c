@@ -324,6 +324,36 @@ done:
     return rc;
 }
 
+/* src/pq_decode.c:5008-5066 — encode of one K or V row into the PQ KV cache: per-vector scale max|v| / 7 (floor
+ * 1e-12), normalise, nearest codeword per half chunk (distance accumulated in dimension order, strict '<').
+ * PARITY UNPINNED: the reference has this only inline in its session step (no entry point to call), and its build
+ * may or may not contract ed*ed + d; `fused` picks. */
+void ibo_pqkv_encode(const float* vec, int dim, int G, int K1, const uint16_t* cb_l, const uint16_t* cb_r,
+                     uint8_t* idx, float* scale, int fused) {
+    int half = G / 2, C = dim / G;
+    float m = 1e-12f;
+    for (int d = 0; d < dim; d++) { float a = fabsf(vec[d]); if (a > m) m = a; }
+    float s = m / 7.0f;
+    if (s < 1e-12f) s = 1e-12f;
+    float inv = 1.0f / s;
+    *scale = s;
+    for (int c = 0; c < C; c++) {
+        for (int side = 0; side < 2; side++) {
+            const uint16_t* cb = side ? cb_r : cb_l;
+            int best = 0; float best_d = 1e30f;
+            for (int k = 0; k < K1; k++) {
+                float d = 0.0f;
+                for (int j = 0; j < half; j++) {
+                    float ed = vec[c * G + side * half + j] * inv - ibo_fp16_to_fp32(cb[(size_t)k * half + j]);
+                    d = fused ? fmaf(ed, ed, d) : d + ed * ed;
+                }
+                if (d < best_d) { best_d = d; best = k; }
+            }
+            idx[side * C + c] = (uint8_t)best;
+        }
+    }
+}
+
 /* src/pq_decode.c:1103-1196 with n_levels == 1, no outliers. */
 int ibo_pq_reconstruct_fp32(int M, int N, int G, int K,
                             const uint16_t* cb_l, const uint16_t* cb_r,

@@ -58,6 +58,9 @@ int ibo_pq_matmul_fp32_ex(int M, int N, int G, int K, int K_l2,
                           const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
                           const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
                           const float* x, float* out, int fused);
+/* src/pq_decode.c:5008-5066 — PQ KV cache encode of one vector (parity unpinned: no entry point in the reference). */
+void ibo_pqkv_encode(const float* vec, int dim, int G, int K1, const uint16_t* cb_l, const uint16_t* cb_r,
+                     uint8_t* idx, float* scale, int fused);
 /* src/pq_decode.c:1103-1196 — dense W[M*N] from codes, every value rounded through fp16. */
 int ibo_pq_reconstruct_fp32(int M, int N, int G, int K,
                             const uint16_t* cb_l, const uint16_t* cb_r,

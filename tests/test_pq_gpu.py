@@ -97,6 +97,33 @@ def test_row_slices_written_in_place(backend, cpu_libs):
     backend.lib.ibcu_clear_error(backend.ctx)
 
 
+@pytest.mark.parametrize("dim,G,K1,n_vec", [(1024, 16, 256, 3), (128, 8, 16, 2), (1024, 16, 100, 1)])
+def test_pq_kv_encode(backend, cpu_libs, dim, G, K1, n_vec):
+    """PQ KV-cache encode (src/pq_decode.c:5008-5066): per-vector scale and nearest codeword per half chunk, against the CPU
+    restatement (which has no entry point of the reference to be pinned to). Codes and scales must be the same bits;
+    a zero vector and duplicated codebook entries (the first of equals wins) are among the cases."""
+    rng = np.random.default_rng(dim + K1)
+    half, Cn = G // 2, dim // G
+    cb_l = _cpu.fp16_bits(rng.standard_normal((K1, half)) * 3.0); cb_r = _cpu.fp16_bits(rng.standard_normal((K1, half)) * 3.0)
+    cb_l[K1 // 2] = cb_l[1]                                  # equal entries: the lower index must win
+    vec = (rng.standard_normal((n_vec, dim)) * 0.7).astype(np.float32)
+    if n_vec > 1:
+        vec[1] = 0.0
+    o = cpu_libs.oracle
+    o.ibo_pqkv_encode.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+    o.ibo_pqkv_encode.restype = None
+    want_idx = np.empty((n_vec, 2 * Cn), np.uint8); want_s = np.empty(n_vec, np.float32)
+    for v in range(n_vec):
+        o.ibo_pqkv_encode(vec[v].ctypes.data, dim, G, K1, cb_l.ctypes.data, cb_r.ctypes.data, want_idx[v].ctypes.data,
+                          want_s[v:].ctypes.data, 1)
+    be = backend
+    dv, dl, dr = be.upload(vec), be.upload(cb_l), be.upload(cb_r)
+    di, ds = be.alloc(n_vec * 2 * Cn), be.alloc(n_vec * 4)
+    be._check(be.lib.ibcu_pqkv_encode(be.ctx, dv.ptr, dim, n_vec, G, K1, dl.ptr, dr.ptr, di.ptr, ds.ptr)); be.sync()
+    assert np.array_equal(be.download(di, np.uint8, n_vec * 2 * Cn).reshape(n_vec, 2 * Cn), want_idx)
+    assert np.array_equal(be.download(ds, np.float32, n_vec), want_s)
+
+
 def test_packed_code_plane_is_a_faithful_copy(backend):
     """ibcu_pq_prepare regroups the codes as [slab of 32 subspaces][group of 16 rows][lane][16 rows]
     (subspace 2 * chunk + side = 32 * slab + lane); padding rows and padding subspaces hold zeros, and the tail
