@@ -503,6 +503,8 @@ int assign_exact_launch(ibcu_ctx* ctx, const float* X, long N, int D, const floa
 }  // namespace
 
 int ibcu_kmeans_assign_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist);   // kmeans_tc.cu
+int ibcu_kmeans_assign_accumulate_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist,
+                                     float* part_sums, int32_t* part_counts, double* part_inertia, int nblocks);
 
 extern "C" void ibcu_kmeans_set_path(ibcu_ctx* ctx, int path) { if (ctx) ctx->kmeans_path = path; }
 
@@ -583,8 +585,8 @@ extern "C" int ibcu_kmeans_lloyd_iter(ibcu_ctx* ctx, const float* X, long N, int
                                       int32_t* idx, float* dist, float* sums, int32_t* counts, double* inertia) {
     IBCU_CHECK_CTX(ctx);
     IBCU_REQUIRE(ctx, dist, "ibcu_kmeans_lloyd_iter: dist buffer required");
-    int rc = ibcu_kmeans_assign(ctx, X, N, D, C, K, idx, dist);
-    if (rc) return rc;
+    IBCU_REQUIRE(ctx, X && C && idx && sums && counts && N > 0 && D >= 1 && D <= KM_MAX_D && K >= 1 && K <= 1024, "ibcu_kmeans_lloyd_iter: bad arguments");
+    int rc = IBCU_OK;
     // One exchange per iteration. Through the peer window: the kernel that finishes this rank's tables stores them into
     // every rank's exchange area and publishes, the next kernel waits for the peers' and adds the tables in rank order.
     // Without a window: the three all-reduces as one grouped NCCL call.
@@ -593,8 +595,35 @@ extern "C" int ibcu_kmeans_lloyd_iter(ibcu_ctx* ctx, const float* X, long N, int
     const size_t slot_bytes = (size_t)K * D * sizeof(float) + (size_t)K * sizeof(int32_t) + 16;
     const int windowed = ctx->world > 1 && !ctx->capturing ? ibcu_exchange_begin(ctx, slot_bytes, &ex) : 0;
     if (!windowed) memset(&ex, 0, sizeof ex);
-    rc = kmeans_accumulate(ctx, X, N, D, K, idx, dist, sums, counts, inertia, ex);
-    if (rc) return rc;
+    // D == 8 on the tensor-memory kernel: the assignment kernel's epilogue adds the points into per-block tables as it
+    // goes, so the accumulate pass costs no second read of X and no launch; only the per-block tables are left to add up
+    bool fused = false;
+    if (D == 8 && ctx->kmeans_path == IBCU_KMEANS_AUTO && ((uintptr_t)X & 15) == 0 && K >= 64 && K <= 256 && (K & 63) == 0) {
+        const long ntile = (N + 127) / 128;
+        const int nblocks = (int)(ntile < ctx->sm_count ? ntile : ctx->sm_count);
+        const size_t KD = (size_t)K * D;
+        const size_t need = (size_t)nblocks * (KD * sizeof(float) + K * sizeof(int32_t) + sizeof(double)) + 64;
+        rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+        if (rc) return rc;
+        double* part_inertia = (double*)ctx->scratch;
+        float* part_sums = (float*)(part_inertia + ((nblocks + 1) & ~1));
+        int32_t* part_counts = (int32_t*)(part_sums + (size_t)nblocks * KD);
+        rc = ibcu_kmeans_assign_accumulate_tc(ctx, X, N, C, K, idx, dist, part_sums, part_counts, part_inertia, nblocks);
+        if (rc == IBCU_OK) {
+            fused = true;
+            const int fin_blocks = (int)((KD + 31) / 32) + (K + 31) / 32 + 1;
+            rc = ibcu_launch(ctx, accumulate_finish_kernel, dim3(fin_blocks), dim3(256), 0, 1, true,
+                             (const float*)part_sums, (const int32_t*)part_counts, (const double*)part_inertia, nblocks, (int)KD, K,
+                             sums, counts, inertia, ex);
+            if (rc) return rc;
+        } else if (rc != IBCU_ERR_STATE) return rc;
+    }
+    if (!fused) {
+        rc = ibcu_kmeans_assign(ctx, X, N, D, C, K, idx, dist);
+        if (rc) return rc;
+        rc = kmeans_accumulate(ctx, X, N, D, K, idx, dist, sums, counts, inertia, ex);
+        if (rc) return rc;
+    }
     if (windowed) {
         ctx->gather_pending = 1;
         GatherWait gw;

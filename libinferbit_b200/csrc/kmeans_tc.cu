@@ -60,6 +60,7 @@ struct TcShared {
     uint32_t tmem_base;
     int abort_flag;
     unsigned cmax2_bits;
+    double inert[TC_EPI_WARPS];
 };
 
 // Best and second-best of the maxima over groups of 8 scores, kept by four independent trackers (tracker q sees groups
@@ -89,8 +90,15 @@ __device__ __forceinline__ Top2 top2_merge(const Top2& a, const Top2& b) {
 // Dynamic shared memory: centroid operand [ch | cl | bias][2 chunks][K rows x 16 B] | constant point chunk pair
 // (1 1 1 0 / 0 0 0 0 per row) | TC_STAGES point operands (xh, xl) | TC_STAGES raw point tiles | exact centroids [K][8] |
 // the same centroids by group [K/8][8 dims][8] | TcShared
+// ACC: the epilogue warps also add every point into the table of its cluster (a table of K x 8 sums and K counts per warp
+// in shared memory, points of a warp in index order: equal clusters among its 32 points take turns), and the block leaves
+// the sum of its eight tables, its counts and its share of the inertia in part_*[blockIdx.x]: the accumulate pass over X of
+// a Lloyd iteration then needs no kernel and no second read of X. The order of the adds is fixed by the grid.
+template <bool ACC>
 __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* __restrict__ X, long N, const float* __restrict__ C, int K,
-                                                                  int32_t* __restrict__ idx, float* __restrict__ dist, int* __restrict__ err) {
+                                                                  int32_t* __restrict__ idx, float* __restrict__ dist, int* __restrict__ err,
+                                                                  float* __restrict__ part_sums, int32_t* __restrict__ part_counts,
+                                                                  double* __restrict__ part_inertia) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t b_chunk = (uint32_t)K * 16u, b_piece = 2u * b_chunk;
@@ -100,7 +108,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
     unsigned char* sRaw = sA + TC_STAGES * TC_A_STAGE;
     float* cex = reinterpret_cast<float*>(sRaw + TC_STAGES * TC_RAW_STAGE);     // [K][8] as given
     float* cgrp = cex + (size_t)K * 8;                                           // [K / 8 groups][8 dims][8 centroids], groups TC_GROUP_STRIDE apart
-    TcShared* sh = reinterpret_cast<TcShared*>(cgrp + (size_t)(K / 8) * TC_GROUP_STRIDE);
+    float* wtab = cgrp + (size_t)(K / 8) * TC_GROUP_STRIDE;                      // ACC: [8 warps][K][8] sums, then [8][K] counts
+    int* wcnt = reinterpret_cast<int*>(wtab + (ACC ? (size_t)TC_EPI_WARPS * K * 8 : 0));
+    TcShared* sh = reinterpret_cast<TcShared*>(wcnt + (ACC ? (size_t)TC_EPI_WARPS * K : 0));
     volatile int* abort_flag = &sh->abort_flag;
     pdl_launch_dependents();
 
@@ -124,6 +134,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
         const int k = e >> 3, d = e & 7;
         cex[e] = c;
         cgrp[(k >> 3) * TC_GROUP_STRIDE + d * 8 + (k & 7)] = c;
+    }
+    if (ACC) {
+        for (int e = tid; e < TC_EPI_WARPS * K * 8; e += TC_THREADS) wtab[e] = 0.0f;
+        for (int e = tid; e < TC_EPI_WARPS * K; e += TC_THREADS) wcnt[e] = 0;
     }
     for (int e = tid; e < 128; e += TC_THREADS) {             // constant chunk pair of the point operand: row e = (1 1 1 0 | 0 0 0 0)
         const uint32_t one = tf32_of(1.0f);
@@ -250,6 +264,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
         // ── epilogue: warp w drains accumulator tile w / 4, rows 32 (w % 4) .. + 31 ──
         const int b = warp >> 2, q = warp & 3;
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)b * 256u;
+        float* mytab = wtab + (size_t)warp * K * 8;
+        int* mycnt = wcnt + (size_t)warp * K;
+        double inert = 0.0;
         for (long i = b; i < n_my; i += 2) {
             const long row = (blockIdx.x + i * gridDim.x) * TC_TILE + q * 32 + lane;
             const bool have = row < N;
@@ -339,6 +356,48 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
                 }
             }
             if (have) { idx[row] = win; if (dist) dist[row] = best; }
+            if (ACC) {
+                // points of the warp that share a cluster take turns in index order; different clusters go together
+                const unsigned grp = __match_any_sync(0xffffffffu, have ? win : -1 - lane);
+                const int rank = __popc(grp & ((1u << lane) - 1u));
+                const int rounds = __reduce_max_sync(0xffffffffu, (unsigned)__popc(grp));
+                for (int r = 0; r < rounds; r++) {
+                    if (have && rank == r) {
+                        float4* t = reinterpret_cast<float4*>(mytab + (size_t)win * 8);
+                        float4 a = t[0], c = t[1];
+                        a.x += xr[0]; a.y += xr[1]; a.z += xr[2]; a.w += xr[3];
+                        c.x += xr[4]; c.y += xr[5]; c.z += xr[6]; c.w += xr[7];
+                        t[0] = a; t[1] = c;
+                        mycnt[win] += 1;
+                    }
+                    __syncwarp();
+                }
+                if (have) inert += (double)best;
+            }
+        }
+        if (ACC) {
+            // the eight tables of the block, added in warp order; every epilogue warp gets here, also after a wait ran out
+            for (int o = 16; o > 0; o >>= 1) inert += __shfl_xor_sync(0xffffffffu, inert, o);
+            asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+            for (int e = tid; e < K * 8; e += TC_EPI_WARPS * 32) {
+                float v = wtab[e];
+#pragma unroll
+                for (int w = 1; w < TC_EPI_WARPS; w++) v += wtab[(size_t)w * K * 8 + e];
+                part_sums[(size_t)blockIdx.x * K * 8 + e] = v;
+            }
+            for (int e = tid; e < K; e += TC_EPI_WARPS * 32) {
+                int v = wcnt[e];
+#pragma unroll
+                for (int w = 1; w < TC_EPI_WARPS; w++) v += wcnt[(size_t)w * K + e];
+                part_counts[(size_t)blockIdx.x * K + e] = v;
+            }
+            if (lane == 0) sh->inert[warp] = inert;
+            asm volatile("bar.sync 1, %0;" :: "n"(TC_EPI_WARPS * 32) : "memory");
+            if (tid == 0) {
+                double t = 0.0;
+                for (int w = 0; w < TC_EPI_WARPS; w++) t += sh->inert[w];
+                part_inertia[blockIdx.x] = t;
+            }
         }
     }
     // ── teardown: every role is out of its loop (all waits are bounded); release tensor memory ──
@@ -355,12 +414,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) assign_tc_kernel(const float* _
 
 // D == 8, K a multiple of 64 up to 256, 16-byte aligned X: the tensor-memory kernel. Returns IBCU_ERR_STATE without
 // touching the context's error when the shape is not its own (the caller takes another kernel).
+static size_t tc_smem_bytes(int K, bool acc) {
+    return 1024 + (size_t)3 * 2 * K * 16 + 2 * TC_A_CHUNK + (size_t)TC_STAGES * (TC_A_STAGE + TC_RAW_STAGE) + (size_t)K * 8 * sizeof(float) +
+           (size_t)(K / 8) * TC_GROUP_STRIDE * sizeof(float) + (acc ? (size_t)TC_EPI_WARPS * K * 9 * sizeof(float) : 0) + sizeof(TcShared) + 64;
+}
+
 int ibcu_kmeans_assign_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist) {
     if (K < 64 || K > 256 || (K & 63) || ((uintptr_t)X & 15)) return IBCU_ERR_STATE;
-    const size_t smem = 1024 + (size_t)3 * 2 * K * 16 + 2 * TC_A_CHUNK + (size_t)TC_STAGES * (TC_A_STAGE + TC_RAW_STAGE) + (size_t)K * 8 * sizeof(float) + (size_t)(K / 8) * TC_GROUP_STRIDE * sizeof(float) + sizeof(TcShared) + 64;
-    IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t smem = tc_smem_bytes(K, false);
+    IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const long ntile = (N + TC_TILE - 1) / TC_TILE;
     long blocks = ntile < ctx->sm_count ? ntile : ctx->sm_count;
     if (blocks < 1) blocks = 1;
-    return ibcu_launch(ctx, assign_tc_kernel, dim3((unsigned)blocks), dim3(TC_THREADS), smem, 1, true, X, N, C, K, idx, dist, ctx->kern_err);
+    return ibcu_launch(ctx, assign_tc_kernel<false>, dim3((unsigned)blocks), dim3(TC_THREADS), smem, 1, true, X, N, C, K, idx, dist, ctx->kern_err,
+                       (float*)nullptr, (int32_t*)nullptr, (double*)nullptr);
+}
+
+// The assignment and the accumulate pass of a Lloyd iteration in one launch: per-block partial tables go to part_* (room for
+// *nblocks blocks of K * 8 sums, K counts and one inertia), which accumulate_finish_kernel then adds up. Same conditions and
+// return convention as above.
+int ibcu_kmeans_assign_accumulate_tc(ibcu_ctx* ctx, const float* X, long N, const float* C, int K, int32_t* idx, float* dist,
+                                     float* part_sums, int32_t* part_counts, double* part_inertia, int nblocks) {
+    if (K < 64 || K > 256 || (K & 63) || ((uintptr_t)X & 15)) return IBCU_ERR_STATE;
+    const size_t smem = tc_smem_bytes(K, true);
+    if (smem > 227 * 1024) return IBCU_ERR_STATE;
+    IBCU_CUDA(ctx, cudaFuncSetAttribute(assign_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    return ibcu_launch(ctx, assign_tc_kernel<true>, dim3((unsigned)nblocks), dim3(TC_THREADS), smem, 1, true, X, N, C, K, idx, dist, ctx->kern_err,
+                       part_sums, part_counts, part_inertia);
 }
