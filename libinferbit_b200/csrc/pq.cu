@@ -4,8 +4,10 @@
 // Data in HBM: codebooks, row scales and the two row-major code planes exactly as the reference
 // holds them, plus one derived array made once per tensor by ibcu_pq_prepare: the codes regrouped into
 // slabs of 32 subspaces (subspace s = 2 * chunk + side) so that lane l of a warp owns subspace 32 j + l:
-//   idx_t[slab j][group g of 16 rows][lane l][16 rows]   (one byte each)
-// A warp instruction that loads 16 bytes per lane reads 512 contiguous bytes: 16 rows x 32 subspaces.
+//   idx_t[slab j][group g of 16 rows][lane l][16 rows]   (one byte each; byte i of lane l is row i ^ (l >> 1) of the group)
+// A warp instruction that loads 16 bytes per lane reads 512 contiguous bytes: 16 rows x 32 subspaces. The rows of a
+// lane are stored in the order in which the lane-to-lane reduction wants them: with value j of lane l standing for
+// row j ^ (l >> 1), every halving step keeps the lower half of the registers and sends the upper half, in every lane.
 // The last 256 bytes of the array hold the largest magnitude of any codebook entry.
 //
 // pq_slab_kernel: grid = (blocks of rows) x (slabs) x (passes of one or two activations). A block builds the lookup table of its slab in shared
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(256) pq_pack_kernel(const uint8_t* __restrict_
         uint32_t w[4] = { 0, 0, 0, 0 };
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            const int r = 16 * g + i;
+            const int r = 16 * g + (i ^ (l >> 1));
             uint32_t v = 0u;
             if (c < C && r < M) {
                 if (packed) { const uint32_t b = src[(size_t)r * ((C + 1) / 2) + (c >> 1)]; v = (c & 1) ? (b >> 4) & 15u : b & 15u; }
@@ -117,16 +119,13 @@ __global__ void __launch_bounds__(512) pq_amax_kernel(const float* __restrict__ 
     }
 }
 
-// one halving step of the butterfly: N values per lane -> N/2, each the sum over the lane pair {l, l ^ o}
+// one halving step of the butterfly: N values per lane -> N/2, each the sum over the lane pair {l, l ^ o}. Value j of
+// lane l stands for index j ^ m(l), where the lane bit o is the bit N/2 of m: the partner's value i is then this lane's
+// value i + N/2, so every lane keeps its lower half and sends its upper half, without a select.
 template <int N>
-__device__ __forceinline__ void fold(float* v, int o, int lane) {
-    const bool up = (lane & o) != 0;
+__device__ __forceinline__ void fold(float* v, int o) {
 #pragma unroll
-    for (int i = 0; i < N / 2; i++) {
-        const float send = up ? v[i] : v[i + N / 2];
-        const float keep = up ? v[i + N / 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-    }
+    for (int i = 0; i < N / 2; i++) v[i] += __shfl_xor_sync(0xffffffffu, v[i + N / 2], o);
 }
 
 // BT activations (1 or 2) share a pass over the codes: table entries are BT floats wide. grid = (blocks of rows,
@@ -275,7 +274,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
                             v[t] = a;
                         }
                         float* dst = lut + ((size_t)k * 32 + lane) * BT;
-                        if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+                        if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = (lane & 1) ? make_float2(v[1], v[0]) : make_float2(v[0], v[1]);
                         else dst[0] = v[0];
                     }
                 } else {
@@ -301,7 +300,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
                                 v[t] = a;
                             }
                             float* dst = lut + ((size_t)k * 32 + lane) * BT;
-                            if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+                            if constexpr (BT == 2) *reinterpret_cast<float2*>(dst) = (lane & 1) ? make_float2(v[1], v[0]) : make_float2(v[0], v[1]);
                             else dst[0] = v[0];
                         }
                     }
@@ -320,7 +319,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
                     }
                     float* dst = lut + ((size_t)k * 32 + lane) * BT;
 #pragma unroll
-                    for (int t = 0; t < BT; t++) dst[t] = v[t];
+                    for (int t = 0; t < BT; t++) dst[BT == 2 ? t ^ (lane & 1) : t] = v[t];
                 }
             }
         }
@@ -381,21 +380,20 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
                     const uint32_t code = (w >> (8 * (i & 3))) & 0xFF;
                     if constexpr (BT == 2) {
                         const float2 q = *reinterpret_cast<const float2*>(lut + ((size_t)code * 32 + lane) * 2);
-                        v[i] = q.x; v[16 + i] = q.y;                                        // index = t * 16 + row
+                        v[2 * i] = q.x; v[2 * i + 1] = q.y;                                 // value 2 i + u: row i ^ (lane >> 1), activation u ^ (lane & 1)
                     } else v[i] = lut[code * 32 + lane];
                 }
                 if (any_dead) {
 #pragma unroll
-                    for (int t = 0; t < BT; t++)
+                    for (int u = 0; u < BT; u++)
 #pragma unroll
-                        for (int i = 0; i < 16; i++) v[t * 16 + i] = dead[t] ? 0.0f : v[t * 16 + i];
+                        for (int i = 0; i < 16; i++) v[i * BT + u] = dead[BT == 2 ? u ^ (lane & 1) : u] ? 0.0f : v[i * BT + u];
                 }
-                if constexpr (BT == 2) { fold<32>(v, 16, lane); fold<16>(v, 8, lane); fold<8>(v, 4, lane); fold<4>(v, 2, lane); fold<2>(v, 1, lane); }
-                else { fold<16>(v, 16, lane); fold<8>(v, 8, lane); fold<4>(v, 4, lane); fold<2>(v, 2, lane); v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1); }
-                // which (activation, row) a lane ends up with: bit 16 of the lane picked the upper half of the
-                // index range in the first step, bit 8 the upper half of that half, and so on
+                if constexpr (BT == 2) { fold<32>(v, 16); fold<16>(v, 8); fold<8>(v, 4); fold<4>(v, 2); fold<2>(v, 1); }
+                else { fold<16>(v, 16); fold<8>(v, 8); fold<4>(v, 4); fold<2>(v, 2); v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1); }
+                // value 0 of lane l is now the sum over the 32 subspaces of row l >> 1 (and, with two activations, of activation l & 1)
                 if constexpr (BT == 2) {
-                    const int t = lane >> 4, r = 16 * g + (lane & 15);                     // index = lane
+                    const int t = lane & 1, r = 16 * g + (lane >> 1);
                     if (t < nb) atomicAdd(p.acc + (size_t)(b0 + t) * p.M_pad + r, (unsigned long long)__float2ll_rn(v[0] * inv_q[t]));
                 } else if ((lane & 1) == 0) {
                     const int r = 16 * g + (lane >> 1);

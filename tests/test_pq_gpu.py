@@ -126,8 +126,9 @@ def test_pq_kv_encode(backend, cpu_libs, dim, G, K1, n_vec):
 
 def test_packed_code_plane_is_a_faithful_copy(backend):
     """ibcu_pq_prepare regroups the codes as [slab of 32 subspaces][group of 16 rows][lane][16 rows]
-    (subspace 2 * chunk + side = 32 * slab + lane); padding rows and padding subspaces hold zeros, and the tail
-    of the array holds the largest codebook magnitude."""
+    (subspace 2 * chunk + side = 32 * slab + lane; byte i of lane l is row i ^ (l >> 1) of the group, the order the
+    kernel's lane-to-lane reduction wants); padding rows and padding subspaces hold zeros, and the tail of the array
+    holds the largest codebook magnitude."""
     rng = np.random.default_rng(3)
     M, N, G, K = 77, 160, 16, 256
     cb_l, cb_r, il, ir, rs, _ = _cpu.make_pq_case(rng, M, N, G, K, 1)
@@ -138,7 +139,9 @@ def test_packed_code_plane_is_a_faithful_copy(backend):
     total = backend.lib.ibcu_pq_idx_t_bytes(M, N, G)
     assert total == nslab * 32 * t.M_pad + 256
     raw = backend.download(t.idx_t, np.uint8, total)
-    plane = raw[:nslab * 32 * t.M_pad].reshape(nslab, t.M_pad // 16, 32, 16)          # [slab][group][lane][row in group]
+    plane = raw[:nslab * 32 * t.M_pad].reshape(nslab, t.M_pad // 16, 32, 16)          # [slab][group][lane][byte]
+    order = np.arange(16)[None, :] ^ (np.arange(32)[:, None] >> 1)                        # [lane][row in group] -> byte
+    plane = np.take_along_axis(plane, np.broadcast_to(order, plane.shape), axis=3)        # [slab][group][lane][row in group]
     sub = plane.transpose(0, 2, 1, 3).reshape(nslab * 32, t.M_pad)                        # [subspace][row]
     assert np.array_equal(sub[0:2 * Cn:2, :M], il.T) and np.array_equal(sub[1:2 * Cn:2, :M], ir.T)
     assert np.all(sub[:, M:] == 0) and np.all(sub[2 * Cn:] == 0)
