@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const uint32_t w = i < 4 ? cw.x : (i < 8 ? cw.y : (i < 12 ? cw.z : cw.w));
-                    const uint32_t code = (w >> (8 * (i & 3))) & 0xFF;
+                    const uint32_t code = __byte_perm(w, 0u, 0x4440u | (i & 3));     // one byte-permute; shift-and-mask became a byte-to-word conversion on the quarter-rate conversion pipe, which then bounded the gather
                     if constexpr (BT == 2) {
                         const float2 q = *reinterpret_cast<const float2*>(lut + ((size_t)code * 32 + lane) * 2);
                         v[2 * i] = q.x; v[2 * i + 1] = q.y;                                 // value 2 i + u: row i ^ (lane >> 1), activation u ^ (lane & 1)
@@ -453,6 +453,192 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
     }
 }
 
+// ── Several activations, plain tensor with shared codebooks of 8-wide entries: pq_wide_kernel ──
+// The gather is bound by the shared-memory pipe: a table read and a lane-to-lane shuffle each move 32 values per cycle, and
+// the reduction over the lanes costs one shuffle per 32 values looked up. Here a lane owns four subspaces (a unit of work is
+// one activation x 128 subspaces, table of 128 KB) and adds their entries in registers before the lanes meet: a quarter of
+// the shuffles. Units x groups of 16 rows form one list that the blocks (one per SM) cut into equal contiguous pieces, so
+// every SM has the same share whatever the shape; a piece that crosses a unit builds a second table. Sums meet in the same
+// fixed-point accumulators; the block whose arrival completes an activation's count of pieces converts that activation.
+constexpr int PW_THREADS = 1024;
+constexpr int PW_WARPS = PW_THREADS / 32;
+constexpr int PW_Q = 4;                                      // subspaces per lane: slabs 4 u .. 4 u + 3 of the code plane
+constexpr int PW_MAXSEG = 8;
+// Table layout: quarters 2 h and 2 h + 1 share a region of 64 KB that starts at shared-memory address 64 KB * (h + 1); entry k of
+// quarter q, lane l sits at byte k * 256 + (q & 1) * 128 + 4 l of its region: bank l as before, and the code is byte 1 of the
+// address, so one byte-permute of the code word and the lane's base address yields the address of a table read. The codebooks
+// and the slices of x live below the first region.
+constexpr size_t PW_SMEM = 3 * 65536;
+constexpr size_t PW_LOW_BYTES = 256 * 2 * 2 * sizeof(float4) + PW_Q * 32 * 9 * sizeof(float);
+
+__global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p, int nunit, int per_block, int* err) {
+    extern __shared__ __align__(16) unsigned char pw_smem[];
+    const uint32_t dyn = (uint32_t)__cvta_generic_to_shared(pw_smem);                                                           // shared-memory address of the dynamic part
+    float4 (*cbf)[2][2] = reinterpret_cast<float4 (*)[2][2]>(pw_smem);                                // [k][side][half of the entry], FP32
+    float (*xs)[9] = reinterpret_cast<float (*)[9]>(pw_smem + 256 * 2 * 2 * sizeof(float4));          // [4 * 32 subspaces][8 (+1)]
+    unsigned char* lut_b = pw_smem + (65536u - dyn);                                                  // the byte at shared-memory address 64 KB
+    if (dyn + PW_LOW_BYTES > 65536u) { if (threadIdx.x == 0) *err = 7001; return; }               // the host reports it at the next sync; cannot happen with this kernel's static data
+    __shared__ int seg_tok[PW_MAXSEG], seg_n[PW_MAXSEG], seg_last[PW_MAXSEG];
+    __shared__ unsigned char sub_dead[PW_Q * 32];             // per subspace of the unit: its chunk falls under the 1 % rule
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G16 = p.M_pad >> 4, nsub = 2 * p.C;
+    // positions in the list of (unit, activation, group) fit 32 bits (the host checks): 64-bit divisions would cost more
+    // instructions per segment than the table build
+    const unsigned total = (unsigned)nunit * (unsigned)p.B * (unsigned)G16;
+    const unsigned lo = min(total, blockIdx.x * (unsigned)per_block);
+    const unsigned hi = min(total, lo + (unsigned)per_block);
+    // weights first, they do not depend on the previous kernel
+    if (tid < 512) {
+        const int side = tid >> 8, k = tid & 255;
+        const uint4 raw = k < p.K ? reinterpret_cast<const uint4*>(side ? p.cb_r : p.cb_l)[k] : make_uint4(0, 0, 0, 0);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        cbf[k][side][0] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        cbf[k][side][1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
+    const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
+    const uint4* plane = reinterpret_cast<const uint4*>(p.idx_t) + lane;
+    pdl_wait();
+
+    // what the block owes the arrival counters: (activation, pieces) of every segment since the last flush
+    int nseg = 0;
+    auto flush = [&]() {
+        __threadfence();
+        __syncthreads();
+        if (tid < nseg) {
+            const unsigned want = (unsigned)nunit * (unsigned)G16;
+            const unsigned old = atomicAdd(p.arrive + seg_tok[tid], (unsigned)seg_n[tid]);
+            seg_last[tid] = old + (unsigned)seg_n[tid] == want;
+            if (seg_last[tid]) p.arrive[seg_tok[tid]] = 0;
+        }
+        __syncthreads();
+        for (int sgi = 0; sgi < nseg; sgi++) {
+            if (!seg_last[sgi]) continue;
+            // every piece of this activation has arrived, each behind its block's fence: plain loads past L1 read the sums
+            __threadfence();
+            const int t = seg_tok[sgi];
+            const unsigned ab = p.amax_bits[t];
+            const float bound = (float)p.N * cbmax * __uint_as_float(ab);
+            int ex = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;
+            ex = max(-60, min(120, ex));
+            const double q = __longlong_as_double((long long)(1023 + ex - 62) << 52);                  // 2^(ex - 62)
+            const bool bad = ab > 0x7f7fffffu;                                                            // a NaN or an Inf among the activations
+            unsigned long long* acc = p.acc + (size_t)t * p.M_pad;
+            for (int r0 = 0; r0 < p.M_pad; r0 += 4 * PW_THREADS) {
+                long long sum[4];
+                float sc[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = r0 + tid + i * PW_THREADS;
+                    sum[i] = r < p.M_pad ? (long long)__ldcg(acc + r) : 0;
+                    sc[i] = r < p.M ? __half2float(p.row_scale[r]) : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = r0 + tid + i * PW_THREADS;
+                    if (r < p.M_pad) acc[r] = 0ull;                                                      // zero for the next call, padded rows too
+                    if (r < p.M) p.out[(size_t)t * p.out_stride + r] = bad ? __int_as_float(0x7fc00000) : (float)((double)sum[i] * q) * sc[i];
+                }
+            }
+        }
+        __syncthreads();
+        nseg = 0;
+    };
+
+    // this thread's activation of a segment: subspace s of a unit covers x[8 s, 8 s + 8)
+    auto load_x = [&](unsigned at_) -> float {
+        if (at_ >= hi) return 0.0f;
+        const unsigned ut_ = at_ / (unsigned)G16;
+        const int u_ = (int)(ut_ / (unsigned)p.B), t_ = (int)(ut_ - (unsigned)u_ * (unsigned)p.B);
+        const int sb = u_ * (PW_Q * 32) + (tid >> 3);
+        return sb < nsub ? p.x[(size_t)t_ * p.N + (size_t)sb * 8 + (tid & 7)] : 0.0f;
+    };
+    float xnext = load_x(lo);
+    for (unsigned at = lo; at < hi;) {
+        const unsigned ut = at / (unsigned)G16;               // unit * B + activation
+        const int g0 = (int)(at - ut * (unsigned)G16);
+        const int g1 = (int)min((unsigned)G16, (unsigned)g0 + (hi - at));
+        const int u = (int)(ut / (unsigned)p.B), t = (int)(ut - (unsigned)u * (unsigned)p.B);
+        at += (unsigned)(g1 - g0);
+        // codes of this warp's first group: in flight during the table build
+        uint4 cd[PW_Q];
+        auto load_codes = [&](int g, int q) {
+            return (4 * u + q < p.nslab && g < g1) ? ld_stream_u4(plane + ((size_t)(4 * u + q) * G16 + g) * 32) : make_uint4(0, 0, 0, 0);
+        };
+#pragma unroll
+        for (int q = 0; q < PW_Q; q++) cd[q] = load_codes(g0 + warp, q);
+        __syncthreads();                                      // the previous segment's gather is done with the table and the slices (first: cbf is staged)
+        if (nseg == PW_MAXSEG) flush();
+        if (tid == 0) { seg_tok[nseg] = t; seg_n[nseg] = g1 - g0; }
+        nseg++;
+        xs[tid >> 3][tid & 7] = xnext;                        // this unit's 1024 activations
+        xnext = load_x(at);                                   // the next segment's, in flight during this one
+        const float amax = __uint_as_float(p.amax_bits[t]);
+        const float bound = (float)p.N * cbmax * amax;
+        int e = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;                                     // bound < 2^e
+        e = max(-60, min(120, e));
+        const float inv_q = __uint_as_float((uint32_t)(127 + 62 - e) << 23);                              // 2^(62 - e)
+        __syncthreads();
+        // the reference drops a chunk (both of its subspaces) whose largest |x| is under 1 % of the largest overall
+        if (tid < PW_Q * 16) {                                // one thread per chunk of the unit
+            float cm = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) cm = fmaxf(cm, fmaxf(fabsf(xs[2 * tid][i]), fabsf(xs[2 * tid + 1][i])));
+            const unsigned char d = amax > 0.0f && u * (PW_Q * 32) + 2 * tid < nsub && !(cm >= amax * 0.01f);
+            sub_dead[2 * tid] = d; sub_dead[2 * tid + 1] = d;
+        }
+        __syncthreads();
+        // table: warp w builds entries k = w + 32 i, two quarters at a time (a codebook entry is read once for the two);
+        // each entry is summed in the same order as in the slab kernel
+        const int side = lane & 1;
+#pragma unroll 1
+        for (int qp = 0; qp < PW_Q; qp += 2) {
+            float xr[2][8];
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const bool dead = sub_dead[(qp + q) * 32 + lane];            // a dropped subspace gets a table of zeros: the gather need not know
+#pragma unroll
+                for (int i = 0; i < 8; i++) xr[q][i] = dead ? 0.0f : xs[(qp + q) * 32 + lane][i];
+            }
+#pragma unroll 2
+            for (int k = warp; k < 256; k += PW_WARPS) {
+                const float4 ca = cbf[k][side][0], cc = cbf[k][side][1];
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    float a = 0.0f;
+                    a = fmaf(ca.x, xr[q][0], a); a = fmaf(ca.y, xr[q][1], a); a = fmaf(ca.z, xr[q][2], a); a = fmaf(ca.w, xr[q][3], a);
+                    a = fmaf(cc.x, xr[q][4], a); a = fmaf(cc.y, xr[q][5], a); a = fmaf(cc.z, xr[q][6], a); a = fmaf(cc.w, xr[q][7], a);
+                    *reinterpret_cast<float*>(lut_b + (size_t)(qp >> 1) * 65536 + (size_t)k * 256 + q * 128 + lane * 4) = a;
+                }
+            }
+        }
+        __syncthreads();                                      // the table is complete
+        for (int g = g0 + warp; g < g1; g += PW_WARPS) {
+            float v[16];
+#pragma unroll
+            for (int q = 0; q < PW_Q; q++) {
+                const uint4 cw = cd[q];
+                cd[q] = load_codes(g + PW_WARPS, q);          // the next group's codes travel while this one is looked up
+                const uint32_t tb = 65536u * (1u + (q >> 1)) + (q & 1) * 128u + lane * 4u;     // entry 0 of this lane's subspace; byte 1 of the address is zero
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const uint32_t w = i < 4 ? cw.x : (i < 8 ? cw.y : (i < 12 ? cw.z : cw.w));
+                    const uint32_t addr = __byte_perm(w, tb, 0x7604u | ((i & 3) << 4));          // bytes (tb3, tb2, code, tb0)
+                    float val;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(val) : "r"(addr) : "memory");
+                    v[i] = q == 0 ? val : v[i] + val;
+                }
+            }
+            fold<16>(v, 16); fold<8>(v, 8); fold<4>(v, 4); fold<2>(v, 2);
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+            if ((lane & 1) == 0)                              // value 0 of lane l: row l >> 1 of the group
+                atomicAdd(p.acc + (size_t)t * p.M_pad + 16 * g + (lane >> 1), (unsigned long long)__float2ll_rn(v[0] * inv_q));
+        }
+    }
+    if (nseg) flush();
+}
+
 // Outlier sidecar (src/pq_decode.c:1394-1409): out[r] += sum over j of (sidecar[r][j] * scale[j]) * x[col[j]], added to the finished
 // rows. grid (blocks of 8 rows, activations), a warp per row, lanes over the outlier columns.
 __global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restrict__ side, const int32_t* __restrict__ cols, const __half* __restrict__ scale,
@@ -474,7 +660,7 @@ __global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restric
     if (lane == 0) out[(size_t)b * out_stride + r] += acc;
 }
 
-struct PqPlan { int C, nslab1, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; };
+struct PqPlan { int C, nslab1, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; int wide, nunit, per_block, nblocks; };
 
 PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     PqPlan pl;
@@ -501,6 +687,15 @@ PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     pl.rows_per_block = gpb * 16;
     pl.row_blocks = (groups + gpb - 1) / gpb;
     pl.acc_words = (size_t)B * t->M_pad;
+    // several activations of a plain tensor with shared 8-wide codebooks: the kernel with four subspaces per lane
+    pl.wide = B >= 2 && t->K_l2 == 0 && t->n_outlier == 0 && t->G == 16 && t->cb_chunk_stride == 0 &&
+              (((uintptr_t)t->codebook_l | (uintptr_t)t->codebook_r) & 15) == 0;
+    pl.nunit = (pl.nslab + PW_Q - 1) / PW_Q;
+    const long total = (long)pl.nunit * B * groups;
+    if (total >= (1l << 30)) pl.wide = 0;                    // the kernel counts its pieces in 32 bits
+    const long nb = total < ctx->sm_count ? total : ctx->sm_count;
+    pl.per_block = (int)((total + nb - 1) / nb);
+    pl.nblocks = (int)((total + pl.per_block - 1) / pl.per_block);
     return pl;
 }
 
@@ -524,6 +719,7 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
         if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 2 * (int)sizeof(float));
         if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_slab_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * (int)sizeof(float));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PW_SMEM);
     });
     if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
     if (pl.bt == 2) {
@@ -533,6 +729,7 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits, p.inner, p.n_inner);
         if (rc) return rc;
         p.amax_bits = amax_bits;
+        if (pl.wide) return ibcu_launch(ctx, pq_wide_kernel, dim3(pl.nblocks), dim3(PW_THREADS), PW_SMEM, 1, true, p, pl.nunit, pl.per_block, ctx->kern_err);
         rc = ex ? ibcu_launch(ctx, pq_slab_kernel<2, true>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p)
                 : ibcu_launch(ctx, pq_slab_kernel<2, false>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
         if (rc) return rc;

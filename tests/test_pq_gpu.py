@@ -22,6 +22,9 @@ def oracle_pq(libs, M, N, G, K, cb_l, cb_r, il, ir, rs, x, stride=0):
     (4096, 14336, 16, 256, 1),      # Mistral-7B down_proj: 1792 subspaces of length 8
     (4096, 14336, 16, 256, 8),
     (1000, 2048, 16, 256, 3),       # rows not a multiple of 16
+    (300, 1200, 16, 100, 5),        # several activations: 150 subspaces, the second unit of 128 is mostly padding; 100 codebook entries
+    (48, 640, 16, 256, 32),         # 32 activations, fewer pieces of work than SMs
+    (16, 40960, 16, 256, 32),       # 1280 units of one group each: a block walks nine of them and reports its arrivals in two batches
     (64, 256, 8, 64, 2), (33, 96, 4, 16, 1), (2048, 512, 32, 256, 1), (5, 16, 16, 256, 1),
 ])
 def test_pq_matches_reference_restatement(backend, cpu_libs, M, N, G, K, B):
@@ -209,13 +212,16 @@ def test_per_subspace_codebooks(backend, cpu_libs):
 
 def test_linearity_at_full_size(backend):
     """Size-independent property at the benchmark shape: with the skip rule inactive the map is linear,
-    f(x + y) = f(x) + f(y) and f(2x) = 2 f(x) exactly."""
+    f(x + y) = f(x) + f(y) and f(2x) = 2 f(x) exactly (the same number of activations in both calls: one activation
+    and several take different kernels, whose FP32 partial sums are ordered differently)."""
     rng = np.random.default_rng(4)
     M, N, G, K = 4096, 14336, 16, 256
     cb_l, cb_r, il, ir, rs, x = _cpu.make_pq_case(rng, M, N, G, K, 2)
     t = backend.make_pq(M, N, G, K, cb_l, cb_r, il, ir, rs)
     fx = backend.pq_matmul(t, x)
-    f2 = backend.pq_matmul(t, 2.0 * x[:1])
-    assert np.array_equal(f2[0], 2.0 * fx[0])
+    f2 = backend.pq_matmul(t, 2.0 * x)
+    assert np.array_equal(f2, 2.0 * fx)
+    f1 = backend.pq_matmul(t, x[:1])
+    assert np.array_equal(backend.pq_matmul(t, 2.0 * x[:1]), 2.0 * f1) and _cpu.close(f1[0], fx[0], 1e-5, 1e-5)
     fs = backend.pq_matmul(t, (x[0] + x[1])[None, :])
     assert _cpu.close(fs[0], fx[0] + fx[1], 1e-3, 1e-4)
