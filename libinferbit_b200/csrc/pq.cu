@@ -480,6 +480,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
     if (dyn + PW_LOW_BYTES > 65536u) { if (threadIdx.x == 0) *err = 7001; return; }               // the host reports it at the next sync; cannot happen with this kernel's static data
     __shared__ int seg_tok[PW_MAXSEG], seg_n[PW_MAXSEG], seg_last[PW_MAXSEG];
     __shared__ unsigned char sub_dead[PW_Q * 32];             // per subspace of the unit: its chunk falls under the 1 % rule
+    __shared__ unsigned amax_s[32], red_s[2][PW_WARPS];       // bit pattern of max |x| of the activations this block meets
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G16 = p.M_pad >> 4, nsub = 2 * p.C;
@@ -499,7 +500,58 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
     }
     const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
     const uint4* plane = reinterpret_cast<const uint4*>(p.idx_t) + lane;
+    // this thread's activation of a segment: subspace s of a unit covers x[8 s, 8 s + 8)
+    auto load_x = [&](unsigned at_) -> float {
+        if (at_ >= hi) return 0.0f;
+        const unsigned ut_ = at_ / (unsigned)G16;
+        const int u_ = (int)(ut_ / (unsigned)p.B), t_ = (int)(ut_ - (unsigned)u_ * (unsigned)p.B);
+        const int sb = u_ * (PW_Q * 32) + (tid >> 3);
+        return sb < nsub ? p.x[(size_t)t_ * p.N + (size_t)sb * 8 + (tid & 7)] : 0.0f;
+    };
     pdl_wait();
+    float xnext = load_x(lo);                                // in flight while the maxima are taken
+    // max |x| of the activations in this block's piece of the list (consecutive ones, two at a time so that their loads
+    // travel together): the 1 % rule and the fixed-point scale need it. As bit patterns: those of non-negative floats
+    // order like the floats, and NaN / Inf sort last.
+    if (lo < hi) {
+        const unsigned ut_lo = lo / (unsigned)G16, ut_hi = (hi - 1) / (unsigned)G16;
+        const int ntok = (int)min((unsigned)p.B, ut_hi - ut_lo + 1);
+        const bool vec_x = (p.N & 3) == 0 && ((uintptr_t)p.x & 15) == 0;
+        for (int j0 = 0; j0 < ntok; j0 += 2) {
+            unsigned m[2] = { 0u, 0u };
+            int tk[2];
+            tk[0] = (int)((ut_lo + (unsigned)j0) % (unsigned)p.B);
+            tk[1] = j0 + 1 < ntok ? (int)((ut_lo + (unsigned)j0 + 1u) % (unsigned)p.B) : tk[0];       // alone: the same activation twice
+            const float* xb0 = p.x + (size_t)tk[0] * p.N;
+            const float* xb1 = p.x + (size_t)tk[1] * p.N;
+            if (vec_x) {
+                const uint4* xa = reinterpret_cast<const uint4*>(xb0);
+                const uint4* xc = reinterpret_cast<const uint4*>(xb1);
+#pragma unroll 4
+                for (int i = tid; i < (p.N >> 2); i += PW_THREADS) {
+                    const uint4 v = xa[i], w = xc[i];
+                    m[0] = max(max(m[0], v.x & 0x7fffffffu), max(max(v.y & 0x7fffffffu, v.z & 0x7fffffffu), v.w & 0x7fffffffu));
+                    m[1] = max(max(m[1], w.x & 0x7fffffffu), max(max(w.y & 0x7fffffffu, w.z & 0x7fffffffu), w.w & 0x7fffffffu));
+                }
+            } else {
+                for (int i = tid; i < p.N; i += PW_THREADS) {
+                    m[0] = max(m[0], __float_as_uint(xb0[i]) & 0x7fffffffu);
+                    m[1] = max(m[1], __float_as_uint(xb1[i]) & 0x7fffffffu);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                m[h] = __reduce_max_sync(0xffffffffu, m[h]);
+                if (lane == 0) red_s[h][warp] = m[h];
+            }
+            __syncthreads();
+            if (warp < 2 && j0 + warp < ntok) {
+                const unsigned r = __reduce_max_sync(0xffffffffu, red_s[warp][lane]);
+                if (lane == 0) amax_s[tk[warp]] = r;
+            }
+            __syncthreads();
+        }
+    }
 
     // what the block owes the arrival counters: (activation, pieces) of every segment since the last flush
     int nseg = 0;
@@ -518,7 +570,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
             // every piece of this activation has arrived, each behind its block's fence: plain loads past L1 read the sums
             __threadfence();
             const int t = seg_tok[sgi];
-            const unsigned ab = p.amax_bits[t];
+            const unsigned ab = amax_s[t];
             const float bound = (float)p.N * cbmax * __uint_as_float(ab);
             int ex = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;
             ex = max(-60, min(120, ex));
@@ -546,15 +598,6 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
         nseg = 0;
     };
 
-    // this thread's activation of a segment: subspace s of a unit covers x[8 s, 8 s + 8)
-    auto load_x = [&](unsigned at_) -> float {
-        if (at_ >= hi) return 0.0f;
-        const unsigned ut_ = at_ / (unsigned)G16;
-        const int u_ = (int)(ut_ / (unsigned)p.B), t_ = (int)(ut_ - (unsigned)u_ * (unsigned)p.B);
-        const int sb = u_ * (PW_Q * 32) + (tid >> 3);
-        return sb < nsub ? p.x[(size_t)t_ * p.N + (size_t)sb * 8 + (tid & 7)] : 0.0f;
-    };
-    float xnext = load_x(lo);
     for (unsigned at = lo; at < hi;) {
         const unsigned ut = at / (unsigned)G16;               // unit * B + activation
         const int g0 = (int)(at - ut * (unsigned)G16);
@@ -574,7 +617,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
         nseg++;
         xs[tid >> 3][tid & 7] = xnext;                        // this unit's 1024 activations
         xnext = load_x(at);                                   // the next segment's, in flight during this one
-        const float amax = __uint_as_float(p.amax_bits[t]);
+        const float amax = __uint_as_float(amax_s[t]);         // written before the barriers above
         const float bound = (float)p.N * cbmax * amax;
         int e = (int)((__float_as_uint(bound) >> 23) & 0xFF) - 126;                                     // bound < 2^e
         e = max(-60, min(120, e));
@@ -722,6 +765,8 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PW_SMEM);
     });
     if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
+    if (pl.bt == 2 && pl.wide)                               // takes the maxima of the activations it meets itself
+        return ibcu_launch(ctx, pq_wide_kernel, dim3(pl.nblocks), dim3(PW_THREADS), PW_SMEM, 1, true, p, pl.nunit, pl.per_block, ctx->kern_err);
     if (pl.bt == 2) {
         // with several activations every block would scan all of them for their maxima: one small launch does it once;
         // its results sit in the last 64 counter slots, which no pass uses
@@ -729,7 +774,6 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         int rc = ibcu_launch(ctx, pq_amax_kernel, dim3(B), dim3(512), 0, 1, true, x, t->N, amax_bits, p.inner, p.n_inner);
         if (rc) return rc;
         p.amax_bits = amax_bits;
-        if (pl.wide) return ibcu_launch(ctx, pq_wide_kernel, dim3(pl.nblocks), dim3(PW_THREADS), PW_SMEM, 1, true, p, pl.nunit, pl.per_block, ctx->kern_err);
         rc = ex ? ibcu_launch(ctx, pq_slab_kernel<2, true>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p)
                 : ibcu_launch(ctx, pq_slab_kernel<2, false>, grid, block, (size_t)256 * 32 * 2 * sizeof(float), 1, true, p);
         if (rc) return rc;
