@@ -99,6 +99,10 @@ int  ib_b200_pq_matmul_fp32_threaded(const ib_b200_pq_tensor* t, const float* x,
 int  ib_b200_pq_matmul_fp32_streaming(const ib_b200_pq_tensor* t, const float* x, float* out);
 /* B activations at once, x[b*N + j] -> out[b*M + r] (the reference loops, src/pq_decode.c:5848-5851). */
 int  ib_b200_pq_matmul_fp32_batch(const ib_b200_pq_tensor* t, const float* x, float* out, int B);
+/* ib_pq_lm_head_topk (src/pq_decode.c:2259-2341): ids and full logits of the K_top rows with the largest first-level
+ * logits, by descending full logit. Host pointers; -1 on a bad argument like the reference (K_top outside 1..M), and
+ * for K_top above 1024, which this backend does not take. */
+int  ib_b200_pq_lm_head_topk(const ib_b200_pq_tensor* t, const float* x, int K_top, float* out_logits, int32_t* out_token_ids);
 void ib_b200_pq_release(const ib_b200_pq_tensor* t);
 
 /* ── k-means (src/pq_kmeans.h:60-74) ─────────────────────────────────────────────────── */

@@ -186,7 +186,8 @@ typedef struct {
 
 /* One-off per tensor (like the reference's ib_pq_lut_cache regrouped index layout,
  * src/pq_decode.c:2687-2737): writes the codes regrouped into slabs of 32 subspaces
- * ([slab][group of 16 rows][lane][16 rows], subspace 2 * chunk + side = 32 * slab + lane) and, after them,
+ * ([slab][group of 16 rows][lane][16 rows], subspace 2 * chunk + side = 32 * slab + lane, byte i of lane l holding
+ * row i ^ (l >> 1) of the group) and, after them,
  * the largest codebook magnitude into idx_t_out, which must hold ibcu_pq_idx_t_bytes(M, N, G) bytes, and
  * fills t->idx_t / t->M_pad. Needs the tensor's codebooks as well as its codes. */
 size_t ibcu_pq_idx_t_bytes(int M, int N, int G);
@@ -218,6 +219,13 @@ int    ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, const floa
  * same device - race and must be serialised by the caller. */
 int    ibcu_pq_matmul_fp32_noalloc(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int B);
 size_t ibcu_pq_noalloc_max_floats(void);
+
+/* ib_pq_lm_head_topk (src/pq_decode.h, body src/pq_decode.c:2259-2341) on the device: first-level logits of all M rows
+ * without the 1 % rule (ib_pq_matmul_fp32_l1_only, :2085-2143), the K_top rows with the largest of them, every level
+ * of those rows (ib_pq_matmul_fp32_subset, :2145-2248), and out_logits[K_top] / out_ids[K_top] in descending order of the
+ * full logit (equal logits: ascending row). 1 <= K_top <= min(M, 1024). Reads the row-major code planes idx_l / idx_r
+ * (and idx2_l / idx2_r), which must still be resident, beside the regrouped copy. x, out_logits, out_ids: device memory. */
+int ibcu_pq_lm_head_topk(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, int K_top, float* out_logits, int32_t* out_ids);
 
 /* PQ-compressed KV cache, encode of n_vec vectors of dim values (src/pq_decode.c:5008-5066: the K or the V row of a
  * position): scale[v] = max|vec| / 7 (at least 1e-12), and per chunk of G normalised values the nearest entry (squared

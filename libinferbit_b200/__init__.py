@@ -182,6 +182,15 @@ class Backend:
         self.sync()
         return self.download(do, np.float32, B * t.M).reshape(B, t.M)
 
+    def pq_lm_head_topk(self, t, x, k_top):
+        """(logits[k_top], ids[k_top]) of ib_pq_lm_head_topk (src/pq_decode.c:2259-2341) for one activation"""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        dx = self.upload(x)
+        dl = self.alloc(k_top * 4); di = self.alloc(k_top * 4)
+        self._check(self.lib.ibcu_pq_lm_head_topk(self.ctx, C.byref(t), dx.ptr, k_top, dl.ptr, di.ptr))
+        self.sync()
+        return self.download(dl, np.float32, k_top), self.download(di, np.int32, k_top)
+
     def kmeans_assign(self, X, Cn, want_dist=False, path=0):
         """path: IBCU_KMEANS_AUTO (0), _EXACT (1) or _MMA_SYNC (2)"""
         X = np.ascontiguousarray(X, np.float32); Cn = np.ascontiguousarray(Cn, np.float32)

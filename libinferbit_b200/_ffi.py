@@ -85,6 +85,7 @@ IBCU_SYMBOLS = {
     "ibcu_pq_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pqkv_encode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_pq_matmul_fp32_strided": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_pq_lm_head_topk": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ibcu_pq_matmul_fp32_noalloc": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pq_noalloc_max_floats": (C.c_size_t, []),
     "ibcu_kmeans_assign": (C.c_int, [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
@@ -208,6 +209,7 @@ HOST_SYMBOLS = {
     "ib_b200_pq_matmul_fp32_threaded": (_i, [C.POINTER(HostPqTensor), _vp, _vp, _vp]),
     "ib_b200_pq_matmul_fp32_streaming": (_i, [C.POINTER(HostPqTensor), _vp, _vp]),
     "ib_b200_pq_matmul_fp32_batch": (_i, [C.POINTER(HostPqTensor), _vp, _vp, _i]),
+    "ib_b200_pq_lm_head_topk": (_i, [C.POINTER(HostPqTensor), _vp, _i, _vp, _vp]),
     "ib_b200_pq_release": (None, [C.POINTER(HostPqTensor)]),
     "ib_b200_kmeans_assign": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
     "ib_b200_kmeans_lloyd": (_i, [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),

@@ -337,6 +337,46 @@ def _pq(lib, ctx, M, N, G, K, B):
             "shape": {"M": M, "N": N, "G": G, "K": K, "B": B}}
 
 
+def _pq_topk(lib, ctx, M, N, G, K, K_l2, k_top):
+    """ib_pq_lm_head_topk on a two-level LM head: first-level matvec over all rows, choice of k_top rows, every level of
+    those rows, order. Eight tensors' code planes (more than L2 together with their regrouped copies) are walked in a ring."""
+    dev = Dev(lib, ctx)
+    rng = np.random.default_rng(5)
+    half, Cn = G // 2, N // G
+    R = 8
+    cb = [dev.upload((rng.standard_normal((K, half)) * 0.02).astype(np.float16)) for _ in range(2)]
+    cb2 = [dev.upload((rng.standard_normal((K_l2, half)) * 0.004).astype(np.float16)) for _ in range(2)]
+    rs = dev.upload(np.ones(M, np.float16))
+    x = dev.upload(rng.standard_normal(N).astype(np.float32))
+    ol = dev.alloc(k_top * 4); oi = dev.alloc(k_top * 4)
+    stride2 = (Cn + 1) // 2 if K_l2 == 16 else Cn
+    ts = []
+    for r in range(R):
+        t = PqT()
+        t.M, t.N, t.G, t.K, t.K_l2 = M, N, G, K, K_l2
+        t.codebook_l, t.codebook_r, t.row_scale, t.cb_chunk_stride = cb[0], cb[1], rs, 0
+        t.codebook2_l, t.codebook2_r = cb2[0], cb2[1]
+        bufs = [dev.alloc(M * Cn), dev.alloc(M * Cn), dev.alloc(M * stride2), dev.alloc(M * stride2)]
+        for j, b in enumerate(bufs):
+            check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, b, M * (Cn if j < 2 else stride2), 300 + 4 * r + j))
+        t.idx_l, t.idx_r, t.idx2_l, t.idx2_r = bufs
+        it = dev.alloc(lib.ibcu_pq_prepared_bytes(C.byref(t)))
+        check(lib, ctx, lib.ibcu_pq_prepare(ctx, C.byref(t), it))
+        ts.append(t)
+
+    def run():
+        for t in ts:
+            check(lib, ctx, lib.ibcu_pq_lm_head_topk(ctx, C.byref(t), x, k_top, ol, oi))
+    gid = dev.graph(run)
+    dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
+    ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid), reps=10) for _ in range(3)) / R
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    algo = 2 * M * Cn + 2 * K * half * 2 + 2 * M + 4 * N + k_top * (2 * Cn + 2 * stride2) + 8 * k_top
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
+            "shape": {"M": M, "N": N, "G": G, "K": K, "K_l2": K_l2, "K_top": k_top}}
+
+
 def _pq_sharded(lib, ctx, rank, world, max_over_ranks, barrier, M, N, G, K, B):
     """The PQ matvec with the rows of every tensor split over the ranks (the reference's threaded form splits rows over
     workers the same way): a rank computes its rows in place into the full-width result, a gather completes it. The

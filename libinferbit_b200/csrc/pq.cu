@@ -47,6 +47,8 @@ struct PqParams {
     int nslab1, K2;
     const __half* cb2_l; const __half* cb2_r;
     const int* inner; int n_inner;
+    int tail_slabs;                            // slabs of the whole code array: the tail with max |codebook entry| follows them
+    int no_skip;                               // the 1 % rule is off (the first-level pass of the top-K head, src/pq_decode.c:2085-2143)
 };
 
 // codes [M][C] x 2 planes -> slabs of 32 subspaces, 16 rows per lane (see the head of the file)
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
         const int lvl0 = EX && (int)blockIdx.y >= p.nslab1;
         if (lvl_smem(lvl0)) { stage_cb(lvl0); staged = lvl0; }
     }
-    const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
+    const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.tail_slabs * G16 * 512));
     // the rows this thread would finish if its block turns out to arrive last (PQ_FIN at a time)
     constexpr int PQ_FIN = 4;
     const int rows = max(0, min(row_hi, p.M) - row_lo);
@@ -356,7 +358,7 @@ __global__ void __launch_bounds__(PQ_THREADS, 2) pq_slab_kernel(const PqParams p
 #pragma unroll
         for (int t = 0; t < BT; t++) {
             dead[t] = false;
-            if (t < nb && s0 + lane < nsub && amax[t] > 0.0f) {
+            if (t < nb && s0 + lane < nsub && amax[t] > 0.0f && !p.no_skip) {
                 const int l0 = lane & ~1;
                 float cm = 0.0f;
                 for (int i = 0; i < half; i++) cm = fmaxf(cm, fmaxf(fabsf(xs[t][l0][i]), fabsf(xs[t][l0 + 1][i])));
@@ -498,7 +500,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
         cbf[k][side][0] = make_float4(f0.x, f0.y, f1.x, f1.y);
         cbf[k][side][1] = make_float4(f2.x, f2.y, f3.x, f3.y);
     }
-    const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.nslab * G16 * 512));
+    const float cbmax = __int_as_float(*reinterpret_cast<const int*>(p.idx_t + (size_t)p.tail_slabs * G16 * 512));
     const uint4* plane = reinterpret_cast<const uint4*>(p.idx_t) + lane;
     // this thread's activation of a segment: subspace s of a unit covers x[8 s, 8 s + 8)
     auto load_x = [&](unsigned at_) -> float {
@@ -628,7 +630,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) pq_wide_kernel(const PqParams p
             float cm = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; i++) cm = fmaxf(cm, fmaxf(fabsf(xs[2 * tid][i]), fabsf(xs[2 * tid + 1][i])));
-            const unsigned char d = amax > 0.0f && u * (PW_Q * 32) + 2 * tid < nsub && !(cm >= amax * 0.01f);
+            const unsigned char d = amax > 0.0f && !p.no_skip && u * (PW_Q * 32) + 2 * tid < nsub && !(cm >= amax * 0.01f);
             sub_dead[2 * tid] = d; sub_dead[2 * tid + 1] = d;
         }
         __syncthreads();
@@ -705,11 +707,11 @@ __global__ void __launch_bounds__(256) pq_outlier_kernel(const int8_t* __restric
 
 struct PqPlan { int C, nslab1, nslab, bt, passes, row_blocks, rows_per_block, slab_blocks; size_t acc_words; int wide, nunit, per_block, nblocks; };
 
-PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
+PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B, bool l1_only = false) {
     PqPlan pl;
     pl.C = (t->N - t->n_outlier) / t->G;
     pl.nslab1 = (2 * pl.C + 31) / 32;
-    pl.nslab = t->K_l2 > 0 ? 2 * pl.nslab1 : pl.nslab1;
+    pl.nslab = (t->K_l2 > 0 && !l1_only) ? 2 * pl.nslab1 : pl.nslab1;
     pl.bt = B >= 2 ? 2 : 1;
     pl.passes = (B + pl.bt - 1) / pl.bt;
     const int slots = ctx->sm_count * 2;
@@ -731,7 +733,7 @@ PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
     pl.row_blocks = (groups + gpb - 1) / gpb;
     pl.acc_words = (size_t)B * t->M_pad;
     // several activations of a plain tensor with shared 8-wide codebooks: the kernel with four subspaces per lane
-    pl.wide = B >= 2 && t->K_l2 == 0 && t->n_outlier == 0 && t->G == 16 && t->cb_chunk_stride == 0 &&
+    pl.wide = B >= 2 && !l1_only && t->K_l2 == 0 && t->n_outlier == 0 && t->G == 16 && t->cb_chunk_stride == 0 &&
               (((uintptr_t)t->codebook_l | (uintptr_t)t->codebook_r) & 15) == 0;
     pl.nunit = (pl.nslab + PW_Q - 1) / PW_Q;
     const long total = (long)pl.nunit * B * groups;
@@ -743,7 +745,7 @@ PqPlan pq_plan(const ibcu_ctx* ctx, const ibcu_pq_t* t, int B) {
 }
 
 int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int out_stride, int B, const PqPlan& pl,
-              unsigned long long* acc, unsigned int* arrive) {
+              unsigned long long* acc, unsigned int* arrive, bool l1_only = false) {
     PqParams p;
     p.M = t->M; p.M_pad = t->M_pad; p.N = t->N; p.G = t->G; p.K = t->K; p.C = pl.C; p.B = B; p.nslab = pl.nslab;
     p.rows_per_block = pl.rows_per_block;
@@ -752,6 +754,7 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
     p.amax_bits = nullptr;
     p.nslab1 = pl.nslab1; p.K2 = t->K_l2; p.cb2_l = (const __half*)t->codebook2_l; p.cb2_r = (const __half*)t->codebook2_r;
     p.inner = t->n_outlier > 0 ? t->inner_cols : nullptr; p.n_inner = t->N - t->n_outlier;
+    p.tail_slabs = t->K_l2 > 0 ? 2 * pl.nslab1 : pl.nslab1; p.no_skip = l1_only ? 1 : 0;
     const bool ex = t->K_l2 > 0 || t->n_outlier > 0;
     const dim3 grid(pl.row_blocks, pl.slab_blocks, pl.passes), block(PQ_THREADS);
     // static plus dynamic shared memory passes 48 KB: opt in once per device
@@ -765,7 +768,7 @@ int pq_launch(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, float* out, int
         if (e == cudaSuccess) e = cudaFuncSetAttribute(pq_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PW_SMEM);
     });
     if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(pq_slab_kernel): %s", cudaGetErrorString(e));
-    if (pl.bt == 2 && pl.wide)                               // takes the maxima of the activations it meets itself
+    if (pl.wide)                               // takes the maxima of the activations it meets itself
         return ibcu_launch(ctx, pq_wide_kernel, dim3(pl.nblocks), dim3(PW_THREADS), PW_SMEM, 1, true, p, pl.nunit, pl.per_block, ctx->kern_err);
     if (pl.bt == 2) {
         // with several activations every block would scan all of them for their maxima: one small launch does it once;
@@ -904,6 +907,278 @@ extern "C" int ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, co
         IBCU_CUDA(ctx, cudaMemsetAsync(ctx->pq_acc, 0, ctx->pq_acc_bytes, ctx->stream));
     }
     return pq_launch(ctx, t, x, out, out_stride, B, pl, (unsigned long long*)((char*)ctx->pq_acc + PQ_COUNTER_BYTES), (unsigned int*)ctx->pq_acc);
+}
+
+// ── top-K LM head (src/pq_decode.c:2259-2341) ───────────────────────────────────────────
+// Four steps on the stream: the first-level matvec over all rows without the 1 % rule (the kernels above), the choice
+// of the K_top rows with the largest first-level logits, every level of those rows, and their order by full logit.
+namespace {
+
+constexpr int TOPK_MAX = 1024;
+constexpr int TOPK_THREADS = 1024;
+
+// What the kernel before wrote (first-level logits, chosen rows, their full logits) is read past L1 (__ldcg): these
+// kernels start while their predecessor still runs, and a read-only-path load after the dependency wait returned the
+// previous call's values here (the chosen rows came out paired with another call's order).
+// keys order like the floats (negative values reversed, positive ones above them)
+__device__ __forceinline__ unsigned topk_key(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One block. The K_top-th largest key by passes of 8-bit digit counts over (key - smallest key), from its highest set bit
+// down: counted from the smallest key the first digit already spreads the rows over the table (logits themselves share
+// their leading bits, and adds to a few shared counters queue behind one another), and later passes only touch the rows
+// of one digit. Then the rows above the threshold in any order and, of the rows equal to it, those with the lowest
+// indices: cand[0 .. K_top). The reference keeps the first row it met among equal first-level logits at the boundary
+// too (a later row replaces the heap's root only when strictly larger), but which equal rows survive inside its heap
+// depends on the heap's shape; equal logits at the boundary are a tie that callers cannot rely on either way.
+// REG: M <= 32 * 1024, every thread keeps its 32 keys in registers and the logits are read once.
+template <bool REG>
+__global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_kernel(const float* __restrict__ coarse, int M, int K_top, int32_t* __restrict__ cand) {
+    __shared__ unsigned hist[256], red_lo[TOPK_THREADS / 32], red_hi[TOPK_THREADS / 32];
+    __shared__ unsigned s_prefix, s_need, s_gt, s_eq_before, warp_tot[TOPK_THREADS / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NREG = REG ? 32 : 1;
+    const int nchunk = (M + TOPK_THREADS - 1) / TOPK_THREADS;
+    unsigned keys[NREG] = {};
+    auto key_at = [&](int j) -> unsigned {                    // key of row tid + 1024 j (REG: j is a constant after unrolling)
+        if (REG) return keys[j];
+        const int i = tid + j * TOPK_THREADS;
+        return i < M ? topk_key(__ldcg(coarse + i)) : 0u;
+    };
+    unsigned lo = 0xffffffffu, hi = 0u;
+    if (REG) {
+#pragma unroll
+        for (int j = 0; j < NREG; j++) {
+            const int i = tid + j * TOPK_THREADS;
+            keys[j] = i < M ? topk_key(__ldcg(coarse + i)) : 0u;
+            if (i < M) { lo = min(lo, keys[j]); hi = max(hi, keys[j]); }
+        }
+    } else {
+        for (int j = 0; j < nchunk; j++) if (tid + j * TOPK_THREADS < M) { const unsigned k = key_at(j); lo = min(lo, k); hi = max(hi, k); }
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo); hi = __reduce_max_sync(0xffffffffu, hi);
+    if (lane == 0) { red_lo[warp] = lo; red_hi[warp] = hi; }
+    if (tid == 0) { s_prefix = 0u; s_need = (unsigned)K_top; }
+    __syncthreads();
+    lo = __reduce_min_sync(0xffffffffu, red_lo[lane]); hi = __reduce_max_sync(0xffffffffu, red_hi[lane]);
+    int shift = 32 - __clz(hi - lo);                          // bits of (key - lo) in use; 0 when all keys are equal
+    while (shift > 0) {
+        const int width = shift < 8 ? shift : 8;
+        const int top = shift;                                // the bits at and above `top` are settled: they equal s_prefix there
+        shift -= width;
+        if (tid < 256) hist[tid] = 0u;
+        __syncthreads();
+        const unsigned prefix = s_prefix, need0 = s_need, mask = top >= 32 ? 0u : 0xffffffffu << top;
+        auto count = [&](int j) {
+            const unsigned k = key_at(j) - lo;
+            if (tid + j * TOPK_THREADS < M && (k & mask) == prefix) atomicAdd(&hist[(k >> shift) & ((1u << width) - 1u)], 1u);
+        };
+        if (REG) {
+#pragma unroll
+            for (int j = 0; j < NREG; j++) count(j);
+        } else {
+            for (int j = 0; j < nchunk; j++) count(j);
+        }
+        __syncthreads();
+        // counts from the top digit down, as running sums over 256 threads: the digit at which the sum reaches what is still needed
+        unsigned c = 0, incl = 0;
+        if (tid < 256) {
+            c = hist[255 - tid];
+            incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const unsigned n = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += n; }
+            if (lane == 31) warp_tot[warp] = incl;
+        }
+        __syncthreads();
+        if (tid < 256) {
+            for (int w = 0; w < warp; w++) incl += warp_tot[w];
+            const unsigned excl = incl - c;
+            if (excl < need0 && need0 <= incl) {
+                s_need = need0 - excl;                        // rows still to take among those whose key starts with (prefix, digit)
+                s_prefix = prefix | ((unsigned)(255 - tid) << shift);
+            }
+        }
+        __syncthreads();
+    }
+    const unsigned T = s_prefix, need_eq = s_need;           // (the K_top-th largest key) - lo; need_eq rows equal to it are taken
+    if (tid == 0) { s_gt = 0u; s_eq_before = 0u; }
+    __syncthreads();
+    const int n_gt = K_top - (int)need_eq;
+    auto place = [&](int j) {
+        const int i = j * TOPK_THREADS + tid;
+        const unsigned k = key_at(j) - lo;
+        const bool gt = i < M && k > T, eq = i < M && k == T;
+        if (gt) { const unsigned slot = atomicAdd(&s_gt, 1u); if ((int)slot < n_gt) cand[slot] = i; }
+        if (__syncthreads_or(eq)) {                           // rows equal to the threshold: taken in index order
+            const unsigned bal = __ballot_sync(0xffffffffu, eq);
+            if (lane == 0) warp_tot[warp] = __popc(bal);
+            __syncthreads();
+            unsigned before = s_eq_before;
+            for (int w = 0; w < warp; w++) before += warp_tot[w];
+            const unsigned rank = before + __popc(bal & ((1u << lane) - 1u));
+            if (eq && rank < need_eq) cand[n_gt + (int)rank] = i;
+            __syncthreads();
+            if (tid == 0) { unsigned t = 0; for (int w = 0; w < TOPK_THREADS / 32; w++) t += warp_tot[w]; s_eq_before += t; }
+            __syncthreads();
+        }
+    };
+    if (REG) {
+#pragma unroll
+        for (int j = 0; j < NREG; j++) if (j < nchunk) place(j);
+    } else {
+        for (int j = 0; j < nchunk; j++) place(j);
+    }
+}
+
+// A block per chosen row: every level of the row, entry times activation (src/pq_decode.c:2145-2248), threads over the
+// chunks so that the dependent reads (code, then codebook entry) of all chunks travel together; a fixed butterfly over
+// the lanes, the warps' sums added in warp order; row scale, then the outlier sidecar.
+constexpr int TOPK_SUB_THREADS = 128;
+__global__ void __launch_bounds__(TOPK_SUB_THREADS) pq_topk_subset_kernel(const ibcu_pq_t t, int C, const float* __restrict__ x, const int32_t* __restrict__ cand,
+                                                                          int K_top, float* __restrict__ refined) {
+    __shared__ float wsum[2][TOPK_SUB_THREADS / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = __ldcg(cand + blockIdx.x), half = t.G >> 1;
+    const bool two = t.K_l2 > 0, packed = t.K_l2 == 16;
+    const size_t l2_stride = packed ? (size_t)((C + 1) / 2) : (size_t)C;
+    const __half* cb1l = reinterpret_cast<const __half*>(t.codebook_l);
+    const __half* cb1r = reinterpret_cast<const __half*>(t.codebook_r);
+    const __half* cb2l = reinterpret_cast<const __half*>(t.codebook2_l);
+    const __half* cb2r = reinterpret_cast<const __half*>(t.codebook2_r);
+    const int32_t* inner = t.n_outlier > 0 ? t.inner_cols : nullptr;
+    const uint8_t* jl = two ? t.idx2_l + (size_t)r * l2_stride : nullptr;
+    const uint8_t* jr = two ? t.idx2_r + (size_t)r * l2_stride : nullptr;
+    // 8-wide entries at 16-byte boundaries and contiguous activations: one 16-byte read per entry, two per slice of x
+    const bool vec = half == 8 && !inner && (t.cb_chunk_stride & 7) == 0 && ((uintptr_t)x & 15) == 0 &&
+                     ((((uintptr_t)cb1l | (uintptr_t)cb1r) & 15) == 0) && (!two || (((uintptr_t)cb2l | (uintptr_t)cb2r) & 15) == 0);
+    float acc = 0.0f;
+    for (int c = tid; c < C; c += TOPK_SUB_THREADS) {
+        const int base = c * t.G;
+        const int a1 = t.idx_l[(size_t)r * C + c], b1 = t.idx_r[(size_t)r * C + c];
+        const __half* el = cb1l + (size_t)c * t.cb_chunk_stride + (size_t)a1 * half;
+        const __half* er = cb1r + (size_t)c * t.cb_chunk_stride + (size_t)b1 * half;
+        const __half *fl = nullptr, *fr = nullptr;
+        if (two) {
+            const int a2 = packed ? ((c & 1) ? (jl[c >> 1] >> 4) & 15 : jl[c >> 1] & 15) : jl[c];
+            const int b2 = packed ? ((c & 1) ? (jr[c >> 1] >> 4) & 15 : jr[c >> 1] & 15) : jr[c];
+            fl = cb2l + (size_t)a2 * half; fr = cb2r + (size_t)b2 * half;
+        }
+        if (vec) {
+            const uint4 ql = *reinterpret_cast<const uint4*>(el), qr = *reinterpret_cast<const uint4*>(er);
+            uint4 pl = make_uint4(0, 0, 0, 0), pr = make_uint4(0, 0, 0, 0);
+            if (two) { pl = *reinterpret_cast<const uint4*>(fl); pr = *reinterpret_cast<const uint4*>(fr); }
+            const float4 x0 = *reinterpret_cast<const float4*>(x + base), x1 = *reinterpret_cast<const float4*>(x + base + 4);
+            const float4 x2 = *reinterpret_cast<const float4*>(x + base + 8), x3 = *reinterpret_cast<const float4*>(x + base + 12);
+            const float xl[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
+            const float xr[8] = { x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w };
+            const __half* hl = reinterpret_cast<const __half*>(&ql); const __half* hr = reinterpret_cast<const __half*>(&qr);
+            const __half* gl = reinterpret_cast<const __half*>(&pl); const __half* gr = reinterpret_cast<const __half*>(&pr);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float wl = __half2float(hl[j]), wr = __half2float(hr[j]);
+                if (two) { wl += __half2float(gl[j]); wr += __half2float(gr[j]); }      // (e1 + e2) x: both levels share the activation
+                acc = fmaf(wl, xl[j], acc);
+                acc = fmaf(wr, xr[j], acc);
+            }
+        } else {
+            for (int j = 0; j < half; j++) {
+                const float xl = x[inner ? inner[base + j] : base + j], xr = x[inner ? inner[base + half + j] : base + half + j];
+                float wl = __half2float(el[j]), wr = __half2float(er[j]);
+                if (two) { wl += __half2float(fl[j]); wr += __half2float(fr[j]); }
+                acc = fmaf(wl, xl, acc);
+                acc = fmaf(wr, xr, acc);
+            }
+        }
+    }
+    float oc = 0.0f;
+    for (int j = tid; j < t.n_outlier; j += TOPK_SUB_THREADS) {
+        const float wgt = (float)t.outlier_sidecar[(size_t)r * t.n_outlier + j] * __half2float(reinterpret_cast<const __half*>(t.outlier_scale)[j]);
+        oc = fmaf(wgt, x[t.outlier_cols[j]], oc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xffffffffu, acc, o); oc += __shfl_xor_sync(0xffffffffu, oc, o); }
+    if (lane == 0) { wsum[0][warp] = acc; wsum[1][warp] = oc; }
+    __syncthreads();
+    if (tid == 0) {
+        float a = wsum[0][0], o = wsum[1][0];
+        for (int w = 1; w < TOPK_SUB_THREADS / 32; w++) { a += wsum[0][w]; o += wsum[1][w]; }
+        refined[blockIdx.x] = a * __half2float(reinterpret_cast<const __half*>(t.row_scale)[r]) + o;
+    }
+}
+
+// One block: the chosen rows by full logit, descending; equal logits by ascending row. Bitonic network over the next
+// power of two.
+__global__ void __launch_bounds__(TOPK_THREADS) pq_topk_sort_kernel(const float* __restrict__ refined, const int32_t* __restrict__ cand, int K_top,
+                                                                    float* __restrict__ out_logits, int32_t* __restrict__ out_ids) {
+    __shared__ float sv[TOPK_MAX];
+    __shared__ int32_t si[TOPK_MAX];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    int n = 1;
+    while (n < K_top) n <<= 1;
+    if (tid < n) { sv[tid] = tid < K_top ? __ldcg(refined + tid) : -INFINITY; si[tid] = tid < K_top ? __ldcg(cand + tid) : 0x7fffffff; }
+    __syncthreads();
+    // a before b: larger logit, then smaller row; NaN logits go last
+    auto before = [](float av, int32_t ai, float bv, int32_t bi) {
+        const bool an = av != av, bn = bv != bv;
+        if (an != bn) return bn;
+        if (!an && av != bv) return av > bv;
+        return ai < bi;
+    };
+    for (int k = 2; k <= n; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const int p = tid ^ j;
+            if (tid < n && p > tid) {
+                const bool up = (tid & k) == 0;               // this pair sorts towards "before first"
+                const float av = sv[tid], bv = sv[p];
+                const int32_t ai = si[tid], bi = si[p];
+                const bool swap = up ? before(bv, bi, av, ai) : before(av, ai, bv, bi);
+                if (swap) { sv[tid] = bv; sv[p] = av; si[tid] = bi; si[p] = ai; }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid < K_top) { out_logits[tid] = sv[tid]; out_ids[tid] = si[tid]; }
+}
+
+}  // namespace
+
+extern "C" int ibcu_pq_lm_head_topk(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, int K_top, float* out_logits, int32_t* out_ids) {
+    IBCU_CHECK_CTX(ctx);
+    IBCU_REQUIRE(ctx, out_logits && out_ids, "ibcu_pq_lm_head_topk: null output");
+    int rc = pq_check(ctx, t, x, out_logits, 1, "ibcu_pq_lm_head_topk");
+    if (rc) return rc;
+    IBCU_REQUIRE(ctx, K_top >= 1 && K_top <= t->M && K_top <= TOPK_MAX, "ibcu_pq_lm_head_topk: K_top=%d not in 1..min(M, %d)", K_top, TOPK_MAX);
+    IBCU_REQUIRE(ctx, t->idx_l && t->idx_r && (t->K_l2 == 0 || (t->idx2_l && t->idx2_r)), "ibcu_pq_lm_head_topk: the row-major code planes must stay resident");
+    const PqPlan pl = pq_plan(ctx, t, 1, true);
+    const size_t need = pq_scratch_bytes(pl);
+    if (ctx->pq_acc_bytes < need) {
+        rc = ibcu_reserve(ctx, &ctx->pq_acc, &ctx->pq_acc_bytes, need);
+        if (rc) return rc;
+        IBCU_CUDA(ctx, cudaMemsetAsync(ctx->pq_acc, 0, ctx->pq_acc_bytes, ctx->stream));
+    }
+    const size_t coarse_bytes = ((size_t)t->M * sizeof(float) + 255) & ~(size_t)255;
+    rc = ibcu_reserve(ctx, &ctx->scratch, &ctx->scratch_bytes, coarse_bytes + 2 * TOPK_MAX * sizeof(float));
+    if (rc) return rc;
+    float* coarse = (float*)ctx->scratch;
+    int32_t* cand = (int32_t*)((char*)ctx->scratch + coarse_bytes);
+    float* refined = (float*)(cand + TOPK_MAX);
+    rc = pq_launch(ctx, t, x, coarse, t->M, 1, pl, (unsigned long long*)((char*)ctx->pq_acc + PQ_COUNTER_BYTES), (unsigned int*)ctx->pq_acc, true);
+    if (rc) return rc;
+    rc = t->M <= 32 * TOPK_THREADS
+             ? ibcu_launch(ctx, pq_topk_select_kernel<true>, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand)
+             : ibcu_launch(ctx, pq_topk_select_kernel<false>, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand);
+    if (rc) return rc;
+    rc = ibcu_launch(ctx, pq_topk_subset_kernel, dim3(K_top), dim3(TOPK_SUB_THREADS), 0, 1, true, *t, pl.C, x, (const int32_t*)cand, K_top, refined);
+    if (rc) return rc;
+    return ibcu_launch(ctx, pq_topk_sort_kernel, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)refined, (const int32_t*)cand, K_top, out_logits, out_ids);
 }
 
 // ── PQ matvec without any allocation ────────────────────────────────────────────────────

@@ -121,6 +121,32 @@ int ib_b200_pq_matmul_fp32_threaded(const ib_b200_pq_tensor* t, const float* x, 
 }
 int ib_b200_pq_matmul_fp32_streaming(const ib_b200_pq_tensor* t, const float* x, float* out) { return ib_b200_pq_matmul_fp32_batch(t, x, out, 1); }
 
+static int pq_topk_unlocked(const ib_b200_pq_tensor* t, const float* x, int K_top, float* out_logits, int32_t* out_token_ids) {
+    if (!t || !x || !out_logits || !out_token_ids) return -1;            /* src/pq_decode.c:2261-2262 */
+    if (K_top <= 0 || K_top > t->M) return -1;
+    if (!g_ib.ctx) { ib_b200_set_error(IBCU_ERR_STATE, "ib_b200_pq_lm_head_topk before ib_b200_init"); return -1; }
+    pq_entry* e = pq_get(t);
+    if (!e) return -1;
+    void *hx, *dx, *ho, *dout;
+    const size_t xb = (size_t)t->N * sizeof(float), ob = (size_t)K_top * (sizeof(float) + sizeof(int32_t));
+    if (ib_b200_stage(0, xb, &hx, &dx) || ib_b200_stage(2, ob, &ho, &dout)) return -1;
+    memcpy(hx, x, xb);
+    int rc = ibcu_memcpy_h2d(g_ib.ctx, dx, hx, xb);
+    if (!rc) rc = ibcu_pq_lm_head_topk(g_ib.ctx, &e->dev, (const float*)dx, K_top, (float*)dout, (int32_t*)((float*)dout + K_top));
+    if (!rc) rc = ibcu_memcpy_d2h(g_ib.ctx, ho, dout, ob);
+    if (!rc) rc = ibcu_sync(g_ib.ctx);
+    if (ib_b200_check(rc, "ib_b200_pq_lm_head_topk")) return -1;
+    memcpy(out_logits, ho, (size_t)K_top * sizeof(float));
+    memcpy(out_token_ids, (const float*)ho + K_top, (size_t)K_top * sizeof(int32_t));
+    return 0;
+}
+int ib_b200_pq_lm_head_topk(const ib_b200_pq_tensor* t, const float* x, int K_top, float* out_logits, int32_t* out_token_ids) {
+    ib_b200_lock();
+    int r = pq_topk_unlocked(t, x, K_top, out_logits, out_token_ids);
+    ib_b200_unlock();
+    return r;
+}
+
 /* ── k-means ── */
 typedef struct { void *X, *C, *idx, *dist, *sums, *counts, *inertia; int owns_X; } km_bufs;
 

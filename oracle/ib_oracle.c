@@ -324,6 +324,137 @@ done:
     return rc;
 }
 
+/* ── top-K LM head (src/pq_decode.c:2085-2341) ──────────────────────────────────────── */
+
+typedef struct {
+    int M, N, G, K, K_l2, C, half, n_outlier, two, packed;
+    const uint16_t *cb1_l, *cb1_r, *cb2_l, *cb2_r, *row_scale, *outlier_scale;
+    const uint8_t *idx1_l, *idx1_r, *idx2_l, *idx2_r;
+    const int32_t* outlier_cols;
+    const int8_t* outlier_sidecar;
+    int* inner;                                  /* [N - n_outlier] the columns that are not outlier columns, ascending */
+} pq_view;
+
+/* src/pq_decode.c:2085-2143 (ib_pq_matmul_fp32_l1_only): first level only, NO 1 % rule, row scale, then the
+ * outlier sidecar; per chunk one table per side, out[r] += TL[i] + TR[j] in chunk order. */
+static void pq_l1_only(const pq_view* v, const float* x, float* out, float* tl, float* tr, float* ent, int fused) {
+    float xs[32];
+    memset(out, 0, (size_t)v->M * sizeof(float));
+    for (int c = 0; c < v->C; c++) {
+        for (int i = 0; i < v->G; i++) xs[i] = x[v->inner[c * v->G + i]];
+        for (int k = 0; k < v->K; k++) {
+            for (int i = 0; i < v->half; i++) ent[i] = ibo_fp16_to_fp32(v->cb1_l[k * v->half + i]);
+            tl[k] = dot_seq(ent, xs, v->half, fused);
+            for (int i = 0; i < v->half; i++) ent[i] = ibo_fp16_to_fp32(v->cb1_r[k * v->half + i]);
+            tr[k] = dot_seq(ent, xs + v->half, v->half, fused);
+        }
+        for (int r = 0; r < v->M; r++)
+            out[r] += tl[v->idx1_l[(size_t)r * v->C + c]] + tr[v->idx1_r[(size_t)r * v->C + c]];
+    }
+    for (int r = 0; r < v->M; r++) out[r] *= ibo_fp16_to_fp32(v->row_scale[r]);
+    for (int j = 0; j < v->n_outlier; j++) {                  /* apply_outliers, src/pq_decode.c:1394-1409 */
+        float os = ibo_fp16_to_fp32(v->outlier_scale[j]), xj = x[v->outlier_cols[j]];
+        for (int r = 0; r < v->M; r++) out[r] += ((float)v->outlier_sidecar[(size_t)r * v->n_outlier + j] * os) * xj;
+    }
+}
+
+/* src/pq_decode.c:2145-2248 (ib_pq_matmul_fp32_subset): every level of one row, entry times activation added
+ * one product at a time in the order left[j], right[j] per j, level 1 then level 2 per chunk. */
+static float pq_row_full(const pq_view* v, const float* x, int r, int fused) {
+    const size_t l2_stride = v->packed ? (size_t)((v->C + 1) / 2) : (size_t)v->C;
+    float acc = 0.0f;
+    for (int c = 0; c < v->C; c++) {
+        const int base = c * v->G;
+        for (int lvl = 0; lvl < (v->two ? 2 : 1); lvl++) {
+            int a, b;
+            const uint16_t *cl, *cr;
+            if (lvl == 0) { a = v->idx1_l[(size_t)r * v->C + c]; b = v->idx1_r[(size_t)r * v->C + c]; cl = v->cb1_l; cr = v->cb1_r; }
+            else {
+                const uint8_t* jl = v->idx2_l + (size_t)r * l2_stride;
+                const uint8_t* jr = v->idx2_r + (size_t)r * l2_stride;
+                a = v->packed ? ((c & 1) ? (jl[c >> 1] >> 4) & 15 : jl[c >> 1] & 15) : jl[c];
+                b = v->packed ? ((c & 1) ? (jr[c >> 1] >> 4) & 15 : jr[c >> 1] & 15) : jr[c];
+                cl = v->cb2_l; cr = v->cb2_r;
+            }
+            for (int j = 0; j < v->half; j++) {
+                float el = ibo_fp16_to_fp32(cl[a * v->half + j]), er = ibo_fp16_to_fp32(cr[b * v->half + j]);
+                float xl = x[v->inner[base + j]], xr = x[v->inner[base + v->half + j]];
+                if (fused) { acc = fmaf(el, xl, acc); acc = fmaf(er, xr, acc); }
+                else { acc += el * xl; acc += er * xr; }
+            }
+        }
+    }
+    acc *= ibo_fp16_to_fp32(v->row_scale[r]);
+    for (int j = 0; j < v->n_outlier; j++) {
+        float w = (float)v->outlier_sidecar[(size_t)r * v->n_outlier + j] * ibo_fp16_to_fp32(v->outlier_scale[j]);
+        if (fused) acc = fmaf(w, x[v->outlier_cols[j]], acc); else acc += w * x[v->outlier_cols[j]];
+    }
+    return acc;
+}
+
+static void heap_sift_down(float* val, int32_t* id, int n, int i) {
+    for (;;) {
+        int l = 2 * i + 1, r = l + 1, m = i;
+        if (l < n && val[l] < val[m]) m = l;
+        if (r < n && val[r] < val[m]) m = r;
+        if (m == i) return;
+        float tv = val[i]; val[i] = val[m]; val[m] = tv;
+        int32_t ti = id[i]; id[i] = id[m]; id[m] = ti;
+        i = m;
+    }
+}
+
+/* src/pq_decode.c:2259-2341 (ib_pq_lm_head_topk): coarse logits from the first level over all rows; the K_top
+ * largest kept in a min-heap seeded with rows 0..K_top-1 (a later row replaces the root only when strictly
+ * larger); those rows refined with every level; insertion sort by refined logit, descending, which keeps the
+ * heap's order among equal logits. coarse_out (may be NULL) receives the M coarse logits. */
+int ibo_pq_lm_head_topk(int M, int N, int G, int K, int K_l2,
+                        const uint16_t* cb1_l, const uint16_t* cb1_r, const uint16_t* cb2_l, const uint16_t* cb2_r,
+                        const uint8_t* idx1_l, const uint8_t* idx1_r, const uint8_t* idx2_l, const uint8_t* idx2_r,
+                        const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
+                        const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
+                        const float* x, int K_top, float* out_logits, int32_t* out_ids, float* coarse_out, int fused) {
+    if (!cb1_l || !cb1_r || !idx1_l || !idx1_r || !row_scale || !x || !out_logits || !out_ids) return -1;
+    if (M <= 0 || N <= 0 || G <= 0 || (G & 1) || G > 32 || K <= 0 || K > 256 || n_outlier < 0 || (N - n_outlier) % G) return -1;
+    if (K_top <= 0 || K_top > M) return -1;
+    pq_view v;
+    memset(&v, 0, sizeof v);
+    v.M = M; v.N = N; v.G = G; v.K = K; v.K_l2 = K_l2; v.half = G / 2; v.n_outlier = n_outlier; v.C = (N - n_outlier) / G;
+    v.two = cb2_l && cb2_r && idx2_l && idx2_r;
+    if (v.two && (K_l2 <= 0 || K_l2 > 256)) return -1;
+    v.packed = v.two && K_l2 == 16;
+    v.cb1_l = cb1_l; v.cb1_r = cb1_r; v.cb2_l = cb2_l; v.cb2_r = cb2_r; v.row_scale = row_scale; v.outlier_scale = outlier_scale;
+    v.idx1_l = idx1_l; v.idx1_r = idx1_r; v.idx2_l = idx2_l; v.idx2_r = idx2_r; v.outlier_cols = outlier_cols; v.outlier_sidecar = outlier_sidecar;
+    int rc = -1;
+    unsigned char* mask = (unsigned char*)calloc((size_t)N, 1);
+    v.inner = (int*)malloc((size_t)(N - n_outlier) * sizeof(int));
+    float* coarse = (float*)malloc((size_t)M * sizeof(float));
+    float* tab = (float*)malloc((size_t)(2 * K + 32) * sizeof(float));
+    float* val = (float*)malloc((size_t)K_top * sizeof(float));
+    int32_t* id = (int32_t*)malloc((size_t)K_top * sizeof(int32_t));
+    if (!mask || !v.inner || !coarse || !tab || !val || !id) goto done;
+    for (int j = 0; j < n_outlier; j++) mask[outlier_cols[j]] = 1;
+    { int kk = 0; for (int j = 0; j < N; j++) if (!mask[j] && kk < N - n_outlier) v.inner[kk++] = j; }
+    pq_l1_only(&v, x, coarse, tab, tab + K, tab + 2 * K, fused);
+    if (coarse_out) memcpy(coarse_out, coarse, (size_t)M * sizeof(float));
+    for (int i = 0; i < K_top; i++) { id[i] = i; val[i] = coarse[i]; }
+    for (int s = K_top / 2 - 1; s >= 0; s--) heap_sift_down(val, id, K_top, s);
+    for (int j = K_top; j < M; j++)
+        if (coarse[j] > val[0]) { val[0] = coarse[j]; id[0] = j; heap_sift_down(val, id, K_top, 0); }
+    for (int i = 0; i < K_top; i++) val[i] = pq_row_full(&v, x, id[i], fused);
+    for (int i = 1; i < K_top; i++) {
+        float tv = val[i]; int32_t ti = id[i]; int j = i - 1;
+        while (j >= 0 && val[j] < tv) { val[j + 1] = val[j]; id[j + 1] = id[j]; j--; }
+        val[j + 1] = tv; id[j + 1] = ti;
+    }
+    memcpy(out_logits, val, (size_t)K_top * sizeof(float));
+    memcpy(out_ids, id, (size_t)K_top * sizeof(int32_t));
+    rc = 0;
+done:
+    free(mask); free(v.inner); free(coarse); free(tab); free(val); free(id);
+    return rc;
+}
+
 /* src/pq_decode.c:5008-5066 — encode of one K or V row into the PQ KV cache: per-vector scale max|v| / 7 (floor
  * 1e-12), normalise, nearest codeword per half chunk (distance accumulated in dimension order, strict '<').
  * PARITY UNPINNED: the reference has this only inline in its session step (no entry point to call), and its build

@@ -58,6 +58,15 @@ int ibo_pq_matmul_fp32_ex(int M, int N, int G, int K, int K_l2,
                           const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
                           const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
                           const float* x, float* out, int fused);
+/* src/pq_decode.c:2259-2341 (ib_pq_lm_head_topk) with its two helpers (:2085-2143 first level only, no 1 % rule;
+ * :2145-2248 every level of the chosen rows): ids and logits of the K_top rows with the largest first-level
+ * logits, ordered by their full logits, descending. coarse_out (may be NULL) receives the M first-level logits. */
+int ibo_pq_lm_head_topk(int M, int N, int G, int K, int K_l2,
+                        const uint16_t* cb1_l, const uint16_t* cb1_r, const uint16_t* cb2_l, const uint16_t* cb2_r,
+                        const uint8_t* idx1_l, const uint8_t* idx1_r, const uint8_t* idx2_l, const uint8_t* idx2_r,
+                        const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
+                        const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
+                        const float* x, int K_top, float* out_logits, int32_t* out_ids, float* coarse_out, int fused);
 /* src/pq_decode.c:5008-5066 — PQ KV cache encode of one vector (parity unpinned: no entry point in the reference). */
 void ibo_pqkv_encode(const float* vec, int dim, int G, int K1, const uint16_t* cb_l, const uint16_t* cb_r,
                      uint8_t* idx, float* scale, int fused);

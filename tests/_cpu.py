@@ -86,6 +86,8 @@ class Libs:
         o.ibo_pq_matmul_fp32.argtypes = [C.c_int] * 4 + [u16, u16, C.c_long, u8, u8, u16, f32, f32, C.c_int, C.POINTER(C.c_int)]
         o.ibo_pq_matmul_fp32_ex.restype = C.c_int
         o.ibo_pq_matmul_fp32_ex.argtypes = [C.c_int] * 5 + [C.c_void_p] * 9 + [C.c_int] + [C.c_void_p] * 5 + [C.c_int]
+        o.ibo_pq_lm_head_topk.restype = C.c_int
+        o.ibo_pq_lm_head_topk.argtypes = [C.c_int] * 5 + [C.c_void_p] * 9 + [C.c_int] + [C.c_void_p] * 4 + [C.c_int] + [C.c_void_p] * 3 + [C.c_int]
         o.ibo_pq_reconstruct_fp32.restype = C.c_int
         o.ibo_pq_reconstruct_fp32.argtypes = [C.c_int] * 4 + [u16, u16, u8, u8, u16, f32]
         o.ibo_kmeans_assign.argtypes = [f32, C.c_long, C.c_int, f32, C.c_int, i32, C.c_void_p, C.c_int]
@@ -112,6 +114,8 @@ class Libs:
             r.ib_kmeans_assign.argtypes = [f32, C.c_int, C.c_int, f32, C.c_int, i32, C.c_void_p]
             r.ib_pq_matmul_fp32.restype = C.c_int
             r.ib_pq_matmul_fp32.argtypes = [C.POINTER(RefPqTensor), f32, f32]
+            r.ib_pq_lm_head_topk.restype = C.c_int
+            r.ib_pq_lm_head_topk.argtypes = [C.POINTER(RefPqTensor), f32, C.c_int, f32, i32]
             r.ib_pq_matmul_fp32_threaded.restype = C.c_int
             r.ib_pq_matmul_fp32_threaded.argtypes = [C.POINTER(RefPqTensor), f32, f32, C.c_void_p]
             r.ib_pq_matmul_fp32_streaming.restype = C.c_int
@@ -182,6 +186,17 @@ def oracle_pq_ex(o, d, xb, fused=1):
                                  d["n_outlier"], _ptr(d, "ocols"), _ptr(d, "oside"), _ptr(d, "oscale"), xb.ctypes.data, out.ctypes.data, fused)
     assert rc == 0
     return out
+
+
+def oracle_pq_topk(o, d, xb, k_top, fused=1, want_coarse=False):
+    """(logits, ids[, coarse]) of the restated ib_pq_lm_head_topk over the arrays of make_pq_case_ex"""
+    logits = np.empty(k_top, np.float32); ids = np.empty(k_top, np.int32); coarse = np.empty(d["M"], np.float32)
+    rc = o.ibo_pq_lm_head_topk(d["M"], d["N"], d["G"], d["K"], d["K_l2"], _ptr(d, "cb1_l"), _ptr(d, "cb1_r"), _ptr(d, "cb2_l"), _ptr(d, "cb2_r"),
+                               _ptr(d, "idx1_l"), _ptr(d, "idx1_r"), _ptr(d, "idx2_l"), _ptr(d, "idx2_r"), _ptr(d, "rs"),
+                               d["n_outlier"], _ptr(d, "ocols"), _ptr(d, "oside"), _ptr(d, "oscale"), xb.ctypes.data, k_top,
+                               logits.ctypes.data, ids.ctypes.data, coarse.ctypes.data, fused)
+    assert rc == 0
+    return (logits, ids, coarse) if want_coarse else (logits, ids)
 
 
 def ref_pq_tensor_ex(d):

@@ -138,6 +138,28 @@ def test_pq_second_level_and_outliers(libs, M, N, G, K, K_l2, n_out):
         assert _cpu.close(a, r, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("M,N,G,K,K_l2,n_out,k_top", [(500, 256, 16, 256, 256, 0, 17), (300, 256, 16, 256, 16, 0, 1), (257, 272, 16, 64, 0, 16, 64),
+                                                     (400, 528, 16, 256, 16, 16, 400), (90, 104, 8, 32, 64, 8, 5)])
+def test_pq_lm_head_topk(libs, M, N, G, K, K_l2, n_out, k_top):
+    """Top-K LM head (src/pq_decode.c:2259-2341): the same token ids in the same order as the compiled reference, logits
+    to rounding (the reference's build decides where products and sums contract)."""
+    rng = np.random.default_rng(M + N + K_l2 + n_out + k_top)
+    d = _cpu.make_pq_case_ex(rng, M, N, G, K, K_l2, n_out, 1)
+    t = _cpu.ref_pq_tensor_ex(d)
+    xb = d["x"][0].copy()
+    xb[:2 * G] *= 1e-4                                        # would fall under the 1 % rule, which this path does not apply
+    rl = np.empty(k_top, np.float32); ri = np.empty(k_top, np.int32)
+    assert libs.ref.ib_pq_lm_head_topk(C.byref(t), xb, k_top, rl, ri) == 0
+    al, ai = _cpu.oracle_pq_topk(libs.oracle, d, xb, k_top)
+    assert np.array_equal(ai, ri)
+    assert _cpu.close(al, rl, rtol=1e-5, atol=1e-6)
+    assert np.all(np.diff(al) <= 0)
+    # bad arguments as the reference: K_top outside 1..M
+    assert libs.ref.ib_pq_lm_head_topk(C.byref(t), xb, 0, rl, ri) == -1
+    assert libs.oracle.ibo_pq_lm_head_topk(M, N, G, K, K_l2, None, None, None, None, None, None, None, None, None, 0, None, None, None,
+                                           xb.ctypes.data, M + 1, al.ctypes.data, ai.ctypes.data, None, 1) == -1
+
+
 def _near_tie_points(rng, D, N):
     Cn = (rng.standard_normal((2, D)) * 0.02).astype(np.float32)
     mid = (Cn[0].astype(np.float64) + Cn[1]) / 2

@@ -57,6 +57,73 @@ def test_pq_second_level_and_outliers(backend, cpu_libs, M, N, G, K, K_l2, n_out
     assert np.array_equal(got, got2)
 
 
+@pytest.mark.parametrize("M,N,G,K,K_l2,n_out,k_top", [
+    (32000, 4096, 16, 256, 16, 0, 64),     # LM head of the 7B shape, 16-entry second level
+    (32000, 4096 + 32, 16, 256, 256, 32, 256),
+    (5000, 1024, 16, 256, 0, 0, 1024),     # single level: the full logits are the first-level ones
+    (300, 8 * 13 + 5, 8, 32, 64, 5, 1), (40, 96, 4, 16, 16, 0, 40),
+    (40000, 256, 16, 256, 16, 0, 100),     # more rows than the selection keeps in registers
+])
+def test_pq_lm_head_topk(backend, cpu_libs, M, N, G, K, K_l2, n_out, k_top):
+    """ib_pq_lm_head_topk (src/pq_decode.c:2259-2341) against its restatement, which is pinned to the compiled reference: the
+    same rows in the same order wherever neighbouring logits differ by more than rounding, logits within tolerance."""
+    rng = np.random.default_rng(M + N + K_l2 + n_out + k_top)
+    d = _cpu.make_pq_case_ex(rng, M, N, G, K, K_l2, n_out, 1)
+    x = d["x"][0].copy()
+    x[:3 * G] *= 1e-4                                         # would fall under the 1 % rule, which this path does not apply
+    t = backend.make_pq_ex(d)
+    gl, gi = backend.pq_lm_head_topk(t, x, k_top)
+    wl, wi, coarse = _cpu.oracle_pq_topk(cpu_libs.oracle, d, x, k_top, want_coarse=True)
+    assert np.all(np.diff(gl) <= 0) and len(set(gi.tolist())) == k_top
+    # the chosen set: equal, except for rows whose first-level logit sits within rounding of the boundary
+    kth = np.sort(coarse)[-k_top]
+    margin = 1e-4 * max(1.0, float(np.max(np.abs(coarse))))
+    sure = set(np.flatnonzero(coarse > kth + margin).tolist())
+    maybe = set(np.flatnonzero(coarse >= kth - margin).tolist())
+    assert sure <= set(gi.tolist()) <= maybe and sure <= set(wi.tolist())
+    # full logits of the rows both chose, and their order
+    full = dict(zip(wi.tolist(), wl.tolist()))
+    both = [(i, v) for i, v in zip(gi.tolist(), gl.tolist()) if i in full]
+    assert len(both) >= len(sure)
+    assert _cpu.close(np.array([v for _, v in both], np.float32), np.array([full[i] for i, _ in both], np.float32), RTOL, ATOL)
+    if set(gi.tolist()) == set(wi.tolist()):                 # a row whose logit is clear of both neighbours sits at the same place
+        tol = 2 * (ATOL + RTOL * np.abs(wl))
+        clear = np.ones(k_top, bool)
+        clear[1:] &= np.abs(np.diff(wl)) > tol[1:]
+        clear[:-1] &= np.abs(np.diff(wl)) > tol[:-1]
+        assert np.array_equal(gi[clear], wi[clear])
+    gl2, gi2 = backend.pq_lm_head_topk(t, x, k_top)          # scratch left clean, same bits again
+    assert np.array_equal(gl, gl2) and np.array_equal(gi, gi2)
+    full_mv = backend.pq_matmul(t, d["x"][0])                 # the matvec still works after the first-level-only launch
+    assert _cpu.close(full_mv[0], _cpu.oracle_pq_ex(cpu_libs.oracle, d, d["x"][0]), RTOL, ATOL)
+    assert backend.lib.ibcu_pq_lm_head_topk(backend.ctx, C.byref(t), backend.upload(x).ptr, 0, 1, 1) == -1
+    backend.lib.ibcu_clear_error(backend.ctx)
+
+
+def test_pq_lm_head_topk_through_the_host_layer(cpu_libs):
+    """ib_b200_pq_lm_head_topk takes the reference's own struct and host pointers."""
+    from libinferbit_b200 import _ffi
+    host = _ffi.load_host()
+    assert host.ib_b200_init(0) == 0, host.ib_b200_last_error()
+    try:
+        rng = np.random.default_rng(21)
+        d = _cpu.make_pq_case_ex(rng, 2000, 1024 + 16, 16, 256, 16, 16, 1)
+        t = _cpu.ref_pq_tensor_ex(d)
+        k_top = 32
+        gl = np.empty(k_top, np.float32); gi = np.empty(k_top, np.int32)
+        x = d["x"][0]
+        host.ib_b200_pq_lm_head_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]   # the reference's struct as it is
+        assert host.ib_b200_pq_lm_head_topk(C.byref(t), x.ctypes.data, k_top, gl.ctypes.data, gi.ctypes.data) == 0, host.ib_b200_last_error()
+        wl, wi = _cpu.oracle_pq_topk(cpu_libs.oracle, d, x, k_top)
+        assert set(gi.tolist()) == set(wi.tolist()) and np.all(np.diff(gl) <= 0)
+        order = {i: v for i, v in zip(wi.tolist(), wl.tolist())}
+        assert _cpu.close(gl, np.array([order[i] for i in gi.tolist()], np.float32), RTOL, ATOL)
+        assert host.ib_b200_pq_lm_head_topk(C.byref(t), x.ctypes.data, 0, gl.ctypes.data, gi.ctypes.data) == -1
+        assert host.ib_b200_pq_lm_head_topk(C.byref(t), x.ctypes.data, 2001, gl.ctypes.data, gi.ctypes.data) == -1
+    finally:
+        host.ib_b200_shutdown()
+
+
 def test_pq_extras_through_the_host_layer(cpu_libs):
     """ib_b200_pq_matmul_fp32 takes the reference's own struct with two levels and outliers (host pointers)."""
     from libinferbit_b200 import _ffi
