@@ -13,7 +13,7 @@ __global__ void __launch_bounds__(256) embed_rows_kernel(const void* __restrict_
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
-    const int tok = tokens[b];
+    const int tok = __ldcg(tokens + b);             // past L1 and not as a read-only load: a kernel just ahead may have written it, and this one starts before that one ends
     const float s = BITS == 16 ? 1.0f : __half2float(scale[tok]);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
         float v;
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(32 * ATT_GMAX) attn_partial_kernel(const float
     pdl_wait();
     gather_wait(gw);                                // q, k, v may be rows that peers pushed
     if (pos0_ptr) {                                 // position read on the device: the same launch serves every position
-        pos0 = *pos0_ptr;
+        pos0 = __ldcg(pos0_ptr);
         att_plan(pos0 + (int)gridDim.z, want, chunk_cap, chunk, nsplit);
     }
     const int kvh = blockIdx.x, sp = blockIdx.y, b = blockIdx.z, pos = pos0 + b;
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
     extern __shared__ __align__(16) float cs[];      // the head's chunk results: [nsplit][hd + 4], then weights [nsplit]
     pdl_launch_dependents();
     pdl_wait();
-    if (pos0_ptr) { int chunk; att_plan(*pos0_ptr + (int)gridDim.y, want, chunk_cap, chunk, nsplit); }
+    if (pos0_ptr) { int chunk; att_plan(__ldcg(pos0_ptr) + (int)gridDim.y, want, chunk_cap, chunk, nsplit); }
     const int h = blockIdx.x, b = blockIdx.y;
     const int pstride = hd + 4, total = nsplit * pstride, total4 = total / 4;
     const float4* src = reinterpret_cast<const float4*>(part + ((size_t)b * n_heads + h) * (size_t)part_rows * pstride);

@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) assign_exact_kernel(const float* __restri
     const int d_all = DT > 0 ? DT : D;
     for (int i = threadIdx.x; i < K * d_all; i += blockDim.x) cs[i] = C[i];
     __syncthreads();
-    const long total = todo ? (long)*n_todo : N;
+    const long total = todo ? (long)__ldcg(n_todo) : N;    // written by the kernel just ahead: read past L1, not as a read-only load
     for (long w = (long)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (long)gridDim.x * blockDim.x) {
         const long i = todo ? (long)todo[w] : w;
         float x[DT > 0 ? DT : KM_MAX_D];
