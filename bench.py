@@ -9,8 +9,9 @@ q and o 4096x4096, k and v 1024x4096, per-row FP16 scales, one FP32 activation (
 one pass over one layer's four projections (q, k, v in one launch sharing the activation, then o);
 consecutive steps walk a ring of distinct weight sets larger than L2, so every byte comes from HBM.
 metric = weight GB/s = algorithmic bytes of a step / device time of a step.
-With N > 1 the output rows of every projection are split over the ranks and all-gathered with NCCL
-(total work fixed: strong scaling).
+With N > 1 the output rows of every projection are split over the ranks and gathered through the peer
+window (tagged stores from the producing kernel's epilogue into every peer's memory, received in the next
+kernel's prologue; NCCL is the plumbing and the comparison line) — total work fixed: strong scaling.
 
 The JSON line also carries, under "other", quick measurements of the other configurations (INT4,
 PQ, k-means, 7B-shape decode step); they are context, not the headline.
