@@ -316,7 +316,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-other", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--case", default=None, help="run one small secondary case alone (for profiler captures): "
-                    "int8_4096x4096_b1, int8_4096x4096_b16, int8_32000x4096_b1, int4_14336x4096_b1, int4_5632x2048_b1, pq_4096x14336_b1, pq_4096x14336_b8, pq_topk_32000x4096_k64, "
+                    "int8_4096x4096_b1, int8_4096x4096_b16, int8_32000x4096_b1, int4_14336x4096_b1, int4_5632x2048_b1, pq_4096x14336_b1, pq_4096x14336_b8, pq_topk_32000x4096_k64, int4g_4096x4096_g128_b1, int4g_14336x4096_g128_b1, "
                     "kmeans_4Mx8_k256, decode_7b_b1, decode_7b_b1_eager (launches issued one by one, for per-kernel profiles)")
     args = ap.parse_args()
     rank, world, local, dist = dist_setup(args.gpus)
@@ -376,6 +376,8 @@ def main():
             "int4_5632x2048_b1": lambda: bs._linear_ring(lib, ctx, 4, 5632, 2048, 1, reps_target_bytes=300e6),
             "pq_4096x14336_b1": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 1),
             "pq_4096x14336_b8": lambda: bs._pq(lib, ctx, 4096, 14336, 16, 256, 8),
+            "int4g_4096x4096_g128_b1": lambda: bs._int4g(lib, ctx, 4096, 4096, 128),
+            "int4g_14336x4096_g128_b1": lambda: bs._int4g(lib, ctx, 14336, 4096, 128),
             "pq_topk_32000x4096_k64": lambda: bs._pq_topk(lib, ctx, 32000, 4096, 16, 256, 16, 64),
             "kmeans_4Mx8_k256": lambda: bs._kmeans(lib, ctx, 0, 1, lambda v: v, sync, iters=2),
             "decode_7b_b1": lambda: bs._decode(lib, host, ctx, 1, 0, 1, lambda v: v, sync, steps=3),

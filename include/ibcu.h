@@ -234,6 +234,25 @@ int ibcu_pq_lm_head_topk(ibcu_ctx* ctx, const ibcu_pq_t* t, const float* x, int 
 int ibcu_pqkv_encode(ibcu_ctx* ctx, const float* vec, int dim, int n_vec, int G, int K1,
                      const uint16_t* cb_l, const uint16_t* cb_r, uint8_t* idx, float* scale);
 
+/* ── group-scaled INT4 matvec ────────────────────────────────────────────────────────── */
+/* The INT4 tensors of the reference's session engine (struct ib_int4_tensor, src/pq_decode.c:3474-3483; arithmetic of
+ * int4_matmul_rows_skip, :3565-3651; skip rule of build_skip_mask, :3854-3882). The reference has these only as static
+ * functions of that engine, so there is no entry point to mirror; the call below is this backend's form of them.
+ * q: [M * N/2] two columns per byte, low nibble = even column, value = nibble - 8; s: fp16 [M * N/G] one scale per row
+ * and group of G columns (G even, N % G == 0); optionally K_out outlier columns per row: outl_idx uint16 [M * K_out],
+ * outl_val fp16 [M * K_out]. All pointers are device pointers. */
+typedef struct {
+    int M, N, G, K_out;
+    const uint8_t*  q;
+    const uint16_t* s;
+    const uint16_t* outl_idx;
+    const uint16_t* outl_val;
+} ibcu_int4g_t;
+/* out[m] = sum_g s[m][g] * sum_{j in g} (nibble(m, j) - 8) * x[j]  +  sum_k outl_val[m][k] * x[outl_idx[m][k]].
+ * eps_act_rel > 0 leaves out the groups whose max|x| is at most eps_act_rel * max|x| (0 = the reference's default: none).
+ * One activation. FP32 sums are ordered differently from the reference's scalar loop: equal to rounding. */
+int ibcu_int4g_matmul_fp32(ibcu_ctx* ctx, const ibcu_int4g_t* t, const float* x, float* out, float eps_act_rel);
+
 /* ── k-means ─────────────────────────────────────────────────────────────────────────── */
 /* ib_kmeans_assign (src/pq_kmeans.h:70-74, src/pq_kmeans.c:399-413): idx[i] = nearest centroid of
  * X[i*D..], direct squared distance in the reference binary's rounding order, strict '<'.

@@ -182,6 +182,26 @@ class Backend:
         self.sync()
         return self.download(do, np.float32, B * t.M).reshape(B, t.M)
 
+    def int4g_matmul(self, q, s, G, x, outl_idx=None, outl_val=None, eps=0.0):
+        """group-scaled INT4 rows (ibcu_int4g_matmul_fp32): q [M, N/2] uint8, s [M, N/G] fp16 bits, one activation"""
+        from ._ffi import Int4gT
+        q = np.ascontiguousarray(q, np.uint8); s = np.ascontiguousarray(s, np.uint16)
+        x = np.ascontiguousarray(x, np.float32).reshape(-1)
+        t = Int4gT()
+        t.M, t.N, t.G = q.shape[0], q.shape[1] * 2, G
+        keep = [self.upload(q), self.upload(s), self.upload(x)]
+        t.q, t.s = keep[0].ptr, keep[1].ptr
+        t.K_out = 0
+        if outl_idx is not None:
+            oi = np.ascontiguousarray(outl_idx, np.uint16); ov = np.ascontiguousarray(outl_val, np.uint16)
+            t.K_out = oi.shape[1]
+            keep += [self.upload(oi), self.upload(ov)]
+            t.outl_idx, t.outl_val = keep[3].ptr, keep[4].ptr
+        do = self.alloc(t.M * 4)
+        self._check(self.lib.ibcu_int4g_matmul_fp32(self.ctx, C.byref(t), keep[2].ptr, do.ptr, float(eps)))
+        self.sync()
+        return self.download(do, np.float32, t.M)
+
     def pq_lm_head_topk(self, t, x, k_top):
         """(logits[k_top], ids[k_top]) of ib_pq_lm_head_topk (src/pq_decode.c:2259-2341) for one activation"""
         x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)

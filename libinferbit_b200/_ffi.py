@@ -36,6 +36,12 @@ class PqT(C.Structure):
                 ("inner_cols", C.c_void_p)]
 
 
+class Int4gT(C.Structure):
+    """ibcu_int4g_t"""
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("G", C.c_int), ("K_out", C.c_int),
+                ("q", C.c_void_p), ("s", C.c_void_p), ("outl_idx", C.c_void_p), ("outl_val", C.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/ibcu.h declares
 IBCU_SYMBOLS = {
     "ibcu_ctx_create": (C.c_int, [C.c_int, c_void_pp]),
@@ -85,6 +91,7 @@ IBCU_SYMBOLS = {
     "ibcu_pq_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pqkv_encode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ibcu_pq_matmul_fp32_strided": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ibcu_int4g_matmul_fp32": (C.c_int, [C.c_void_p, C.POINTER(Int4gT), C.c_void_p, C.c_void_p, C.c_float]),
     "ibcu_pq_lm_head_topk": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ibcu_pq_matmul_fp32_noalloc": (C.c_int, [C.c_void_p, C.POINTER(PqT), C.c_void_p, C.c_void_p, C.c_int]),
     "ibcu_pq_noalloc_max_floats": (C.c_size_t, []),

@@ -337,6 +337,38 @@ def _pq(lib, ctx, M, N, G, K, B):
             "shape": {"M": M, "N": N, "G": G, "K": K, "B": B}}
 
 
+def _int4g(lib, ctx, M, N, G):
+    """group-scaled INT4 rows, one activation; a ring of tensors larger than L2"""
+    from ._ffi import Int4gT
+    dev = Dev(lib, ctx)
+    rng = np.random.default_rng(9)
+    wbytes, sbytes = M * N // 2, 2 * M * (N // G)
+    R = max(2, int(300e6 // (wbytes + sbytes)) + 1)
+    x = dev.upload(rng.standard_normal(N).astype(np.float32))
+    out = dev.alloc(M * 4)
+    ts = []
+    for r in range(R):
+        t = Int4gT()
+        t.M, t.N, t.G, t.K_out = M, N, G, 0
+        q = dev.alloc(wbytes); sc = dev.alloc(sbytes)
+        check(lib, ctx, lib.ibcu_fill_hash_bytes(ctx, q, wbytes, 500 + r))
+        check(lib, ctx, lib.ibcu_fill_hash_fp16_uniform(ctx, sc, M * (N // G), 600 + r, 0.002, 0.02))
+        t.q, t.s = q, sc
+        ts.append(t)
+
+    def run():
+        for t in ts:
+            check(lib, ctx, lib.ibcu_int4g_matmul_fp32(ctx, C.byref(t), x, out, 0.0))
+    gid = dev.graph(run)
+    dev.spin_up(lambda: lib.ibcu_graph_launch(ctx, gid))
+    ms = min(dev.timed(lambda: lib.ibcu_graph_launch(ctx, gid), reps=10) for _ in range(3)) / R
+    lib.ibcu_graph_destroy(ctx, gid)
+    dev.free_all()
+    algo = wbytes + sbytes + 4 * N + 4 * M
+    return {"us": ms * 1e3, "GBps": algo / ms / 1e6, "algorithmic_bytes": algo, "bound": "hbm",
+            "shape": {"bits": 4, "group": G, "M": M, "N": N, "B": 1}}
+
+
 def _pq_topk(lib, ctx, M, N, G, K, K_l2, k_top):
     """ib_pq_lm_head_topk on a two-level LM head: first-level matvec over all rows, choice of k_top rows, every level of
     those rows, order. Eight tensors' code planes (more than L2 together with their regrouped copies) are walked in a ring."""

@@ -455,6 +455,56 @@ done:
     return rc;
 }
 
+/* src/pq_decode.c:3565-3651 (int4_matmul_rows_skip, scalar form) with the skip mask of :3854-3882 (build_skip_mask;
+ * eps_act_rel <= 0 is the reference's default: no group is left out): group-scaled INT4 rows of the session engine.
+ * gacc += lo * x[j] + hi * x[j + 1] per byte, acc += scale * gacc per group, then the row's outlier columns.
+ * PARITY UNPINNED: static functions of the reference's session engine, reachable only through a model file of its
+ * own format; `fused` picks whether products and sums contract as an -mfma build may. */
+int ibo_int4g_matmul_fp32(int M, int N, int G, const uint8_t* q, const uint16_t* s, int K_out,
+                          const uint16_t* outl_idx, const uint16_t* outl_val, const float* x, float* out,
+                          float eps_act_rel, int fused) {
+    if (!q || !s || !x || !out || M <= 0 || N <= 0 || G <= 0 || (G & 1) || N % G || K_out < 0) return -1;
+    if (K_out > 0 && (!outl_idx || !outl_val)) return -1;
+    const int ng = N / G;
+    unsigned char* skip = NULL;
+    if (eps_act_rel > 0.0f) {
+        float xmax = 0.0f;
+        for (int j = 0; j < N; j++) { float a = fabsf(x[j]); if (a > xmax) xmax = a; }
+        const float thr = eps_act_rel * xmax;
+        skip = (unsigned char*)malloc((size_t)ng);
+        if (!skip) return -1;
+        for (int g = 0; g < ng; g++) {
+            float gm = 0.0f;
+            for (int j = 0; j < G; j++) { float a = fabsf(x[g * G + j]); if (a > gm) gm = a; }
+            skip[g] = gm <= thr;
+        }
+    }
+    for (int m = 0; m < M; m++) {
+        const uint8_t* qrow = q + (size_t)m * (N / 2);
+        float acc = 0.0f;
+        for (int g = 0; g < ng; g++) {
+            if (skip && skip[g]) continue;
+            const float scale = ibo_fp16_to_fp32(s[(size_t)m * ng + g]);
+            const float* xg = x + g * G;
+            float gacc = 0.0f;
+            for (int j = 0; j < G; j += 2) {
+                const uint8_t b = qrow[(g * G + j) / 2];
+                const float lo = (float)((int)(b & 0x0F) - 8), hi = (float)((int)(b >> 4) - 8);
+                if (fused) gacc += fmaf(lo, xg[j], hi * xg[j + 1]);
+                else gacc += lo * xg[j] + hi * xg[j + 1];
+            }
+            if (fused) acc = fmaf(scale, gacc, acc); else acc += scale * gacc;
+        }
+        for (int k = 0; k < K_out; k++) {
+            const float v = ibo_fp16_to_fp32(outl_val[(size_t)m * K_out + k]), xv = x[outl_idx[(size_t)m * K_out + k]];
+            if (fused) acc = fmaf(v, xv, acc); else acc += v * xv;
+        }
+        out[m] = acc;
+    }
+    free(skip);
+    return 0;
+}
+
 /* src/pq_decode.c:5008-5066 — encode of one K or V row into the PQ KV cache: per-vector scale max|v| / 7 (floor
  * 1e-12), normalise, nearest codeword per half chunk (distance accumulated in dimension order, strict '<').
  * PARITY UNPINNED: the reference has this only inline in its session step (no entry point to call), and its build

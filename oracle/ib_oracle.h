@@ -67,6 +67,11 @@ int ibo_pq_lm_head_topk(int M, int N, int G, int K, int K_l2,
                         const uint16_t* row_scale, int n_outlier, const int32_t* outlier_cols,
                         const int8_t* outlier_sidecar, const uint16_t* outlier_scale,
                         const float* x, int K_top, float* out_logits, int32_t* out_ids, float* coarse_out, int fused);
+/* src/pq_decode.c:3565-3651, :3854-3882 — group-scaled INT4 rows of the session engine (parity unpinned: static
+ * functions there, no entry point). eps_act_rel <= 0: no group is left out (the reference's default). */
+int ibo_int4g_matmul_fp32(int M, int N, int G, const uint8_t* q, const uint16_t* s, int K_out,
+                          const uint16_t* outl_idx, const uint16_t* outl_val, const float* x, float* out,
+                          float eps_act_rel, int fused);
 /* src/pq_decode.c:5008-5066 — PQ KV cache encode of one vector (parity unpinned: no entry point in the reference). */
 void ibo_pqkv_encode(const float* vec, int dim, int G, int K1, const uint16_t* cb_l, const uint16_t* cb_r,
                      uint8_t* idx, float* scale, int fused);

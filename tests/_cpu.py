@@ -86,6 +86,8 @@ class Libs:
         o.ibo_pq_matmul_fp32.argtypes = [C.c_int] * 4 + [u16, u16, C.c_long, u8, u8, u16, f32, f32, C.c_int, C.POINTER(C.c_int)]
         o.ibo_pq_matmul_fp32_ex.restype = C.c_int
         o.ibo_pq_matmul_fp32_ex.argtypes = [C.c_int] * 5 + [C.c_void_p] * 9 + [C.c_int] + [C.c_void_p] * 5 + [C.c_int]
+        o.ibo_int4g_matmul_fp32.restype = C.c_int
+        o.ibo_int4g_matmul_fp32.argtypes = [C.c_int] * 3 + [C.c_void_p] * 2 + [C.c_int] + [C.c_void_p] * 4 + [C.c_float, C.c_int]
         o.ibo_pq_lm_head_topk.restype = C.c_int
         o.ibo_pq_lm_head_topk.argtypes = [C.c_int] * 5 + [C.c_void_p] * 9 + [C.c_int] + [C.c_void_p] * 4 + [C.c_int] + [C.c_void_p] * 3 + [C.c_int]
         o.ibo_pq_reconstruct_fp32.restype = C.c_int
@@ -184,6 +186,28 @@ def oracle_pq_ex(o, d, xb, fused=1):
     rc = o.ibo_pq_matmul_fp32_ex(d["M"], d["N"], d["G"], d["K"], d["K_l2"], _ptr(d, "cb1_l"), _ptr(d, "cb1_r"), _ptr(d, "cb2_l"), _ptr(d, "cb2_r"),
                                  _ptr(d, "idx1_l"), _ptr(d, "idx1_r"), _ptr(d, "idx2_l"), _ptr(d, "idx2_r"), _ptr(d, "rs"),
                                  d["n_outlier"], _ptr(d, "ocols"), _ptr(d, "oside"), _ptr(d, "oscale"), xb.ctypes.data, out.ctypes.data, fused)
+    assert rc == 0
+    return out
+
+
+def make_int4g_case(rng, M, N, G, K_out=0):
+    """group-scaled INT4 rows: nibbles uniform, fp16 group scales, one activation, optional per-row outlier columns"""
+    q = rng.integers(0, 256, size=(M, N // 2), dtype=np.uint8)
+    s = fp16_bits(rng.uniform(0.002, 0.02, (M, N // G)))
+    x = rng.standard_normal(N).astype(np.float32)
+    oi = ov = None
+    if K_out:
+        oi = np.stack([rng.choice(N, K_out, replace=False) for _ in range(M)]).astype(np.uint16)
+        ov = fp16_bits(rng.standard_normal((M, K_out)) * 0.05)
+    return q, s, x, oi, ov
+
+
+def oracle_int4g(o, q, s, G, x, oi=None, ov=None, eps=0.0, fused=1):
+    M, N = q.shape[0], q.shape[1] * 2
+    out = np.empty(M, np.float32)
+    rc = o.ibo_int4g_matmul_fp32(M, N, G, q.ctypes.data, s.ctypes.data, 0 if oi is None else oi.shape[1],
+                                 None if oi is None else oi.ctypes.data, None if ov is None else ov.ctypes.data,
+                                 x.ctypes.data, out.ctypes.data, eps, fused)
     assert rc == 0
     return out
 

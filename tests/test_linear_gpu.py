@@ -354,3 +354,29 @@ def test_full_size_head_and_rows_longer_than_shared_memory(backend, cpu_libs, bi
     got = backend.linear(w, s16, x, bits)
     want = oracle_linear(cpu_libs, w, s16, x, bits)
     assert _cpu.close(got, want, RTOL, ATOL * max(1.0, float(np.abs(want).max()))), float(np.max(np.abs(got - want)))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,G,K_out,eps", [
+    (4096, 4096, 128, 0, 0.0),        # attention projection of the 7B shape, groups of 128
+    (5632, 2048, 64, 8, 0.0),         # TinyLlama up_proj shape with eight outlier columns per row
+    (4099, 14336, 32, 0, 0.0),        # rows not a multiple of the four a warp carries; rows longer than one pass of the lanes
+    (1000, 4096, 128, 16, 0.05),      # groups under 5 % of the largest activation are left out
+    (33, 96, 32, 3, 0.0), (40, 48, 16, 2, 0.0), (17, 200, 8, 0, 0.2),   # small shapes; the last two take the generic kernel
+])
+def test_group_scaled_int4_rows(backend, cpu_libs, M, N, G, K_out, eps):
+    """Group-scaled INT4 rows of the reference's session engine (src/pq_decode.c:3565-3651; skip rule :3854-3882) against
+    their restatement (parity unpinned: static functions in the reference), within the float bar."""
+    rng = np.random.default_rng(M + N + G + K_out)
+    q, s, x, oi, ov = _cpu.make_int4g_case(rng, M, N, G, K_out)
+    if eps:
+        x[: N // 4] *= 1e-3                                   # a quarter of the groups fall under the threshold
+    got = backend.int4g_matmul(q, s, G, x, oi, ov, eps)
+    want = _cpu.oracle_int4g(cpu_libs.oracle, q, s, G, x, oi, ov, eps)
+    assert _cpu.close(got, want, RTOL, ATOL), float(np.max(np.abs(got - want)))
+    if eps:                                                   # the rule is visible: without it the result differs
+        full = _cpu.oracle_int4g(cpu_libs.oracle, q, s, G, x, oi, ov, 0.0)
+        assert not np.array_equal(full, want)
+    assert np.array_equal(got, backend.int4g_matmul(q, s, G, x, oi, ov, eps))       # same bits again
+    # linearity at full size: f(2x) = 2 f(x) exactly (every product and sum scales by a power of two)
+    assert np.array_equal(backend.int4g_matmul(q, s, G, 2.0 * x, oi, ov, eps), 2.0 * got)
