@@ -636,6 +636,9 @@ def other_configs(lib, host, ctx, rank, world, dist, max_over_ranks, barrier, pe
         out["int8_head_32000x4096_b1"] = _linear_ring(lib, ctx, 8, 32000, 4096, 1)
         out["pq_down_4096x14336_b1"] = _pq(lib, ctx, 4096, 14336, 16, 256, 1)
         out["pq_down_4096x14336_b8"] = _pq(lib, ctx, 4096, 14336, 16, 256, 8)
+        out["pq_topk_head_32000x4096_k64"] = _pq_topk(lib, ctx, 32000, 4096, 16, 256, 16, 64)
+        out["int4_group128_4096x4096_b1"] = _int4g(lib, ctx, 4096, 4096, 128)
+        out["int4_group128_14336x4096_b1"] = _int4g(lib, ctx, 14336, 4096, 128)
     if world > 1:
         out["pq_down_4096x14336_b1_row_sharded"] = _pq_sharded(lib, ctx, rank, world, max_over_ranks, barrier, 4096, 14336, 16, 256, 1)
     out["kmeans_4Mx8_k256"] = _kmeans(lib, ctx, rank, world, max_over_ranks, barrier)
