@@ -91,9 +91,20 @@ typedef struct {
     void* _arena; size_t _arena_size; void* _mmap_base; size_t _mmap_size; int _owns_mmap;
 } ib_b200_pq_tensor;
 
-/* ib_pq_matmul_fp32: out[M] = W x. Single-level tensors without outlier columns; anything else
- * returns -1 (as the reference does for a bad argument). The tensor's arrays are copied to HBM on
- * first use and cached by the address of the struct; ib_b200_pq_release drops the copy. */
+/* Field-for-field copies of ib_pq_raw_tensor and ib_pq_multi (src/pq_decode.h:108-131): what the multi-tensor file
+ * reader fills (ib_pq_load_multi in include/inferbit_gpu.h). */
+typedef struct {
+    char* name; void* data; int dtype; int ndim; int shape[4]; size_t size_bytes; int _owns_data;
+} ib_b200_pq_raw_tensor;
+typedef struct {
+    int n; char** names; ib_b200_pq_tensor* tensors; void* _mmap_base; size_t _mmap_size;
+    int n_raw; ib_b200_pq_raw_tensor* raw_tensors; char* config_json;
+} ib_b200_pq_multi;
+
+/* ib_pq_matmul_fp32: out[M] = W x. One or two levels (second level: at most 256 entries, one-byte or 4-bit packed
+ * indices), optional int8 outlier sidecar, formats "l1", "l2", "l1_l2" (or none, for a struct filled by hand); the
+ * pyramid format and uint16 second-level indices return -1 (as the reference does for a bad argument). The tensor's
+ * arrays are copied to HBM on first use and cached by the address of the struct; ib_b200_pq_release drops the copy. */
 int  ib_b200_pq_matmul_fp32(const ib_b200_pq_tensor* t, const float* x, float* out);
 int  ib_b200_pq_matmul_fp32_threaded(const ib_b200_pq_tensor* t, const float* x, float* out, void* pool);
 int  ib_b200_pq_matmul_fp32_streaming(const ib_b200_pq_tensor* t, const float* x, float* out);

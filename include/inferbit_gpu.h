@@ -16,6 +16,7 @@
 #define INFERBIT_GPU_H
 #include <stddef.h>
 #include <stdint.h>
+#include "ib_b200.h"
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -78,6 +79,22 @@ IBG_API int         inferbit_model_default_bits(const inferbit_model* model);
 IBG_API size_t      inferbit_model_weight_memory(const inferbit_model* model);
 IBG_API size_t      inferbit_model_kv_memory(const inferbit_model* model);
 IBG_API size_t      inferbit_model_total_memory(const inferbit_model* model);
+
+/* ── product-quantised tensors from files (src/pq_decode.h:89-135, :189, :2259) ──────────
+ * The reference's loader names for its "IBF v5" files, filling the reference's own structs (ib_b200_pq_tensor and
+ * ib_b200_pq_multi are field-for-field ib_pq_tensor and ib_pq_multi), and its matvec names over the GPU:
+ * ib_pq_load_single reads the first tensor of a file, ib_pq_load_multi all of them with their names, the raw tensors
+ * and the free-form config object (as compact JSON text); both return 0, or -1 with the output zeroed, under the
+ * reference's checks (src/pq_decode.c:391-546). Arrays live in host memory owned by the struct until ib_pq_free /
+ * ib_pq_multi_free, which also drop the tensor's copy in HBM. Memory-mapped opening (ib_pq_open_mmap) is not provided:
+ * the arrays go to HBM on first use anyway. */
+IBG_API int  ib_pq_load_single(const char* path, ib_b200_pq_tensor* out);
+IBG_API void ib_pq_free(ib_b200_pq_tensor* t);
+IBG_API int  ib_pq_load_multi(const char* path, ib_b200_pq_multi* out);
+IBG_API void ib_pq_multi_free(ib_b200_pq_multi* m);
+IBG_API const ib_b200_pq_tensor* ib_pq_multi_find(const ib_b200_pq_multi* m, const char* name);
+IBG_API int  ib_pq_matmul_fp32(const ib_b200_pq_tensor* t, const float* x, float* out);
+IBG_API int  ib_pq_lm_head_topk(const ib_b200_pq_tensor* t, const float* x, int K_top, float* out_logits, int32_t* out_token_ids);
 
 #ifdef __cplusplus
 }

@@ -283,6 +283,13 @@ FRONT_SYMBOLS = {
     "inferbit_model_weight_memory": (_sz, [_vp]),
     "inferbit_model_kv_memory": (_sz, [_vp]),
     "inferbit_model_total_memory": (_sz, [_vp]),
+    "ib_pq_load_single": (_i, [C.c_char_p, _vp]),
+    "ib_pq_free": (None, [_vp]),
+    "ib_pq_load_multi": (_i, [C.c_char_p, _vp]),
+    "ib_pq_multi_free": (None, [_vp]),
+    "ib_pq_multi_find": (_vp, [_vp, C.c_char_p]),
+    "ib_pq_matmul_fp32": (_i, [_vp, _vp, _vp]),
+    "ib_pq_lm_head_topk": (_i, [_vp, _vp, _i, _vp, _vp]),
 }
 
 _libfront = None

@@ -47,7 +47,7 @@ static pq_entry* pq_get(const ib_b200_pq_tensor* t) {
     const int K2 = two ? (t->K_l2 > 0 ? t->K_l2 : t->K) : 0;                 /* src/pq_decode.c:1099-1101 */
     const int l2_bytes = t->l2_idx_bytes > 0 ? t->l2_idx_bytes : 1;
     if ((t->n_levels != 1 && t->n_levels != 2) || t->n_outlier < 0 || t->n_outlier >= t->N || t->G <= 0 || (t->G & 1) ||
-        (t->N - t->n_outlier) % t->G || t->K < 1 || t->K > 256 || t->format != 0 ||
+        (t->N - t->n_outlier) % t->G || t->K < 1 || t->K > 256 || t->format < 0 || t->format > 3 ||      /* 4: the pyramid format, other arithmetic */
         !t->codebook_l1_l || !t->codebook_l1_r || !t->indices_l1_l || !t->indices_l1_r || !t->row_scale ||
         (two && (K2 > 256 || (K2 != 16 && l2_bytes != 1) || !t->codebook_l2_l || !t->codebook_l2_r || !t->indices_l2_l || !t->indices_l2_r)) ||
         (t->n_outlier > 0 && (!t->outlier_cols || !t->outlier_sidecar || !t->outlier_scale))) {

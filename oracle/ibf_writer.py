@@ -58,3 +58,55 @@ def write_ibf(path, cfg, layers, head, emb, name="b200-parity-mini"):
         f.write(js)
         f.write(bytes((-(32 + len(js))) % 64))
         f.write(bytes(blob))
+
+
+def write_ibf_v5(path, tensors, raw_tensors=None, config=None, reserve_pad=64):
+    """Writes a product-quantised model file as the reference's readers take it (src/pq_decode.c:391-546, :726-852): 32-byte
+    preamble ("INFERBIT", version 5, header length), JSON header padded with spaces, then the blocks.
+    tensors: {name: dict(format=..., M, N, G, K, n_levels, K_l2=0, rotate=False, l2_packed_bits=0, n_outlier=0, blocks={key: ndarray})};
+    raw_tensors: {name: ndarray}; config: any JSON-able dict."""
+    dtype_names = {"float32": "float32", "float16": "float16", "int32": "int32", "int16": "int16", "int8": "int8", "uint8": "uint8", "uint16": "uint16"}
+    blobs, off = [], 0
+
+    def place(arr):
+        nonlocal off
+        b = np.ascontiguousarray(arr).tobytes()
+        at = off
+        blobs.append(b)
+        off += len(b)
+        pad = (-off) % 16
+        if pad:
+            blobs.append(bytes(pad)); off += pad
+        return {"offset": at, "size": len(b)}
+
+    header = {"tensors": {}}
+    for name, t in tensors.items():
+        tm = {"format": t["format"], "shape": [t["M"], t["N"]], "G": t["G"], "K": t["K"], "n_levels": t["n_levels"],
+              "rotate": bool(t.get("rotate", False)), "K_l2": t.get("K_l2", 0)}
+        if t.get("l2_packed_bits", 0):
+            tm["l2_packed_bits"] = t["l2_packed_bits"]
+        if t.get("n_outlier", 0):
+            tm["outlier"] = {"n_cols": t["n_outlier"]}
+        for key, arr in t["blocks"].items():
+            tm[key] = place(arr)
+        header["tensors"][name] = tm
+    if raw_tensors:
+        header["raw_tensors"] = {}
+        for name, arr in raw_tensors.items():
+            arr = np.ascontiguousarray(arr)
+            blk = place(arr)
+            header["raw_tensors"][name] = {"dtype": dtype_names[str(arr.dtype)], "shape": list(arr.shape), **blk}
+    if config is not None:
+        header["config"] = config
+    # the header names its own length through weight_data_start: reserve first, then fill in
+    header["weight_data_start"] = 0
+    reserve = len(json.dumps(header).encode()) + reserve_pad
+    header["weight_data_start"] = 32 + reserve
+    text = json.dumps(header).encode()
+    assert len(text) <= reserve
+    with open(path, "wb") as f:
+        f.write(b"INFERBIT" + struct.pack("<II", 5, reserve) + bytes(16))
+        f.write(text + b" " * (reserve - len(text)))
+        for b in blobs:
+            f.write(b)
+    return header

@@ -63,6 +63,49 @@ class RefPqTensor(C.Structure):
                 ("_mmap_base", C.c_void_p), ("_mmap_size", C.c_size_t), ("_owns_mmap", C.c_int)]
 
 
+class RefPqRaw(C.Structure):
+    """ib_pq_raw_tensor (src/pq_decode.h:108-116)"""
+    _fields_ = [("name", C.c_char_p), ("data", C.c_void_p), ("dtype", C.c_int), ("ndim", C.c_int), ("shape", C.c_int * 4),
+                ("size_bytes", C.c_size_t), ("_owns_data", C.c_int)]
+
+
+class RefPqMulti(C.Structure):
+    """ib_pq_multi (src/pq_decode.h:120-131)"""
+    _fields_ = [("n", C.c_int), ("names", C.POINTER(C.c_char_p)), ("tensors", C.POINTER(RefPqTensor)), ("_mmap_base", C.c_void_p),
+                ("_mmap_size", C.c_size_t), ("n_raw", C.c_int), ("raw_tensors", C.POINTER(RefPqRaw)), ("config_json", C.c_char_p)]
+
+
+def pq_file_tensor(d, fmt):
+    """the writer's description of the tensor that make_pq_case_ex made"""
+    blocks = {"codebook_l1_l": d["cb1_l"], "codebook_l1_r": d["cb1_r"], "indices_l1_l": d["idx1_l"], "indices_l1_r": d["idx1_r"], "row_scale": d["rs"]}
+    if d["K_l2"]:
+        blocks.update({"codebook_l2_l": d["cb2_l"], "codebook_l2_r": d["cb2_r"], "indices_l2_l": d["idx2_l"], "indices_l2_r": d["idx2_r"]})
+    if d["n_outlier"]:
+        blocks.update({"outlier_cols": d["ocols"], "outlier_sidecar": d["oside"], "outlier_scale": d["oscale"]})
+    return dict(format=fmt, M=d["M"], N=d["N"], G=d["G"], K=d["K"], n_levels=2 if d["K_l2"] else 1, K_l2=d["K_l2"],
+                n_outlier=d["n_outlier"], blocks=blocks)
+
+
+def pq_tensor_arrays(t):
+    """every array of a loaded ib_pq_tensor (either library's), as numpy copies keyed like the file's blocks"""
+    half, Cn = t.G // 2, t.C
+    K2 = t.K_l2 if t.K_l2 > 0 else t.K
+
+    def arr(ptr, dtype, n):
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(n * np.dtype(dtype).itemsize,)).view(dtype).copy() if ptr and n else None
+    out = {"codebook_l1_l": arr(t.codebook_l1_l, np.uint16, t.K * half), "codebook_l1_r": arr(t.codebook_l1_r, np.uint16, t.K * half),
+           "indices_l1_l": arr(t.indices_l1_l, np.uint8, t.M * Cn), "indices_l1_r": arr(t.indices_l1_r, np.uint8, t.M * Cn),
+           "row_scale": arr(t.row_scale, np.uint16, t.M)}
+    if t.n_levels == 2:
+        row = (Cn + 1) // 2 if K2 == 16 else Cn * (2 if t.l2_packed_bits > 0 else t.l2_idx_bytes)
+        out.update({"codebook_l2_l": arr(t.codebook_l2_l, np.uint16, K2 * half), "codebook_l2_r": arr(t.codebook_l2_r, np.uint16, K2 * half),
+                    "indices_l2_l": arr(t.indices_l2_l, np.uint8, t.M * row), "indices_l2_r": arr(t.indices_l2_r, np.uint8, t.M * row)})
+    if t.n_outlier > 0:
+        out.update({"outlier_cols": arr(t.outlier_cols, np.int32, t.n_outlier), "outlier_sidecar": arr(t.outlier_sidecar, np.int8, t.M * t.n_outlier),
+                    "outlier_scale": arr(t.outlier_scale, np.uint16, t.n_outlier)})
+    return out
+
+
 def build_oracle():
     subprocess.run(["make", "-s", "-C", ORACLE_DIR, "oracle"], check=True)
 
@@ -116,6 +159,9 @@ class Libs:
             r.ib_kmeans_assign.argtypes = [f32, C.c_int, C.c_int, f32, C.c_int, i32, C.c_void_p]
             r.ib_pq_matmul_fp32.restype = C.c_int
             r.ib_pq_matmul_fp32.argtypes = [C.POINTER(RefPqTensor), f32, f32]
+            r.ib_pq_load_single.restype = C.c_int; r.ib_pq_load_single.argtypes = [C.c_char_p, C.POINTER(RefPqTensor)]
+            r.ib_pq_load_multi.restype = C.c_int; r.ib_pq_load_multi.argtypes = [C.c_char_p, C.POINTER(RefPqMulti)]
+            r.ib_pq_free.argtypes = [C.POINTER(RefPqTensor)]; r.ib_pq_multi_free.argtypes = [C.POINTER(RefPqMulti)]
             r.ib_pq_lm_head_topk.restype = C.c_int
             r.ib_pq_lm_head_topk.argtypes = [C.POINTER(RefPqTensor), f32, C.c_int, f32, i32]
             r.ib_pq_matmul_fp32_threaded.restype = C.c_int

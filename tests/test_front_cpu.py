@@ -117,3 +117,107 @@ def test_valid_file_without_a_gpu_is_an_error_not_a_fallback(front, tmp_path):
     ibf_model.write_ibf(path)
     assert front.inferbit_load(path.encode(), None) is None
     assert "no usable B200" in _err(front)
+
+
+# ── product-quantised model files ("IBF v5"): ib_pq_load_single / ib_pq_load_multi ──
+def _v5_cases(tmp_path):
+    import numpy as np
+    from oracle import ibf_writer
+    from tests import _cpu
+    rng = np.random.default_rng(77)
+    ds = {"layers.0.down": _cpu.make_pq_case_ex(rng, 40, 256, 16, 256, 0, 0, 1),
+          "layers.0.gate": _cpu.make_pq_case_ex(rng, 33, 272, 16, 256, 16, 16, 1),      # 4-bit packed second level + outlier columns
+          "head": _cpu.make_pq_case_ex(rng, 24, 104, 8, 32, 64, 8, 1)}
+    fmts = {"layers.0.down": "pq2d_v1_l1", "layers.0.gate": "pq2d_v1_l1_l2", "head": "pq2d_v1_l1_l2"}
+    raws = {"tok_embeddings": rng.standard_normal((7, 5)).astype(np.float16), "norm": rng.standard_normal(11).astype(np.float32),
+            "ids": np.arange(6, dtype=np.int32)}
+    cfg = {"arch": "llama", "hidden": 256, "rope": {"theta": 10000.5, "scaled": False}, "names": ["a", "b\"c"], "none": None}
+    path = os.path.join(str(tmp_path), "m.ibf")
+    ibf_writer.write_ibf_v5(path, {k: _cpu.pq_file_tensor(d, fmts[k]) for k, d in ds.items()}, raws, cfg)
+    return path, ds, raws, cfg
+
+
+def _multi_as_dict(m):
+    import numpy as np
+    from tests import _cpu
+    out = {"tensors": {}, "raw": {}, "config": json.loads(m.config_json.decode()) if m.config_json else None}
+    for i in range(m.n):
+        t = m.tensors[i]
+        scal = {f: getattr(t, f) for f in ("M", "N", "G", "K", "K_l2", "n_levels", "rotate", "n_outlier", "format", "C", "l2_idx_bytes", "l2_packed_bits")}
+        out["tensors"][m.names[i].decode()] = (scal, _cpu.pq_tensor_arrays(t))
+    for i in range(m.n_raw):
+        r = m.raw_tensors[i]
+        data = np.ctypeslib.as_array(C.cast(r.data, C.POINTER(C.c_uint8)), shape=(r.size_bytes,)).copy()
+        out["raw"][r.name.decode()] = (r.dtype, r.ndim, list(r.shape)[:r.ndim], data)
+    return out
+
+
+def _same(a, b):
+    import numpy as np
+    assert a["config"] == b["config"] and a["tensors"].keys() == b["tensors"].keys() and list(a["tensors"]) == list(b["tensors"])
+    for k in a["tensors"]:
+        assert a["tensors"][k][0] == b["tensors"][k][0], k
+        for key, arr in a["tensors"][k][1].items():
+            assert np.array_equal(arr, b["tensors"][k][1][key]), (k, key)
+    assert list(a["raw"]) == list(b["raw"])
+    for k in a["raw"]:
+        assert a["raw"][k][:3] == b["raw"][k][:3] and np.array_equal(a["raw"][k][3], b["raw"][k][3])
+
+
+def test_pq_file_reader_matches_the_reference(front, tmp_path):
+    """ib_pq_load_multi / ib_pq_load_single of this library fill the reference's structs with what the compiled reference's
+    own readers produce from the same file (every scalar field, every array, names in file order, raw tensors, config), and
+    refuse the files the reference refuses."""
+    import numpy as np
+    from tests import _cpu
+    path, ds, raws, cfg = _v5_cases(tmp_path)
+    mine = _cpu.RefPqMulti()
+    assert front.ib_pq_load_multi(path.encode(), C.byref(mine)) == 0
+    got = _multi_as_dict(mine)
+    assert got["config"] == cfg and list(got["tensors"]) == list(ds)
+    for name, d in ds.items():                                # against what was written
+        scal, arrs = got["tensors"][name]
+        assert (scal["M"], scal["N"], scal["G"], scal["K"], scal["K_l2"], scal["n_outlier"], scal["C"]) == (d["M"], d["N"], d["G"], d["K"], d["K_l2"], d["n_outlier"], d["C"])
+        assert np.array_equal(arrs["indices_l1_l"], d["idx1_l"].reshape(-1)) and np.array_equal(arrs["row_scale"], d["rs"].reshape(-1))
+    for name, a in raws.items():
+        assert np.array_equal(got["raw"][name][3], np.frombuffer(a.tobytes(), np.uint8)) and got["raw"][name][2] == list(a.shape)
+    ref = _cpu.load().ref
+    if ref is not None:
+        theirs = _cpu.RefPqMulti()
+        assert ref.ib_pq_load_multi(path.encode(), C.byref(theirs)) == 0
+        _same(got, _multi_as_dict(theirs))
+        ref.ib_pq_multi_free(C.byref(theirs))
+    # the single-tensor reader takes the first tensor of the file
+    one = _cpu.RefPqTensor()
+    assert front.ib_pq_load_single(path.encode(), C.byref(one)) == 0
+    first = next(iter(ds))
+    assert np.array_equal(_cpu.pq_tensor_arrays(one)["indices_l1_r"], ds[first]["idx1_r"].reshape(-1)) and one.format == 1
+    found = front.ib_pq_multi_find(C.byref(mine), b"head")
+    assert found and C.cast(found, C.POINTER(_cpu.RefPqTensor)).contents.M == ds["head"]["M"]
+    assert not front.ib_pq_multi_find(C.byref(mine), b"nope")
+    front.ib_pq_free(C.byref(one))
+    assert one.M == 0 and not one._arena
+    front.ib_pq_multi_free(C.byref(mine))
+    assert mine.n == 0 and not mine.tensors
+    # files both refuse: truncated blocks, wrong version, a block of the wrong size, a second level outside {16, 64, K}
+    raw = open(path, "rb").read()
+    bad = {}
+    bad["truncated"] = raw[:len(raw) - 100]
+    bad["version"] = raw[:8] + struct.pack("<I", 4) + raw[12:]
+    hl = struct.unpack("<I", raw[12:16])[0]
+    hdr = json.loads(raw[32:32 + hl].decode())
+    h2 = json.loads(json.dumps(hdr)); h2["tensors"]["layers.0.down"]["row_scale"]["size"] += 2
+    h3 = json.loads(json.dumps(hdr)); h3["tensors"]["head"]["K_l2"] = 48
+    for key, h in (("size", h2), ("k_l2", h3)):
+        text = json.dumps(h).encode()
+        assert len(text) <= hl
+        bad[key] = raw[:32] + text + b" " * (hl - len(text)) + raw[32 + hl:]
+    for key, blob in bad.items():
+        p = os.path.join(str(tmp_path), key + ".ibf")
+        open(p, "wb").write(blob)
+        m = _cpu.RefPqMulti()
+        assert front.ib_pq_load_multi(p.encode(), C.byref(m)) == -1 and m.n == 0, key
+        if ref is not None:
+            t = _cpu.RefPqMulti()
+            assert ref.ib_pq_load_multi(p.encode(), C.byref(t)) == -1, key
+    assert front.ib_pq_load_single(b"/nonexistent/file.ibf", C.byref(one)) == -1 and front.ib_pq_load_single(None, C.byref(one)) == -1

@@ -129,3 +129,38 @@ def test_front_per_tensor_bit_widths(front, tmp_path, cpu_libs):
         assert front.inferbit_forward(m, p(toks[i:i + 1].copy()), 1, p(got), V) == 0, _err(front)
         assert _close_logits(got, want), (i, float(np.max(np.abs(got - want))))
     front.inferbit_free(m)
+
+
+def test_pq_tensors_from_a_file_run_on_the_gpu(front, cpu_libs, tmp_path):
+    """A product-quantised model file read by ib_pq_load_multi (the reference's name and struct) feeds ib_pq_matmul_fp32 and
+    ib_pq_lm_head_topk of the same library: a loaded tensor carries the file's format tag (1..3), which the host layer
+    takes; results against the restatement."""
+    from libinferbit_b200 import _ffi as ffi
+    from oracle import ibf_writer
+    host = ffi.load_host()
+    assert host.ib_b200_init(0) == 0, host.ib_b200_last_error()
+    try:
+        rng = np.random.default_rng(31)
+        ds = {"down": _cpu.make_pq_case_ex(rng, 512, 1024, 16, 256, 0, 0, 1),
+              "head": _cpu.make_pq_case_ex(rng, 3000, 512 + 16, 16, 256, 16, 16, 1)}
+        fmts = {"down": "pq2d_v1_l1", "head": "pq2d_v1_l1_l2"}
+        path = str(tmp_path / "pq.ibf")
+        ibf_writer.write_ibf_v5(path, {k: _cpu.pq_file_tensor(d, fmts[k]) for k, d in ds.items()})
+        m = _cpu.RefPqMulti()
+        assert front.ib_pq_load_multi(path.encode(), C.byref(m)) == 0
+        for name, d in ds.items():
+            t = front.ib_pq_multi_find(C.byref(m), name.encode())
+            assert t
+            x = d["x"][0]
+            out = np.empty(d["M"], np.float32)
+            assert front.ib_pq_matmul_fp32(t, x.ctypes.data, out.ctypes.data) == 0, host.ib_b200_last_error()
+            assert _cpu.close(out, _cpu.oracle_pq_ex(cpu_libs.oracle, d, x), 1e-3, 1e-4)
+        d = ds["head"]
+        gl = np.empty(20, np.float32); gi = np.empty(20, np.int32)
+        assert front.ib_pq_lm_head_topk(front.ib_pq_multi_find(C.byref(m), b"head"), d["x"][0].ctypes.data, 20, gl.ctypes.data, gi.ctypes.data) == 0
+        wl, wi = _cpu.oracle_pq_topk(cpu_libs.oracle, d, d["x"][0], 20)
+        assert set(gi.tolist()) == set(wi.tolist()) and np.all(np.diff(gl) <= 0)
+        front.ib_pq_multi_free(C.byref(m))                    # also drops the copies in HBM
+        assert m.n == 0
+    finally:
+        host.ib_b200_shutdown()
