@@ -36,8 +36,8 @@ def test_libinferbit_front_exports_every_declared_symbol():
     lib = _ffi.load_front()
     txt = open(os.path.join(ROOT, "include", "inferbit_gpu.h")).read()
     txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
-    names = sorted(set(re.findall(r"\b(inferbit_[a-z0-9_]+)\s*\(", txt)))
-    assert len(names) >= 23
+    names = sorted(set(re.findall(r"\b((?:inferbit|ib_pq)_[a-z0-9_]+)\s*\(", txt)))
+    assert len(names) >= 30 and "ib_pq_load_multi" in names
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(_ffi.FRONT_SYMBOLS) == names
