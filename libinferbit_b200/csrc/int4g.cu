@@ -19,6 +19,7 @@
 // reference's scalar loop and the activation is rounded to 2^-30 of its largest magnitude: equal to the reference within
 // the float bar, not bit for bit; f(2x) = 2 f(x) exactly.
 #include "common.cuh"
+#include <mutex>
 
 namespace {
 
@@ -265,12 +266,13 @@ extern "C" int ibcu_int4g_matmul_fp32(ibcu_ctx* ctx, const ibcu_int4g_t* t, cons
     const bool fast = (t->N & 31) == 0 && (t->G & 31) == 0 && smem <= 200 * 1024 &&
                       (((uintptr_t)t->q | (uintptr_t)x) & 15) == 0 && ((uintptr_t)t->s & 3) == 0;
     if (fast) {
-        static bool attr_set[64];
-        if (!attr_set[ctx->device & 63]) {
-            IBCU_CUDA(ctx, cudaFuncSetAttribute(int4g_kernel<4, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            IBCU_CUDA(ctx, cudaFuncSetAttribute(int4g_kernel<2, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            attr_set[ctx->device & 63] = true;
-        }
+        static std::once_flag once[64];                      // dynamic shared memory beyond 48 KB: opt in once per device
+        cudaError_t e = cudaSuccess;
+        std::call_once(once[ctx->device & 63], [&] {
+            e = cudaFuncSetAttribute(int4g_kernel<4, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(int4g_kernel<2, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        });
+        if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(int4g_kernel): %s", cudaGetErrorString(e));
         const int per_sm = smem <= 100 * 1024 ? 2 : 1;
         const int slots = ctx->sm_count * per_sm;
         // four rows per warp amortise the activation's limbs best; with few rows two per warp give every SM its blocks
