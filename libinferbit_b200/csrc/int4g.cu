@@ -25,7 +25,7 @@ namespace {
 
 constexpr int I4G_THREADS = 256;
 constexpr int I4G_WARPS = I4G_THREADS / 32;
-constexpr int I4G_STAGES = 4;                                // steps of a warp's ring of weights in shared memory
+constexpr int I4G_STAGES = 4;                                // steps of a warp's ring of weights in shared memory (a power of two)
 
 struct I4gParams {
     int M, N, G, K_out;
@@ -49,6 +49,10 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nchunk = p.N >> 5, ng = p.N / p.G, cpg = p.G >> 5;     // chunks per group
+    // group of a chunk: a shift when a group is a power-of-two number of chunks (runtime divisions in the step loop cost
+    // as many instructions as the dot products they index)
+    const int cpg_sh = (cpg & (cpg - 1)) == 0 ? 31 - __clz(cpg) : -1;
+    auto group_of = [&](int c) { return cpg_sh >= 0 ? c >> cpg_sh : c / cpg; };
     float* sxs = reinterpret_cast<float*>(xl + p.N);
     unsigned char* skip = reinterpret_cast<unsigned char*>(sxs + ((nchunk + 3) & ~3));     // keeps the ring behind it 16-byte aligned
     pdl_wait();
@@ -117,28 +121,33 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
     const int ntile = (p.M + ROWS - 1) / ROWS;
     const int my_tiles = tile0 < ntile ? (ntile - tile0 + tstride - 1) / tstride : 0;
     const int nstep = my_tiles * npass;
-    auto issue = [&](int q) {                                 // requests step q (nothing beyond the last step: an empty group keeps the count)
+    int iq = 0, ipass = 0, itile = tile0;                     // the step to request next, its pass and its tile
+    auto issue = [&]() {                                      // requests the next step (nothing beyond the last: an empty group keeps the count)
+        const int q = iq++;
         if (q < nstep) {
-            const int tile = tile0 + (q / npass) * tstride, c = lane + 32 * (q % npass);
-            const bool on = c < nchunk && !(p.eps > 0.0f && skip[c / cpg]);
-            const uint32_t dst = ring_s + (uint32_t)((q % STAGES) * STAGE_WORDS) * 4u;
+            const int tile = itile, c = lane + 32 * ipass;
+            if (++ipass == npass) { ipass = 0; itile += tstride; }
+            const int g = group_of(c < nchunk ? c : 0);
+            const bool on = c < nchunk && !(p.eps > 0.0f && skip[g]);
+            const uint32_t dst = ring_s + (uint32_t)((q & (STAGES - 1)) * STAGE_WORDS) * 4u;
 #pragma unroll
             for (int u = 0; u < ROWS; u++) {
                 const int r = min(tile * ROWS + u, p.M - 1);  // rows past the end repeat the last one and are not stored
                 const int cc = on ? c : 0;
                 const unsigned nb = on ? 16u : 0u;            // a chunk that is off is filled with zeros: scale 0 times 0
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst + (uint32_t)(u * 32 + lane) * 16u), "l"(wq + (size_t)r * nchunk + cc), "r"(nb) : "memory");
-                const uintptr_t sa = (uintptr_t)(p.s + (size_t)r * ng + cc / cpg) & ~(uintptr_t)3;
+                const uintptr_t sa = (uintptr_t)(p.s + (size_t)r * ng + (on ? g : 0)) & ~(uintptr_t)3;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" :: "r"(dst + (uint32_t)(ROWS * 32 * 4 + u * 32 + lane) * 4u), "l"(sa), "r"(on ? 4u : 0u) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 #pragma unroll
-    for (int q = 0; q < STAGES - 1; q++) issue(q);
+    for (int q = 0; q < STAGES - 1; q++) issue();
     float acc[ROWS];
+    int pass = 0, tile = tile0, stage = 0;
     for (int q = 0; q < nstep; q++) {
-        const int pass = q % npass, tile = tile0 + (q / npass) * tstride, r0 = tile * ROWS;
+        const int r0 = tile * ROWS;
         if (pass == 0) {
 #pragma unroll
             for (int u = 0; u < ROWS; u++) acc[u] = 0.0f;
@@ -146,7 +155,7 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
         asm volatile("cp.async.wait_group %0;" :: "n"(STAGES - 2) : "memory");
         __syncwarp();
         const int c = lane + 32 * pass;
-        const uint32_t* st = ring + (q % STAGES) * STAGE_WORDS;
+        const uint32_t* st = ring + stage * STAGE_WORDS;
         uint4 w[ROWS];
         float sc[ROWS];
 #pragma unroll
@@ -154,11 +163,11 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
             w[u] = reinterpret_cast<const uint4*>(st)[u * 32 + lane];
             const uint32_t pair = st[ROWS * 32 * 4 + u * 32 + lane];
             const int r = min(r0 + u, p.M - 1);
-            const bool hi = (((uintptr_t)(p.s + (size_t)r * ng + (c < nchunk ? c : 0) / cpg)) & 2) != 0;
+            const bool hi = (((uintptr_t)(p.s + (size_t)r * ng + group_of(c < nchunk ? c : 0))) & 2) != 0;
             sc[u] = __half2float(__ushort_as_half((unsigned short)(hi ? pair >> 16 : pair & 0xffffu)));
         }
         __syncwarp();                                         // every lane has taken its words: the stage may be refilled
-        issue(q + STAGES - 1);
+        issue();
         if (c < nchunk) {
             uint32_t xw[32];
 #pragma unroll
@@ -198,6 +207,8 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
                 if (lane == 0 && r0 + u < p.M) p.out[r0 + u] = t;
             }
         }
+        if (++pass == npass) { pass = 0; tile += tstride; }
+        stage = (stage + 1) & (STAGES - 1);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
