@@ -100,6 +100,30 @@ def test_pq_lm_head_topk(backend, cpu_libs, M, N, G, K, K_l2, n_out, k_top):
     backend.lib.ibcu_clear_error(backend.ctx)
 
 
+def test_pq_lm_head_topk_equal_logits(backend, cpu_libs):
+    """Rows with equal logits: the lowest rows are kept at the boundary and equal full logits come out in ascending row order,
+    which is also what the reference's heap and stable insertion sort give when every row is equal."""
+    rng = np.random.default_rng(5)
+    d = _cpu.make_pq_case_ex(rng, 3000, 256, 16, 256, 16, 0, 1)
+    for key in ("idx1_l", "idx1_r", "idx2_l", "idx2_r"):
+        d[key][:] = d[key][0]                                 # every row is row 0
+    d["rs"][:] = d["rs"][0]
+    t = backend.make_pq_ex(d)
+    gl, gi = backend.pq_lm_head_topk(t, d["x"][0], 7)
+    wl, wi = _cpu.oracle_pq_topk(cpu_libs.oracle, d, d["x"][0], 7)
+    assert np.array_equal(gi, np.arange(7)) and np.array_equal(wi, np.arange(7)) and np.all(gl == gl[0])
+    # two values: rows 100.. carry a larger scale, the boundary falls inside the smaller value's rows
+    half = d["rs"].copy(); half[:] = _cpu.fp16_bits(np.float32(0.5)); half[100:110] = _cpu.fp16_bits(np.float32(1.0))
+    d["rs"][:] = half
+    t2 = backend.make_pq_ex(d)
+    gl, gi = backend.pq_lm_head_topk(t2, d["x"][0], 14)
+    big = set(range(100, 110))
+    if _cpu.oracle_pq_topk(cpu_libs.oracle, d, d["x"][0], 1)[0][0] > 0:      # positive logits: the scaled rows lead, then the lowest of the rest
+        assert set(gi[:10].tolist()) == big and gi[10:].tolist() == [0, 1, 2, 3]
+    else:                                                     # negative logits: the scaled rows are the smallest and are not chosen
+        assert gi.tolist() == list(range(14))
+
+
 def test_pq_lm_head_topk_through_the_host_layer(cpu_libs):
     """ib_b200_pq_lm_head_topk takes the reference's own struct and host pointers."""
     from libinferbit_b200 import _ffi
