@@ -21,6 +21,7 @@
 // largest codebook magnitude and N. The block that arrives last for its rows (an arrival counter) reads the
 // accumulators back, leaves them zero for the next call, applies the row scale and stores.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <mutex>
 
 namespace {
@@ -926,40 +927,27 @@ __device__ __forceinline__ unsigned topk_key(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// One block. The K_top-th largest key by passes of 8-bit digit counts over (key - smallest key), from its highest set bit
-// down: counted from the smallest key the first digit already spreads the rows over the table (logits themselves share
-// their leading bits, and adds to a few shared counters queue behind one another), and later passes only touch the rows
-// of one digit. Then the rows above the threshold in any order and, of the rows equal to it, those with the lowest
-// indices: cand[0 .. K_top). The reference keeps the first row it met among equal first-level logits at the boundary
-// too (a later row replaces the heap's root only when strictly larger), but which equal rows survive inside its heap
-// depends on the heap's shape; equal logits at the boundary are a tie that callers cannot rely on either way.
-// REG: M <= 32 * 1024, every thread keeps its 32 keys in registers and the logits are read once.
-template <bool REG>
+// One block (the fallback for more rows than the cluster kernel below keeps in registers). The K_top-th largest key by
+// passes of 8-bit digit counts over (key - smallest key), from its highest set bit down: counted from the smallest key
+// the first digit already spreads the rows over the table (logits themselves share their leading bits, and adds to a
+// few shared counters queue behind one another), and later passes only touch the rows of one digit. Then the rows above
+// the threshold in any order and, of the rows equal to it, those with the lowest indices: cand[0 .. K_top). The
+// reference keeps the first row it met among equal first-level logits at the boundary too (a later row replaces the
+// heap's root only when strictly larger), but which equal rows survive inside its heap depends on the heap's shape;
+// equal logits at the boundary are a tie that callers cannot rely on either way.
 __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_kernel(const float* __restrict__ coarse, int M, int K_top, int32_t* __restrict__ cand) {
     __shared__ unsigned hist[256], red_lo[TOPK_THREADS / 32], red_hi[TOPK_THREADS / 32];
     __shared__ unsigned s_prefix, s_need, s_gt, s_eq_before, warp_tot[TOPK_THREADS / 32];
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int NREG = REG ? 32 : 1;
     const int nchunk = (M + TOPK_THREADS - 1) / TOPK_THREADS;
-    unsigned keys[NREG] = {};
-    auto key_at = [&](int j) -> unsigned {                    // key of row tid + 1024 j (REG: j is a constant after unrolling)
-        if (REG) return keys[j];
+    auto key_at = [&](int j) -> unsigned {                    // key of row tid + 1024 j
         const int i = tid + j * TOPK_THREADS;
         return i < M ? topk_key(__ldcg(coarse + i)) : 0u;
     };
     unsigned lo = 0xffffffffu, hi = 0u;
-    if (REG) {
-#pragma unroll
-        for (int j = 0; j < NREG; j++) {
-            const int i = tid + j * TOPK_THREADS;
-            keys[j] = i < M ? topk_key(__ldcg(coarse + i)) : 0u;
-            if (i < M) { lo = min(lo, keys[j]); hi = max(hi, keys[j]); }
-        }
-    } else {
-        for (int j = 0; j < nchunk; j++) if (tid + j * TOPK_THREADS < M) { const unsigned k = key_at(j); lo = min(lo, k); hi = max(hi, k); }
-    }
+    for (int j = 0; j < nchunk; j++) if (tid + j * TOPK_THREADS < M) { const unsigned k = key_at(j); lo = min(lo, k); hi = max(hi, k); }
     lo = __reduce_min_sync(0xffffffffu, lo); hi = __reduce_max_sync(0xffffffffu, hi);
     if (lane == 0) { red_lo[warp] = lo; red_hi[warp] = hi; }
     if (tid == 0) { s_prefix = 0u; s_need = (unsigned)K_top; }
@@ -973,15 +961,9 @@ __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_kernel(const floa
         if (tid < 256) hist[tid] = 0u;
         __syncthreads();
         const unsigned prefix = s_prefix, need0 = s_need, mask = top >= 32 ? 0u : 0xffffffffu << top;
-        auto count = [&](int j) {
+        for (int j = 0; j < nchunk; j++) {
             const unsigned k = key_at(j) - lo;
             if (tid + j * TOPK_THREADS < M && (k & mask) == prefix) atomicAdd(&hist[(k >> shift) & ((1u << width) - 1u)], 1u);
-        };
-        if (REG) {
-#pragma unroll
-            for (int j = 0; j < NREG; j++) count(j);
-        } else {
-            for (int j = 0; j < nchunk; j++) count(j);
         }
         __syncthreads();
         // counts from the top digit down, as running sums over 256 threads: the digit at which the sum reaches what is still needed
@@ -1008,7 +990,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_kernel(const floa
     if (tid == 0) { s_gt = 0u; s_eq_before = 0u; }
     __syncthreads();
     const int n_gt = K_top - (int)need_eq;
-    auto place = [&](int j) {
+    for (int j = 0; j < nchunk; j++) {
         const int i = j * TOPK_THREADS + tid;
         const unsigned k = key_at(j) - lo;
         const bool gt = i < M && k > T, eq = i < M && k == T;
@@ -1025,13 +1007,114 @@ __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_kernel(const floa
             if (tid == 0) { unsigned t = 0; for (int w = 0; w < TOPK_THREADS / 32; w++) t += warp_tot[w]; s_eq_before += t; }
             __syncthreads();
         }
-    };
-    if (REG) {
-#pragma unroll
-        for (int j = 0; j < NREG; j++) if (j < nchunk) place(j);
-    } else {
-        for (int j = 0; j < nchunk; j++) place(j);
     }
+}
+
+// The same selection by a cluster of eight blocks: a block keeps chunks rank, rank + 8, ... of 1024 rows (NREG keys per
+// thread), counts its digits in its own table, and every block adds the eight tables through distributed shared memory
+// and reaches the same decision. Places in cand: rows above the threshold first, then rows equal to it, both in index
+// order (counts per chunk, summed over the chunks ahead), so the list is the same from run to run. One block of 1024
+// threads takes about 20 us for 32000 rows, most of it barriers and shared-memory adds that wait for one another.
+constexpr int TOPK_CL = 8;
+template <int NREG>
+__global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_cluster_kernel(const float* __restrict__ coarse, int M, int K_top, int32_t* __restrict__ cand) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ unsigned hist[256], red_lo[TOPK_THREADS / 32], red_hi[TOPK_THREADS / 32], warp_tot[TOPK_THREADS / 32];
+    __shared__ unsigned s_lo, s_hi, s_prefix, s_need;
+    __shared__ unsigned cnt_gt[NREG], cnt_eq[NREG], all_gt[NREG * TOPK_CL], all_eq[NREG * TOPK_CL];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned rank = cluster.block_rank();
+    unsigned keys[NREG];
+    unsigned lo = 0xffffffffu, hi = 0u;
+#pragma unroll
+    for (int j = 0; j < NREG; j++) {
+        const int i = (j * TOPK_CL + (int)rank) * TOPK_THREADS + tid;      // chunk j * 8 + rank
+        keys[j] = i < M ? topk_key(__ldcg(coarse + i)) : 0u;
+        if (i < M) { lo = min(lo, keys[j]); hi = max(hi, keys[j]); }
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo); hi = __reduce_max_sync(0xffffffffu, hi);
+    if (lane == 0) { red_lo[warp] = lo; red_hi[warp] = hi; }
+    __syncthreads();
+    lo = __reduce_min_sync(0xffffffffu, red_lo[lane]); hi = __reduce_max_sync(0xffffffffu, red_hi[lane]);
+    if (tid == 0) { s_lo = lo; s_hi = hi; s_prefix = 0u; s_need = (unsigned)K_top; }
+    cluster.sync();
+    for (unsigned r = 0; r < (unsigned)TOPK_CL; r++) {        // a block without rows leaves lo = all ones, hi = 0
+        lo = min(lo, *cluster.map_shared_rank(&s_lo, r));
+        hi = max(hi, *cluster.map_shared_rank(&s_hi, r));
+    }
+    int shift = hi >= lo ? 32 - __clz(hi - lo) : 0;           // bits of (key - lo) in use; 0 when all keys are equal
+    while (shift > 0) {                                       // the same number of rounds in every block: the barriers below are the cluster's
+        const int width = shift < 8 ? shift : 8;
+        const int top = shift;
+        shift -= width;
+        if (tid < 256) hist[tid] = 0u;
+        __syncthreads();
+        const unsigned prefix = s_prefix, need0 = s_need, mask = top >= 32 ? 0u : 0xffffffffu << top;
+#pragma unroll
+        for (int j = 0; j < NREG; j++) {
+            const int i = (j * TOPK_CL + (int)rank) * TOPK_THREADS + tid;
+            const unsigned k = keys[j] - lo;
+            if (i < M && (k & mask) == prefix) atomicAdd(&hist[(k >> shift) & ((1u << width) - 1u)], 1u);
+        }
+        cluster.sync();                                       // every block's table is complete
+        unsigned c = 0, incl = 0;
+        if (tid < 256) {
+            for (unsigned r = 0; r < (unsigned)TOPK_CL; r++) c += cluster.map_shared_rank(hist, r)[255 - tid];
+            incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const unsigned n = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += n; }
+            if (lane == 31) warp_tot[warp] = incl;
+        }
+        __syncthreads();
+        if (tid < 256) {
+            for (int w = 0; w < warp; w++) incl += warp_tot[w];
+            const unsigned excl = incl - c;
+            if (excl < need0 && need0 <= incl) {
+                s_need = need0 - excl;
+                s_prefix = prefix | ((unsigned)(255 - tid) << shift);
+            }
+        }
+        cluster.sync();                                       // nobody reads a table any more: it may be cleared for the next round
+    }
+    const unsigned T = s_prefix, need_eq = s_need;
+    const int n_gt = K_top - (int)need_eq;
+    // rows above the threshold and rows equal to it, per chunk
+    bool gt[NREG], eq[NREG];
+#pragma unroll
+    for (int j = 0; j < NREG; j++) {
+        const int i = (j * TOPK_CL + (int)rank) * TOPK_THREADS + tid;
+        const unsigned k = keys[j] - lo;
+        gt[j] = i < M && k > T; eq[j] = i < M && k == T;
+        const int ng = __syncthreads_count(gt[j]), ne = __syncthreads_count(eq[j]);
+        if (tid == 0) { cnt_gt[j] = (unsigned)ng; cnt_eq[j] = (unsigned)ne; }
+    }
+    cluster.sync();
+    if (tid < NREG * TOPK_CL) {                               // chunk c = j * 8 + r lives in block r, slot j
+        const unsigned r = (unsigned)tid % TOPK_CL, j = (unsigned)tid / TOPK_CL;
+        all_gt[tid] = cluster.map_shared_rank(cnt_gt, r)[j];
+        all_eq[tid] = cluster.map_shared_rank(cnt_eq, r)[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NREG; j++) {
+        const int cidx = j * TOPK_CL + (int)rank, i = cidx * TOPK_THREADS + tid;
+        if (all_gt[cidx] == 0 && all_eq[cidx] == 0) continue;                      // uniform over the block
+        unsigned before_gt = 0, before_eq = 0;
+        for (int c2 = 0; c2 < cidx; c2++) { before_gt += all_gt[c2]; before_eq += all_eq[c2]; }
+        const unsigned bg = __ballot_sync(0xffffffffu, gt[j]), be = __ballot_sync(0xffffffffu, eq[j]);
+        __syncthreads();                                      // warp_tot of the previous chunk has been read
+        if (lane == 0) warp_tot[warp] = (unsigned)__popc(bg) | ((unsigned)__popc(be) << 16);
+        __syncthreads();
+        unsigned wg = 0, we = 0;
+        for (int w = 0; w < warp; w++) { wg += warp_tot[w] & 0xffffu; we += warp_tot[w] >> 16; }
+        const unsigned lower = (1u << lane) - 1u;
+        if (gt[j]) { const unsigned slot = before_gt + wg + (unsigned)__popc(bg & lower); if ((int)slot < n_gt) cand[slot] = i; }
+        if (eq[j]) { const unsigned rk = before_eq + we + (unsigned)__popc(be & lower); if (rk < need_eq) cand[n_gt + (int)rk] = i; }
+    }
+    cluster.sync();                                           // no block leaves while another may still read its counts
 }
 
 // A block per chosen row: every level of the row, entry times activation (src/pq_decode.c:2145-2248), threads over the
@@ -1172,9 +1255,12 @@ extern "C" int ibcu_pq_lm_head_topk(ibcu_ctx* ctx, const ibcu_pq_t* t, const flo
     float* refined = (float*)(cand + TOPK_MAX);
     rc = pq_launch(ctx, t, x, coarse, t->M, 1, pl, (unsigned long long*)((char*)ctx->pq_acc + PQ_COUNTER_BYTES), (unsigned int*)ctx->pq_acc, true);
     if (rc) return rc;
-    rc = t->M <= 32 * TOPK_THREADS
-             ? ibcu_launch(ctx, pq_topk_select_kernel<true>, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand)
-             : ibcu_launch(ctx, pq_topk_select_kernel<false>, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand);
+    if (t->M <= 4 * TOPK_CL * TOPK_THREADS)
+        rc = ibcu_launch(ctx, pq_topk_select_cluster_kernel<4>, dim3(TOPK_CL), dim3(TOPK_THREADS), 0, TOPK_CL, true, (const float*)coarse, t->M, K_top, cand);
+    else if (t->M <= 32 * TOPK_CL * TOPK_THREADS)
+        rc = ibcu_launch(ctx, pq_topk_select_cluster_kernel<32>, dim3(TOPK_CL), dim3(TOPK_THREADS), 0, TOPK_CL, true, (const float*)coarse, t->M, K_top, cand);
+    else
+        rc = ibcu_launch(ctx, pq_topk_select_kernel, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand);
     if (rc) return rc;
     rc = ibcu_launch(ctx, pq_topk_subset_kernel, dim3(K_top), dim3(TOPK_SUB_THREADS), 0, 1, true, *t, pl.C, x, (const int32_t*)cand, K_top, refined);
     if (rc) return rc;

@@ -62,7 +62,8 @@ def test_pq_second_level_and_outliers(backend, cpu_libs, M, N, G, K, K_l2, n_out
     (32000, 4096 + 32, 16, 256, 256, 32, 256),
     (5000, 1024, 16, 256, 0, 0, 1024),     # single level: the full logits are the first-level ones
     (300, 8 * 13 + 5, 8, 32, 64, 5, 1), (40, 96, 4, 16, 16, 0, 40),
-    (40000, 256, 16, 256, 16, 0, 100),     # more rows than the selection keeps in registers
+    (40000, 256, 16, 256, 16, 0, 100),     # more rows than four keys per thread of the cluster: its 32-key instance
+    (270000, 32, 16, 256, 0, 0, 50),       # more rows than the cluster keeps in registers: the one-block selection
 ])
 def test_pq_lm_head_topk(backend, cpu_libs, M, N, G, K, K_l2, n_out, k_top):
     """ib_pq_lm_head_topk (src/pq_decode.c:2259-2341) against its restatement, which is pinned to the compiled reference: the
