@@ -115,8 +115,8 @@ class CpuBaseline:
                 subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "oracle"], check=True)
             self.kind, self.lib, self.threads = "port", C.CDLL(port), 1
 
-    def _base(self, value, unit, sample):
-        return {"value": value, "unit": unit, "cores": self.threads, "kind": self.kind, "sample": sample}
+    def _base(self, value, unit, sample, cores=None):
+        return {"value": value, "unit": unit, "cores": self.threads if cores is None else cores, "kind": self.kind, "sample": sample}
 
     def matvec_int8(self, out, w, s32, x, M, N):
         if self.kind == "reference":
@@ -201,6 +201,23 @@ class CpuBaseline:
         fn = lambda: [self.lib.ib_pq_matmul_fp32_threaded(C.byref(t), x.ctypes.data + 4 * b * N, out.ctypes.data + 4 * b * M, self.pool) for b in range(B)]
         tt, reps = _time_calls(fn, 1.5)
         return self._base(algo_bytes / tt / 1e9, "GB/s", f"best of {reps}: ib_pq_matmul_fp32_threaded x {B}")
+
+    def pq_topk(self, M, N, G, K, K_l2, k_top, algo_bytes):
+        if self.kind != "reference":
+            return None
+        sys.path.insert(0, ROOT)
+        from tests import _cpu
+        rng = np.random.default_rng(5)
+        d = _cpu.make_pq_case_ex(rng, M, N, G, K, K_l2, 0, 1)
+        t = _cpu.ref_pq_tensor_ex(d)
+        logits = np.empty(k_top, np.float32); ids = np.empty(k_top, np.int32)
+        self.lib.ib_pq_lm_head_topk.restype = C.c_int
+        self.lib.ib_pq_lm_head_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        x = d["x"][0]
+        fn = lambda: self.lib.ib_pq_lm_head_topk(C.byref(t), x.ctypes.data, k_top, logits.ctypes.data, ids.ctypes.data)
+        assert fn() == 0
+        tt, reps = _time_calls(fn, 1.5)
+        return self._base(algo_bytes / tt / 1e9, "GB/s", f"best of {reps}: ib_pq_lm_head_topk (one thread: the reference's top-K head has no pooled form)", cores=1)
 
     def kmeans_assign(self, N, D, K):
         if self.kind != "reference":
@@ -486,7 +503,11 @@ def main():
                 if not isinstance(e, dict):
                     continue
                 try:
-                    if name.startswith("w4a8_"):
+                    if name.startswith("int4_group"):
+                        e["cpu_baseline"] = None              # the reference has this matvec only as static functions of its session engine
+                    elif name.startswith("pq_topk_"):
+                        sh = e["shape"]; e["cpu_baseline"] = cpu.pq_topk(sh["M"], sh["N"], sh["G"], sh["K"], sh["K_l2"], sh["K_top"], e["algorithmic_bytes"])
+                    elif name.startswith("w4a8_"):
                         sh = e["shape"]; e["cpu_baseline"] = cpu.w4a8(sh["M"], sh["N"], sh["B"], e["algorithmic_bytes"])
                     elif name.startswith(("int4_", "int8_")):
                         sh = e["shape"]; e["cpu_baseline"] = cpu.linear(sh["bits"], sh["M"], sh["N"], sh["B"], e["algorithmic_bytes"])
