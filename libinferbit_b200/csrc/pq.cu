@@ -911,8 +911,8 @@ extern "C" int ibcu_pq_matmul_fp32_strided(ibcu_ctx* ctx, const ibcu_pq_t* t, co
 }
 
 // ── top-K LM head (src/pq_decode.c:2259-2341) ───────────────────────────────────────────
-// Four steps on the stream: the first-level matvec over all rows without the 1 % rule (the kernels above), the choice
-// of the K_top rows with the largest first-level logits, every level of those rows, and their order by full logit.
+// Three launches: the first-level matvec over all rows without the 1 % rule (the kernels above), the choice of the
+// K_top rows with the largest first-level logits, and every level of those rows, whose last block orders them by full logit.
 namespace {
 
 constexpr int TOPK_MAX = 1024;
@@ -1121,9 +1121,13 @@ __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_select_cluster_kernel(co
 // chunks so that the dependent reads (code, then codebook entry) of all chunks travel together; a fixed butterfly over
 // the lanes, the warps' sums added in warp order; row scale, then the outlier sidecar.
 constexpr int TOPK_SUB_THREADS = 128;
-__global__ void __launch_bounds__(TOPK_SUB_THREADS) pq_topk_subset_kernel(const ibcu_pq_t t, int C, const float* __restrict__ x, const int32_t* __restrict__ cand,
-                                                                          int K_top, float* __restrict__ refined) {
+__global__ void __launch_bounds__(TOPK_SUB_THREADS) pq_topk_subset_kernel(const ibcu_pq_t t, int C, const float* __restrict__ x, const int32_t* cand,
+                                                                          int K_top, float* refined, unsigned* done,
+                                                                          float* __restrict__ out_logits, int32_t* __restrict__ out_ids) {
     __shared__ float wsum[2][TOPK_SUB_THREADS / 32];
+    __shared__ float sv[TOPK_MAX];
+    __shared__ int32_t si[TOPK_MAX];
+    __shared__ int last_s;
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1192,21 +1196,18 @@ __global__ void __launch_bounds__(TOPK_SUB_THREADS) pq_topk_subset_kernel(const 
         float a = wsum[0][0], o = wsum[1][0];
         for (int w = 1; w < TOPK_SUB_THREADS / 32; w++) { a += wsum[0][w]; o += wsum[1][w]; }
         refined[blockIdx.x] = a * __half2float(reinterpret_cast<const __half*>(t.row_scale)[r]) + o;
+        // the block that finishes last orders the rows: by full logit, descending; equal logits by ascending row
+        __threadfence();
+        const unsigned n_done = atomicAdd(done, 1u);
+        last_s = n_done == gridDim.x - 1;
+        if (last_s) *done = 0u;                               // zero again for the next call
     }
-}
-
-// One block: the chosen rows by full logit, descending; equal logits by ascending row. Bitonic network over the next
-// power of two.
-__global__ void __launch_bounds__(TOPK_THREADS) pq_topk_sort_kernel(const float* __restrict__ refined, const int32_t* __restrict__ cand, int K_top,
-                                                                    float* __restrict__ out_logits, int32_t* __restrict__ out_ids) {
-    __shared__ float sv[TOPK_MAX];
-    __shared__ int32_t si[TOPK_MAX];
-    pdl_launch_dependents();
-    pdl_wait();
-    const int tid = threadIdx.x;
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
     int n = 1;
     while (n < K_top) n <<= 1;
-    if (tid < n) { sv[tid] = tid < K_top ? __ldcg(refined + tid) : -INFINITY; si[tid] = tid < K_top ? __ldcg(cand + tid) : 0x7fffffff; }
+    for (int e = tid; e < n; e += TOPK_SUB_THREADS) { sv[e] = e < K_top ? __ldcg(refined + e) : -INFINITY; si[e] = e < K_top ? __ldcg(cand + e) : 0x7fffffff; }
     __syncthreads();
     // a before b: larger logit, then smaller row; NaN logits go last
     auto before = [](float av, int32_t ai, float bv, int32_t bi) {
@@ -1215,20 +1216,22 @@ __global__ void __launch_bounds__(TOPK_THREADS) pq_topk_sort_kernel(const float*
         if (!an && av != bv) return av > bv;
         return ai < bi;
     };
-    for (int k = 2; k <= n; k <<= 1) {
+    for (int k = 2; k <= n; k <<= 1) {                        // bitonic network over the next power of two
         for (int j = k >> 1; j > 0; j >>= 1) {
-            const int p = tid ^ j;
-            if (tid < n && p > tid) {
-                const bool up = (tid & k) == 0;               // this pair sorts towards "before first"
-                const float av = sv[tid], bv = sv[p];
-                const int32_t ai = si[tid], bi = si[p];
-                const bool swap = up ? before(bv, bi, av, ai) : before(av, ai, bv, bi);
-                if (swap) { sv[tid] = bv; sv[p] = av; si[tid] = bi; si[p] = ai; }
+            for (int e = tid; e < n; e += TOPK_SUB_THREADS) {
+                const int p = e ^ j;
+                if (p > e) {
+                    const bool up = (e & k) == 0;             // this pair sorts towards "before first"
+                    const float av = sv[e], bv = sv[p];
+                    const int32_t ai = si[e], bi = si[p];
+                    const bool swap = up ? before(bv, bi, av, ai) : before(av, ai, bv, bi);
+                    if (swap) { sv[e] = bv; sv[p] = av; si[e] = bi; si[p] = ai; }
+                }
             }
             __syncthreads();
         }
     }
-    if (tid < K_top) { out_logits[tid] = sv[tid]; out_ids[tid] = si[tid]; }
+    for (int e = tid; e < K_top; e += TOPK_SUB_THREADS) { out_logits[e] = sv[e]; out_ids[e] = si[e]; }
 }
 
 }  // namespace
@@ -1262,9 +1265,10 @@ extern "C" int ibcu_pq_lm_head_topk(ibcu_ctx* ctx, const ibcu_pq_t* t, const flo
     else
         rc = ibcu_launch(ctx, pq_topk_select_kernel, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)coarse, t->M, K_top, cand);
     if (rc) return rc;
-    rc = ibcu_launch(ctx, pq_topk_subset_kernel, dim3(K_top), dim3(TOPK_SUB_THREADS), 0, 1, true, *t, pl.C, x, (const int32_t*)cand, K_top, refined);
-    if (rc) return rc;
-    return ibcu_launch(ctx, pq_topk_sort_kernel, dim3(1), dim3(TOPK_THREADS), 0, 1, true, (const float*)refined, (const int32_t*)cand, K_top, out_logits, out_ids);
+    // arrival counter of the row kernel: a slot of the counter area that no matvec launch uses (zero between calls)
+    unsigned* done = (unsigned int*)ctx->pq_acc + (PQ_COUNTER_BYTES / sizeof(unsigned) - 128);
+    return ibcu_launch(ctx, pq_topk_subset_kernel, dim3(K_top), dim3(TOPK_SUB_THREADS), 0, 1, true, *t, pl.C, x, (const int32_t*)cand, K_top, refined, done,
+                       out_logits, out_ids);
 }
 
 // ── PQ matvec without any allocation ────────────────────────────────────────────────────
