@@ -14,7 +14,7 @@
 // instructions per weight, 25 us for 14336 x 4096) this is 1.7 instructions per weight.
 // The limb words sit in shared memory per chunk as eight 16-byte pieces (piece 2 j + e: limbs 0..3 of the even (e = 0)
 // or odd columns of the chunk's j-th group of eight), rotated by chunk % 8 so that lanes reading consecutive chunks hit
-// different banks. A warp owns ROWS rows at a time; lane l takes chunks l, l + 32, ...; weights and scales come through a
+// different banks. A warp owns two rows at a time; lane l takes chunks l, l + 32, ...; weights and scales come through a
 // ring of asynchronous copies per warp, STAGES - 1 steps ahead of their use. A fixed butterfly adds the lanes. Sums are ordered differently from the
 // reference's scalar loop and the activation is rounded to 2^-30 of its largest magnitude: equal to the reference within
 // the float bar, not bit for bit; f(2x) = 2 f(x) exactly.
@@ -25,6 +25,7 @@ namespace {
 
 constexpr int I4G_THREADS = 256;
 constexpr int I4G_WARPS = I4G_THREADS / 32;
+constexpr int I4G_ROWS = 2;                                  // rows a warp carries through a pass over the columns
 constexpr int I4G_STAGES = 4;                                // steps of a warp's ring of weights in shared memory (a power of two)
 
 struct I4gParams {
@@ -273,26 +274,28 @@ extern "C" int ibcu_int4g_matmul_fp32(ibcu_ctx* ctx, const ibcu_int4g_t* t, cons
     p.q = t->q; p.s = (const __half*)t->s; p.outl_idx = t->outl_idx; p.outl_val = (const __half*)t->outl_val;
     p.x = x; p.out = out; p.eps = eps_act_rel;
     const size_t xbytes = (size_t)t->N * sizeof(float) + (((size_t)(t->N / 32) + 3) & ~(size_t)3) * sizeof(float) + (((size_t)(t->N / t->G) + 15) & ~(size_t)15);
-    const size_t smem = xbytes + (size_t)I4G_WARPS * I4G_STAGES * 4 * 32 * 5 * sizeof(uint32_t);       // the larger of the two instances' rings
+    const size_t smem = xbytes + (size_t)I4G_WARPS * I4G_STAGES * I4G_ROWS * 32 * 5 * sizeof(uint32_t);
     const bool fast = (t->N & 31) == 0 && (t->G & 31) == 0 && smem <= 200 * 1024 &&
                       (((uintptr_t)t->q | (uintptr_t)x) & 15) == 0 && ((uintptr_t)t->s & 3) == 0;
     if (fast) {
         static std::once_flag once[64];                      // dynamic shared memory beyond 48 KB: opt in once per device
         cudaError_t e = cudaSuccess;
         std::call_once(once[ctx->device & 63], [&] {
-            e = cudaFuncSetAttribute(int4g_kernel<4, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(int4g_kernel<2, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            e = cudaFuncSetAttribute(int4g_kernel<I4G_ROWS, I4G_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         });
         if (e != cudaSuccess) return ibcu_fail(ctx, IBCU_ERR_CUDA, "cudaFuncSetAttribute(int4g_kernel): %s", cudaGetErrorString(e));
-        const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+        // Two rows per warp (four measured slower on both benchmark shapes: 9.1 against 6.9 us and 15.0 against 14.3 us).
+        // With more tiles than two blocks per SM can take, three blocks share an SM; with fewer, the launch asks for more
+        // shared memory than it needs so that at most two do and the blocks spread over the SMs (256 blocks packed three
+        // to an SM: 8.3 us; two to an SM: 6.9 us).
+        const size_t ring = (size_t)I4G_WARPS * I4G_STAGES * I4G_ROWS * 32 * 5 * sizeof(uint32_t);
+        const size_t need = xbytes + ring;
+        const int tiles = (t->M + I4G_WARPS * I4G_ROWS - 1) / (I4G_WARPS * I4G_ROWS);
+        const bool crowd = tiles > 2 * ctx->sm_count && need <= 70 * 1024;
+        const size_t ask = crowd ? need : (need > 100 * 1024 ? need : 100 * 1024);
+        const int per_sm = crowd ? 3 : (ask <= 110 * 1024 ? 2 : 1);
         const int slots = ctx->sm_count * per_sm;
-        // four rows per warp amortise the activation's limbs best; with few rows two per warp give every SM its blocks
-        const bool four = (t->M + I4G_WARPS * 4 - 1) / (I4G_WARPS * 4) >= slots;
-        const int rows = four ? 4 : 2;
-        const int tiles = (t->M + I4G_WARPS * rows - 1) / (I4G_WARPS * rows);
-        const int blocks = tiles < slots ? tiles : slots;
-        return four ? ibcu_launch(ctx, int4g_kernel<4, I4G_STAGES>, dim3(blocks), dim3(I4G_THREADS), smem, 1, true, p)
-                    : ibcu_launch(ctx, int4g_kernel<2, I4G_STAGES>, dim3(blocks), dim3(I4G_THREADS), smem, 1, true, p);
+        return ibcu_launch(ctx, int4g_kernel<I4G_ROWS, I4G_STAGES>, dim3(tiles < slots ? tiles : slots), dim3(I4G_THREADS), ask, 1, true, p);
     }
     unsigned char* skip = nullptr;
     if (eps_act_rel > 0.0f) {
