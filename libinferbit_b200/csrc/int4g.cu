@@ -56,6 +56,46 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
     auto group_of = [&](int c) { return cpg_sh >= 0 ? c >> cpg_sh : c / cpg; };
     float* sxs = reinterpret_cast<float*>(xl + p.N);
     unsigned char* skip = reinterpret_cast<unsigned char*>(sxs + ((nchunk + 3) & ~3));     // keeps the ring behind it 16-byte aligned
+    // ── rows: a warp walks its tiles of ROWS rows, lane l the chunks l, l + 32, ...; (tile, pass over 32 chunks) form one
+    //    sequence of steps, and the weights (16 bytes per lane and row) and scales of step q + STAGES - 1 are on their way
+    //    into the warp's ring in shared memory while step q is worked on ──
+    const uint4* wq = reinterpret_cast<const uint4*>(p.q);
+    constexpr int STAGE_WORDS = ROWS * 32 * 5;                // per row 32 lanes x (16 bytes of weights + 4 bytes holding the scale)
+    uint32_t* ring = reinterpret_cast<uint32_t*>(skip + ((ng + 15) & ~15)) + (size_t)warp * STAGES * STAGE_WORDS;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+    const int npass = (nchunk + 31) >> 5;
+    const int tile0 = blockIdx.x * I4G_WARPS + warp, tstride = gridDim.x * I4G_WARPS;
+    const int ntile = (p.M + ROWS - 1) / ROWS;
+    const int my_tiles = tile0 < ntile ? (ntile - tile0 + tstride - 1) / tstride : 0;
+    const int nstep = my_tiles * npass;
+    int iq = 0, ipass = 0, itile = tile0;                     // the step to request next, its pass and its tile
+    auto issue = [&]() {                                      // requests the next step (nothing beyond the last: an empty group keeps the count)
+        const int q = iq++;
+        if (q < nstep) {
+            const int tile = itile, c = lane + 32 * ipass;
+            if (++ipass == npass) { ipass = 0; itile += tstride; }
+            const int g = group_of(c < nchunk ? c : 0);
+            const bool on = c < nchunk && !(p.eps > 0.0f && skip[g]);
+            const uint32_t dst = ring_s + (uint32_t)((q & (STAGES - 1)) * STAGE_WORDS) * 4u;
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) {
+                const int r = min(tile * ROWS + u, p.M - 1);  // rows past the end repeat the last one and are not stored
+                const int cc = on ? c : 0;
+                const unsigned nb = on ? 16u : 0u;            // a chunk that is off is filled with zeros: scale 0 times 0
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst + (uint32_t)(u * 32 + lane) * 16u), "l"(wq + (size_t)r * nchunk + cc), "r"(nb) : "memory");
+                const uintptr_t sa = (uintptr_t)(p.s + (size_t)r * ng + (on ? g : 0)) & ~(uintptr_t)3;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" :: "r"(dst + (uint32_t)(ROWS * 32 * 4 + u * 32 + lane) * 4u), "l"(sa), "r"(on ? 4u : 0u) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // weights and scales do not depend on the kernel ahead: without the skip rule the first steps are requested before the wait
+    // for it, and travel while the activation is converted
+    const bool early = !(p.eps > 0.0f);
+    if (early) {
+#pragma unroll
+        for (int q = 0; q < STAGES - 1; q++) issue();
+    }
     pdl_wait();
     // max |x|, then the fixed-point scale: 2^sh max|x| in [2^29, 2^30)
     float amax = 0.0f;
@@ -110,41 +150,10 @@ __global__ void __launch_bounds__(I4G_THREADS) int4g_kernel(const I4gParams p) {
         if (on && j == 0) sxs[c] = fs;
     }
     __syncthreads();
-    // ── rows: a warp walks its tiles of ROWS rows, lane l the chunks l, l + 32, ...; (tile, pass over 32 chunks) form one
-    //    sequence of steps, and the weights (16 bytes per lane and row) and scales of step q + STAGES - 1 are on their way
-    //    into the warp's ring in shared memory while step q is worked on ──
-    const uint4* wq = reinterpret_cast<const uint4*>(p.q);
-    constexpr int STAGE_WORDS = ROWS * 32 * 5;                // per row 32 lanes x (16 bytes of weights + 4 bytes holding the scale)
-    uint32_t* ring = reinterpret_cast<uint32_t*>(skip + ((ng + 15) & ~15)) + (size_t)warp * STAGES * STAGE_WORDS;
-    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-    const int npass = (nchunk + 31) >> 5;
-    const int tile0 = blockIdx.x * I4G_WARPS + warp, tstride = gridDim.x * I4G_WARPS;
-    const int ntile = (p.M + ROWS - 1) / ROWS;
-    const int my_tiles = tile0 < ntile ? (ntile - tile0 + tstride - 1) / tstride : 0;
-    const int nstep = my_tiles * npass;
-    int iq = 0, ipass = 0, itile = tile0;                     // the step to request next, its pass and its tile
-    auto issue = [&]() {                                      // requests the next step (nothing beyond the last: an empty group keeps the count)
-        const int q = iq++;
-        if (q < nstep) {
-            const int tile = itile, c = lane + 32 * ipass;
-            if (++ipass == npass) { ipass = 0; itile += tstride; }
-            const int g = group_of(c < nchunk ? c : 0);
-            const bool on = c < nchunk && !(p.eps > 0.0f && skip[g]);
-            const uint32_t dst = ring_s + (uint32_t)((q & (STAGES - 1)) * STAGE_WORDS) * 4u;
+    if (!early) {
 #pragma unroll
-            for (int u = 0; u < ROWS; u++) {
-                const int r = min(tile * ROWS + u, p.M - 1);  // rows past the end repeat the last one and are not stored
-                const int cc = on ? c : 0;
-                const unsigned nb = on ? 16u : 0u;            // a chunk that is off is filled with zeros: scale 0 times 0
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst + (uint32_t)(u * 32 + lane) * 16u), "l"(wq + (size_t)r * nchunk + cc), "r"(nb) : "memory");
-                const uintptr_t sa = (uintptr_t)(p.s + (size_t)r * ng + (on ? g : 0)) & ~(uintptr_t)3;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" :: "r"(dst + (uint32_t)(ROWS * 32 * 4 + u * 32 + lane) * 4u), "l"(sa), "r"(on ? 4u : 0u) : "memory");
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-#pragma unroll
-    for (int q = 0; q < STAGES - 1; q++) issue();
+        for (int q = 0; q < STAGES - 1; q++) issue();
+    }
     float acc[ROWS];
     int pass = 0, tile = tile0, stage = 0;
     for (int q = 0; q < nstep; q++) {
