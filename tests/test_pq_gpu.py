@@ -25,6 +25,7 @@ def oracle_pq(libs, M, N, G, K, cb_l, cb_r, il, ir, rs, x, stride=0):
     (300, 1200, 16, 100, 5),        # several activations: 150 subspaces, the second unit of 128 is mostly padding; 100 codebook entries
     (48, 640, 16, 256, 32),         # 32 activations, fewer pieces of work than SMs
     (16, 40960, 16, 256, 32),       # 1280 units of one group each: a block walks nine of them and reports its arrivals in two batches
+    (512, 1024, 16, 256, 2),        # two activations: one pass of the slab kernel with entries two floats wide
     (64, 256, 8, 64, 2), (33, 96, 4, 16, 1), (2048, 512, 32, 256, 1), (5, 16, 16, 256, 1),
 ])
 def test_pq_matches_reference_restatement(backend, cpu_libs, M, N, G, K, B):
